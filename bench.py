@@ -1,0 +1,354 @@
+"""Benchmark of the quantized decode path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload NAME] [--impl reference]
+
+Prints ONE JSON line (rank 0). Workloads:
+
+  gemv_sweep_1b   BASELINE config 2: the Llama-3.2-1B linear shapes at M=1 (q/o, k/v, gate/up,
+                  down as int4 and int8, lm_head int8), bf16 activations, group 128. A step is
+                  one pass over a pool of distinct weight copies of every shape (the pool of
+                  each shape exceeds L2, so every launch streams from HBM). value = algorithmic
+                  bytes moved per second over the whole pass.
+
+`--impl reference` times the CPU oracle (a numpy restatement of the reference's real mode;
+the reference itself is Python and is not shipped to the GPU box) on a bounded sample of the
+same workload, on all host threads.
+"""
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import tempfile
+import threading
+import time
+
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+L2_BYTES = 126 * 1024 * 1024
+
+# (name, N, K, bits) -- BASELINE config 2
+SWEEP_1B = [
+    ("q_o.int4", 2048, 2048, 4), ("k_v.int4", 512, 2048, 4), ("gate_up.int4", 8192, 2048, 4),
+    ("down.int4", 2048, 8192, 4),
+    ("q_o.int8", 2048, 2048, 8), ("k_v.int8", 512, 2048, 8), ("gate_up.int8", 8192, 2048, 8),
+    ("down.int8", 2048, 8192, 8),
+    ("lm_head.int8", 128256, 2048, 8),
+]
+
+
+def algorithmic_bytes(n, k, bits, m=1, out_bytes=2):
+    """Packed codes + one fp32 scale per (row, group of 128) + bf16 x + the output."""
+    return n * k * bits // 8 + n * (-(-k // 128)) * 4 + m * k * 2 + m * n * out_bytes
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as fh:
+            return json.load(fh), "measured"
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}, "fallback"
+
+
+class ClockSampler:
+    """nvidia-smi clocks / throttle reasons sampled every 200 ms while the timed region runs."""
+
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+             "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index = index
+        self.proc = None
+        self.path = None
+
+    def __enter__(self):
+        try:
+            fd, self.path = tempfile.mkstemp(suffix=".csv")
+            os.close(fd)
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
+                 "-lms", "200", "-i", str(self.index)],
+                stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
+        except OSError:
+            self.proc = None
+        return self
+
+    def __exit__(self, *exc):
+        if self.proc is not None:
+            time.sleep(0.25)
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+
+    def summary(self):
+        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": []}
+        if not self.path or not os.path.exists(self.path):
+            return out
+        sm, reasons = [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        with open(self.path) as fh:
+            for line in fh:
+                cols = [c.strip() for c in line.split(",")]
+                if len(cols) < 9:
+                    continue
+                try:
+                    sm.append(float(cols[1]))
+                    out["sm_max_mhz"] = float(cols[2])
+                except ValueError:
+                    continue
+                for name, col in zip(names, cols[5:9]):
+                    if col.lower().startswith("active"):
+                        reasons.add(name)
+        os.unlink(self.path)
+        if sm:
+            sm.sort()
+            out["sm_mhz"] = sm[len(sm) // 2]
+        out["reasons"] = sorted(reasons)
+        return out
+
+
+# --------------------------------------------------------------------------- GPU arm
+def build_pool(device):
+    """For every shape: enough distinct quantized copies to exceed twice the L2 size."""
+    from llmquant_b200.core import QuantizationArgs, QuantizationScheme
+    from llmquant_b200.quantizers import KernelQuantLinear
+
+    pool = []
+    for name, n, k, bits in SWEEP_1B:
+        scheme = QuantizationScheme(
+            weights=QuantizationArgs(num_bits=bits, strategy="group", group_size=128),
+            input_activations=None)
+        g = torch.Generator(device="cpu").manual_seed(len(pool))
+        per_copy = algorithmic_bytes(n, k, bits)
+        copies = max(2, -(-2 * L2_BYTES // per_copy))
+        # two distinct random weights, cloned to fill the pool (values do not affect speed)
+        base = []
+        for _ in range(2):
+            w = (torch.randn(n, k, generator=g) * 0.02).to(torch.bfloat16).to(device)
+            lin = torch.nn.Linear(k, n, bias=False, device="meta")
+            lin.weight = torch.nn.Parameter(w, requires_grad=False)
+            base.append(KernelQuantLinear.from_linear(lin, scheme))
+            del w, lin
+        weights = [(m.codes, m.scales_t) for m in base]
+        while len(weights) < copies:
+            src = base[len(weights) % 2]
+            weights.append((src.codes.clone(), src.scales_t.clone()))
+        x = (torch.randn(1, k, generator=g)).to(torch.bfloat16).to(device)
+        pool.append({"name": name, "n": n, "k": k, "bits": bits, "mod": base[0], "weights": weights,
+                     "x": x, "bytes": per_copy})
+    return pool
+
+
+def capture_shape_graph(entry):
+    """One CUDA graph that launches the GEMV once per weight copy of this shape."""
+    x = entry["x"]
+    outs = [torch.empty(1, entry["n"], dtype=torch.bfloat16, device=x.device) for _ in entry["weights"]]
+    entry["outs"] = outs
+    mod = entry["mod"]
+
+    def run():
+        from llmquant_b200 import native
+        for (codes, scales_t), out in zip(entry["weights"], outs):
+            native.call("lq_wq_gemv_stream", x.data_ptr(), x.stride(0), codes.data_ptr(),
+                        scales_t.data_ptr(), 0, 0, out.data_ptr(), native.LQ_BF16, 1,
+                        mod.out_features, mod.in_features, mod._kd, mod._span, mod._srp,
+                        mod.out_group, mod.num_bits, 0, native.stream_ptr(x.device))
+
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        run()
+    torch.cuda.current_stream().wait_stream(side)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        run()
+    entry["graph"] = graph
+
+
+def run_gpu(args, rank, world, device):
+    import torch.distributed as dist
+
+    pool = build_pool(device)
+    for entry in pool:
+        capture_shape_graph(entry)
+    launches_per_step = sum(len(e["weights"]) for e in pool)
+    bytes_per_step = sum(e["bytes"] * len(e["weights"]) for e in pool)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(args.warmup):
+        for entry in pool:
+            entry["graph"].replay()
+    barrier()
+
+    # ---- value: inputs resident in HBM, one event pair per shape per step
+    events = [[(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
+               for _ in pool] for _ in range(args.steps)]
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with ClockSampler(torch.cuda.current_device()) as clocks:
+        barrier()
+        start.record()
+        for s in range(args.steps):
+            for entry, (e0, e1) in zip(pool, events[s]):
+                e0.record()
+                entry["graph"].replay()
+                e1.record()
+        stop.record()
+        barrier()
+    total_ms = start.elapsed_time(stop)
+    shape_ms = [sum(events[s][i][0].elapsed_time(events[s][i][1]) for s in range(args.steps)) / args.steps
+                for i in range(len(pool))]
+    kernel_ms = sum(shape_ms)
+
+    # ---- e2e: the module call a user makes, x from pinned host memory, y read back
+    host_x = [e["x"].cpu().pin_memory() for e in pool]
+    host_y = [torch.empty(1, e["n"], dtype=torch.bfloat16).pin_memory() for e in pool]
+    h2d = sum(x.numel() * 2 for x in host_x)
+    d2h = sum(y.numel() * 2 for y in host_y)
+
+    def e2e_step(step):
+        for i, entry in enumerate(pool):
+            xd = host_x[i].to(device, non_blocking=True)
+            host_y[i].copy_(entry["mod"](xd), non_blocking=True)
+        torch.cuda.synchronize()
+
+    for s in range(max(3, args.warmup)):
+        e2e_step(s)
+    barrier()
+    t0 = time.perf_counter()
+    for s in range(args.steps):
+        e2e_step(s)
+    barrier()
+    e2e_s = (time.perf_counter() - t0) / args.steps
+    e2e_bytes = sum(e["bytes"] for e in pool)
+
+    times = torch.tensor([total_ms, kernel_ms, e2e_s], dtype=torch.float64, device=device)
+    if world > 1:
+        dist.all_reduce(times, op=dist.ReduceOp.MAX)
+    total_ms, kernel_ms, e2e_s = times.tolist()
+    ms_per_step = total_ms / args.steps
+    peaks, peak_kind = measured_peaks()
+
+    value = world * bytes_per_step / (ms_per_step * 1e-3) / 1e9
+    achieved = bytes_per_step / (kernel_ms * 1e-3) / 1e9
+    line = {
+        "metric": "quant_gemv_hbm_gbs", "value": round(value, 1), "unit": "GB/s",
+        "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": round(ms_per_step, 4), "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "int4/int8 codes x bf16, fp32 accumulate", "data": "synthetic",
+        "config": {"workload": "gemv_sweep_1b (BASELINE config 2: Llama-3.2-1B linear shapes, M=1)",
+                   "group_size": 128, "launches_per_step": launches_per_step,
+                   "l2_policy": "each shape cycles a pool of distinct weight copies > 2x L2",
+                   "parallelism": f"replicas x{world}" if world > 1 else "single"},
+        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peaks["hbm_gbs"],
+                     "unit": "GB/s", "frac": round(achieved / peaks["hbm_gbs"], 4),
+                     "frac_of_nominal_8TBs": round(achieved / 8000.0, 4), "peak_kind": peak_kind,
+                     "traffic": None, "kernel": "gemv_stream_kernel"},
+        "shapes": {e["name"]: {"us_per_launch": round(ms * 1e3 / len(e["weights"]), 3),
+                               "gbs": round(e["bytes"] * len(e["weights"]) / (ms * 1e-3) / 1e9, 1)}
+                   for e, ms in zip(pool, shape_ms)},
+        "e2e": {"value": round(world * e2e_bytes / e2e_s / 1e9, 2), "unit": "GB/s",
+                "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
+        "gpu_launches": launches_per_step * args.steps,
+        "clocks": clocks.summary(),
+    }
+    if rank == 0:
+        line["cpu_baseline"] = cpu_baseline(sample_seconds=12.0)
+        print(json.dumps(line), flush=True)
+
+
+# --------------------------------------------------------------------------- CPU arm
+def cpu_baseline(sample_seconds=15.0, steps=None):
+    """The oracle's real-mode linear (numpy restatement of quantizers/real.py:76-103 of the
+    reference) on the sweep shapes, M=1, on all host threads, bounded in time."""
+    import numpy as np
+
+    import oracle
+
+    rng = np.random.default_rng(0)
+    done_bytes, spent, used = 0, 0.0, []
+    budget = sample_seconds
+    for name, n, k, bits in SWEEP_1B:
+        if name.startswith("lm_head"):
+            n = 16032  # one eighth of the vocabulary keeps the sample bounded
+        w = oracle.round_to_dtype((rng.standard_normal((n, k)) * 0.02).astype(np.float32), "bf16")
+        x = oracle.round_to_dtype(rng.standard_normal((1, k)).astype(np.float32), "bf16")
+        q, scale = oracle.quantize_weight(w, bits, 128)
+        oracle.real_linear(x, q, scale, bits, 128)  # warm-up
+        reps = steps or 3
+        t0 = time.perf_counter()
+        for _ in range(reps):
+            oracle.real_linear(x, q, scale, bits, 128, out_dtype="bf16")
+        dt = (time.perf_counter() - t0) / reps
+        done_bytes += algorithmic_bytes(n, k, bits)
+        spent += dt
+        used.append(name if n != 16032 else name + "[16032 rows]")
+        if spent * 3 > budget:
+            break
+    return {"value": round(done_bytes / spent / 1e9, 3), "unit": "GB/s",
+            "cores": os.cpu_count(), "kind": "port",
+            "sample": "one M=1 forward per shape (median-free mean of 3) over: " + ", ".join(used)}
+
+
+def run_reference(args, rank):
+    if rank != 0:
+        return
+    base = cpu_baseline(sample_seconds=60.0, steps=max(1, args.steps))
+    line = {
+        "impl": "reference", "metric": "quant_gemv_hbm_gbs", "value": base["value"], "unit": "GB/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": None, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "int codes x fp32 (numpy)", "data": "synthetic",
+        "config": {"workload": "gemv_sweep_1b (BASELINE config 2: Llama-3.2-1B linear shapes, M=1)",
+                   "group_size": 128},
+        "cpu_baseline": base,
+        "e2e": {"value": base["value"], "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--workload", default="gemv_sweep_1b")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3)
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference":
+        run_reference(args, rank)
+        return
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the kernel path has no CPU fallback")
+    torch.cuda.set_device(local)
+    device = torch.device("cuda", local)
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=device)
+    try:
+        run_gpu(args, rank, world, device)
+    finally:
+        if world > 1:
+            import torch.distributed as dist
+            dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

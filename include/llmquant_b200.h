@@ -1,0 +1,123 @@
+/* C ABI of libllmquant_b200.so -- hand-written sm_100a kernels for the quantized-linear and
+ * quantized-KV path of pjh5672/llm-quant.
+ *
+ * Conventions
+ *   - every pointer named *_d / documented "device" is a CUDA device pointer on the current
+ *     device; the library never allocates, frees or synchronizes;
+ *   - `stream` is a cudaStream_t passed as void* (NULL = the legacy default stream);
+ *     every call only enqueues work, so all entry points are CUDA-graph capturable;
+ *   - return value 0 = ok, otherwise one of LQ_ERR_*; lq_last_error() returns the message
+ *     of the last failing call on the calling thread;
+ *   - dtype ids: LQ_F32 / LQ_F16 / LQ_BF16.
+ *
+ * Each entry point cites the reference interface (path inside pjh5672/llm-quant) whose
+ * role it takes.
+ */
+#ifndef LLMQUANT_B200_H_
+#define LLMQUANT_B200_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+enum { LQ_F32 = 0, LQ_F16 = 1, LQ_BF16 = 2 };
+
+enum {
+  LQ_OK = 0,
+  LQ_ERR_ARG = 1,      /* bad shape / size / alignment */
+  LQ_ERR_DTYPE = 2,    /* unsupported dtype id */
+  LQ_ERR_LAUNCH = 3,   /* the CUDA runtime rejected the launch */
+  LQ_ERR_UNSUPPORTED = 4
+};
+
+int lq_version(void);
+const char* lq_last_error(void);
+
+/* ---------------------------------------------------------------- quantize / dequantize */
+
+/* Fused symmetric RTN quant-dequant over groups of `group_size` along the last axis.
+ * Replaces fake_quant_group (llmquant/cuda/csrc/fake_quant.cu:88-139, bound at
+ * csrc/fake_quant.cpp:22-29). x, out: [groups * group_size] of `dtype`; scale_out: fp32
+ * [groups] or NULL. num_bits in [2, 8]. Bit-exact with core/quant_ops.py:26-37. */
+int lq_fake_quant_group(const void* x, void* out, float* scale_out, int64_t groups,
+                        int group_size, int num_bits, int dtype, void* stream);
+
+/* Same arithmetic, but emits the integer codes (int8) and the fp32 scale per group instead
+ * of the dequantized values: the dynamic activation quantizer of the A8 path
+ * (quantizers/real.py:88-90) and the arithmetic of the KV cache's quantize-on-write
+ * (quantizers/fake.py:52-54). */
+int lq_quantize_group_i8(const void* x, int8_t* codes, float* scale_out, int64_t groups,
+                         int group_size, int num_bits, int dtype, void* stream);
+
+/* One-shot weight quantizer: w [N, K] -> canonical codes [N, G, group_size] int8 (K padded
+ * with zeros, per head when head_dim > 0) and scales [scale_rows, G] fp32, where
+ * scale_rows = ceil(N / out_group) if out_group > 0 else N. Replaces quantize_weight +
+ * group_view as called by KernelQuantLinear.from_linear (quantizers/real.py:29-47,
+ * quantizers/kernel.py:56-66; scale rule core/observers.py:74-98). */
+int lq_quantize_weight(const void* w, int dtype, int N, int K, int group_size, int head_dim,
+                       int out_group, int num_bits, int8_t* canonical, float* wscale,
+                       void* stream);
+
+/* Nibble codec of the model.bin payload: value + 8, even index -> low nibble
+ * (packing/packing.py:20-40). n_codes must be even. */
+int lq_pack_int4(const int8_t* codes, uint8_t* packed, int64_t n_codes, void* stream);
+int lq_unpack_int4(const uint8_t* packed, int8_t* codes, int64_t n_codes, void* stream);
+
+/* Dequantize canonical codes to a dense [N, G*group_size] matrix of `dtype`:
+ * (qweight * broadcast_scale).to(dtype), KernelQuantLinear._dequantized_weight
+ * (quantizers/kernel.py:68-79). */
+int lq_dequant_weight(const int8_t* canonical, const float* wscale, void* out, int dtype,
+                      int N, int groups, int group_size, int out_group, void* stream);
+
+/* ---------------------------------------------------------------- decode GEMV */
+
+/* Drop-in for wq_gemv (llmquant/cuda/csrc/wq_gemv.cu:134-185, bound at fake_quant.cpp:30-37):
+ * out[m, n] = sum_g wscale[row(n), g] * sum_k x[m, g, k] * q[n, g, k], fp32 accumulate,
+ * on the reference's canonical layout. x [M, G*group_size], qweight [N, G, group_size] int8,
+ * wscale [scale_rows, G] fp32, out [M, N] in x's dtype. group_size % 4 == 0. */
+int lq_wq_gemv(const void* x, const int8_t* qweight, const float* wscale, void* out, int M,
+               int N, int groups, int group_size, int out_group, int dtype, void* stream);
+
+/* Device ("streaming") layout of one quantized linear, built once per layer:
+ *   codes   [N, Kd] int8 (bits = 8) or [N, Kd/2] bytes of biased nibbles, low nibble first
+ *           (bits = 4); rows are 16-byte aligned; head padding of the canonical form is
+ *           stripped when head_dim < group_size (span = head_dim), otherwise span =
+ *           group_size and Kd = G * group_size;
+ *   scales  [G, SRp] fp32, SRp = scale_rows rounded up to 4 (group-major so that four
+ *           consecutive output rows' scales are one 128-bit load).
+ * lq_stream_layout_sizes returns Kd, span, SRp for a canonical shape. There is no
+ * counterpart in the reference, which feeds canonical int8 to its kernel. */
+int lq_stream_layout_sizes(int groups, int group_size, int head_dim, int bits, int scale_rows,
+                           int* Kd, int* span, int* SRp);
+int lq_repack_stream(const int8_t* canonical, const float* wscale, void* codes, float* scales_t,
+                     int N, int groups, int group_size, int head_dim, int bits, int scale_rows,
+                     void* stream);
+/* Exact inverse of lq_repack_stream (used to rebuild `qweight` for save_packed_model). */
+int lq_unrepack_stream(const void* codes, const float* scales_t, int8_t* canonical, float* wscale,
+                       int N, int groups, int group_size, int head_dim, int bits, int scale_rows,
+                       void* stream);
+
+/* Streaming layout -> dense [N, K] matrix of `dtype` (code * scale, rounded once): the
+ * operand KernelQuantLinear._dequantized_weight builds for the library GEMM
+ * (quantizers/kernel.py:68-79), without the canonical padding columns. */
+int lq_dequant_stream(const void* codes, const float* scales_t, void* out, int dtype, int N, int K,
+                      int Kd, int span, int SRp, int out_group, int bits, void* stream);
+
+/* Decode GEMV on the streaming layout, M <= 8 activation rows.
+ * x [M, K] bf16 (row stride ldx elements), K real in_features (K <= Kd; columns beyond K
+ * read as zero), out [M, N] of out_dtype (LQ_BF16 or LQ_F32), bias bf16 [N] or NULL,
+ * residual (out_dtype, [M, N]) or NULL added after the bias.
+ * variant: 0 = default, 1 = fp32 FMA arithmetic, 2 = integer dot-product arithmetic.
+ * Takes the role of wq_gemv.cu:45-130 inside KernelQuantLinear.forward
+ * (quantizers/kernel.py:81-95). */
+int lq_wq_gemv_stream(const void* x, int ldx, const void* codes, const float* scales_t,
+                      const void* bias, const void* residual, void* out, int out_dtype, int M,
+                      int N, int K, int Kd, int span, int SRp, int out_group, int bits,
+                      int variant, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* LLMQUANT_B200_H_ */

@@ -1,0 +1,75 @@
+// Shared helpers for the sm_100a kernels behind the C ABI in include/llmquant_b200.h.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include <cstdarg>
+#include <cstdio>
+
+#include "../../include/llmquant_b200.h"
+
+namespace lq {
+
+constexpr float kScaleEps = 1e-8f;  // floor of every abs-max scale
+constexpr int kSmCount = 148;       // B200; grids are sized from the queried value at run time
+
+// Thread-local message returned by lq_last_error().
+char* error_buffer();
+int fail(int code, const char* fmt, ...);
+int check_launch(const char* what);
+int sm_count();
+
+#define LQ_REQUIRE(cond, code, ...)            \
+  do {                                         \
+    if (!(cond)) return lq::fail(code, __VA_ARGS__); \
+  } while (0)
+
+template <typename T>
+struct Conv;
+template <>
+struct Conv<float> {
+  static __device__ __forceinline__ float to_f32(float v) { return v; }
+  static __device__ __forceinline__ float from_f32(float v) { return v; }
+};
+template <>
+struct Conv<__half> {
+  static __device__ __forceinline__ float to_f32(__half v) { return __half2float(v); }
+  static __device__ __forceinline__ __half from_f32(float v) { return __float2half_rn(v); }
+};
+template <>
+struct Conv<__nv_bfloat16> {
+  static __device__ __forceinline__ float to_f32(__nv_bfloat16 v) { return __bfloat162float(v); }
+  static __device__ __forceinline__ __nv_bfloat16 from_f32(float v) { return __float2bfloat16_rn(v); }
+};
+
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+// The one quantization rule of the path: IEEE division, round-half-even, clamp.
+__device__ __forceinline__ float scale_of(float amax, float qmax) {
+  return fmaxf(__fdiv_rn(amax, qmax), kScaleEps);
+}
+__device__ __forceinline__ float code_of(float v, float scale, float qmin, float qmax) {
+  return fminf(fmaxf(rintf(__fdiv_rn(v, scale)), qmin), qmax);
+}
+
+#define LQ_DISPATCH_DTYPE(dtype, T, ...)                   \
+  switch (dtype) {                                         \
+    case LQ_F32: { using T = float; __VA_ARGS__; break; }  \
+    case LQ_F16: { using T = __half; __VA_ARGS__; break; } \
+    case LQ_BF16: { using T = __nv_bfloat16; __VA_ARGS__; break; } \
+    default: return lq::fail(LQ_ERR_DTYPE, "x must be float32, float16 or bfloat16, got dtype id %d", (int)(dtype)); \
+  }
+
+}  // namespace lq

@@ -1,0 +1,93 @@
+"""ctypes binding of libllmquant_b200.so (the C ABI in include/llmquant_b200.h).
+
+The library is built offline by `python -m llmquant_b200.build`; there is no JIT and no
+fallback. Loading fails loudly if the shared object is missing, and every non-zero status
+from the library is raised as a RuntimeError carrying the library's message.
+"""
+
+import ctypes
+import functools
+import pathlib
+import re
+
+import torch
+
+PKG = pathlib.Path(__file__).resolve().parent
+LIB_PATH = PKG / "libllmquant_b200.so"
+HEADER = PKG.parent / "include" / "llmquant_b200.h"
+
+LQ_F32, LQ_F16, LQ_BF16 = 0, 1, 2
+DTYPE_ID = {torch.float32: LQ_F32, torch.float16: LQ_F16, torch.bfloat16: LQ_BF16}
+
+_P, _I, _L = ctypes.c_void_p, ctypes.c_int, ctypes.c_int64
+_IP = ctypes.POINTER(ctypes.c_int)
+
+# name -> argtypes; every function returns int status unless listed in _RESTYPE
+_SIGNATURES = {
+    "lq_version": [],
+    "lq_last_error": [],
+    "lq_fake_quant_group": [_P, _P, _P, _L, _I, _I, _I, _P],
+    "lq_quantize_group_i8": [_P, _P, _P, _L, _I, _I, _I, _P],
+    "lq_quantize_weight": [_P, _I, _I, _I, _I, _I, _I, _I, _P, _P, _P],
+    "lq_pack_int4": [_P, _P, _L, _P],
+    "lq_unpack_int4": [_P, _P, _L, _P],
+    "lq_dequant_weight": [_P, _P, _P, _I, _I, _I, _I, _I, _P],
+    "lq_wq_gemv": [_P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P],
+    "lq_stream_layout_sizes": [_I, _I, _I, _I, _I, _IP, _IP, _IP],
+    "lq_repack_stream": [_P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P],
+    "lq_unrepack_stream": [_P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P],
+    "lq_dequant_stream": [_P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P],
+    "lq_wq_gemv_stream": [_P, _I, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _I, _P],
+}
+_RESTYPE = {"lq_last_error": ctypes.c_char_p}
+
+
+def declared_symbols(header: pathlib.Path = HEADER):
+    """Every function name the public header declares."""
+    text = re.sub(r"/\*.*?\*/", "", header.read_text(), flags=re.S)
+    return sorted(set(re.findall(r"\b(lq_[a-z0-9_]+)\s*\(", text)))
+
+
+@functools.lru_cache(maxsize=1)
+def library() -> ctypes.CDLL:
+    if not LIB_PATH.exists():
+        raise RuntimeError(
+            f"{LIB_PATH} is missing: build it with `python -m llmquant_b200.build` "
+            "(the CUDA kernels are compiled offline; there is no fallback path)"
+        )
+    lib = ctypes.CDLL(str(LIB_PATH))
+    for name, argtypes in _SIGNATURES.items():
+        fn = getattr(lib, name)
+        fn.argtypes = argtypes
+        fn.restype = _RESTYPE.get(name, ctypes.c_int)
+    return lib
+
+
+def last_error() -> str:
+    msg = library().lq_last_error()
+    return msg.decode("utf-8", "replace") if msg else ""
+
+
+def check(status: int):
+    if status:
+        raise RuntimeError(last_error() or f"libllmquant_b200 returned status {status}")
+
+
+def stream_ptr(device=None) -> int:
+    return torch.cuda.current_stream(device).cuda_stream
+
+
+def ptr(t) -> int:
+    return 0 if t is None else t.data_ptr()
+
+
+def call(name: str, *args):
+    """Invoke one entry point and raise on a non-zero status."""
+    check(getattr(library(), name)(*args))
+
+
+def stream_layout_sizes(groups, group_size, head_dim, bits, scale_rows):
+    kd, span, srp = ctypes.c_int(), ctypes.c_int(), ctypes.c_int()
+    call("lq_stream_layout_sizes", groups, group_size, head_dim or 0, bits, scale_rows,
+         ctypes.byref(kd), ctypes.byref(span), ctypes.byref(srp))
+    return kd.value, span.value, srp.value

@@ -1,0 +1,24 @@
+"""The deployed ("kernel") implementation of a quantized layer and of the quantized KV cache."""
+
+from llmquant_b200.quantizers.kernel import (
+    DECODE_MAX_ROWS,
+    KERNEL_MAX_ROWS,
+    KernelQuantLinear,
+    pad_activation,
+    quantize_weight_canonical,
+)
+
+AVAILABLE_MODES = frozenset({"kernel"})
+
+
+def quant_linear_for(mode: str):
+    """The module class a mode swaps each Linear for (llmquant/quantizers/dispatch.py:12-34)."""
+    if mode == "kernel":
+        return KernelQuantLinear
+    raise ValueError(f"unsupported mode {mode!r}, expected one of {sorted(AVAILABLE_MODES)}")
+
+
+__all__ = [
+    "AVAILABLE_MODES", "DECODE_MAX_ROWS", "KERNEL_MAX_ROWS", "KernelQuantLinear",
+    "pad_activation", "quant_linear_for", "quantize_weight_canonical",
+]

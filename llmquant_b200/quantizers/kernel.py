@@ -1,0 +1,241 @@
+"""`KernelQuantLinear`: the drop-in Linear whose weight stays integer into the CUDA kernels.
+
+Same constructor, `from_linear`, attributes and forward contract as the reference module
+(llmquant/quantizers/kernel.py:31-103), so `save_packed_model` / `load_packed_model` and the
+modifier treat it identically. What differs is underneath:
+
+  * the weight is quantized on the GPU by the library (bit-identical codes and scales);
+  * it is held in the streaming layout -- true nibbles for int4 (0.5 byte per weight in
+    HBM, where the reference keeps one byte), head padding stripped, scales group-major --
+    and the canonical `[N, groups, group_size]` int8 tensor is rebuilt on demand by an
+    exact inverse (`.qweight`), so the file format is unchanged;
+  * up to DECODE_MAX_ROWS activation rows go through the streaming GEMV; more rows take
+    the prefill path.
+"""
+
+import torch
+import torch.nn as nn
+
+from llmquant_b200 import native
+from llmquant_b200.core.scheme import QuantizationScheme
+
+# rows the streaming GEMV accepts; the reference switches to its library-GEMM path above 4
+# (llmquant/quantizers/kernel.py:27-28)
+KERNEL_MAX_ROWS = 4
+DECODE_MAX_ROWS = 8
+GEMV_VARIANT = 0  # 0 = library default; see lq_wq_gemv_stream
+
+
+def _canonical_geometry(out_features, in_features, args):
+    """Shape of the canonical tensor and its scale table for one Linear."""
+    gs = args.group_size
+    if args.head_dim:
+        if in_features % args.head_dim:
+            raise ValueError(
+                f"last dim {in_features} is not a multiple of head_dim {args.head_dim}")
+        groups = (in_features // args.head_dim) * -(-args.head_dim // gs)
+    else:
+        groups = -(-in_features // gs)
+    scale_rows = -(-out_features // args.out_group) if args.out_group else out_features
+    return groups, scale_rows
+
+
+def quantize_weight_canonical(weight: torch.Tensor, args):
+    """GPU quantizer: `[N, K]` weight -> canonical int8 `[N, G, gs]` and fp32 `[scale_rows, G]`.
+
+    The device-side equivalent of quantize_weight + group_view as used by from_linear
+    (llmquant/quantizers/real.py:29-47, llmquant/quantizers/kernel.py:60-66)."""
+    if not weight.is_cuda:
+        raise RuntimeError("weight must be a CUDA tensor: the kernel path has no CPU fallback")
+    if weight.dtype not in native.DTYPE_ID:
+        raise RuntimeError(f"weight must be float32, float16 or bfloat16, got {weight.dtype}")
+    if args.strategy != "group":
+        raise ValueError("the kernel path quantizes weights per group along the reduction axis")
+    w = weight.detach().contiguous()
+    n, k = w.shape
+    groups, scale_rows = _canonical_geometry(n, k, args)
+    canonical = torch.empty(n, groups, args.group_size, dtype=torch.int8, device=w.device)
+    wscale = torch.empty(scale_rows, groups, dtype=torch.float32, device=w.device)
+    with torch.cuda.device(w.device):
+        native.call("lq_quantize_weight", w.data_ptr(), native.DTYPE_ID[w.dtype], n, k,
+                    args.group_size, args.head_dim or 0, args.out_group or 0, args.num_bits,
+                    canonical.data_ptr(), wscale.data_ptr(), native.stream_ptr(w.device))
+    return canonical, wscale
+
+
+def pad_activation(flat, args):
+    """Pad x the way the canonical weight's K axis was padded (kernel.py:17-25 of the
+    reference). Only the canonical-layout GEMV needs it; the streaming layout does not."""
+    gs = args.group_size
+    if args.head_dim:
+        lead, k = flat.shape[:-1], flat.shape[-1]
+        per_head = flat.reshape(*lead, k // args.head_dim, args.head_dim)
+        tail = args.head_dim % gs
+        if tail:
+            per_head = nn.functional.pad(per_head, (0, gs - tail))
+        return per_head.reshape(*lead, -1)
+    tail = flat.shape[-1] % gs
+    return nn.functional.pad(flat, (0, gs - tail)) if tail else flat
+
+
+class KernelQuantLinear(nn.Module):
+    """Linear backed by integer weights in HBM, dequantized inside the kernels."""
+
+    def __init__(self, qweight, wscale, bias, scheme: QuantizationScheme, in_features: int):
+        super().__init__()
+        if not qweight.is_cuda:
+            raise RuntimeError(
+                "KernelQuantLinear needs CUDA tensors: the kernel path has no CPU fallback")
+        native.library()  # fail here, loudly, if the library was not built
+        args = scheme.weights
+        self.scheme = scheme
+        self.bias = bias
+        self.out_features = qweight.shape[0]
+        self.in_features = in_features
+        self.canonical_shape = tuple(qweight.shape)
+        self.padded_in_features = qweight.shape[1] * qweight.shape[2]
+        self.out_group = args.out_group or 0
+        self.num_bits = args.num_bits
+        self._weight_args = args
+        self._scale_rows = wscale.shape[0]
+        n, groups, gs = qweight.shape
+        qweight = qweight.contiguous()
+        wscale = wscale.contiguous().float()
+        try:
+            if args.num_bits not in (4, 8):
+                raise RuntimeError("unsupported")
+            kd, span, srp = native.stream_layout_sizes(groups, gs, args.head_dim, args.num_bits,
+                                                       self._scale_rows)
+            self._stream = True
+        except RuntimeError:
+            self._stream = False
+        if self._stream:
+            self._kd, self._span, self._srp = kd, span, srp
+            codes = torch.empty(n, kd * args.num_bits // 8, dtype=torch.uint8, device=qweight.device)
+            scales_t = torch.empty(groups, srp, dtype=torch.float32, device=qweight.device)
+            with torch.cuda.device(qweight.device):
+                native.call("lq_repack_stream", qweight.data_ptr(), wscale.data_ptr(),
+                            codes.data_ptr(), scales_t.data_ptr(), n, groups, gs,
+                            args.head_dim or 0, args.num_bits, self._scale_rows,
+                            native.stream_ptr(qweight.device))
+            self.register_buffer("codes", codes, persistent=False)
+            self.register_buffer("scales_t", scales_t, persistent=False)
+        else:
+            # geometry the streaming GEMV does not cover: keep the canonical tensors and use
+            # the canonical-layout kernel
+            self.register_buffer("_qweight", qweight, persistent=False)
+            self.register_buffer("_wscale", wscale, persistent=False)
+        self._bias_bf16 = None
+
+    # ---- construction -----------------------------------------------------------------
+    @classmethod
+    def from_linear(cls, linear: nn.Linear, scheme: QuantizationScheme):
+        if scheme.weights is None:
+            raise ValueError("the kernel path needs a weight scheme; bf16 weights stay nn.Linear")
+        canonical, wscale = quantize_weight_canonical(linear.weight, scheme.weights)
+        return cls(canonical, wscale, linear.bias, scheme, linear.in_features)
+
+    # ---- the reference's tensors, rebuilt exactly -----------------------------------------
+    def _unrepack(self):
+        n, groups, gs = self.canonical_shape
+        dev = self.codes.device
+        qweight = torch.empty(n, groups, gs, dtype=torch.int8, device=dev)
+        wscale = torch.empty(self._scale_rows, groups, dtype=torch.float32, device=dev)
+        with torch.cuda.device(dev):
+            native.call("lq_unrepack_stream", self.codes.data_ptr(), self.scales_t.data_ptr(),
+                        qweight.data_ptr(), wscale.data_ptr(), n, groups, gs,
+                        self._weight_args.head_dim or 0, self.num_bits, self._scale_rows,
+                        native.stream_ptr(dev))
+        return qweight, wscale
+
+    @property
+    def qweight(self):
+        """Canonical `[N, groups, group_size]` int8 codes (what model.bin stores)."""
+        return self._unrepack()[0] if self._stream else self._qweight
+
+    @property
+    def wscale(self):
+        """`[scale_rows, groups]` fp32 scales."""
+        return self._unrepack()[1] if self._stream else self._wscale
+
+    def weight_bytes(self) -> int:
+        """Bytes one decode step streams for this layer's weight and scales."""
+        if self._stream:
+            return self.codes.numel() + self._scale_rows * self.canonical_shape[1] * 4
+        return self._qweight.numel() + self._wscale.numel() * 4
+
+    # ---- forward ------------------------------------------------------------------------
+    def _dequantized_weight(self, dtype):
+        """Dense `[out, in]` weight in the activation dtype for the library-GEMM path."""
+        dev = self.codes.device if self._stream else self._qweight.device
+        if not self._stream:
+            n, groups, gs = self.canonical_shape
+            out = torch.empty(n, groups * gs, dtype=dtype, device=dev)
+            with torch.cuda.device(dev):
+                native.call("lq_dequant_weight", self._qweight.data_ptr(), self._wscale.data_ptr(),
+                            out.data_ptr(), native.DTYPE_ID[dtype], n, groups, gs, self.out_group,
+                            native.stream_ptr(dev))
+            return out
+        out = torch.empty(self.out_features, self.in_features, dtype=dtype, device=dev)
+        with torch.cuda.device(dev):
+            native.call("lq_dequant_stream", self.codes.data_ptr(), self.scales_t.data_ptr(),
+                        out.data_ptr(), native.DTYPE_ID[dtype], self.out_features, self.in_features,
+                        self._kd, self._span, self._srp, self.out_group, self.num_bits,
+                        native.stream_ptr(dev))
+        return out
+
+    def gemv(self, flat, out_dtype=None, residual=None, variant=None):
+        """Streaming GEMV on `[M <= 8, K]` bf16 rows. Returns `[M, N]` (bf16 or fp32)."""
+        m = flat.shape[0]
+        out_dtype = out_dtype or torch.bfloat16
+        out = torch.empty(m, self.out_features, dtype=out_dtype, device=flat.device)
+        if m == 0:
+            return out
+        bias = None
+        if self.bias is not None:
+            if self._bias_bf16 is None or self._bias_bf16.device != flat.device:
+                self._bias_bf16 = self.bias.detach().to(device=flat.device, dtype=torch.bfloat16).contiguous()
+            bias = self._bias_bf16
+        if flat.stride(-1) != 1:
+            flat = flat.contiguous()
+        with torch.cuda.device(flat.device):
+            native.call("lq_wq_gemv_stream", flat.data_ptr(), flat.stride(0), self.codes.data_ptr(),
+                        self.scales_t.data_ptr(), native.ptr(bias), native.ptr(residual),
+                        out.data_ptr(), native.DTYPE_ID[out_dtype], m, self.out_features,
+                        self.in_features, self._kd, self._span, self._srp, self.out_group,
+                        self.num_bits, GEMV_VARIANT if variant is None else variant,
+                        native.stream_ptr(flat.device))
+        return out
+
+    def forward(self, x):
+        if not x.is_cuda:
+            raise RuntimeError("x must be a CUDA tensor: the kernel path has no CPU fallback")
+        shape = x.shape
+        flat = x.reshape(-1, shape[-1])
+        m = flat.shape[0]
+        if self._stream and m <= DECODE_MAX_ROWS and flat.dtype == torch.bfloat16:
+            out = self.gemv(flat)
+        elif not self._stream and m <= DECODE_MAX_ROWS:
+            from llmquant_b200.cuda.build import load_extension
+
+            padded = pad_activation(flat, self._weight_args)
+            out = load_extension().wq_gemv(padded, self._qweight, self._wscale, self.out_group)
+            if self.bias is not None:
+                out = out + self.bias.to(out.dtype)
+        else:
+            weight = self._dequantized_weight(flat.dtype)
+            if not self._stream:
+                flat = pad_activation(flat, self._weight_args)
+            out = flat @ weight.T
+            if self.bias is not None:
+                out = out + self.bias.to(out.dtype)
+        return out.reshape(*shape[:-1], self.out_features).to(x.dtype)
+
+    def extra_repr(self):
+        act = self.scheme.input_activations
+        return (
+            f"in_features={self.in_features}, out_features={self.out_features}, "
+            f"w{self.num_bits}a{act.num_bits if act else 16}, "
+            f"group_size={self._weight_args.group_size}, layout="
+            f"{'stream' if self._stream else 'canonical'}"
+        )
