@@ -157,7 +157,7 @@ def test_bias_residual_leading_dims_and_prefill_branch():
     from llmquant_b200.quantizers import DECODE_MAX_ROWS, KernelQuantLinear
 
     torch.manual_seed(0)
-    biased = torch.nn.Linear(2048, 512, bias=True).cuda().to(torch.bfloat16)
+    biased = torch.nn.Linear(2048, 512, bias=True).cuda().to(torch.bfloat16).requires_grad_(False)
     torch.nn.init.constant_(biased.bias, 1.5)
     module = KernelQuantLinear.from_linear(biased, preset_name_to_scheme("W8A16"))
     out = module(torch.zeros(1, 2048, device="cuda", dtype=torch.bfloat16))
