@@ -117,6 +117,76 @@ int lq_wq_gemv_stream(const void* x, int ldx, const void* codes, const float* sc
                       int N, int K, int Kd, int span, int SRp, int out_group, int bits,
                       int variant, void* stream);
 
+/* ---------------------------------------------------------------- quantized KV cache
+ * Storage per layer: codes [B, Hkv, Tmax, D] int8, scales [B, Hkv, Tmax, ceil(D/128)] fp32.
+ * A position / length can be given on the host (`pos`, `len`) or through a device int64
+ * (`pos_dev`, `len_dev`, which win when non-NULL), so a captured graph follows a moving
+ * cursor. */
+
+/* Quantize-on-write: T_new new tokens of K and V ([B, H, T_new, D], element strides for
+ * (b, h, t) in k_strides / v_strides, D contiguous) into the cache at `pos`. Takes the role
+ * of FakeQuantCache.update's two fake_quantize calls (llmquant/quantizers/fake.py:52-55). */
+int lq_kv_write(const void* k, const void* v, const int64_t* k_strides, const int64_t* v_strides,
+                int dtype, int8_t* k_codes, int8_t* v_codes, float* k_scales, float* v_scales,
+                int B, int H, int T_new, int D, int Tmax, const int64_t* pos_dev, int64_t pos,
+                int num_bits, void* stream);
+
+/* codes * scale, rounded to `dtype`: out [B, H, T_len, D] contiguous -- the tensors
+ * FakeQuantCache.update returns (llmquant/quantizers/fake.py:55). */
+int lq_kv_dequant(const int8_t* codes, const float* scales, void* out, int dtype, int B, int H,
+                  int T_len, int D, int Tmax, void* stream);
+
+/* One decode token: rotary embedding of the q and k heads of a fused q|k|v row
+ * ([B, (Hq + 2 Hkv) * D] bf16; cos/sin tables [table_len, D] bf16), q to q_out [B, Hq, D]
+ * bf16, k and v quantized into the cache at the cursor. In the reference these are
+ * transformers' apply_rotary_pos_emb followed by FakeQuantCache.update. */
+int lq_rope_kv_write(const void* qkv, const void* cos_table, const void* sin_table, void* q_out,
+                     int8_t* k_codes, int8_t* v_codes, float* k_scales, float* v_scales, int B,
+                     int Hq, int Hkv, int D, int Tmax, int table_len, const int64_t* pos_dev,
+                     int64_t pos, int num_bits, int pdl, void* stream);
+
+/* Dequantize-on-read decode attention: q [B, Hq, D] bf16 against the first
+ * (len or *len_dev) + len_add cached tokens, softmax(q k^T * scaling) v, out [B, Hq, D] bf16.
+ * The cached tokens are cut into `splits` slices processed by different CTAs; `scratch`
+ * (lq_attn_decode_scratch_bytes) holds their partial results. head_dim 64 or 128,
+ * Hq / Hkv in {1, 2, 4, 8}. The reference has no such kernel: it attends over the bf16
+ * tensors its cache returns through transformers' attention. */
+int64_t lq_attn_decode_scratch_bytes(int B, int Hq, int D, int splits);
+int lq_attn_decode_kv_i8(const void* q, const int8_t* k_codes, const int8_t* v_codes,
+                         const float* k_scales, const float* v_scales, void* out, void* scratch,
+                         int B, int Hq, int Hkv, int D, int Tmax, const int64_t* len_dev,
+                         int64_t len, int len_add, float scaling, int splits, int pdl, void* stream);
+
+/* The same GEMV with the work of the neighbouring decoder-layer ops folded in. All fields
+ * of lq_wq_gemv_stream, plus:
+ *   norm_weight / norm_eps  bf16 [K] or NULL: RMSNorm applied to x inside the kernel
+ *                           (x * rsqrt(mean(x^2) + eps), rounded to bf16, times weight,
+ *                           rounded to bf16 -- the arithmetic of a bf16 RMSNorm module);
+ *   epilogue                0 = none; 1 = rows are (gate, up) pairs and the output is
+ *                           silu(gate) * up, [M, N/2];
+ *   pdl                     1 = launch with programmatic stream serialization: the kernel
+ *                           streams its first weights while the previous kernel on the
+ *                           stream drains, and waits for it before touching x.
+ * These fusions have no counterpart in the reference, which runs them as separate PyTorch
+ * ops between its wq_gemv calls (llmquant/quantizers/kernel.py:81-95 is the call site). */
+typedef struct lq_gemv_args {
+  const void* x;
+  int ldx;
+  const void* norm_weight;
+  float norm_eps;
+  const void* codes;
+  const float* scales_t;
+  const void* bias;
+  const void* residual;
+  void* out;
+  int out_dtype;
+  int M, N, K, Kd, span, SRp, out_group, bits;
+  int epilogue;
+  int variant;
+  int pdl;
+} lq_gemv_args;
+int lq_wq_gemv_fused(const lq_gemv_args* args, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -1,0 +1,531 @@
+// Decode GEMV (M <= 8 activation rows) over the streaming layout, plus the layout's
+// repack / un-repack kernels.
+//
+// Layout (see include/llmquant_b200.h): codes [N, Kd] int8 or [N, Kd/2] nibble bytes, rows
+// contiguous and 16-byte aligned; scales transposed to [G, SRp]. A warp reads one
+// contiguous 512-byte "slab" of a row per instruction (32 lanes x one 128-bit load), so HBM
+// sees whole 128-byte lines and nothing is fetched twice.
+//
+// Work split: a lane owns a fixed 16-byte column position (its "chunk": 16 int8 or 32 int4
+// codes, always inside one scale group) and walks DOWN the rows. Everything that depends
+// only on the column -- the activation values, their block exponent, the nibble-bias
+// correction -- is prepared once per lane and stays in registers; the row loop is: 128-bit
+// weight load, dot product, one multiply by the (group, row) scale. Warps of a CTA split the
+// K axis (KW of them cover a row) and the rows (RW row-warps); the KW partial sums meet in
+// shared memory behind a named barrier that only those KW warps join. No tensor cores: the
+// kernel is HBM-bound and the arithmetic is sized to stay under the instruction-issue
+// budget of a 6.5 TB/s stream.
+//
+// Arithmetic variants (argument `variant`):
+//   1  fp32: codes turned into floats with a mantissa-injection trick (no I2F), fp32 FMA
+//      with the bf16 activations widened exactly. Same operations as the reference kernel
+//      (llmquant/cuda/csrc/wq_gemv.cu:78-112), different summation order.
+//   2/3  integer dot products (dp4a). The lane's activation chunk is re-expressed exactly as
+//      a block-floating-point integer vector (shared power-of-two exponent, 16-bit (2) or
+//      24-bit (3) mantissas split into byte planes); chunk sums are exact integer
+//      arithmetic, converted once to fp32 and scaled. bf16 inputs within 2^-7 (2) / 2^-15
+//      (3) of the chunk maximum are represented exactly; smaller ones are rounded at
+//      2^-15 / 2^-23 of the chunk maximum.
+#pragma once
+#include "common.cuh"
+
+namespace lq {
+namespace gemv {
+
+constexpr int kU = 4;           // output rows per batch (one float4 of scales)
+constexpr int kMaxWarps = 16;   // warps per CTA
+
+struct GemvParams {
+  const __nv_bfloat16* x;
+  int ldx;
+  const uint8_t* codes;
+  const float* scales;
+  const __nv_bfloat16* bias;
+  const void* residual;
+  void* out;
+  int out_f32;
+  int M, N, K, Kd, rowbytes, span, SRp, out_group;
+  int KW, RW, S;
+  int nbatch;
+  const void* norm_weight;
+  float norm_eps;
+  int pdl;
+};
+
+__device__ __forceinline__ uint4 ldg_stream(const void* p) {
+  uint4 v;
+  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(p));
+  return v;
+}
+
+__device__ __forceinline__ int dp4a_ss(unsigned a, unsigned b, int c) {
+  int d;
+  asm("dp4a.s32.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+  return d;
+}
+__device__ __forceinline__ int dp4a_su(unsigned a, unsigned b, int c) {  // a signed, b unsigned
+  int d;
+  asm("dp4a.s32.u32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+  return d;
+}
+__device__ __forceinline__ int dp4a_uu(unsigned a, unsigned b, int c) {
+  int d;
+  asm("dp4a.u32.u32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+  return d;
+}
+__device__ __forceinline__ int dp4a_us(unsigned a, unsigned b, int c) {  // a unsigned, b signed
+  int d;
+  asm("dp4a.u32.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+  return d;
+}
+
+// ------------------------------------------------------------------ per-lane activation state
+// VAR 1: the chunk as fp32. VAR 2/3: byte planes of the block-floating-point mantissas,
+// ordered like the weight bytes they meet (int4: even-k plane words then odd-k plane words).
+template <int BITS, int VAR>
+struct XChunk;
+
+template <int BITS>
+struct XChunk<BITS, 1> {
+  static constexpr int EPL = BITS == 8 ? 16 : 32;
+  float v[EPL];
+  __device__ __forceinline__ void build(const float* xf) {
+#pragma unroll
+    for (int i = 0; i < EPL; ++i) v[i] = xf[i];
+  }
+  // one row's chunk (four 32-bit words) against this activation chunk
+  __device__ __forceinline__ float dot(const uint4& w) const {
+    const unsigned ww[4] = {w.x, w.y, w.z, w.w};
+    float acc = 0.f;
+    if (BITS == 8) {
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        const unsigned u = ww[q] ^ 0x80808080u;  // signed byte -> byte + 128
+#pragma unroll
+        for (int b = 0; b < 4; ++b) {
+          // bytes [b, 0, 0, 0x4B] = float 2^23 + (code + 128)
+          const float f = __uint_as_float(__byte_perm(u, 0x4B000000u, 0x7440u | b));
+          acc = fmaf(v[q * 4 + b], f - 8388736.f, acc);
+        }
+      }
+    } else {
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+#pragma unroll
+        for (int b = 0; b < 8; ++b) {
+          const unsigned nib = (ww[q] >> (4 * b)) & 0xFu;
+          const float f = __uint_as_float(nib | 0x4B000000u);  // 2^23 + (code + 8)
+          acc = fmaf(v[q * 8 + b], f - 8388616.f, acc);
+        }
+      }
+    }
+    return acc;
+  }
+};
+
+template <int BITS, int PLANES>
+struct XPlanes {
+  static constexpr int EPL = BITS == 8 ? 16 : 32;
+  static constexpr int WORDS = EPL / 4;  // plane words
+  unsigned hi[WORDS];
+  unsigned mid[PLANES == 3 ? WORDS : 1];
+  unsigned lo[WORDS];
+  int bias_hi, bias_mid, bias_lo;  // -8 * sum(plane bytes): the nibble bias, int4 only
+  float unit;                      // value of one mantissa unit (a power of two)
+
+  __device__ __forceinline__ void build(const float* xf) {
+    float amax = 0.f;
+#pragma unroll
+    for (int i = 0; i < EPL; ++i) amax = fmaxf(amax, fabsf(xf[i]));
+    // e = floor(log2(amax)), clamped so both powers of two below stay normal floats
+    int e = (int)((__float_as_uint(amax) >> 23) & 0xFF) - 127;
+    e = max(e, -100);
+    constexpr int MBITS = PLANES == 3 ? 22 : 14;  // |mantissa| < 2^(MBITS+1)
+    const float up = __uint_as_float((unsigned)(127 + MBITS - e) << 23);
+    unit = __uint_as_float((unsigned)(127 - MBITS + e) << 23);
+    int m[EPL];
+#pragma unroll
+    for (int i = 0; i < EPL; ++i) m[i] = __float2int_rn(xf[i] * up);
+    int sh = 0, sm = 0, sl = 0;
+#pragma unroll
+    for (int w = 0; w < WORDS; ++w) {
+      unsigned ph = 0, pm = 0, pl = 0;
+#pragma unroll
+      for (int b = 0; b < 4; ++b) {
+        // int8: word w byte b meets k = 4w+b. int4: words 0..3 are the even k of weight
+        // word w (k = 8w + 2b), words 4..7 the odd k of weight word w-4.
+        int k;
+        if (BITS == 8) k = 4 * w + b;
+        else k = w < 4 ? 8 * w + 2 * b : 8 * (w - 4) + 2 * b + 1;
+        const int mv = m[k];
+        const int h = PLANES == 3 ? (mv >> 16) : (mv >> 8);
+        const int mdl = (mv >> 8) & 0xFF;
+        const int l = mv & 0xFF;
+        ph |= (unsigned)(h & 0xFF) << (8 * b);
+        pm |= (unsigned)mdl << (8 * b);
+        pl |= (unsigned)l << (8 * b);
+        sh += h; sm += mdl; sl += l;
+      }
+      hi[w] = ph;
+      if (PLANES == 3) mid[w] = pm;
+      lo[w] = pl;
+    }
+    bias_hi = BITS == 4 ? -8 * sh : 0;
+    bias_mid = BITS == 4 ? -8 * sm : 0;
+    bias_lo = BITS == 4 ? -8 * sl : 0;
+  }
+
+  __device__ __forceinline__ float dot(const uint4& w) const {
+    const unsigned ww[4] = {w.x, w.y, w.z, w.w};
+    int ah = bias_hi, am = bias_mid, al = bias_lo;
+    if (BITS == 8) {
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        ah = dp4a_ss(ww[q], hi[q], ah);
+        if (PLANES == 3) am = dp4a_su(ww[q], mid[q], am);
+        al = dp4a_su(ww[q], lo[q], al);
+      }
+    } else {
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        const unsigned ev = ww[q] & 0x0F0F0F0Fu;
+        const unsigned od = (ww[q] >> 4) & 0x0F0F0F0Fu;
+        ah = dp4a_us(ev, hi[q], ah);
+        ah = dp4a_us(od, hi[q + 4], ah);
+        if (PLANES == 3) {
+          am = dp4a_uu(ev, mid[q], am);
+          am = dp4a_uu(od, mid[q + 4], am);
+        }
+        al = dp4a_uu(ev, lo[q], al);
+        al = dp4a_uu(od, lo[q + 4], al);
+      }
+    }
+    if (PLANES == 3) return fmaf((float)ah, 65536.f, (float)(am * 256 + al)) * unit;
+    return (float)(ah * 256 + al) * unit;
+  }
+};
+
+template <int BITS>
+struct XChunk<BITS, 2> : XPlanes<BITS, 2> {};
+template <int BITS>
+struct XChunk<BITS, 3> : XPlanes<BITS, 3> {};
+
+// ------------------------------------------------------------------ the kernel
+template <int SPW>
+struct WeightBatch {
+  uint4 w[SPW][kU];   // one 16-byte chunk per (slab, row)
+  float sc[SPW][kU];  // the (group, row) scales that go with them
+};
+
+// EPI 0: out[m, n] = acc (+ bias) (+ residual).  EPI 1: rows come in (gate, up) pairs and
+// out[m, n/2] = silu(gate) * up with the roundings of a bf16 MLP (gate, up, silu(gate) and
+// the product are each rounded to bf16).
+template <int BITS, int VAR, int M, int SPW, int EPI>
+__global__ void __launch_bounds__(kMaxWarps * 32)
+gemv_stream_kernel(const GemvParams p) {
+  constexpr int EPL = BITS == 8 ? 16 : 32;
+  __shared__ float red[2][kMaxWarps][M * kU];
+  __shared__ float nrm[kMaxWarps][M];
+
+  const int lane = threadIdx.x & 31;
+  const int warp = threadIdx.x >> 5;
+  const int kw = warp % p.KW;
+  const int rw = warp / p.KW;
+  const int barrier_id = 1 + rw;
+  const int barrier_threads = p.KW * 32;
+
+  // ---- column geometry (independent of the activations)
+  int cb[SPW];   // byte offset of the chunk inside a row, -1 if outside the row
+  int grp[SPW];  // scale group of the chunk
+#pragma unroll
+  for (int j = 0; j < SPW; ++j) {
+    const int s = kw + j * p.KW;
+    const int off = s * 512 + lane * 16;
+    const bool live = s < p.S && off < p.rowbytes;
+    cb[j] = live ? off : -1;
+    grp[j] = live ? (off * (8 / BITS)) / p.span : 0;
+  }
+
+  // ---- rows: batches of kU, a contiguous balanced range per row-warp slot
+  const int slots = gridDim.x * p.RW;
+  const int slot = blockIdx.x * p.RW + rw;
+  const int b_begin = (int)(((int64_t)p.nbatch * slot) / slots);
+  const int b_end = (int)(((int64_t)p.nbatch * (slot + 1)) / slots);
+
+  auto load_batch = [&](int b, WeightBatch<SPW>& wb) {
+    const int n0 = b * kU;
+#pragma unroll
+    for (int j = 0; j < SPW; ++j) {
+#pragma unroll
+      for (int u = 0; u < kU; ++u) {
+        const int n = min(n0 + u, p.N - 1);
+        if (cb[j] >= 0) wb.w[j][u] = ldg_stream(p.codes + (int64_t)n * p.rowbytes + cb[j]);
+        else wb.w[j][u] = make_uint4(0, 0, 0, 0);
+      }
+      if (p.out_group == 0) {
+        const float4 s4 = __ldg(reinterpret_cast<const float4*>(p.scales + (int64_t)grp[j] * p.SRp + n0));
+        wb.sc[j][0] = s4.x; wb.sc[j][1] = s4.y; wb.sc[j][2] = s4.z; wb.sc[j][3] = s4.w;
+      } else {
+#pragma unroll
+        for (int u = 0; u < kU; ++u)
+          wb.sc[j][u] = __ldg(p.scales + (int64_t)grp[j] * p.SRp + min(n0 + u, p.N - 1) / p.out_group);
+      }
+    }
+  };
+
+  // The weights do not depend on the kernel before this one: start streaming them, THEN
+  // wait for the producer of x (programmatic dependent launch; a no-op otherwise) and let
+  // the kernel after this one begin its own weight prefetch.
+  WeightBatch<SPW> bufA, bufB;
+  if (b_begin < b_end) load_batch(b_begin, bufA);
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+
+  // ---- optional fused RMSNorm: rstd[m] = 1 / sqrt(mean(x^2) + eps) over the whole row
+  float rstd[M];
+  if (p.norm_weight != nullptr) {
+    float ss[M];
+#pragma unroll
+    for (int m = 0; m < M; ++m) {
+      ss[m] = 0.f;
+#pragma unroll
+      for (int j = 0; j < SPW; ++j) {
+        if (cb[j] < 0 || m >= p.M) continue;
+        const int k0 = cb[j] * (8 / BITS);
+        const __nv_bfloat16* xr = p.x + (int64_t)m * p.ldx + k0;
+        for (int i = 0; i < EPL; ++i)
+          if (k0 + i < p.K) { const float v = __bfloat162float(xr[i]); ss[m] = fmaf(v, v, ss[m]); }
+      }
+      ss[m] = warp_sum(ss[m]);
+    }
+    if (p.KW > 1) {
+      if (lane == 0) {
+#pragma unroll
+        for (int m = 0; m < M; ++m) nrm[warp][m] = ss[m];
+      }
+      asm volatile("bar.sync %0, %1;" ::"r"(barrier_id), "r"(barrier_threads) : "memory");
+#pragma unroll
+      for (int m = 0; m < M; ++m) {
+        float t = 0.f;
+        for (int w = 0; w < p.KW; ++w) t += nrm[rw * p.KW + w][m];
+        ss[m] = t;
+      }
+    }
+#pragma unroll
+    for (int m = 0; m < M; ++m) rstd[m] = __frsqrt_rn(ss[m] / (float)p.K + p.norm_eps);
+  }
+
+  // ---- per-lane activation state
+  XChunk<BITS, VAR> xc[M][SPW];
+#pragma unroll
+  for (int j = 0; j < SPW; ++j) {
+    const bool live = cb[j] >= 0;
+    const int k0 = live ? cb[j] * (8 / BITS) : 0;
+#pragma unroll
+    for (int m = 0; m < M; ++m) {
+      float xf[EPL];
+      const __nv_bfloat16* xr = p.x + (int64_t)m * p.ldx + k0;
+      const bool full = live && m < p.M && k0 + EPL <= p.K &&
+                        ((reinterpret_cast<uintptr_t>(xr) & 15) == 0);
+      if (full) {
+#pragma unroll
+        for (int v = 0; v < EPL / 8; ++v) {
+          const uint4 raw = __ldg(reinterpret_cast<const uint4*>(xr) + v);
+          const unsigned r[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+          for (int t = 0; t < 4; ++t) {
+            xf[v * 8 + 2 * t] = __uint_as_float(r[t] << 16);
+            xf[v * 8 + 2 * t + 1] = __uint_as_float(r[t] & 0xFFFF0000u);
+          }
+        }
+      } else {
+#pragma unroll
+        for (int i = 0; i < EPL; ++i)
+          xf[i] = (live && m < p.M && k0 + i < p.K) ? __bfloat162float(xr[i]) : 0.f;
+      }
+      if (p.norm_weight != nullptr) {
+        // weight * bf16(x * rstd), the product rounded to bf16 again: the two roundings of
+        // a bf16 RMSNorm module
+        const __nv_bfloat16* gw = reinterpret_cast<const __nv_bfloat16*>(p.norm_weight) + k0;
+#pragma unroll
+        for (int i = 0; i < EPL; ++i) {
+          const float g = (live && k0 + i < p.K) ? __bfloat162float(gw[i]) : 0.f;
+          const float nx = __bfloat162float(__float2bfloat16_rn(xf[i] * rstd[m]));
+          xf[i] = __bfloat162float(__float2bfloat16_rn(g * nx));
+        }
+      }
+      xc[m][j].build(xf);
+    }
+  }
+
+  // ---- the row loop, software-pipelined one batch ahead
+  auto process = [&](int b, int parity, const WeightBatch<SPW>& wb) {
+    const int n0 = b * kU;
+    float acc[M][kU];
+#pragma unroll
+    for (int m = 0; m < M; ++m)
+#pragma unroll
+      for (int u = 0; u < kU; ++u) acc[m][u] = 0.f;
+#pragma unroll
+    for (int j = 0; j < SPW; ++j) {
+      if (cb[j] >= 0) {
+#pragma unroll
+        for (int u = 0; u < kU; ++u)
+#pragma unroll
+          for (int m = 0; m < M; ++m)
+            acc[m][u] = fmaf(xc[m][j].dot(wb.w[j][u]), wb.sc[j][u], acc[m][u]);
+      }
+    }
+#pragma unroll
+    for (int m = 0; m < M; ++m)
+#pragma unroll
+      for (int u = 0; u < kU; ++u) acc[m][u] = warp_sum(acc[m][u]);
+
+    if (p.KW > 1) {
+      float* mine = red[parity][warp];
+      if (lane == 0) {
+#pragma unroll
+        for (int m = 0; m < M; ++m)
+#pragma unroll
+          for (int u = 0; u < kU; ++u) mine[m * kU + u] = acc[m][u];
+      }
+      asm volatile("bar.sync %0, %1;" ::"r"(barrier_id), "r"(barrier_threads) : "memory");
+    }
+    if (kw == 0) {
+      float total = 0.f;
+      if (lane < M * kU) {
+        if (p.KW > 1) {
+          for (int w = 0; w < p.KW; ++w) total += red[parity][rw * p.KW + w][lane];
+        } else {
+#pragma unroll
+          for (int mm = 0; mm < M; ++mm)
+#pragma unroll
+            for (int uu = 0; uu < kU; ++uu)
+              if (mm * kU + uu == lane) total = acc[mm][uu];
+        }
+      }
+      const int m = lane / kU, u = lane % kU;
+      const int n = n0 + u;
+      if (EPI == 1) {
+        const float up = __shfl_down_sync(0xffffffffu, total, 1);
+        if (lane < M * kU && (u & 1) == 0 && n + 1 < p.N && m < p.M) {
+          const float g = __bfloat162float(__float2bfloat16_rn(total));
+          const float uq = __bfloat162float(__float2bfloat16_rn(up));
+          const float sg = __bfloat162float(__float2bfloat16_rn(g / (1.f + expf(-g))));
+          const float y = sg * uq;
+          const int64_t o = (int64_t)m * (p.N / 2) + n / 2;
+          if (p.out_f32) reinterpret_cast<float*>(p.out)[o] = __bfloat162float(__float2bfloat16_rn(y));
+          else reinterpret_cast<__nv_bfloat16*>(p.out)[o] = __float2bfloat16_rn(y);
+        }
+      } else if (lane < M * kU && n < p.N && m < p.M) {
+        if (p.bias != nullptr) total += __bfloat162float(p.bias[n]);
+        const int64_t o = (int64_t)m * p.N + n;
+        if (p.out_f32) {
+          if (p.residual != nullptr) total += reinterpret_cast<const float*>(p.residual)[o];
+          reinterpret_cast<float*>(p.out)[o] = total;
+        } else {
+          if (p.residual != nullptr) {
+            // a bf16 layer output added to a bf16 residual stream: round, add, round
+            total = __bfloat162float(__float2bfloat16_rn(total)) +
+                    __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p.residual)[o]);
+          }
+          reinterpret_cast<__nv_bfloat16*>(p.out)[o] = __float2bfloat16_rn(total);
+        }
+      }
+    }
+  };
+
+  for (int b = b_begin; b < b_end; b += 2) {
+    if (b + 1 < b_end) load_batch(b + 1, bufB);
+    process(b, 0, bufA);
+    if (b + 1 < b_end) {
+      if (b + 2 < b_end) load_batch(b + 2, bufA);
+      process(b + 1, 1, bufB);
+    }
+  }
+}
+
+template <int BITS, int VAR, int M, int SPW, int EPI>
+int launch_one(const GemvParams& p, int threads, cudaStream_t s) {
+  static thread_local int occ_threads = 0, occ = 0;
+  if (occ_threads != threads) {
+    int n = 0;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(
+            &n, gemv_stream_kernel<BITS, VAR, M, SPW, EPI>, threads, 0) != cudaSuccess || n <= 0) {
+      cudaGetLastError();
+      n = 1;
+    }
+    occ = n;
+    occ_threads = threads;
+  }
+  // One row batch per row-warp slot until every SM holds its full complement of CTAs;
+  // beyond that the slots take several batches each (a single resident wave, no tail).
+  const int want = (p.nbatch + p.RW - 1) / p.RW;
+  const int cap = sm_count() * occ;
+  int grid = want < cap ? want : cap;
+  if (grid < 1) grid = 1;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)grid);
+  cfg.blockDim = dim3((unsigned)threads);
+  cfg.dynamicSmemBytes = 0;
+  cfg.stream = s;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = p.pdl ? 1 : 0;
+  cudaError_t e = cudaLaunchKernelEx(&cfg, gemv_stream_kernel<BITS, VAR, M, SPW, EPI>, p);
+  if (e != cudaSuccess) {
+    cudaGetLastError();
+    return fail(LQ_ERR_LAUNCH, "lq_wq_gemv: %s", cudaGetErrorString(e));
+  }
+  return LQ_OK;
+}
+
+// Activation rows one pass can keep in registers next to SPW column chunks per lane; wider
+// requests run as several passes over the weight.
+template <int BITS, int VAR>
+constexpr int max_rows(int spw) {
+  if (spw == 1) return (BITS == 4 && VAR == 1) ? 2 : 4;
+  if (spw == 2) return BITS == 8 ? (VAR == 1 ? 1 : 2) : 1;
+  return 1;
+}
+
+template <int BITS, int VAR, int EPI>
+int launch_m(const GemvParams& p, int spw, int threads, cudaStream_t s) {
+  if (spw == 1) {
+    if (p.M == 1) return launch_one<BITS, VAR, 1, 1, EPI>(p, threads, s);
+    if (p.M == 2) return launch_one<BITS, VAR, 2, 1, EPI>(p, threads, s);
+    if constexpr (max_rows<BITS, VAR>(1) >= 4) return launch_one<BITS, VAR, 4, 1, EPI>(p, threads, s);
+  } else if (spw == 2) {
+    if (p.M == 1) return launch_one<BITS, VAR, 1, 2, EPI>(p, threads, s);
+    if constexpr (max_rows<BITS, VAR>(2) >= 2) return launch_one<BITS, VAR, 2, 2, EPI>(p, threads, s);
+  } else if (spw == 4) {
+    if constexpr (EPI == 0) {
+      if (p.M == 1) return launch_one<BITS, VAR, 1, 4, 0>(p, threads, s);
+    }
+  }
+  return fail(LQ_ERR_UNSUPPORTED, "internal: no GEMV instance for M=%d spw=%d", p.M, spw);
+}
+
+template <int BITS, int VAR>
+int launch_passes(GemvParams p, const lq_gemv_args& a, int spw, int threads, cudaStream_t s) {
+  const int step = max_rows<BITS, VAR>(spw);
+  const size_t out_es = p.out_f32 ? 4 : 2;
+  const int n_out = a.epilogue == 1 ? a.N / 2 : a.N;
+  for (int m0 = 0; m0 < a.M; m0 += step) {
+    p.M = a.M - m0 < step ? a.M - m0 : step;
+    p.x = (const __nv_bfloat16*)a.x + (int64_t)m0 * p.ldx;
+    p.out = (char*)a.out + (size_t)m0 * n_out * out_es;
+    p.residual = a.residual ? (const char*)a.residual + (size_t)m0 * n_out * out_es : nullptr;
+    const int rc = a.epilogue == 1 ? launch_m<BITS, VAR, 1>(p, spw, threads, s)
+                                   : launch_m<BITS, VAR, 0>(p, spw, threads, s);
+    if (rc) return rc;
+  }
+  return LQ_OK;
+}
+
+}  // namespace gemv
+}  // namespace lq

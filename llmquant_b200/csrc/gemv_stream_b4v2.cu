@@ -1,0 +1,10 @@
+// Instantiation unit: streaming GEMV, 4-bit codes, arithmetic variant 2.
+#include "gemv_stream.cuh"
+
+namespace lq {
+namespace gemv {
+int run_b4v2(GemvParams p, const lq_gemv_args& a, int spw, int threads, cudaStream_t s) {
+  return launch_passes<4, 2>(p, a, spw, threads, s);
+}
+}  // namespace gemv
+}  // namespace lq

@@ -39,7 +39,30 @@ _SIGNATURES = {
     "lq_dequant_stream": [_P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P],
     "lq_wq_gemv_stream": [_P, _I, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _I, _P],
 }
-_RESTYPE = {"lq_last_error": ctypes.c_char_p}
+_SIGNATURES.update({
+    "lq_kv_write": [_P, _P, _P, _P, _I, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P, _L, _I, _P],
+    "lq_kv_dequant": [_P, _P, _P, _I, _I, _I, _I, _I, _I, _P],
+    "lq_rope_kv_write": [_P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P, _L, _I, _I, _P],
+    "lq_attn_decode_scratch_bytes": [_I, _I, _I, _I],
+    "lq_attn_decode_kv_i8": [_P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P, _L, _I,
+                             ctypes.c_float, _I, _I, _P],
+})
+_RESTYPE = {"lq_last_error": ctypes.c_char_p, "lq_attn_decode_scratch_bytes": ctypes.c_int64}
+
+
+class GemvArgs(ctypes.Structure):
+    """Mirror of `lq_gemv_args` (include/llmquant_b200.h)."""
+
+    _fields_ = [
+        ("x", _P), ("ldx", _I), ("norm_weight", _P), ("norm_eps", ctypes.c_float),
+        ("codes", _P), ("scales_t", _P), ("bias", _P), ("residual", _P), ("out", _P),
+        ("out_dtype", _I), ("M", _I), ("N", _I), ("K", _I), ("Kd", _I), ("span", _I),
+        ("SRp", _I), ("out_group", _I), ("bits", _I), ("epilogue", _I), ("variant", _I),
+        ("pdl", _I),
+    ]
+
+
+_SIGNATURES["lq_wq_gemv_fused"] = [ctypes.POINTER(GemvArgs), _P]
 
 
 def declared_symbols(header: pathlib.Path = HEADER):

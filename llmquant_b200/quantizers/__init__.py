@@ -8,6 +8,8 @@ from llmquant_b200.quantizers.kernel import (
     quantize_weight_canonical,
 )
 
+from llmquant_b200.quantizers.kv_cache import KernelQuantCache, QuantizedKVLayer, make_cache_factory
+
 AVAILABLE_MODES = frozenset({"kernel"})
 
 
@@ -19,6 +21,7 @@ def quant_linear_for(mode: str):
 
 
 __all__ = [
-    "AVAILABLE_MODES", "DECODE_MAX_ROWS", "KERNEL_MAX_ROWS", "KernelQuantLinear",
+    "AVAILABLE_MODES", "DECODE_MAX_ROWS", "KERNEL_MAX_ROWS", "KernelQuantCache", "KernelQuantLinear",
+    "QuantizedKVLayer", "make_cache_factory",
     "pad_activation", "quant_linear_for", "quantize_weight_canonical",
 ]

@@ -13,6 +13,8 @@ modifier treat it identically. What differs is underneath:
     the prefill path.
 """
 
+import ctypes
+
 import torch
 import torch.nn as nn
 
@@ -184,11 +186,18 @@ class KernelQuantLinear(nn.Module):
                         native.stream_ptr(dev))
         return out
 
-    def gemv(self, flat, out_dtype=None, residual=None, variant=None):
-        """Streaming GEMV on `[M <= 8, K]` bf16 rows. Returns `[M, N]` (bf16 or fp32)."""
+    def gemv(self, flat, out_dtype=None, residual=None, variant=None, norm_weight=None,
+             norm_eps=1e-5, epilogue=0, pdl=False, out=None):
+        """Streaming GEMV on `[M <= 8, K]` bf16 rows -> `[M, N]` (bf16 or fp32).
+
+        Optional fusions (see `lq_wq_gemv_fused`): RMSNorm of the input rows by `norm_weight`,
+        `epilogue=1` for silu(gate) * up over interleaved (gate, up) rows, a residual added to
+        the output, and `pdl` to overlap the weight prefetch with the previous kernel."""
         m = flat.shape[0]
         out_dtype = out_dtype or torch.bfloat16
-        out = torch.empty(m, self.out_features, dtype=out_dtype, device=flat.device)
+        n_out = self.out_features // 2 if epilogue == 1 else self.out_features
+        if out is None:
+            out = torch.empty(m, n_out, dtype=out_dtype, device=flat.device)
         if m == 0:
             return out
         bias = None
@@ -198,13 +207,16 @@ class KernelQuantLinear(nn.Module):
             bias = self._bias_bf16
         if flat.stride(-1) != 1:
             flat = flat.contiguous()
+        args = native.GemvArgs(
+            x=flat.data_ptr(), ldx=flat.stride(0), norm_weight=native.ptr(norm_weight),
+            norm_eps=norm_eps, codes=self.codes.data_ptr(), scales_t=self.scales_t.data_ptr(),
+            bias=native.ptr(bias), residual=native.ptr(residual), out=out.data_ptr(),
+            out_dtype=native.DTYPE_ID[out_dtype], M=m, N=self.out_features, K=self.in_features,
+            Kd=self._kd, span=self._span, SRp=self._srp, out_group=self.out_group,
+            bits=self.num_bits, epilogue=epilogue,
+            variant=GEMV_VARIANT if variant is None else variant, pdl=1 if pdl else 0)
         with torch.cuda.device(flat.device):
-            native.call("lq_wq_gemv_stream", flat.data_ptr(), flat.stride(0), self.codes.data_ptr(),
-                        self.scales_t.data_ptr(), native.ptr(bias), native.ptr(residual),
-                        out.data_ptr(), native.DTYPE_ID[out_dtype], m, self.out_features,
-                        self.in_features, self._kd, self._span, self._srp, self.out_group,
-                        self.num_bits, GEMV_VARIANT if variant is None else variant,
-                        native.stream_ptr(flat.device))
+            native.call("lq_wq_gemv_fused", ctypes.byref(args), native.stream_ptr(flat.device))
         return out
 
     def forward(self, x):

@@ -1,0 +1,252 @@
+"""Fused greedy decoder for Llama-class models whose linears are `KernelQuantLinear`.
+
+The reference decodes by calling the transformers model once per token -- each projection a
+separate `wq_gemv` launch with PyTorch ops in between (RMSNorm, RoPE, cache update, SiLU,
+residual adds), optionally replayed from a CUDA graph (llmquant/runtime/graph_decode.py:52-131).
+This decoder walks the same layer sequence with the library's kernels only:
+
+    per layer   GEMV[RMSNorm -> q|k|v]  ->  RoPE + int8 KV write  ->  int8-KV decode attention
+                -> GEMV[o_proj + residual]  ->  GEMV[RMSNorm -> gate|up -> silu*mul]
+                -> GEMV[down_proj + residual]
+    then        GEMV[final RMSNorm -> lm_head]  ->  argmax  ->  embedding row of the new token
+
+q/k/v and gate/up are concatenated once at construction so each is one pass over one weight.
+Every launch uses programmatic dependent launch, so a kernel's first weight loads overlap the
+tail of the kernel before it. One step is captured into a CUDA graph and replayed per token;
+the write cursor of the KV cache lives in device memory. Prefill runs through the
+transformers modules (eagerly, as in the reference) into the same integer cache.
+
+The arithmetic (bf16 roundings of RMSNorm, RoPE, SiLU*mul and the residual adds) follows
+transformers' Llama modules, so greedy tokens match the module-by-module path.
+"""
+
+import torch
+
+from llmquant_b200 import native
+from llmquant_b200.core.scheme import QuantizationScheme
+from llmquant_b200.quantizers.kernel import KernelQuantLinear
+from llmquant_b200.quantizers.kv_cache import KernelQuantCache
+
+
+def _fuse_rows(modules, interleave=False):
+    """One KernelQuantLinear holding the rows of several (same geometry, same scheme)."""
+    first = modules[0]
+    args = first.scheme.weights
+    for m in modules[1:]:
+        a = m.scheme.weights
+        same = (a.num_bits, a.group_size, a.head_dim, a.out_group) == (
+            args.num_bits, args.group_size, args.head_dim, args.out_group)
+        if not same or m.in_features != first.in_features or not m._stream:
+            raise ValueError("projections to fuse must share one weight scheme and input width")
+    if args.out_group and any(m.out_features % args.out_group for m in modules):
+        raise ValueError("row groups would straddle the fused projections")
+    codes = [m.qweight for m in modules]
+    scales = [m.wscale for m in modules]
+    if interleave:
+        if len({m.out_features for m in modules}) != 1 or args.out_group:
+            raise ValueError("interleaving needs equal row counts and per-row scales")
+        qweight = torch.stack(codes, dim=1).reshape(-1, *codes[0].shape[1:])
+        wscale = torch.stack(scales, dim=1).reshape(-1, scales[0].shape[1])
+    else:
+        qweight = torch.cat(codes, dim=0)
+        wscale = torch.cat(scales, dim=0)
+    bias = None
+    if any(m.bias is not None for m in modules):
+        if interleave:
+            raise ValueError("the fused gate/up epilogue takes no bias")
+        parts = [m.bias if m.bias is not None
+                 else torch.zeros(m.out_features, dtype=torch.bfloat16, device=qweight.device)
+                 for m in modules]
+        bias = torch.cat([p.detach().to(torch.bfloat16) for p in parts])
+    return KernelQuantLinear(qweight.contiguous(), wscale.contiguous(), bias, first.scheme,
+                             first.in_features)
+
+
+def supports(model) -> bool:
+    """Whether `model` is a Llama-layout decoder fully on kernel-mode linears."""
+    try:
+        layers = model.model.layers
+        cfg = model.config
+    except AttributeError:
+        return False
+    if not torch.cuda.is_available() or len(layers) == 0:
+        return False
+    names = ("q_proj", "k_proj", "v_proj", "o_proj")
+    for layer in layers:
+        attn, mlp = getattr(layer, "self_attn", None), getattr(layer, "mlp", None)
+        if attn is None or mlp is None:
+            return False
+        mods = [getattr(attn, n, None) for n in names]
+        mods += [getattr(mlp, n, None) for n in ("gate_proj", "up_proj", "down_proj")]
+        if not all(isinstance(m, KernelQuantLinear) and m._stream for m in mods):
+            return False
+    head_dim = getattr(cfg, "head_dim", None) or cfg.hidden_size // cfg.num_attention_heads
+    groups = cfg.num_attention_heads // cfg.num_key_value_heads
+    return head_dim in (64, 128) and groups in (1, 2, 4, 8) and cfg.hidden_act == "silu"
+
+
+class FusedLlamaDecoder:
+    """Greedy decode of a kernel-mode Llama: eager prefill, then one replayed graph per token."""
+
+    def __init__(self, model, max_batch: int, max_len: int, kv_bits: int = 8, use_graph: bool = True,
+                 pdl: bool = True):
+        if not supports(model):
+            raise ValueError("FusedLlamaDecoder needs a Llama-layout model whose attention and MLP "
+                             "linears are KernelQuantLinear (head_dim 64/128, silu MLP)")
+        if max_batch > 8:
+            raise ValueError("the decode GEMV takes at most 8 rows; batch > 8 is not built yet")
+        cfg = model.config
+        self.model = model
+        self.device = next(model.parameters()).device
+        self.B, self.max_len, self.kv_bits = max_batch, max_len, kv_bits
+        self.use_graph, self.pdl = use_graph, pdl
+        self.hidden = cfg.hidden_size
+        self.Hq, self.Hkv = cfg.num_attention_heads, cfg.num_key_value_heads
+        self.D = getattr(cfg, "head_dim", None) or cfg.hidden_size // cfg.num_attention_heads
+        self.eps = cfg.rms_norm_eps
+        self.scaling = self.D ** -0.5
+        self.vocab = cfg.vocab_size
+        dev, bf16 = self.device, torch.bfloat16
+
+        self.layers = []
+        for layer in model.model.layers:
+            attn, mlp = layer.self_attn, layer.mlp
+            self.layers.append({
+                "qkv": _fuse_rows([attn.q_proj, attn.k_proj, attn.v_proj]),
+                "o": attn.o_proj,
+                "gate_up": _fuse_rows([mlp.gate_proj, mlp.up_proj], interleave=True),
+                "down": mlp.down_proj,
+                "ln1": layer.input_layernorm.weight.detach().to(bf16).contiguous(),
+                "ln2": layer.post_attention_layernorm.weight.detach().to(bf16).contiguous(),
+            })
+        self.final_norm = model.model.norm.weight.detach().to(bf16).contiguous()
+        self.lm_head = model.lm_head
+        self.embed = model.model.embed_tokens.weight
+
+        # rotary tables from the model's own module, so scaling variants come along
+        positions = torch.arange(max_len, device=dev)[None]
+        probe = torch.zeros(1, 1, self.D, dtype=bf16, device=dev)
+        with torch.no_grad():
+            cos, sin = model.model.rotary_emb(probe, positions)
+        self.cos = cos[0].to(bf16).contiguous()
+        self.sin = sin[0].to(bf16).contiguous()
+
+        B, H = self.B, self.hidden
+        inter = self.layers[0]["down"].in_features
+        self.h = [torch.zeros(B, H, dtype=bf16, device=dev) for _ in range(2)]
+        self.qkv = torch.zeros(B, (self.Hq + 2 * self.Hkv) * self.D, dtype=bf16, device=dev)
+        self.q_rot = torch.zeros(B, self.Hq * self.D, dtype=bf16, device=dev)
+        self.attn = torch.zeros(B, self.Hq * self.D, dtype=bf16, device=dev)
+        self.act = torch.zeros(B, inter, dtype=bf16, device=dev)
+        self.logits = torch.zeros(B, self.vocab, dtype=bf16, device=dev)
+        self.tokens = torch.zeros(B, dtype=torch.long, device=dev)
+        self.pos = torch.zeros(1, dtype=torch.long, device=dev)
+        self.history = torch.zeros(B, max_len + 1, dtype=torch.long, device=dev)
+        want = max(1, -(-2 * 148 // (B * self.Hkv)))
+        self.splits = max(1, min(want, max_len // 64 or 1))
+        nbytes = native.library().lq_attn_decode_scratch_bytes(B, self.Hq, self.D, self.splits)
+        self.scratch = torch.zeros(nbytes // 4, dtype=torch.float32, device=dev)
+        self.cache = KernelQuantCache(kv_bits, max_cache_len=max_len)
+        self.graph = None
+        self.launches_per_step = len(self.layers) * 7 + 1
+
+    # ------------------------------------------------------------------ one token
+    def _step_kernels(self):
+        stream = native.stream_ptr(self.device)
+        pdl = 1 if self.pdl else 0
+        cur, nxt = self.h
+        cur.copy_(self.embed.index_select(0, self.tokens))
+        pos_ptr = self.pos.data_ptr()
+        for spec, cache in zip(self.layers, self.cache.layers):
+            spec["qkv"].gemv(cur, norm_weight=spec["ln1"], norm_eps=self.eps, pdl=self.pdl, out=self.qkv)
+            native.call("lq_rope_kv_write", self.qkv.data_ptr(), self.cos.data_ptr(), self.sin.data_ptr(),
+                        self.q_rot.data_ptr(), cache.k_codes.data_ptr(), cache.v_codes.data_ptr(),
+                        cache.k_scales.data_ptr(), cache.v_scales.data_ptr(), self.B, self.Hq,
+                        self.Hkv, self.D, cache.capacity, self.cos.shape[0], pos_ptr, 0,
+                        self.kv_bits, pdl, stream)
+            native.call("lq_attn_decode_kv_i8", self.q_rot.data_ptr(), cache.k_codes.data_ptr(),
+                        cache.v_codes.data_ptr(), cache.k_scales.data_ptr(), cache.v_scales.data_ptr(),
+                        self.attn.data_ptr(), self.scratch.data_ptr(), self.B, self.Hq, self.Hkv,
+                        self.D, cache.capacity, pos_ptr, 0, 1, self.scaling, self.splits, pdl, stream)
+            spec["o"].gemv(self.attn, residual=cur, pdl=self.pdl, out=nxt)
+            spec["gate_up"].gemv(nxt, norm_weight=spec["ln2"], norm_eps=self.eps, epilogue=1,
+                                 pdl=self.pdl, out=self.act)
+            spec["down"].gemv(self.act, residual=nxt, pdl=self.pdl, out=cur)
+        if isinstance(self.lm_head, KernelQuantLinear) and self.lm_head._stream:
+            self.lm_head.gemv(cur, norm_weight=self.final_norm, norm_eps=self.eps, pdl=self.pdl,
+                              out=self.logits)
+        else:
+            with torch.no_grad():
+                self.logits.copy_(self.lm_head(self.model.model.norm(cur)))
+        torch.argmax(self.logits, dim=-1, out=self.tokens)
+        self.pos.add_(1)
+        self.history.index_copy_(1, self.pos, self.tokens.unsqueeze(1))
+
+    # ------------------------------------------------------------------ prefill / capture
+    @torch.no_grad()
+    def prefill(self, input_ids):
+        """Eager pass over the prompt through the transformers modules into the int cache.
+        Returns the first generated token per sequence, [B]."""
+        if input_ids.shape[0] != self.B:
+            raise ValueError(f"decoder was built for batch {self.B}, got {input_ids.shape[0]}")
+        prompt = input_ids.shape[1]
+        if prompt >= self.max_len:
+            raise ValueError(f"prompt of {prompt} tokens does not fit a cache of {self.max_len}")
+        for layer in self.cache.layers:
+            layer.reset()
+        out = self.model(input_ids, past_key_values=self.cache, use_cache=True, logits_to_keep=1)
+        first = out.logits[:, -1].argmax(-1)
+        self.tokens.copy_(first)
+        self.pos.fill_(prompt)
+        self.history.zero_()
+        self.history[:, :prompt] = input_ids
+        self.history[:, prompt] = first
+        return first
+
+    @torch.no_grad()
+    def capture(self):
+        """Warm up on a side stream, then capture one step. The warm-up and the capture write
+        real entries at the cursor; the cursor and token are restored afterwards and the
+        entries are overwritten by the first replay."""
+        saved_pos, saved_tok = self.pos.clone(), self.tokens.clone()
+        saved_hist = self.history.clone()
+        side = torch.cuda.Stream(self.device)
+        side.wait_stream(torch.cuda.current_stream(self.device))
+        with torch.cuda.stream(side):
+            for _ in range(2):
+                self.pos.copy_(saved_pos)
+                self.tokens.copy_(saved_tok)
+                self._step_kernels()
+        torch.cuda.current_stream(self.device).wait_stream(side)
+        torch.cuda.synchronize(self.device)
+        self.pos.copy_(saved_pos)
+        self.tokens.copy_(saved_tok)
+        self.graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(self.graph):
+            self._step_kernels()
+        self.pos.copy_(saved_pos)
+        self.tokens.copy_(saved_tok)
+        self.history.copy_(saved_hist)
+
+    @torch.no_grad()
+    def step(self):
+        """Decode one token for every sequence (in place: tokens, pos, history advance)."""
+        if self.use_graph:
+            if self.graph is None:
+                self.capture()
+            self.graph.replay()
+        else:
+            self._step_kernels()
+
+    @torch.no_grad()
+    def generate(self, input_ids, max_new_tokens: int):
+        """Greedy generation; returns prompt + new tokens, like `model.generate(do_sample=False)`."""
+        prompt = input_ids.shape[1]
+        if prompt + max_new_tokens > self.max_len:
+            raise ValueError("prompt + new tokens exceed the decoder's cache")
+        self.prefill(input_ids.to(self.device))
+        for _ in range(max_new_tokens - 1):
+            self.step()
+        for layer in self.cache.layers:
+            layer.length = prompt + max_new_tokens - 1
+        return self.history[:, : prompt + max_new_tokens].clone()

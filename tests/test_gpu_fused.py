@@ -1,0 +1,137 @@
+"""The fused GEMV options (RMSNorm prologue, silu*mul epilogue, residual, dependent launch)
+against the numpy restatement of transformers' layer ops, and the whole decoder against the
+reference's real-mode run of a seeded tiny Llama (tests/golden/tiny_llama.npz)."""
+
+import numpy as np
+import pytest
+import torch
+
+import oracle
+from gpu_util import rel_l2, seeded
+from llmquant_b200.core import QuantConfig, QuantizationArgs, QuantizationScheme, oneshot
+from oracle import llama_ops
+
+pytestmark = pytest.mark.gpu
+
+
+def _module(w, bits):
+    from llmquant_b200.quantizers import KernelQuantLinear
+
+    scheme = QuantizationScheme(
+        weights=QuantizationArgs(num_bits=bits, strategy="group", group_size=128), input_activations=None)
+    linear = torch.nn.Linear(w.shape[1], w.shape[0], bias=False)
+    linear.weight.data = w
+    return KernelQuantLinear.from_linear(linear.cuda(), scheme)
+
+
+@pytest.mark.parametrize("bits", [4, 8])
+@pytest.mark.parametrize("M", [1, 4])
+@pytest.mark.parametrize("k", [2048, 4096])
+def test_rmsnorm_prologue(bits, M, k):
+    w = seeded((512, k), 1, 0.02, torch.bfloat16)
+    x = (seeded((M, k), 2) * 3).bfloat16()
+    gamma = (seeded((k,), 3) * 0.1 + 1).bfloat16()
+    module = _module(w, bits)
+    got = module.gemv(x.cuda(), out_dtype=torch.float32, norm_weight=gamma.cuda(), norm_eps=1e-5, pdl=True)
+    q, scale = oracle.quantize_weight(w.float().numpy(), bits, 128)
+    normed = llama_ops.rmsnorm(x.float().numpy(), gamma.float().numpy(), 1e-5)
+    want = oracle.real_linear(normed, q, scale, bits, 128)
+    assert rel_l2(got.cpu().numpy(), want) <= 1e-3
+
+
+@pytest.mark.parametrize("bits", [4, 8])
+@pytest.mark.parametrize("M", [1, 3])
+def test_silu_mul_epilogue_and_residual(bits, M):
+    from llmquant_b200.runtime.decoder import _fuse_rows
+
+    k, inter = 2048, 1024
+    gate_w = seeded((inter, k), 4, 0.02, torch.bfloat16)
+    up_w = seeded((inter, k), 5, 0.02, torch.bfloat16)
+    x = seeded((M, k), 6).bfloat16()
+    gate, up = _module(gate_w, bits), _module(up_w, bits)
+    fused = _fuse_rows([gate, up], interleave=True)
+    got = fused.gemv(x.cuda(), epilogue=1)
+    assert got.shape == (M, inter)
+    g = gate(x.cuda()).float().cpu().numpy()
+    u = up(x.cuda()).float().cpu().numpy()
+    want = llama_ops.silu_mul(g, u)
+    assert rel_l2(got.float().cpu().numpy(), want) <= 2e-3
+    # concatenated (q|k|v style) rows give the rows of the parts
+    both = _fuse_rows([gate, up]).gemv(x.cuda())
+    assert torch.equal(both[:, :inter], gate(x.cuda())) and torch.equal(both[:, inter:], up(x.cuda()))
+    res = seeded((M, inter), 7).bfloat16().cuda()
+    with_res = gate.gemv(x.cuda(), residual=res)
+    want_res = (gate(x.cuda()).float() + res.float()).bfloat16()
+    assert torch.equal(with_res, want_res)
+
+
+def _kernel_model(kw):
+    from oracle.real_mode import tiny_llama
+
+    model = tiny_llama(seed=0, **kw).cuda()
+    cfg = QuantConfig(attn_weight="int8", mlp_weight="int4", head_weight="int8", kv_cache="int8")
+    return oneshot(model, cfg.to_modifier(mode="kernel"))
+
+
+def _agreement(tokens, want):
+    same = (tokens == want).all(0)
+    return int(np.argmin(same)) if not same.all() else len(same)
+
+
+@pytest.mark.parametrize("tag,kw", [("hd64", dict(head_dim=64)),
+                                    ("hd128", dict(head_dim=128, hidden=512, inter=1024))])
+def test_decoder_against_the_reference_real_mode_run(golden, tag, kw):
+    """Random-init logits are nearly flat, so a 1-ulp bf16 difference can flip an argmax and the
+    streams part ways for good. The hard gate is therefore teacher-forced: feeding the
+    reference's own tokens, every step's logits agree to rel-L2 <= 1e-2 and the argmax agrees
+    wherever the reference's top-2 margin exceeds the numeric noise. Free-running agreement is
+    checked on the prefix before the first low-margin step."""
+    from llmquant_b200.quantizers import make_cache_factory
+    from llmquant_b200.runtime.decoder import FusedLlamaDecoder
+    from oracle.real_mode import greedy
+
+    blob = golden("tiny_llama")
+    model = _kernel_model(kw)
+    prompt = torch.from_numpy(blob[f"{tag}_prompt"]).cuda()
+    want_tokens, want_logits = blob[f"{tag}_tokens"], blob[f"{tag}_logits"]
+    n_prompt, new = prompt.shape[1], want_logits.shape[1]
+
+    # (1) module-by-module path through transformers with the integer cache, teacher-forced
+    cache = make_cache_factory(8)()
+    ids = torch.from_numpy(want_tokens).cuda()
+    with torch.no_grad():
+        out = model(ids[:, :-1], past_key_values=cache, use_cache=True)
+    got = out.logits[:, n_prompt - 1:].float().cpu().numpy()
+    assert got.shape == want_logits.shape
+    top2 = np.sort(want_logits, -1)[..., -2:]
+    margin = top2[..., 1] - top2[..., 0]
+    noise = np.abs(got - want_logits).max(-1)
+    assert rel_l2(got, want_logits) <= 1e-2
+    decided = margin > 4 * noise
+    assert decided.mean() > 0.5
+    assert (got.argmax(-1) == want_logits.argmax(-1))[decided].all()
+
+    # (2) the fused decoder, free-running, eager and graphed: identical to each other, and
+    # identical to the reference up to the first undecided step
+    first_undecided = int(np.argmin(decided.all(0))) if not decided.all() else new
+    streams = []
+    for use_graph in (False, True):
+        dec = FusedLlamaDecoder(model, prompt.shape[0], n_prompt + new + 1, kv_bits=8, use_graph=use_graph)
+        tokens = dec.generate(prompt, new).cpu().numpy()
+        streams.append(tokens)
+        agree = _agreement(tokens[:, n_prompt:], want_tokens[:, n_prompt:])
+        assert agree >= first_undecided, (use_graph, agree, first_undecided)
+    assert np.array_equal(streams[0], streams[1])
+
+    # (3) the fused decoder teacher-forced: its logits at every step against the reference
+    dec = FusedLlamaDecoder(model, prompt.shape[0], n_prompt + new + 1, kv_bits=8, use_graph=False)
+    dec.prefill(prompt)
+    fused_logits = []
+    for i in range(1, new):
+        dec.tokens.copy_(ids[:, n_prompt + i - 1])
+        dec.step()
+        fused_logits.append(dec.logits.float().cpu().numpy())
+    fused_logits = np.stack(fused_logits, 1)
+    assert rel_l2(fused_logits, want_logits[:, 1:]) <= 1e-2
+    ok = (fused_logits.argmax(-1) == want_logits[:, 1:].argmax(-1))[decided[:, 1:]]
+    assert ok.all()
