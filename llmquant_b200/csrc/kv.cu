@@ -213,8 +213,12 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, const int8_t* __restrict
     for (int i = 0; i < DPL; ++i) acc[g][i] = 0.f;
   }
   const int64_t head_row = ((int64_t)b * Hkv + kvh) * Tmax;
-  for (int t = t_lo + grp; t < t_hi; t += NGRP) {
-    const int64_t row = head_row + t;
+  // The trip count is the same for every lane of the warp (the shuffles below name all 32
+  // lanes); a lane group whose token falls past the slice computes on zeros and is masked.
+  for (int t0 = t_lo; t0 < t_hi; t0 += NGRP) {
+    const int t = t0 + grp;
+    const bool valid = t < t_hi;
+    const int64_t row = head_row + (valid ? t : t_lo);
     int8_t kb[DPL], vb[DPL];
     if (DPL == 16) {
       *reinterpret_cast<uint4*>(kb) = *reinterpret_cast<const uint4*>(kc + row * D + sub * DPL);
@@ -238,22 +242,24 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, const int8_t* __restrict
       d += __shfl_xor_sync(0xffffffffu, d, 4);
       s[g] = d * sk;
     }
-    float vf[DPL];
+    if (valid) {
+      float vf[DPL];
 #pragma unroll
-    for (int i = 0; i < DPL; ++i) vf[i] = (float)vb[i] * sv;
+      for (int i = 0; i < DPL; ++i) vf[i] = (float)vb[i] * sv;
 #pragma unroll
-    for (int g = 0; g < G; ++g) {
-      if (s[g] > m[g]) {  // rare after the first tokens: rescale only when the maximum moves
-        const float corr = __expf(m[g] - s[g]);
-        l[g] *= corr;
+      for (int g = 0; g < G; ++g) {
+        if (s[g] > m[g]) {  // rare after the first tokens: rescale only when the maximum moves
+          const float corr = __expf(m[g] - s[g]);
+          l[g] *= corr;
 #pragma unroll
-        for (int i = 0; i < DPL; ++i) acc[g][i] *= corr;
-        m[g] = s[g];
+          for (int i = 0; i < DPL; ++i) acc[g][i] *= corr;
+          m[g] = s[g];
+        }
+        const float p = __expf(s[g] - m[g]);
+        l[g] += p;
+#pragma unroll
+        for (int i = 0; i < DPL; ++i) acc[g][i] = fmaf(p, vf[i], acc[g][i]);
       }
-      const float p = __expf(s[g] - m[g]);
-      l[g] += p;
-#pragma unroll
-      for (int i = 0; i < DPL; ++i) acc[g][i] = fmaf(p, vf[i], acc[g][i]);
     }
   }
 
