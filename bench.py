@@ -4,6 +4,12 @@
 
 Prints ONE JSON line (rank 0). Workloads:
 
+  decode_8b       (default) BASELINE config 5: random-init Llama-3-8B, attention int8, MLP int4
+                  (group 128), lm_head int8, int8 KV cache, batch 1, 4096-token uniform-random
+                  prompt, greedy decode. A step is one decoded token through the fused decoder
+                  (one CUDA-graph replay). value = decoded tokens per second.
+  decode_1b       BASELINE config 3: the same for the Llama-3.2-1B shape, 512-token prompt.
+
   gemv_sweep_1b   BASELINE config 2: the Llama-3.2-1B linear shapes at M=1 (q/o, k/v, gate/up,
                   down as int4 and int8, lm_head int8), bf16 activations, group 128. A step is
                   one pass over a pool of distinct weight copies of every shape (the pool of
@@ -137,10 +143,10 @@ def build_pool(device):
             lin.weight = torch.nn.Parameter(w, requires_grad=False)
             base.append(KernelQuantLinear.from_linear(lin, scheme))
             del w, lin
-        weights = [(m.codes, m.scales_t) for m in base]
+        weights = [(m.codes, m.scale_tiles) for m in base]
         while len(weights) < copies:
             src = base[len(weights) % 2]
-            weights.append((src.codes.clone(), src.scales_t.clone()))
+            weights.append((src.codes.clone(), src.scale_tiles.clone()))
         x = (torch.randn(1, k, generator=g)).to(torch.bfloat16).to(device)
         pool.append({"name": name, "n": n, "k": k, "bits": bits, "mod": base[0], "weights": weights,
                      "x": x, "bytes": per_copy})
@@ -156,11 +162,11 @@ def capture_shape_graph(entry):
 
     def run():
         from llmquant_b200 import native
-        for (codes, scales_t), out in zip(entry["weights"], outs):
+        for (codes, scale_tiles), out in zip(entry["weights"], outs):
             native.call("lq_wq_gemv_stream", x.data_ptr(), x.stride(0), codes.data_ptr(),
-                        scales_t.data_ptr(), 0, 0, out.data_ptr(), native.LQ_BF16, 1,
-                        mod.out_features, mod.in_features, mod._kd, mod._span, mod._srp,
-                        mod.out_group, mod.num_bits, 0, native.stream_ptr(x.device))
+                        scale_tiles.data_ptr(), 0, 0, out.data_ptr(), native.LQ_BF16, 1,
+                        mod.out_features, mod.in_features, mod._kd, mod._span, mod.num_bits, 0,
+                        native.stream_ptr(x.device))
 
     side = torch.cuda.Stream()
     side.wait_stream(torch.cuda.current_stream())
@@ -269,6 +275,158 @@ def run_gpu(args, rank, world, device):
         print(json.dumps(line), flush=True)
 
 
+# --------------------------------------------------------------------------- decode workload
+DECODE = {
+    "decode_8b": dict(shape="llama-3-8b", prompt=4096, label="BASELINE config 5: random-init Llama-3-8B"),
+    "decode_1b": dict(shape="llama-3.2-1b", prompt=512, label="BASELINE config 3: random-init Llama-3.2-1B"),
+}
+
+
+def decode_step_bytes(dec, context):
+    """Algorithmic HBM bytes of one decoded token: packed codes + scales of every linear, the
+    int8 K and V rows and their scales read by attention, the embedding row."""
+    total = 0
+    for spec in dec.layers:
+        for key in ("qkv", "o", "gate_up", "down"):
+            total += spec[key].weight_bytes()
+    if hasattr(dec.lm_head, "weight_bytes"):
+        total += dec.lm_head.weight_bytes()
+    else:
+        total += dec.lm_head.weight.numel() * 2
+    kv = 2 * dec.B * dec.Hkv * context * (dec.D + 4)
+    return total + kv * len(dec.layers) + dec.B * dec.hidden * 2
+
+
+def run_decode(args, rank, world, device):
+    import torch.distributed as dist
+
+    from llmquant_b200.core import QuantConfig
+    from llmquant_b200.runtime.decoder import FusedLlamaDecoder
+    from llmquant_b200.runtime.random_init import llama_config, random_quantized_llama
+
+    spec = DECODE[args.workload]
+    batch, prompt = args.batch, args.prompt or spec["prompt"]
+    quant = QuantConfig(attn_weight="int8", mlp_weight="int4", head_weight="int8", kv_cache="int8")
+    model = random_quantized_llama(llama_config(spec["shape"]), quant, device, seed=rank)
+    new = args.warmup + 2 * args.steps + 8
+    dec = FusedLlamaDecoder(model, batch, prompt + new + 8, kv_bits=8)
+    g = torch.Generator().manual_seed(1 + rank)
+    host_ids = torch.randint(0, model.config.vocab_size, (batch, prompt), generator=g).pin_memory()
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    dec.prefill(host_ids.to(device, non_blocking=True))
+    dec.capture()
+    for _ in range(args.warmup):
+        dec.step()
+    barrier()
+
+    # ---- value: the token loop entirely on the device
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with ClockSampler(torch.cuda.current_device()) as clocks:
+        barrier()
+        start.record()
+        for _ in range(args.steps):
+            dec.step()
+        stop.record()
+        barrier()
+    step_ms = start.elapsed_time(stop) / args.steps
+    context = prompt + args.warmup + args.steps // 2
+
+    # ---- e2e: every step feeds the token from pinned host memory and reads the new one back
+    host_tok = dec.tokens.cpu().pin_memory()
+    for _ in range(3):
+        dec.tokens.copy_(host_tok, non_blocking=True)
+        dec.step()
+        host_tok.copy_(dec.tokens, non_blocking=True)
+        torch.cuda.synchronize()
+    barrier()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        dec.tokens.copy_(host_tok, non_blocking=True)
+        dec.step()
+        host_tok.copy_(dec.tokens, non_blocking=True)
+        torch.cuda.synchronize()
+    barrier()
+    e2e_s = (time.perf_counter() - t0) / args.steps
+
+    times = torch.tensor([step_ms, e2e_s], dtype=torch.float64, device=device)
+    if world > 1:
+        dist.all_reduce(times, op=dist.ReduceOp.MAX)
+    step_ms, e2e_s = times.tolist()
+    peaks, peak_kind = measured_peaks()
+    step_bytes = decode_step_bytes(dec, context)
+    achieved = step_bytes / (step_ms * 1e-3) / 1e9
+    line = {
+        "metric": "decode_tokens_per_s", "value": round(world * batch / (step_ms * 1e-3), 1),
+        "unit": "tok/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": round(step_ms, 4), "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "int4/int8 codes x bf16, fp32 accumulate", "data": "synthetic",
+        "config": {"workload": f"{args.workload} ({spec['label']}, attn int8 / mlp int4 g128 / "
+                               f"lm_head int8 / int8 KV, greedy)",
+                   "batch": batch, "prompt_tokens": prompt, "context_at_timing": context,
+                   "l2_policy": f"{step_bytes / 1e6:.0f} MB of weights and KV streamed per step, larger than L2",
+                   "parallelism": f"replicas x{world}" if world > 1 else "single"},
+        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peaks["hbm_gbs"],
+                     "unit": "GB/s", "frac": round(achieved / peaks["hbm_gbs"], 4),
+                     "frac_of_nominal_8TBs": round(achieved / 8000.0, 4), "peak_kind": peak_kind,
+                     "traffic": None, "kernel": "gemv_stream_kernel (whole decode step timed)",
+                     "bytes_per_step": step_bytes},
+        "e2e": {"value": round(world * batch / e2e_s, 1), "unit": "tok/s",
+                "h2d_bytes_per_step": batch * 8, "d2h_bytes_per_step": batch * 8},
+        "gpu_launches": dec.launches_per_step * args.steps,
+        "clocks": clocks.summary(),
+    }
+    if rank == 0:
+        line["cpu_baseline"] = cpu_decode_baseline(spec["shape"], reps=1)
+        print(json.dumps(line), flush=True)
+
+
+def cpu_decode_baseline(shape_name, reps=1):
+    """Real-mode linears of ONE decoder layer plus lm_head (torch CPU restatement of
+    quantizers/real.py:76-103 of the reference), batch 1, one token; the per-token time of the
+    whole model is layers x layer time + head time."""
+    from llmquant_b200.runtime.random_init import SHAPES
+    from oracle.real_mode import RealLinear
+
+    shp = SHAPES[shape_name]
+    h, inter, d = shp["hidden_size"], shp["intermediate_size"], shp["head_dim"]
+    nq, nkv = shp["num_attention_heads"] * d, shp["num_key_value_heads"] * d
+    parts = [("q", nq, h, 8, 1), ("k", nkv, h, 8, 2), ("o", h, nq, 8, 1), ("gate", inter, h, 4, 2),
+             ("down", h, inter, 4, 1)]
+    torch.manual_seed(0)
+    layer_s = 0.0
+    for _, n, k, bits, count in parts:
+        lin = torch.nn.Linear(k, n, bias=False).to(torch.bfloat16)
+        mod = RealLinear(lin, bits)
+        x = torch.randn(1, k).bfloat16()
+        mod(x)
+        t0 = time.perf_counter()
+        for _ in range(reps):
+            mod(x)
+        layer_s += count * (time.perf_counter() - t0) / reps
+        del lin, mod
+    # lm_head on one eighth of the vocabulary, scaled
+    rows = shp["vocab_size"] // 8
+    lin = torch.nn.Linear(h, rows, bias=False).to(torch.bfloat16)
+    mod = RealLinear(lin, 8)
+    x = torch.randn(1, h).bfloat16()
+    mod(x)
+    t0 = time.perf_counter()
+    for _ in range(reps):
+        mod(x)
+    head_s = 8 * (time.perf_counter() - t0) / reps
+    token_s = shp["num_hidden_layers"] * layer_s + head_s
+    return {"value": round(1.0 / token_s, 4), "unit": "tok/s", "cores": torch.get_num_threads(),
+            "kind": "port",
+            "sample": f"real-mode linears of one {shape_name} decoder layer (q, k, o, gate, down timed; "
+                      f"k/v and gate/up counted twice) + lm_head on 1/8 of the vocabulary, M=1; "
+                      f"token time = {shp['num_hidden_layers']} x layer + head"}
+
+
 # --------------------------------------------------------------------------- CPU arm
 def cpu_baseline(sample_seconds=15.0, steps=None):
     """The oracle's real-mode linear (numpy restatement of quantizers/real.py:76-103 of the
@@ -305,6 +463,21 @@ def cpu_baseline(sample_seconds=15.0, steps=None):
 def run_reference(args, rank):
     if rank != 0:
         return
+    if args.workload in DECODE:
+        spec = DECODE[args.workload]
+        base = cpu_decode_baseline(spec["shape"], reps=max(1, min(args.steps, 3)))
+        line = {
+            "impl": "reference", "metric": "decode_tokens_per_s", "value": base["value"], "unit": "tok/s",
+            "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(1e3 / base["value"], 2),
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "int codes x fp32 (torch CPU)", "data": "synthetic",
+            "config": {"workload": f"{args.workload} ({spec['label']}, attn int8 / mlp int4 g128 / "
+                                   f"lm_head int8 / int8 KV, greedy)", "batch": 1},
+            "cpu_baseline": base,
+            "e2e": {"value": base["value"], "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        }
+        print(json.dumps(line), flush=True)
+        return
     base = cpu_baseline(sample_seconds=60.0, steps=max(1, args.steps))
     line = {
         "impl": "reference", "metric": "quant_gemv_hbm_gbs", "value": base["value"], "unit": "GB/s",
@@ -322,10 +495,12 @@ def run_reference(args, rank):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--steps", type=int, default=64)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
-    ap.add_argument("--workload", default="gemv_sweep_1b")
+    ap.add_argument("--workload", default="decode_8b", choices=["decode_8b", "decode_1b", "gemv_sweep_1b"])
+    ap.add_argument("--batch", type=int, default=1)
+    ap.add_argument("--prompt", type=int, default=0, help="prompt tokens (0 = the workload's own)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
 
@@ -343,7 +518,10 @@ def main():
         import torch.distributed as dist
         dist.init_process_group("nccl", device_id=device)
     try:
-        run_gpu(args, rank, world, device)
+        if args.workload in DECODE:
+            run_decode(args, rank, world, device)
+        else:
+            run_gpu(args, rank, world, device)
     finally:
         if world > 1:
             import torch.distributed as dist

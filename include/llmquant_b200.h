@@ -81,41 +81,49 @@ int lq_wq_gemv(const void* x, const int8_t* qweight, const float* wscale, void* 
                int N, int groups, int group_size, int out_group, int dtype, void* stream);
 
 /* Device ("streaming") layout of one quantized linear, built once per layer:
- *   codes   [N, Kd] int8 (bits = 8) or [N, Kd/2] bytes of biased nibbles, low nibble first
- *           (bits = 4); rows are 16-byte aligned; head padding of the canonical form is
- *           stripped when head_dim < group_size (span = head_dim), otherwise span =
- *           group_size and Kd = G * group_size;
- *   scales  [G, SRp] fp32, SRp = scale_rows rounded up to 4 (group-major so that four
- *           consecutive output rows' scales are one 128-bit load).
- * lq_stream_layout_sizes returns Kd, span, SRp for a canonical shape. There is no
+ *   codes        [N, Kd] int8 (bits = 8) or [N, Kd/2] bytes of biased nibbles, low nibble
+ *                first (bits = 4) -- byte-identical to the model.bin payload when no head
+ *                padding is involved; rows are 16-byte aligned and contiguous, so four
+ *                consecutive rows are one contiguous piece of memory; head padding of the
+ *                canonical form is stripped when head_dim < group_size (span = head_dim),
+ *                otherwise span = group_size and Kd = G * group_size;
+ *   scale_tiles  [NP/4, G, 4] fp32, NP = N rounded up to 4: the scales of four consecutive
+ *                output rows for every group, contiguous per row tile (rows that share a
+ *                scale under out_group each get their copy).
+ * lq_stream_layout_sizes returns Kd, span, NP for a canonical shape. There is no
  * counterpart in the reference, which feeds canonical int8 to its kernel. */
-int lq_stream_layout_sizes(int groups, int group_size, int head_dim, int bits, int scale_rows,
-                           int* Kd, int* span, int* SRp);
-int lq_repack_stream(const int8_t* canonical, const float* wscale, void* codes, float* scales_t,
-                     int N, int groups, int group_size, int head_dim, int bits, int scale_rows,
+int lq_stream_layout_sizes(int N, int groups, int group_size, int head_dim, int bits, int* Kd,
+                           int* span, int* NP);
+int lq_repack_stream(const int8_t* canonical, const float* wscale, void* codes, float* scale_tiles,
+                     int N, int groups, int group_size, int head_dim, int bits, int out_group,
                      void* stream);
 /* Exact inverse of lq_repack_stream (used to rebuild `qweight` for save_packed_model). */
-int lq_unrepack_stream(const void* codes, const float* scales_t, int8_t* canonical, float* wscale,
-                       int N, int groups, int group_size, int head_dim, int bits, int scale_rows,
-                       void* stream);
+int lq_unrepack_stream(const void* codes, const float* scale_tiles, int8_t* canonical,
+                       float* wscale, int N, int groups, int group_size, int head_dim, int bits,
+                       int out_group, void* stream);
 
 /* Streaming layout -> dense [N, K] matrix of `dtype` (code * scale, rounded once): the
  * operand KernelQuantLinear._dequantized_weight builds for the library GEMM
  * (quantizers/kernel.py:68-79), without the canonical padding columns. */
-int lq_dequant_stream(const void* codes, const float* scales_t, void* out, int dtype, int N, int K,
-                      int Kd, int span, int SRp, int out_group, int bits, void* stream);
+int lq_dequant_stream(const void* codes, const float* scale_tiles, void* out, int dtype, int N,
+                      int K, int Kd, int span, int bits, void* stream);
 
 /* Decode GEMV on the streaming layout, M <= 8 activation rows.
  * x [M, K] bf16 (row stride ldx elements), K real in_features (K <= Kd; columns beyond K
  * read as zero), out [M, N] of out_dtype (LQ_BF16 or LQ_F32), bias bf16 [N] or NULL,
  * residual (out_dtype, [M, N]) or NULL added after the bias.
- * variant: 0 = default, 1 = fp32 FMA arithmetic, 2 = integer dot-product arithmetic.
+ * variant: 0 = default, 1 = fp32 FMA arithmetic, 2 / 3 = integer dot products on 16- / 24-bit
+ * block-floating-point activations.
  * Takes the role of wq_gemv.cu:45-130 inside KernelQuantLinear.forward
  * (quantizers/kernel.py:81-95). */
-int lq_wq_gemv_stream(const void* x, int ldx, const void* codes, const float* scales_t,
+int lq_wq_gemv_stream(const void* x, int ldx, const void* codes, const float* scale_tiles,
                       const void* bias, const void* residual, void* out, int out_dtype, int M,
-                      int N, int K, int Kd, int span, int SRp, int out_group, int bits,
-                      int variant, void* stream);
+                      int N, int K, int Kd, int span, int bits, int variant, void* stream);
+
+/* The GEMV's waits on its shared-memory pipeline are bounded; if one ever expires the kernel
+ * records a non-zero word and returns. This reads (and clears) that word; it synchronizes
+ * with the device, so it is for tests and diagnostics. -1 = the word could not be read. */
+int lq_gemv_device_error(void);
 
 /* ---------------------------------------------------------------- quantized KV cache
  * Storage per layer: codes [B, Hkv, Tmax, D] int8, scales [B, Hkv, Tmax, ceil(D/128)] fp32.
@@ -175,12 +183,12 @@ typedef struct lq_gemv_args {
   const void* norm_weight;
   float norm_eps;
   const void* codes;
-  const float* scales_t;
+  const float* scale_tiles;
   const void* bias;
   const void* residual;
   void* out;
   int out_dtype;
-  int M, N, K, Kd, span, SRp, out_group, bits;
+  int M, N, K, Kd, span, bits;
   int epilogue;
   int variant;
   int pdl;

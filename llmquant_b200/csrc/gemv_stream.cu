@@ -44,15 +44,21 @@ __global__ void repack_codes_kernel(const int8_t* __restrict__ canonical, uint8_
   }
 }
 
-__global__ void transpose_scales_kernel(const float* __restrict__ wscale, float* __restrict__ scales_t,
-                                        int scale_rows, int groups, int SRp, int inverse) {
+// wscale [scale_rows, G] <-> scale tiles [ceil(N/4), G, 4] (one entry per output row; rows that
+// share a scale under out_group get copies of it)
+__global__ void scale_tiles_kernel(const float* __restrict__ wscale, float* __restrict__ tiles,
+                                   int N, int groups, int out_group, int NP, int inverse) {
   const int64_t i0 = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   const int64_t stride = (int64_t)gridDim.x * blockDim.x;
-  const int64_t total = (int64_t)groups * SRp;
+  const int64_t total = (int64_t)NP * groups;
   for (int64_t i = i0; i < total; i += stride) {
-    const int g = (int)(i / SRp), r = (int)(i % SRp);
-    if (!inverse) scales_t[i] = r < scale_rows ? wscale[(int64_t)r * groups + g] : 0.f;
-    else if (r < scale_rows) const_cast<float*>(wscale)[(int64_t)r * groups + g] = scales_t[i];
+    const int u = (int)(i % 4);
+    const int g = (int)((i / 4) % groups);
+    const int n = (int)(i / (4 * (int64_t)groups)) * 4 + u;
+    const int64_t sr = out_group > 0 ? n / out_group : n;
+    if (!inverse) tiles[i] = n < N ? wscale[sr * groups + g] : 0.f;
+    else if (n < N && (out_group == 0 || n % out_group == 0))
+      const_cast<float*>(wscale)[sr * groups + g] = tiles[i];
   }
 }
 
@@ -60,7 +66,7 @@ __global__ void transpose_scales_kernel(const float* __restrict__ wscale, float*
 template <typename T>
 __global__ void dequant_stream_kernel(const uint8_t* __restrict__ codes, const float* __restrict__ scales_t,
                                       T* __restrict__ out, int N, int K, int rowbytes, int span,
-                                      int SRp, int out_group, int bits) {
+                                      int groups, int bits) {
   const int64_t total = (int64_t)N * K;
   const int64_t i0 = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   const int64_t stride = (int64_t)gridDim.x * blockDim.x;
@@ -72,31 +78,31 @@ __global__ void dequant_stream_kernel(const uint8_t* __restrict__ codes, const f
       const uint8_t b = codes[(int64_t)n * rowbytes + (k >> 1)];
       code = (int)((k & 1) ? (b >> 4) : (b & 0xF)) - 8;
     }
-    const float s = scales_t[(int64_t)(k / span) * SRp + (out_group > 0 ? n / out_group : n)];
+    const float s = scales_t[((int64_t)(n / 4) * groups + k / span) * 4 + (n & 3)];
     out[i] = Conv<T>::from_f32(__fmul_rn((float)code, s));
   }
 }
 
-int layout_sizes(int groups, int gs, int head_dim, int bits, int scale_rows, int* Kd, int* span,
-                 int* SRp) {
+int layout_sizes(int N, int groups, int gs, int head_dim, int bits, int* Kd, int* span, int* NP) {
   LQ_REQUIRE(bits == 4 || bits == 8, LQ_ERR_ARG, "unsupported num_bits %d, expected 4 or 8", bits);
-  LQ_REQUIRE(groups >= 0 && gs > 0 && head_dim >= 0 && scale_rows >= 0, LQ_ERR_ARG, "bad layout arguments");
+  LQ_REQUIRE(N >= 0 && groups >= 0 && gs > 0 && head_dim >= 0, LQ_ERR_ARG, "bad layout arguments");
   const int sp = (head_dim > 0 && head_dim < gs) ? head_dim : gs;
   const int epl = bits == 8 ? 16 : 32;
   LQ_REQUIRE(sp % epl == 0, LQ_ERR_UNSUPPORTED,
              "group span %d is not a multiple of %d codes; use the canonical-layout GEMV", sp, epl);
   *span = sp;
   *Kd = groups * sp;
-  *SRp = (scale_rows + 3) / 4 * 4;
+  *NP = (N + 3) / 4 * 4;
   return LQ_OK;
 }
 
-int repack_common(const int8_t* canonical, const float* wscale, void* codes, float* scales_t, int N,
-                  int groups, int gs, int head_dim, int bits, int scale_rows, void* stream,
+int repack_common(const int8_t* canonical, const float* wscale, void* codes, float* tiles, int N,
+                  int groups, int gs, int head_dim, int bits, int out_group, void* stream,
                   int inverse) {
-  int Kd, span, SRp;
-  const int rc = layout_sizes(groups, gs, head_dim, bits, scale_rows, &Kd, &span, &SRp);
+  int Kd, span, NP;
+  const int rc = layout_sizes(N, groups, gs, head_dim, bits, &Kd, &span, &NP);
   if (rc) return rc;
+  LQ_REQUIRE(out_group >= 0, LQ_ERR_ARG, "out_group must be >= 0");
   if (N == 0 || groups == 0) return LQ_OK;
   cudaStream_t s = (cudaStream_t)stream;
   const int64_t total = (int64_t)N * Kd * bits / 8;
@@ -105,49 +111,77 @@ int repack_common(const int8_t* canonical, const float* wscale, void* codes, flo
   int64_t want = (total + 255) / 256;
   repack_codes_kernel<<<(unsigned)(want < 148 * 32 ? want : 148 * 32), 256, 0, s>>>(
       canonical, (uint8_t*)codes, total, groups, gs, span, bits, inverse);
-  want = ((int64_t)groups * SRp + 255) / 256;
-  transpose_scales_kernel<<<(unsigned)(want < 148 * 8 ? want : 148 * 8), 256, 0, s>>>(
-      wscale, scales_t, scale_rows, groups, SRp, inverse);
+  want = ((int64_t)groups * NP + 255) / 256;
+  scale_tiles_kernel<<<(unsigned)(want < 148 * 8 ? want : 148 * 8), 256, 0, s>>>(
+      wscale, tiles, N, groups, out_group, NP, inverse);
   return check_launch(inverse ? "lq_unrepack_stream" : "lq_repack_stream");
+}
+
+__device__ int g_gemv_error = 0;
+
+int* error_word() {
+  static thread_local int cached_dev = -1;
+  static thread_local int* cached = nullptr;
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return nullptr;
+  if (dev != cached_dev) {
+    void* ptr = nullptr;
+    if (cudaGetSymbolAddress(&ptr, g_gemv_error) != cudaSuccess) {
+      cudaGetLastError();
+      return nullptr;
+    }
+    cached = (int*)ptr;
+    cached_dev = dev;
+  }
+  return cached;
 }
 
 }  // namespace
 }  // namespace lq
 
-extern "C" int lq_stream_layout_sizes(int groups, int group_size, int head_dim, int bits,
-                                      int scale_rows, int* Kd, int* span, int* SRp) {
-  return lq::layout_sizes(groups, group_size, head_dim, bits, scale_rows, Kd, span, SRp);
+extern "C" int lq_stream_layout_sizes(int N, int groups, int group_size, int head_dim, int bits,
+                                      int* Kd, int* span, int* NP) {
+  return lq::layout_sizes(N, groups, group_size, head_dim, bits, Kd, span, NP);
 }
 
 extern "C" int lq_repack_stream(const int8_t* canonical, const float* wscale, void* codes,
-                                float* scales_t, int N, int groups, int group_size, int head_dim,
-                                int bits, int scale_rows, void* stream) {
-  return lq::repack_common(canonical, wscale, codes, scales_t, N, groups, group_size, head_dim,
-                           bits, scale_rows, stream, 0);
+                                float* scale_tiles, int N, int groups, int group_size, int head_dim,
+                                int bits, int out_group, void* stream) {
+  return lq::repack_common(canonical, wscale, codes, scale_tiles, N, groups, group_size, head_dim,
+                           bits, out_group, stream, 0);
 }
 
-extern "C" int lq_unrepack_stream(const void* codes, const float* scales_t, int8_t* canonical,
+extern "C" int lq_unrepack_stream(const void* codes, const float* scale_tiles, int8_t* canonical,
                                   float* wscale, int N, int groups, int group_size, int head_dim,
-                                  int bits, int scale_rows, void* stream) {
-  return lq::repack_common(canonical, wscale, const_cast<void*>(codes), const_cast<float*>(scales_t),
-                           N, groups, group_size, head_dim, bits, scale_rows, stream, 1);
+                                  int bits, int out_group, void* stream) {
+  return lq::repack_common(canonical, wscale, const_cast<void*>(codes), const_cast<float*>(scale_tiles),
+                           N, groups, group_size, head_dim, bits, out_group, stream, 1);
 }
 
-extern "C" int lq_dequant_stream(const void* codes, const float* scales_t, void* out, int dtype,
-                                 int N, int K, int Kd, int span, int SRp, int out_group, int bits,
-                                 void* stream) {
+extern "C" int lq_dequant_stream(const void* codes, const float* scale_tiles, void* out, int dtype,
+                                 int N, int K, int Kd, int span, int bits, void* stream) {
   using namespace lq;
   LQ_REQUIRE(bits == 4 || bits == 8, LQ_ERR_ARG, "unsupported num_bits %d, expected 4 or 8", bits);
-  LQ_REQUIRE(N >= 0 && K >= 0 && Kd >= K && span > 0, LQ_ERR_ARG, "bad shape N=%d K=%d Kd=%d", N, K, Kd);
+  LQ_REQUIRE(N >= 0 && K >= 0 && Kd >= K && span > 0 && Kd % span == 0, LQ_ERR_ARG,
+             "bad shape N=%d K=%d Kd=%d", N, K, Kd);
   if (N == 0 || K == 0) return LQ_OK;
   const int64_t want = ((int64_t)N * K + 255) / 256;
   const unsigned grid = (unsigned)(want < 148 * 64 ? want : 148 * 64);
   cudaStream_t s = (cudaStream_t)stream;
   LQ_DISPATCH_DTYPE(dtype, T, {
-    dequant_stream_kernel<T><<<grid, 256, 0, s>>>((const uint8_t*)codes, scales_t, (T*)out, N, K,
-                                                  Kd * bits / 8, span, SRp, out_group, bits);
+    dequant_stream_kernel<T><<<grid, 256, 0, s>>>((const uint8_t*)codes, scale_tiles, (T*)out, N, K,
+                                                  Kd * bits / 8, span, Kd / span, bits);
   });
   return check_launch("lq_dequant_stream");
+}
+
+extern "C" int lq_gemv_device_error(void) {
+  int* word = lq::error_word();
+  if (word == nullptr) return -1;
+  int value = 0;
+  if (cudaMemcpy(&value, word, sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess) return -1;
+  if (value != 0) cudaMemset(word, 0, sizeof(int));
+  return value;
 }
 
 extern "C" int lq_wq_gemv_fused(const lq_gemv_args* a, void* stream) {
@@ -163,34 +197,42 @@ extern "C" int lq_wq_gemv_fused(const lq_gemv_args* a, void* stream) {
   const int epl = bits == 8 ? 16 : 32;
   LQ_REQUIRE(a->span > 0 && a->span % epl == 0 && Kd % a->span == 0, LQ_ERR_ARG,
              "group span %d must be a positive multiple of %d dividing Kd=%d", a->span, epl, Kd);
-  LQ_REQUIRE(a->SRp % 4 == 0 && a->out_group >= 0, LQ_ERR_ARG, "scale row pitch must be a multiple of 4");
-  LQ_REQUIRE(a->x && a->codes && a->scales_t && a->out, LQ_ERR_ARG, "null tensor pointer");
-  LQ_REQUIRE(((uintptr_t)a->codes % 16) == 0 && ((uintptr_t)a->scales_t % 16) == 0, LQ_ERR_ARG,
+  LQ_REQUIRE(a->x && a->codes && a->scale_tiles && a->out, LQ_ERR_ARG, "null tensor pointer");
+  LQ_REQUIRE(((uintptr_t)a->codes % 16) == 0 && ((uintptr_t)a->scale_tiles % 16) == 0, LQ_ERR_ARG,
              "codes and scales must be 16-byte aligned");
   LQ_REQUIRE(a->ldx >= K, LQ_ERR_ARG, "x row stride %d is shorter than K=%d", a->ldx, K);
   LQ_REQUIRE(a->epilogue == 0 || a->epilogue == 1, LQ_ERR_ARG, "unknown epilogue %d", a->epilogue);
   if (a->epilogue == 1)
-    LQ_REQUIRE(N % 4 == 0 && a->bias == nullptr && a->residual == nullptr && a->out_group == 0,
-               LQ_ERR_ARG, "the silu-mul epilogue needs N %% 4 == 0 and no bias / residual / row groups");
+    LQ_REQUIRE(N % 4 == 0 && a->bias == nullptr && a->residual == nullptr, LQ_ERR_ARG,
+               "the silu-mul epilogue needs N %% 4 == 0 and no bias / residual");
   int variant = a->variant == 0 ? 2 : a->variant;
   LQ_REQUIRE(variant >= 1 && variant <= 3, LQ_ERR_ARG, "unknown arithmetic variant %d", variant);
 
   GemvParams p;
-  p.ldx = a->ldx; p.codes = (const uint8_t*)a->codes; p.scales = a->scales_t;
+  p.ldx = a->ldx; p.codes = (const uint8_t*)a->codes; p.scales = a->scale_tiles;
   p.bias = (const __nv_bfloat16*)a->bias;
   p.out_f32 = a->out_dtype == LQ_F32;
-  p.N = N; p.K = K; p.Kd = Kd; p.rowbytes = Kd * bits / 8; p.span = a->span; p.SRp = a->SRp;
-  p.out_group = a->out_group;
+  p.N = N; p.K = K; p.Kd = Kd; p.rowbytes = Kd * bits / 8; p.span = a->span;
+  p.groups = Kd / a->span;
   p.norm_weight = a->norm_weight; p.norm_eps = a->norm_eps; p.pdl = a->pdl;
+  p.error_word = error_word();
+  LQ_REQUIRE(p.error_word != nullptr, LQ_ERR_LAUNCH, "cannot resolve the device error word");
   p.S = (p.rowbytes + 511) / 512;
   int spw = 1;
   while (spw <= 4 && (p.S + spw - 1) / spw > kMaxWarps) spw *= 2;
   LQ_REQUIRE(spw <= 4, LQ_ERR_UNSUPPORTED, "reduction axis too long for the streaming GEMV (Kd=%d)", Kd);
   LQ_REQUIRE(!(spw == 4 && a->epilogue == 1), LQ_ERR_UNSUPPORTED, "reduction axis too long for the fused epilogue");
   p.KW = (p.S + spw - 1) / spw;
-  p.RW = p.KW >= 8 ? 1 : 8 / p.KW;
   p.nbatch = (N + kU - 1) / kU;
-  const int threads = p.KW * p.RW * 32;
+  p.tile_bytes = kU * p.rowbytes;
+  p.scale_bytes = p.groups * kU * (int)sizeof(float);
+  p.stage_bytes = (p.tile_bytes + p.scale_bytes + 127) / 128 * 128;
+  int stages = (48 * 1024) / p.stage_bytes;
+  stages = stages < 2 ? 2 : (stages > kMaxStages ? kMaxStages : stages);
+  LQ_REQUIRE((size_t)stages * p.stage_bytes <= 200 * 1024, LQ_ERR_UNSUPPORTED,
+             "row tile of %d bytes does not fit the shared-memory ring", p.stage_bytes);
+  p.stages = stages;
+  const int threads = (p.KW + 1) * 32;
   cudaStream_t s = (cudaStream_t)stream;
   if (bits == 8) {
     if (variant == 1) return run_b8v1(p, *a, spw, threads, s);
@@ -202,14 +244,13 @@ extern "C" int lq_wq_gemv_fused(const lq_gemv_args* a, void* stream) {
   return run_b4v3(p, *a, spw, threads, s);
 }
 
-extern "C" int lq_wq_gemv_stream(const void* x, int ldx, const void* codes, const float* scales_t,
+extern "C" int lq_wq_gemv_stream(const void* x, int ldx, const void* codes, const float* scale_tiles,
                                  const void* bias, const void* residual, void* out, int out_dtype,
-                                 int M, int N, int K, int Kd, int span, int SRp, int out_group,
-                                 int bits, int variant, void* stream) {
+                                 int M, int N, int K, int Kd, int span, int bits, int variant,
+                                 void* stream) {
   lq_gemv_args a = {};
-  a.x = x; a.ldx = ldx; a.codes = codes; a.scales_t = scales_t; a.bias = bias;
+  a.x = x; a.ldx = ldx; a.codes = codes; a.scale_tiles = scale_tiles; a.bias = bias;
   a.residual = residual; a.out = out; a.out_dtype = out_dtype; a.M = M; a.N = N; a.K = K;
-  a.Kd = Kd; a.span = span; a.SRp = SRp; a.out_group = out_group; a.bits = bits;
-  a.variant = variant;
+  a.Kd = Kd; a.span = span; a.bits = bits; a.variant = variant;
   return lq_wq_gemv_fused(&a, stream);
 }

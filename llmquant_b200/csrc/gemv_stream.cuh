@@ -2,19 +2,28 @@
 // repack / un-repack kernels.
 //
 // Layout (see include/llmquant_b200.h): codes [N, Kd] int8 or [N, Kd/2] nibble bytes, rows
-// contiguous and 16-byte aligned; scales transposed to [G, SRp]. A warp reads one
-// contiguous 512-byte "slab" of a row per instruction (32 lanes x one 128-bit load), so HBM
-// sees whole 128-byte lines and nothing is fetched twice.
+// contiguous and 16-byte aligned, so four consecutive rows are ONE contiguous piece of
+// memory; scales in tiles [ceil(N/4), G, 4] so the scales of those four rows are one
+// contiguous piece too.
 //
-// Work split: a lane owns a fixed 16-byte column position (its "chunk": 16 int8 or 32 int4
-// codes, always inside one scale group) and walks DOWN the rows. Everything that depends
-// only on the column -- the activation values, their block exponent, the nibble-bias
-// correction -- is prepared once per lane and stays in registers; the row loop is: 128-bit
-// weight load, dot product, one multiply by the (group, row) scale. Warps of a CTA split the
-// K axis (KW of them cover a row) and the rows (RW row-warps); the KW partial sums meet in
-// shared memory behind a named barrier that only those KW warps join. No tensor cores: the
-// kernel is HBM-bound and the arithmetic is sized to stay under the instruction-issue
-// budget of a 6.5 TB/s stream.
+// Data movement: a producer warp streams row tiles (4 rows x the whole K axis, plus their
+// scale tile) from HBM into a ring of shared-memory stages with bulk asynchronous copies
+// (cp.async.bulk, completion counted on an mbarrier per stage); tens of KB per SM are in
+// flight at any time without occupying registers. The first stages are requested BEFORE the
+// kernel waits for its producer kernel (programmatic dependent launch), because weights do
+// not depend on it.
+//
+// Work split: KW consumer warps cover the K axis. A lane owns a fixed 16-byte column
+// position (its "chunk": 16 int8 or 32 int4 codes, always inside one scale group) and
+// walks DOWN the rows. Everything that depends only on the column -- the activation values,
+// their block exponent, the nibble-bias correction -- is prepared once per lane and stays in
+// registers; per row: one 128-bit shared-memory load, a dot product, one multiply by the
+// (group, row) scale. The KW partial sums meet in shared memory behind a named barrier. No
+// tensor cores: the kernel is HBM-bound and the arithmetic is sized to stay under the
+// instruction-issue budget of a 6.5 TB/s stream.
+//
+// Every wait on an mbarrier is bounded by a clock limit; on expiry the kernel records an
+// error word (lq_gemv_device_error) and returns instead of spinning.
 //
 // Arithmetic variants (argument `variant`):
 //   1  fp32: codes turned into floats with a mantissa-injection trick (no I2F), fp32 FMA
@@ -33,7 +42,8 @@ namespace lq {
 namespace gemv {
 
 constexpr int kU = 4;           // output rows per batch (one float4 of scales)
-constexpr int kMaxWarps = 16;   // warps per CTA
+constexpr int kMaxWarps = 16;   // consumer warps per CTA (one more warp produces)
+constexpr int kMaxStages = 8;
 
 struct GemvParams {
   const __nv_bfloat16* x;
@@ -44,19 +54,56 @@ struct GemvParams {
   const void* residual;
   void* out;
   int out_f32;
-  int M, N, K, Kd, rowbytes, span, SRp, out_group;
-  int KW, RW, S;
+  int M, N, K, Kd, rowbytes, span, groups;
+  int KW, S;
   int nbatch;
+  int stages, stage_bytes, tile_bytes, scale_bytes;
   const void* norm_weight;
   float norm_eps;
   int pdl;
+  int* error_word;
 };
 
-__device__ __forceinline__ uint4 ldg_stream(const void* p) {
+// ---- mbarrier / bulk-copy primitives (shared::cta addresses as 32-bit values)
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+  return (uint32_t)__cvta_generic_to_shared(p);
+}
+__device__ __forceinline__ void mbar_init(uint32_t bar, int count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+// Bounded wait: false if the phase did not complete within ~1 s of SM clock.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+  const long long t0 = clock64();
+  for (;;) {
+    uint32_t done;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.b32 %0, 1, 0, p;\n\t}"
+        : "=r"(done)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    if (done) return true;
+    if (clock64() - t0 > 2000000000LL) return false;
+  }
+}
+__device__ __forceinline__ void bulk_g2s(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+      ::"r"(dst), "l"(src), "r"(bytes), "r"(bar)
+      : "memory");
+}
+__device__ __forceinline__ uint4 lds128(uint32_t addr) {
   uint4 v;
-  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+  asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
                : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
-               : "l"(p));
+               : "r"(addr));
   return v;
 }
 
@@ -213,73 +260,92 @@ template <int BITS>
 struct XChunk<BITS, 3> : XPlanes<BITS, 3> {};
 
 // ------------------------------------------------------------------ the kernel
-template <int SPW>
-struct WeightBatch {
-  uint4 w[SPW][kU];   // one 16-byte chunk per (slab, row)
-  float sc[SPW][kU];  // the (group, row) scales that go with them
-};
+// Sums four per-lane values over the warp with 6 shuffles: afterwards lane l holds the total
+// of value (l & 3).
+__device__ __forceinline__ float reduce4(const float (&v)[kU], int lane) {
+  const bool o1 = lane & 1, o2 = lane & 2;
+  float a = o1 ? v[1] : v[0];
+  a += __shfl_xor_sync(0xffffffffu, o1 ? v[0] : v[1], 1);
+  float b = o1 ? v[3] : v[2];
+  b += __shfl_xor_sync(0xffffffffu, o1 ? v[2] : v[3], 1);
+  float c = o2 ? b : a;
+  c += __shfl_xor_sync(0xffffffffu, o2 ? a : b, 2);
+  c += __shfl_xor_sync(0xffffffffu, c, 4);
+  c += __shfl_xor_sync(0xffffffffu, c, 8);
+  c += __shfl_xor_sync(0xffffffffu, c, 16);
+  return c;
+}
 
 // EPI 0: out[m, n] = acc (+ bias) (+ residual).  EPI 1: rows come in (gate, up) pairs and
 // out[m, n/2] = silu(gate) * up with the roundings of a bf16 MLP (gate, up, silu(gate) and
 // the product are each rounded to bf16).
 template <int BITS, int VAR, int M, int SPW, int EPI>
-__global__ void __launch_bounds__(kMaxWarps * 32)
+__global__ void __launch_bounds__((kMaxWarps + 1) * 32)
 gemv_stream_kernel(const GemvParams p) {
   constexpr int EPL = BITS == 8 ? 16 : 32;
+  extern __shared__ __align__(128) uint8_t ring[];
+  __shared__ __align__(8) uint64_t full_bar[kMaxStages], empty_bar[kMaxStages];
   __shared__ float red[2][kMaxWarps][M * kU];
   __shared__ float nrm[kMaxWarps][M];
 
   const int lane = threadIdx.x & 31;
   const int warp = threadIdx.x >> 5;
-  const int kw = warp % p.KW;
-  const int rw = warp / p.KW;
-  const int barrier_id = 1 + rw;
-  const int barrier_threads = p.KW * 32;
+  const int KW = p.KW;
+  const int barrier_threads = KW * 32;
 
-  // ---- column geometry (independent of the activations)
+  // contiguous balanced range of row batches for this CTA
+  const int b_begin = (int)(((int64_t)p.nbatch * blockIdx.x) / gridDim.x);
+  const int b_end = (int)(((int64_t)p.nbatch * (blockIdx.x + 1)) / gridDim.x);
+  const int nb = b_end - b_begin;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < p.stages; ++s) {
+      mbar_init(smem_u32(&full_bar[s]), 1);
+      mbar_init(smem_u32(&empty_bar[s]), KW);
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncthreads();
+
+  // ------------------------------------------------------------ producer warp
+  if (warp == KW) {
+    if (lane == 0) {
+      for (int it = 0; it < nb; ++it) {
+        const int s = it % p.stages;
+        if (it >= p.stages) {
+          if (!mbar_wait(smem_u32(&empty_bar[s]), ((it / p.stages) - 1) & 1)) {
+            atomicExch(p.error_word, 1);
+            break;
+          }
+        }
+        const int b = b_begin + it;
+        const int rows = min(kU, p.N - b * kU);
+        const uint32_t bytes = (uint32_t)rows * p.rowbytes;
+        const uint32_t bar = smem_u32(&full_bar[s]);
+        const uint32_t dst = smem_u32(ring + (size_t)s * p.stage_bytes);
+        mbar_expect_tx(bar, bytes + p.scale_bytes);
+        bulk_g2s(dst, p.codes + (int64_t)b * kU * p.rowbytes, bytes, bar);
+        bulk_g2s(dst + p.tile_bytes, p.scales + (int64_t)b * p.groups * kU, p.scale_bytes, bar);
+      }
+    }
+    return;
+  }
+
+  // ------------------------------------------------------------ consumer warps
+  const int kw = warp;
   int cb[SPW];   // byte offset of the chunk inside a row, -1 if outside the row
   int grp[SPW];  // scale group of the chunk
 #pragma unroll
   for (int j = 0; j < SPW; ++j) {
-    const int s = kw + j * p.KW;
+    const int s = kw + j * KW;
     const int off = s * 512 + lane * 16;
     const bool live = s < p.S && off < p.rowbytes;
     cb[j] = live ? off : -1;
     grp[j] = live ? (off * (8 / BITS)) / p.span : 0;
   }
 
-  // ---- rows: batches of kU, a contiguous balanced range per row-warp slot
-  const int slots = gridDim.x * p.RW;
-  const int slot = blockIdx.x * p.RW + rw;
-  const int b_begin = (int)(((int64_t)p.nbatch * slot) / slots);
-  const int b_end = (int)(((int64_t)p.nbatch * (slot + 1)) / slots);
-
-  auto load_batch = [&](int b, WeightBatch<SPW>& wb) {
-    const int n0 = b * kU;
-#pragma unroll
-    for (int j = 0; j < SPW; ++j) {
-#pragma unroll
-      for (int u = 0; u < kU; ++u) {
-        const int n = min(n0 + u, p.N - 1);
-        if (cb[j] >= 0) wb.w[j][u] = ldg_stream(p.codes + (int64_t)n * p.rowbytes + cb[j]);
-        else wb.w[j][u] = make_uint4(0, 0, 0, 0);
-      }
-      if (p.out_group == 0) {
-        const float4 s4 = __ldg(reinterpret_cast<const float4*>(p.scales + (int64_t)grp[j] * p.SRp + n0));
-        wb.sc[j][0] = s4.x; wb.sc[j][1] = s4.y; wb.sc[j][2] = s4.z; wb.sc[j][3] = s4.w;
-      } else {
-#pragma unroll
-        for (int u = 0; u < kU; ++u)
-          wb.sc[j][u] = __ldg(p.scales + (int64_t)grp[j] * p.SRp + min(n0 + u, p.N - 1) / p.out_group);
-      }
-    }
-  };
-
-  // The weights do not depend on the kernel before this one: start streaming them, THEN
-  // wait for the producer of x (programmatic dependent launch; a no-op otherwise) and let
-  // the kernel after this one begin its own weight prefetch.
-  WeightBatch<SPW> bufA, bufB;
-  if (b_begin < b_end) load_batch(b_begin, bufA);
+  // x is produced by the kernel before this one: wait for it (a no-op without programmatic
+  // dependent launch), then let the kernel after this one start its own weight stream.
   asm volatile("griddepcontrol.wait;" ::: "memory");
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
@@ -300,16 +366,16 @@ gemv_stream_kernel(const GemvParams p) {
       }
       ss[m] = warp_sum(ss[m]);
     }
-    if (p.KW > 1) {
+    if (KW > 1) {
       if (lane == 0) {
 #pragma unroll
         for (int m = 0; m < M; ++m) nrm[warp][m] = ss[m];
       }
-      asm volatile("bar.sync %0, %1;" ::"r"(barrier_id), "r"(barrier_threads) : "memory");
+      asm volatile("bar.sync 1, %0;" ::"r"(barrier_threads) : "memory");
 #pragma unroll
       for (int m = 0; m < M; ++m) {
         float t = 0.f;
-        for (int w = 0; w < p.KW; ++w) t += nrm[rw * p.KW + w][m];
+        for (int w = 0; w < KW; ++w) t += nrm[w][m];
         ss[m] = t;
       }
     }
@@ -360,9 +426,33 @@ gemv_stream_kernel(const GemvParams p) {
     }
   }
 
-  // ---- the row loop, software-pipelined one batch ahead
-  auto process = [&](int b, int parity, const WeightBatch<SPW>& wb) {
-    const int n0 = b * kU;
+  // ---- the row loop over the ring
+  const uint32_t ring_base = smem_u32(ring);
+  for (int it = 0; it < nb; ++it) {
+    const int s = it % p.stages;
+    const int parity = it & 1;
+    const int n0 = (b_begin + it) * kU;
+    if (!mbar_wait(smem_u32(&full_bar[s]), (it / p.stages) & 1)) {
+      // the KW warps wait for the same stage, so they all give up here together
+      if (lane == 0) atomicExch(p.error_word, 2);
+      return;
+    }
+    const uint32_t stage = ring_base + (uint32_t)s * p.stage_bytes;
+    uint4 wv[SPW][kU];
+    float sc[SPW][kU];
+#pragma unroll
+    for (int j = 0; j < SPW; ++j) {
+      if (cb[j] >= 0) {
+#pragma unroll
+        for (int u = 0; u < kU; ++u) wv[j][u] = lds128(stage + u * p.rowbytes + cb[j]);
+        const uint4 s4 = lds128(stage + p.tile_bytes + grp[j] * 16);
+        sc[j][0] = __uint_as_float(s4.x); sc[j][1] = __uint_as_float(s4.y);
+        sc[j][2] = __uint_as_float(s4.z); sc[j][3] = __uint_as_float(s4.w);
+      }
+    }
+    __syncwarp();
+    if (lane == 0) mbar_arrive(smem_u32(&empty_bar[s]));  // the stage can be refilled
+
     float acc[M][kU];
 #pragma unroll
     for (int m = 0; m < M; ++m)
@@ -375,35 +465,31 @@ gemv_stream_kernel(const GemvParams p) {
         for (int u = 0; u < kU; ++u)
 #pragma unroll
           for (int m = 0; m < M; ++m)
-            acc[m][u] = fmaf(xc[m][j].dot(wb.w[j][u]), wb.sc[j][u], acc[m][u]);
+            acc[m][u] = fmaf(xc[m][j].dot(wv[j][u]), sc[j][u], acc[m][u]);
       }
     }
+    float tot[M];
 #pragma unroll
-    for (int m = 0; m < M; ++m)
-#pragma unroll
-      for (int u = 0; u < kU; ++u) acc[m][u] = warp_sum(acc[m][u]);
+    for (int m = 0; m < M; ++m) tot[m] = reduce4(acc[m], lane);  // lane l: row (l & 3)
 
-    if (p.KW > 1) {
-      float* mine = red[parity][warp];
-      if (lane == 0) {
+    if (KW > 1) {
+      if (lane < kU) {
 #pragma unroll
-        for (int m = 0; m < M; ++m)
-#pragma unroll
-          for (int u = 0; u < kU; ++u) mine[m * kU + u] = acc[m][u];
+        for (int m = 0; m < M; ++m) red[parity][warp][m * kU + lane] = tot[m];
       }
-      asm volatile("bar.sync %0, %1;" ::"r"(barrier_id), "r"(barrier_threads) : "memory");
+      asm volatile("bar.sync 1, %0;" ::"r"(barrier_threads) : "memory");
     }
     if (kw == 0) {
       float total = 0.f;
-      if (lane < M * kU) {
-        if (p.KW > 1) {
-          for (int w = 0; w < p.KW; ++w) total += red[parity][rw * p.KW + w][lane];
-        } else {
+      if (KW > 1) {
+        if (lane < M * kU)
+          for (int w = 0; w < KW; ++w) total += red[parity][w][lane];
+      } else {
+        // lane u (< 4) holds row u for every m: lane (m, u) fetches it (all lanes shuffle)
 #pragma unroll
-          for (int mm = 0; mm < M; ++mm)
-#pragma unroll
-            for (int uu = 0; uu < kU; ++uu)
-              if (mm * kU + uu == lane) total = acc[mm][uu];
+        for (int m = 0; m < M; ++m) {
+          const float v = __shfl_sync(0xffffffffu, tot[m], lane % kU);
+          if (lane / kU == m) total = v;
         }
       }
       const int m = lane / kU, u = lane % kU;
@@ -435,48 +521,48 @@ gemv_stream_kernel(const GemvParams p) {
         }
       }
     }
-  };
-
-  for (int b = b_begin; b < b_end; b += 2) {
-    if (b + 1 < b_end) load_batch(b + 1, bufB);
-    process(b, 0, bufA);
-    if (b + 1 < b_end) {
-      if (b + 2 < b_end) load_batch(b + 2, bufA);
-      process(b + 1, 1, bufB);
-    }
   }
 }
 
 template <int BITS, int VAR, int M, int SPW, int EPI>
 int launch_one(const GemvParams& p, int threads, cudaStream_t s) {
+  auto kern = gemv_stream_kernel<BITS, VAR, M, SPW, EPI>;
+  const size_t smem = (size_t)p.stages * p.stage_bytes;
+  static thread_local bool attr_set = false;
+  if (!attr_set) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024) != cudaSuccess) {
+      cudaGetLastError();
+      return fail(LQ_ERR_LAUNCH, "lq_wq_gemv: cannot raise the dynamic shared memory limit");
+    }
+    attr_set = true;
+  }
   static thread_local int occ_threads = 0, occ = 0;
-  if (occ_threads != threads) {
+  static thread_local size_t occ_smem = 0;
+  if (occ_threads != threads || occ_smem != smem) {
     int n = 0;
-    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(
-            &n, gemv_stream_kernel<BITS, VAR, M, SPW, EPI>, threads, 0) != cudaSuccess || n <= 0) {
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kern, threads, smem) != cudaSuccess || n <= 0) {
       cudaGetLastError();
       n = 1;
     }
     occ = n;
     occ_threads = threads;
+    occ_smem = smem;
   }
-  // One row batch per row-warp slot until every SM holds its full complement of CTAs;
-  // beyond that the slots take several batches each (a single resident wave, no tail).
-  const int want = (p.nbatch + p.RW - 1) / p.RW;
+  // a single resident wave: one row batch per CTA until every SM holds its complement
   const int cap = sm_count() * occ;
-  int grid = want < cap ? want : cap;
+  int grid = p.nbatch < cap ? p.nbatch : cap;
   if (grid < 1) grid = 1;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3((unsigned)grid);
   cfg.blockDim = dim3((unsigned)threads);
-  cfg.dynamicSmemBytes = 0;
+  cfg.dynamicSmemBytes = smem;
   cfg.stream = s;
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = p.pdl ? 1 : 0;
-  cudaError_t e = cudaLaunchKernelEx(&cfg, gemv_stream_kernel<BITS, VAR, M, SPW, EPI>, p);
+  cudaError_t e = cudaLaunchKernelEx(&cfg, kern, p);
   if (e != cudaSuccess) {
     cudaGetLastError();
     return fail(LQ_ERR_LAUNCH, "lq_wq_gemv: %s", cudaGetErrorString(e));

@@ -34,10 +34,11 @@ _SIGNATURES = {
     "lq_dequant_weight": [_P, _P, _P, _I, _I, _I, _I, _I, _P],
     "lq_wq_gemv": [_P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P],
     "lq_stream_layout_sizes": [_I, _I, _I, _I, _I, _IP, _IP, _IP],
+    "lq_gemv_device_error": [],
     "lq_repack_stream": [_P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P],
     "lq_unrepack_stream": [_P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P],
-    "lq_dequant_stream": [_P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P],
-    "lq_wq_gemv_stream": [_P, _I, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _I, _P],
+    "lq_dequant_stream": [_P, _P, _P, _I, _I, _I, _I, _I, _I, _P],
+    "lq_wq_gemv_stream": [_P, _I, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P],
 }
 _SIGNATURES.update({
     "lq_kv_write": [_P, _P, _P, _P, _I, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P, _L, _I, _P],
@@ -55,10 +56,9 @@ class GemvArgs(ctypes.Structure):
 
     _fields_ = [
         ("x", _P), ("ldx", _I), ("norm_weight", _P), ("norm_eps", ctypes.c_float),
-        ("codes", _P), ("scales_t", _P), ("bias", _P), ("residual", _P), ("out", _P),
+        ("codes", _P), ("scale_tiles", _P), ("bias", _P), ("residual", _P), ("out", _P),
         ("out_dtype", _I), ("M", _I), ("N", _I), ("K", _I), ("Kd", _I), ("span", _I),
-        ("SRp", _I), ("out_group", _I), ("bits", _I), ("epilogue", _I), ("variant", _I),
-        ("pdl", _I),
+        ("bits", _I), ("epilogue", _I), ("variant", _I), ("pdl", _I),
     ]
 
 
@@ -109,8 +109,9 @@ def call(name: str, *args):
     check(getattr(library(), name)(*args))
 
 
-def stream_layout_sizes(groups, group_size, head_dim, bits, scale_rows):
-    kd, span, srp = ctypes.c_int(), ctypes.c_int(), ctypes.c_int()
-    call("lq_stream_layout_sizes", groups, group_size, head_dim or 0, bits, scale_rows,
-         ctypes.byref(kd), ctypes.byref(span), ctypes.byref(srp))
-    return kd.value, span.value, srp.value
+def stream_layout_sizes(n, groups, group_size, head_dim, bits):
+    """(Kd, span, NP) of the streaming layout for a canonical [n, groups, group_size] weight."""
+    kd, span, np_ = ctypes.c_int(), ctypes.c_int(), ctypes.c_int()
+    call("lq_stream_layout_sizes", n, groups, group_size, head_dim or 0, bits,
+         ctypes.byref(kd), ctypes.byref(span), ctypes.byref(np_))
+    return kd.value, span.value, np_.value

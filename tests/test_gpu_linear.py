@@ -150,6 +150,8 @@ def test_config1_output(golden):
         got32 = module.gemv(x, out_dtype=torch.float32)
         assert rel_l2(got32.cpu().numpy(), blob[key]) <= TOL_F32
     assert (bits_of(module(x)) == bits_of(module(x))).all()  # deterministic
+    from llmquant_b200 import native
+    assert native.library().lq_gemv_device_error() == 0  # no pipeline wait ever expired
 
 
 def test_bias_residual_leading_dims_and_prefill_branch():

@@ -57,7 +57,7 @@ def test_saved_file_is_byte_identical_to_the_reference(golden, tmp_path):
                                      tensors[f"{name}.wscale"], tensors.get(f"{name}.bias"), "cuda")
         original = getattr(model, name)
         assert torch.equal(rebuilt.codes, original.codes)
-        assert torch.equal(rebuilt.scales_t, original.scales_t)
+        assert torch.equal(rebuilt.scale_tiles, original.scale_tiles)
         assert torch.equal(rebuilt.qweight, original.qweight)
         x = torch.randn(2, 256, device="cuda", dtype=torch.bfloat16)
         assert torch.equal(rebuilt(x), original(x))

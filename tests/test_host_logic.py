@@ -49,10 +49,10 @@ def test_argument_errors_come_back_as_messages():
         native.call("lq_wq_gemv", 0, 0, 0, 0, 1, 8, 2, 6, 0, native.LQ_BF16, 0)
     with pytest.raises(RuntimeError, match="float32, float16 or bfloat16"):
         native.call("lq_fake_quant_group", 8, 8, 0, 4, 128, 8, 7, 0)
-    kd, span, srp = native.stream_layout_sizes(32, 128, 64, 8, 2048)
-    assert (kd, span, srp) == (2048, 64, 2048)
-    kd, span, srp = native.stream_layout_sizes(16, 128, 0, 4, 10)
-    assert (kd, span, srp) == (2048, 128, 12)
+    kd, span, npad = native.stream_layout_sizes(2048, 32, 128, 64, 8)
+    assert (kd, span, npad) == (2048, 64, 2048)
+    kd, span, npad = native.stream_layout_sizes(10, 16, 128, 0, 4)
+    assert (kd, span, npad) == (2048, 128, 12)
 
 
 def test_scheme_rules():
