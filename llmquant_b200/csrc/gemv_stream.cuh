@@ -548,8 +548,14 @@ int launch_one(const GemvParams& p, int threads, cudaStream_t s) {
     occ_threads = threads;
     occ_smem = smem;
   }
-  // a single resident wave: one row batch per CTA until every SM holds its complement
-  const int cap = sm_count() * occ;
+  // A single resident wave: one row batch per CTA until every SM holds its complement. The
+  // rings of one kernel are kept to about half an SM's shared memory, so that the CTAs of the
+  // NEXT kernel on the stream (programmatic dependent launch) find room to become resident
+  // and fill their own rings while this kernel is still computing.
+  int per_sm = occ;
+  const int by_smem = (int)((112 * 1024) / (smem > 0 ? smem : 1));
+  if (by_smem >= 1 && per_sm > by_smem) per_sm = by_smem;
+  const int cap = sm_count() * per_sm;
   int grid = p.nbatch < cap ? p.nbatch : cap;
   if (grid < 1) grid = 1;
   cudaLaunchConfig_t cfg = {};
@@ -574,7 +580,7 @@ int launch_one(const GemvParams& p, int threads, cudaStream_t s) {
 // requests run as several passes over the weight.
 template <int BITS, int VAR>
 constexpr int max_rows(int spw) {
-  if (spw == 1) return (BITS == 4 && VAR == 1) ? 2 : 4;
+  if (spw == 1) return (BITS == 4 && VAR != 2) ? 2 : 4;  // keep the instances free of register spills
   if (spw == 2) return BITS == 8 ? (VAR == 1 ? 1 : 2) : 1;
   return 1;
 }
