@@ -275,6 +275,60 @@ def run_gpu(args, rank, world, device):
         print(json.dumps(line), flush=True)
 
 
+# --------------------------------------------------------------------------- one GEMV shape
+def run_gemv_one(args, device):
+    """One shape, a few weight copies (> L2 together), back-to-back launches: the small case
+    used for kernel profiles. Prints a short JSON line of its own."""
+    from llmquant_b200.core import QuantizationArgs, QuantizationScheme
+    from llmquant_b200.quantizers import KernelQuantLinear
+
+    n, k, bits = args.n, args.k, args.bits
+    scheme = QuantizationScheme(
+        weights=QuantizationArgs(num_bits=bits, strategy="group", group_size=128), input_activations=None)
+    per_copy = algorithmic_bytes(n, k, bits)
+    copies = max(2, -(-int(1.5 * L2_BYTES) // per_copy))
+    g = torch.Generator(device=device).manual_seed(0)
+    mods = []
+    for _ in range(copies):
+        w = (torch.randn(n, k, generator=g, device=device) * 0.02).to(torch.bfloat16)
+        lin = torch.nn.Linear(k, n, bias=False, device="meta")
+        lin.weight = torch.nn.Parameter(w, requires_grad=False)
+        mods.append(KernelQuantLinear.from_linear(lin, scheme))
+        del w, lin
+    x = torch.randn(args.batch, k, generator=g, device=device).to(torch.bfloat16)
+    gamma = torch.ones(k, dtype=torch.bfloat16, device=device) if args.norm else None
+    n_out = n // 2 if args.epilogue else n
+    out = torch.empty(args.batch, n_out, dtype=torch.bfloat16, device=device)
+
+    def once():
+        for m in mods:
+            m.gemv(x, norm_weight=gamma, epilogue=args.epilogue, pdl=bool(args.pdl), out=out,
+                   variant=args.variant)
+
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        for _ in range(args.warmup):
+            once()
+    torch.cuda.current_stream().wait_stream(side)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        once()
+    graph.replay()
+    torch.cuda.synchronize()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for _ in range(args.steps):
+        graph.replay()
+    stop.record()
+    torch.cuda.synchronize()
+    us = start.elapsed_time(stop) * 1e3 / (args.steps * copies)
+    print(json.dumps({"workload": "gemv_one", "n": n, "k": k, "bits": bits, "rows": args.batch,
+                      "copies": copies, "us_per_launch": round(us, 2),
+                      "gbs": round(per_copy / us / 1e3, 1), "graph_replay": True, "pdl": args.pdl}), flush=True)
+
+
 # --------------------------------------------------------------------------- decode workload
 DECODE = {
     "decode_8b": dict(shape="llama-3-8b", prompt=4096, label="BASELINE config 5: random-init Llama-3-8B"),
@@ -498,7 +552,14 @@ def main():
     ap.add_argument("--steps", type=int, default=64)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
-    ap.add_argument("--workload", default="decode_8b", choices=["decode_8b", "decode_1b", "gemv_sweep_1b"])
+    ap.add_argument("--workload", default="decode_8b", choices=["decode_8b", "decode_1b", "gemv_sweep_1b", "gemv_one"])
+    ap.add_argument("--n", type=int, default=28672)
+    ap.add_argument("--k", type=int, default=4096)
+    ap.add_argument("--bits", type=int, default=4)
+    ap.add_argument("--epilogue", type=int, default=0)
+    ap.add_argument("--norm", type=int, default=0)
+    ap.add_argument("--pdl", type=int, default=1)
+    ap.add_argument("--variant", type=int, default=0)
     ap.add_argument("--batch", type=int, default=1)
     ap.add_argument("--prompt", type=int, default=0, help="prompt tokens (0 = the workload's own)")
     args = ap.parse_args()
@@ -518,7 +579,9 @@ def main():
         import torch.distributed as dist
         dist.init_process_group("nccl", device_id=device)
     try:
-        if args.workload in DECODE:
+        if args.workload == "gemv_one":
+            run_gemv_one(args, device)
+        elif args.workload in DECODE:
             run_decode(args, rank, world, device)
         else:
             run_gpu(args, rank, world, device)

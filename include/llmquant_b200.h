@@ -125,6 +125,11 @@ int lq_wq_gemv_stream(const void* x, int ldx, const void* codes, const float* sc
  * with the device, so it is for tests and diagnostics. -1 = the word could not be read. */
 int lq_gemv_device_error(void);
 
+/* Diagnostics: when set to a device buffer of 8 * grid uint64, every GEMV CTA writes
+ * %globaltimer stamps of its phases there (start, barriers ready, producer kernel done,
+ * activations prepared, first tile landed, end). NULL (the default) switches it off. */
+void lq_gemv_set_timeline(void* device_buffer);
+
 /* ---------------------------------------------------------------- quantized KV cache
  * Storage per layer: codes [B, Hkv, Tmax, D] int8, scales [B, Hkv, Tmax, ceil(D/128)] fp32.
  * A position / length can be given on the host (`pos`, `len`) or through a device int64
@@ -164,6 +169,24 @@ int lq_attn_decode_kv_i8(const void* q, const int8_t* k_codes, const int8_t* v_c
                          const float* k_scales, const float* v_scales, void* out, void* scratch,
                          int B, int Hq, int Hkv, int D, int Tmax, const int64_t* len_dev,
                          int64_t len, int len_add, float scaling, int splits, int pdl, void* stream);
+
+/* The attention block of one decode step as a single launch: rotary embedding of q and k
+ * from the fused q|k|v row, quantize-and-append of the new token's K and V at the cursor,
+ * attention over the cache including the new token, and the merge of the slices (done by
+ * the CTA that finishes last). out [B, Hq, D] bf16. `scratch` (lq_attn_fused_scratch_bytes)
+ * must be zero before the FIRST call; every call leaves its tail (the tickets) at zero
+ * again. Same arithmetic as lq_rope_kv_write followed by lq_attn_decode_kv_i8. */
+int64_t lq_attn_fused_scratch_bytes(int B, int Hq, int Hkv, int D, int splits);
+/* Non-zero if a bounded wait inside lq_attn_decode_fused ever expired (reads and clears the
+ * word; synchronizes with the device: for tests and diagnostics). */
+int lq_attn_device_error(void);
+/* Diagnostics, as lq_gemv_set_timeline: 8 uint64 stamps per CTA of lq_attn_decode_fused. */
+void lq_attn_set_timeline(void* device_buffer);
+int lq_attn_decode_fused(const void* qkv, const void* cos_table, const void* sin_table,
+                         int8_t* k_codes, int8_t* v_codes, float* k_scales, float* v_scales,
+                         void* out, void* scratch, int B, int Hq, int Hkv, int D, int Tmax,
+                         int table_len, const int64_t* pos_dev, int64_t pos, int num_bits,
+                         float scaling, int splits, int pdl, void* stream);
 
 /* The same GEMV with the work of the neighbouring decoder-layer ops folded in. All fields
  * of lq_wq_gemv_stream, plus:

@@ -118,6 +118,7 @@ int repack_common(const int8_t* canonical, const float* wscale, void* codes, flo
 }
 
 __device__ int g_gemv_error = 0;
+unsigned long long* g_debug_timeline = nullptr;  // host-side: where kernels write their stamps
 
 int* error_word() {
   static thread_local int cached_dev = -1;
@@ -175,6 +176,10 @@ extern "C" int lq_dequant_stream(const void* codes, const float* scale_tiles, vo
   return check_launch("lq_dequant_stream");
 }
 
+extern "C" void lq_gemv_set_timeline(void* device_buffer) {
+  lq::g_debug_timeline = (unsigned long long*)device_buffer;
+}
+
 extern "C" int lq_gemv_device_error(void) {
   int* word = lq::error_word();
   if (word == nullptr) return -1;
@@ -216,6 +221,7 @@ extern "C" int lq_wq_gemv_fused(const lq_gemv_args* a, void* stream) {
   p.groups = Kd / a->span;
   p.norm_weight = a->norm_weight; p.norm_eps = a->norm_eps; p.pdl = a->pdl;
   p.error_word = error_word();
+  p.debug = g_debug_timeline;
   LQ_REQUIRE(p.error_word != nullptr, LQ_ERR_LAUNCH, "cannot resolve the device error word");
   p.S = (p.rowbytes + 511) / 512;
   int spw = 1;
@@ -227,7 +233,11 @@ extern "C" int lq_wq_gemv_fused(const lq_gemv_args* a, void* stream) {
   p.tile_bytes = kU * p.rowbytes;
   p.scale_bytes = p.groups * kU * (int)sizeof(float);
   p.stage_bytes = (p.tile_bytes + p.scale_bytes + 127) / 128 * 128;
-  int stages = (48 * 1024) / p.stage_bytes;
+  // Ring depth: enough CTAs per SM for ~20 consumer warps (the dot products are dependent
+  // chains and need warps to hide their latency), all rings together within ~112 KB per SM so
+  // that the next kernel's CTAs can become resident early (see launch_one).
+  const int want_ctas = (20 + p.KW - 1) / p.KW;
+  int stages = (112 * 1024) / (want_ctas * p.stage_bytes);
   stages = stages < 2 ? 2 : (stages > kMaxStages ? kMaxStages : stages);
   LQ_REQUIRE((size_t)stages * p.stage_bytes <= 200 * 1024, LQ_ERR_UNSUPPORTED,
              "row tile of %d bytes does not fit the shared-memory ring", p.stage_bytes);

@@ -62,50 +62,18 @@ struct GemvParams {
   float norm_eps;
   int pdl;
   int* error_word;
+  unsigned long long* debug;  // optional per-CTA timeline (8 stamps per CTA), normally null
 };
 
-// ---- mbarrier / bulk-copy primitives (shared::cta addresses as 32-bit values)
-__device__ __forceinline__ uint32_t smem_u32(const void* p) {
-  return (uint32_t)__cvta_generic_to_shared(p);
+__device__ __forceinline__ unsigned long long global_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
 }
-__device__ __forceinline__ void mbar_init(uint32_t bar, int count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
-}
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-// Bounded wait: false if the phase did not complete within ~1 s of SM clock.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
-  const long long t0 = clock64();
-  for (;;) {
-    uint32_t done;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.b32 %0, 1, 0, p;\n\t}"
-        : "=r"(done)
-        : "r"(bar), "r"(parity)
-        : "memory");
-    if (done) return true;
-    if (clock64() - t0 > 2000000000LL) return false;
-  }
-}
-__device__ __forceinline__ void bulk_g2s(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
-  asm volatile(
-      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-      ::"r"(dst), "l"(src), "r"(bytes), "r"(bar)
-      : "memory");
-}
-__device__ __forceinline__ uint4 lds128(uint32_t addr) {
-  uint4 v;
-  asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
-               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
-               : "r"(addr));
-  return v;
-}
+#define LQ_STAMP(slot)                                                             \
+  do {                                                                             \
+    if (p.debug != nullptr && threadIdx.x == 0) p.debug[(size_t)blockIdx.x * 8 + (slot)] = global_ns(); \
+  } while (0)
 
 __device__ __forceinline__ int dp4a_ss(unsigned a, unsigned b, int c) {
   int d;
@@ -292,6 +260,7 @@ gemv_stream_kernel(const GemvParams p) {
   const int warp = threadIdx.x >> 5;
   const int KW = p.KW;
   const int barrier_threads = KW * 32;
+  LQ_STAMP(0);
 
   // contiguous balanced range of row batches for this CTA
   const int b_begin = (int)(((int64_t)p.nbatch * blockIdx.x) / gridDim.x);
@@ -346,8 +315,10 @@ gemv_stream_kernel(const GemvParams p) {
 
   // x is produced by the kernel before this one: wait for it (a no-op without programmatic
   // dependent launch), then let the kernel after this one start its own weight stream.
+  LQ_STAMP(1);
   asm volatile("griddepcontrol.wait;" ::: "memory");
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  LQ_STAMP(2);
 
   // ---- optional fused RMSNorm: rstd[m] = 1 / sqrt(mean(x^2) + eps) over the whole row
   float rstd[M];
@@ -361,8 +332,22 @@ gemv_stream_kernel(const GemvParams p) {
         if (cb[j] < 0 || m >= p.M) continue;
         const int k0 = cb[j] * (8 / BITS);
         const __nv_bfloat16* xr = p.x + (int64_t)m * p.ldx + k0;
-        for (int i = 0; i < EPL; ++i)
-          if (k0 + i < p.K) { const float v = __bfloat162float(xr[i]); ss[m] = fmaf(v, v, ss[m]); }
+        if (k0 + EPL <= p.K && ((reinterpret_cast<uintptr_t>(xr) & 15) == 0)) {
+#pragma unroll
+          for (int v = 0; v < EPL / 8; ++v) {
+            const uint4 raw = __ldg(reinterpret_cast<const uint4*>(xr) + v);
+            const unsigned r[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+            for (int t = 0; t < 4; ++t) {
+              const float lo = __uint_as_float(r[t] << 16), hi = __uint_as_float(r[t] & 0xFFFF0000u);
+              ss[m] = fmaf(lo, lo, ss[m]);
+              ss[m] = fmaf(hi, hi, ss[m]);
+            }
+          }
+        } else {
+          for (int i = 0; i < EPL; ++i)
+            if (k0 + i < p.K) { const float v = __bfloat162float(xr[i]); ss[m] = fmaf(v, v, ss[m]); }
+        }
       }
       ss[m] = warp_sum(ss[m]);
     }
@@ -415,9 +400,25 @@ gemv_stream_kernel(const GemvParams p) {
         // weight * bf16(x * rstd), the product rounded to bf16 again: the two roundings of
         // a bf16 RMSNorm module
         const __nv_bfloat16* gw = reinterpret_cast<const __nv_bfloat16*>(p.norm_weight) + k0;
+        float gf[EPL];
+        if (live && k0 + EPL <= p.K && ((reinterpret_cast<uintptr_t>(gw) & 15) == 0)) {
+#pragma unroll
+          for (int v = 0; v < EPL / 8; ++v) {
+            const uint4 raw = __ldg(reinterpret_cast<const uint4*>(gw) + v);
+            const unsigned r[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+            for (int t = 0; t < 4; ++t) {
+              gf[v * 8 + 2 * t] = __uint_as_float(r[t] << 16);
+              gf[v * 8 + 2 * t + 1] = __uint_as_float(r[t] & 0xFFFF0000u);
+            }
+          }
+        } else {
+#pragma unroll
+          for (int i = 0; i < EPL; ++i) gf[i] = (live && k0 + i < p.K) ? __bfloat162float(gw[i]) : 0.f;
+        }
 #pragma unroll
         for (int i = 0; i < EPL; ++i) {
-          const float g = (live && k0 + i < p.K) ? __bfloat162float(gw[i]) : 0.f;
+          const float g = gf[i];
           const float nx = __bfloat162float(__float2bfloat16_rn(xf[i] * rstd[m]));
           xf[i] = __bfloat162float(__float2bfloat16_rn(g * nx));
         }
@@ -426,6 +427,7 @@ gemv_stream_kernel(const GemvParams p) {
     }
   }
 
+  LQ_STAMP(3);
   // ---- the row loop over the ring
   const uint32_t ring_base = smem_u32(ring);
   for (int it = 0; it < nb; ++it) {
@@ -437,6 +439,7 @@ gemv_stream_kernel(const GemvParams p) {
       if (lane == 0) atomicExch(p.error_word, 2);
       return;
     }
+    if (it == 0) LQ_STAMP(4);
     const uint32_t stage = ring_base + (uint32_t)s * p.stage_bytes;
     uint4 wv[SPW][kU];
     float sc[SPW][kU];
@@ -522,6 +525,7 @@ gemv_stream_kernel(const GemvParams p) {
       }
     }
   }
+  LQ_STAMP(5);
 }
 
 template <int BITS, int VAR, int M, int SPW, int EPI>

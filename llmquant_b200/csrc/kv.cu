@@ -11,6 +11,8 @@
 //
 // Positions and lengths can come from device memory (an int64 counter), so every kernel is
 // CUDA-graph capturable with a moving write cursor.
+#include <type_traits>
+
 #include "common.cuh"
 
 namespace lq {
@@ -346,6 +348,27 @@ int launch_pdl(Kern kern, dim3 grid, dim3 block, cudaStream_t s, int pdl, const 
   return LQ_OK;
 }
 
+template <typename Kern, typename... Args>
+int launch_pdl_smem(Kern kern, dim3 grid, dim3 block, size_t smem, cudaStream_t s, int pdl,
+                    const char* what, Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = s;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl ? 1 : 0;
+  cudaError_t e = cudaLaunchKernelEx(&cfg, kern, args...);
+  if (e != cudaSuccess) {
+    cudaGetLastError();
+    return fail(LQ_ERR_LAUNCH, "%s: %s", what, cudaGetErrorString(e));
+  }
+  return LQ_OK;
+}
+
 }  // namespace
 }  // namespace lq
 
@@ -442,4 +465,448 @@ extern "C" int lq_attn_decode_kv_i8(const void* q, const int8_t* k_codes, const 
   return launch_pdl(attn_combine_kernel, dim3((unsigned)Hq, (unsigned)B), dim3((unsigned)((D + 31) / 32 * 32)),
                     s, pdl, "lq_attn_decode_kv_i8(combine)", (const float*)part_o, (const float*)part_ml,
                     (__nv_bfloat16*)out, Hq, D, splits);
+}
+
+// ---------------------------------------------------------------- one kernel per layer: RoPE + KV write + attention + merge
+// The decode step's attention block as a single launch. grid (NS, Hkv, B), 128 threads.
+// Every CTA rotates the G query heads of its KV head itself (a few hundred multiply-adds)
+// instead of reading them back from a separate kernel's output. The CTA of the last slice
+// also rotates and quantizes the new token's K and V rows, appends them to the cache at the
+// cursor and folds them into its softmax from registers, so the cached tokens [0, pos) are
+// the only thing read from HBM. Slices meet through the scratch arrays; the CTA that
+// finishes last (an atomic ticket per KV head) merges them and writes the bf16 output, then
+// puts the ticket back to zero for the next launch.
+namespace lq {
+namespace {
+
+constexpr int kFusedThreads = 256;            // 8 warps: 16 lanes per token, 2 tokens per warp
+constexpr int kFusedChunkBytes = 28 * 1024;  // K (and as much V) staged per chunk of a slice
+
+template <int D, int G>
+__global__ void __launch_bounds__(kFusedThreads)
+attn_fused_kernel(const __nv_bfloat16* __restrict__ qkv, const __nv_bfloat16* __restrict__ cos_t,
+                  const __nv_bfloat16* __restrict__ sin_t, int8_t* kc, int8_t* vc, float* ks, float* vs,
+                  __nv_bfloat16* __restrict__ out, float* part_o, float* part_ml, int* tickets,
+                  int Hq, int Hkv, int Tmax, int table_len, const int64_t* pos_dev, int64_t pos_host,
+                  float scaling, float qmin, float qmax, int* error_word, unsigned long long* debug) {
+#define ATT_STAMP(slot) do { if (debug != nullptr && threadIdx.x == 0) { unsigned long long t_; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_)); debug[((size_t)(blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x) * 8 + (slot)] = t_; } } while (0)
+  constexpr int DPL = D / 16;  // dims per lane
+  constexpr int NGRP = 16;     // lane groups per CTA (8 warps x 2)
+  constexpr int NT = kFusedThreads;
+  constexpr int HALF = D / 2;
+  constexpr int CAP = kFusedChunkBytes / D;  // tokens per staged chunk
+  extern __shared__ __align__(128) uint8_t stage[];  // K codes [CAP, D], V codes [CAP, D], scores [CAP, G]
+  __shared__ __align__(8) uint64_t bar;
+  __shared__ float sk_s[CAP], sv_s[CAP];
+  __shared__ float q_s[G][D];
+  __shared__ float knew_s[D], vnew_s[D];
+  __shared__ float m_s[NGRP][G], l_s[NGRP][G];
+  __shared__ float newscale_s[2];
+  __shared__ int last_s;
+  float (*o_s)[G][D] = reinterpret_cast<float (*)[G][D]>(stage);  // reused after the loop
+
+  const int ns = gridDim.x, split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int sub = lane & 15, grp = warp * 2 + (lane >> 4);
+  ATT_STAMP(0);
+  // The cursor was advanced by the previous step, long before the kernel ahead of this one
+  // started, and the cached rows [0, pos) are older still: both may be read before the
+  // dependency wait, so the slice's first chunk is already on its way while q is computed.
+  int64_t pos = read_pos(pos_dev, pos_host);   // index of the new token = number of cached ones
+  if (pos < 0) pos = 0;
+  if (pos > Tmax - 1) pos = Tmax - 1;
+  const int64_t len = pos;
+  const int per = (int)((len + ns - 1) / ns);
+  const int t_lo = split * per;
+  const int t_hi = (int)min((int64_t)(t_lo + per), len);
+  const int64_t head_row = ((int64_t)b * Hkv + kvh) * Tmax;
+  const uint32_t bar_a = smem_u32(&bar);
+  const uint32_t k_a = smem_u32(stage), v_a = k_a + CAP * D;
+
+  auto issue = [&](int c_lo) {  // one thread: request K and V codes of a chunk
+    const int n = min(CAP, t_hi - c_lo);
+    const uint32_t bytes = (uint32_t)n * D;
+    mbar_expect_tx(bar_a, 2 * bytes);
+    bulk_g2s(k_a, kc + (head_row + c_lo) * D, bytes, bar_a);
+    bulk_g2s(v_a, vc + (head_row + c_lo) * D, bytes, bar_a);
+  };
+  if (threadIdx.x == 0) {
+    mbar_init(bar_a, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    if (t_lo < t_hi) issue(t_lo);
+  }
+
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+
+  ATT_STAMP(1);
+  const int64_t tpos = pos < table_len ? pos : table_len - 1;
+  const int heads = Hq + 2 * Hkv;
+  const __nv_bfloat16* row = qkv + (int64_t)b * heads * D;
+  auto r16 = [](float x) { return __bfloat162float(__float2bfloat16_rn(x)); };
+
+  // ---- rotate the G query heads (bf16 arithmetic of apply_rotary_pos_emb), pre-scaled
+  for (int i = threadIdx.x; i < G * HALF; i += NT) {
+    const int g = i / HALF, d = i % HALF;
+    const __nv_bfloat16* src = row + (int64_t)(kvh * G + g) * D;
+    const float a = __bfloat162float(src[d]), c = __bfloat162float(src[d + HALF]);
+    const float c0 = __bfloat162float(cos_t[tpos * D + d]), s0 = __bfloat162float(sin_t[tpos * D + d]);
+    const float c1 = __bfloat162float(cos_t[tpos * D + d + HALF]), s1 = __bfloat162float(sin_t[tpos * D + d + HALF]);
+    q_s[g][d] = r16(r16(a * c0) + r16(-c * s0)) * scaling;
+    q_s[g][d + HALF] = r16(r16(c * c1) + r16(a * s1)) * scaling;
+  }
+  ATT_STAMP(2);
+  // ---- the last slice owns the new token: rotate K, quantize K and V, append to the cache
+  const bool owner = split == ns - 1;
+  if (owner && warp < 2) {
+    const bool is_v = warp == 1;
+    const __nv_bfloat16* src = row + (int64_t)(Hq + (is_v ? Hkv : 0) + kvh) * D;
+    float val[D / 32];
+    float amax = 0.f;
+#pragma unroll
+    for (int j = 0; j < D / 32; ++j) {
+      const int d = lane + 32 * j;
+      float x = __bfloat162float(src[d]);
+      if (!is_v) {
+        const int partner = d < HALF ? d + HALF : d - HALF;
+        const float y = __bfloat162float(src[partner]);
+        const float cc = __bfloat162float(cos_t[tpos * D + d]), ss = __bfloat162float(sin_t[tpos * D + d]);
+        x = d < HALF ? r16(r16(x * cc) + r16(-y * ss)) : r16(r16(x * cc) + r16(y * ss));
+      }
+      val[j] = x;
+      amax = fmaxf(amax, fabsf(x));
+    }
+    amax = warp_max(amax);
+    const float scale = scale_of(amax, qmax);
+    const int64_t crow = head_row + pos;
+    if (lane == 0) { (is_v ? vs : ks)[crow] = scale; newscale_s[is_v] = scale; }
+#pragma unroll
+    for (int j = 0; j < D / 32; ++j) {
+      const int d = lane + 32 * j;
+      const float code = code_of(val[j], scale, qmin, qmax);
+      (is_v ? vc : kc)[crow * D + d] = (int8_t)code;
+      (is_v ? vnew_s : knew_s)[d] = code;
+    }
+  }
+
+  // Online softmax per chunk, in two passes over the staged codes: scores first (their
+  // maximum is then known for the whole CTA), probabilities and the V sum second. No value
+  // depends on the previous token inside a pass, so the loops pipeline freely.
+  float M[G], l[G], acc[G][DPL];   // M is the same in every thread of the CTA
+#pragma unroll
+  for (int g = 0; g < G; ++g) {
+    M[g] = -INFINITY; l[g] = 0.f;
+#pragma unroll
+    for (int i = 0; i < DPL; ++i) acc[g][i] = 0.f;
+  }
+  float* sc_s = reinterpret_cast<float*>(stage + 2 * (size_t)CAP * D);  // [CAP][G] scores
+  using Vec = typename std::conditional<DPL == 8, uint2, uint32_t>::type;
+  auto raise_max = [&](const float (&cmax)[G]) {  // CTA-wide maximum, then rescale what we hold
+    if (sub == 0) {
+#pragma unroll
+      for (int g = 0; g < G; ++g) m_s[grp][g] = cmax[g];
+    }
+    __syncthreads();
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+      float mm = M[g];
+      for (int r = 0; r < NGRP; ++r) mm = fmaxf(mm, m_s[r][g]);
+      if (mm > M[g]) {
+        const float corr = (M[g] == -INFINITY) ? 0.f : __expf(M[g] - mm);
+        l[g] *= corr;
+#pragma unroll
+        for (int i = 0; i < DPL; ++i) acc[g][i] *= corr;
+        M[g] = mm;
+      }
+    }
+    __syncthreads();  // m_s is free again
+  };
+
+  ATT_STAMP(3);
+  // ---- cached tokens of this slice, chunk by chunk out of shared memory
+  bool dead = false;
+  int phase = 0;
+  for (int c_lo = t_lo; c_lo < t_hi; c_lo += CAP) {
+    const int n = min(CAP, t_hi - c_lo);
+    for (int i = threadIdx.x; i < n; i += NT) {
+      sk_s[i] = ks[head_row + c_lo + i];
+      sv_s[i] = vs[head_row + c_lo + i];
+    }
+    __syncthreads();  // also orders q_s before its first use
+    if (!mbar_wait(bar_a, phase)) { dead = true; break; }  // every thread waits on the same phase
+    phase ^= 1;
+    float cmax[G];
+#pragma unroll
+    for (int g = 0; g < G; ++g) cmax[g] = -INFINITY;
+    // pass 1 (warp-uniform trip count: the shuffles name all 32 lanes)
+#pragma unroll 2
+    for (int i0 = 0; i0 < n; i0 += NGRP) {
+      const int i = i0 + grp;
+      const bool valid = i < n;
+      const int r = valid ? i : 0;
+      int8_t kb[DPL];
+      *reinterpret_cast<Vec*>(kb) = *reinterpret_cast<const Vec*>(stage + (size_t)r * D + sub * DPL);
+      const float sk = sk_s[r];
+#pragma unroll
+      for (int g = 0; g < G; ++g) {
+        float d = 0.f;
+#pragma unroll
+        for (int j = 0; j < DPL; ++j) d = fmaf(q_s[g][sub * DPL + j], (float)kb[j], d);
+        d += __shfl_xor_sync(0xffffffffu, d, 1);
+        d += __shfl_xor_sync(0xffffffffu, d, 2);
+        d += __shfl_xor_sync(0xffffffffu, d, 4);
+        d += __shfl_xor_sync(0xffffffffu, d, 8);
+        d *= sk;
+        if (valid) {
+          cmax[g] = fmaxf(cmax[g], d);
+          if (sub == 0) sc_s[r * G + g] = d;
+        }
+      }
+    }
+    raise_max(cmax);  // (its barriers also publish sc_s)
+    // pass 2
+#pragma unroll 2
+    for (int i0 = 0; i0 < n; i0 += NGRP) {
+      const int i = i0 + grp;
+      if (i < n) {
+        int8_t vb[DPL];
+        *reinterpret_cast<Vec*>(vb) = *reinterpret_cast<const Vec*>(stage + (size_t)(CAP + i) * D + sub * DPL);
+        const float sv = sv_s[i];
+        float vf[DPL];
+#pragma unroll
+        for (int j = 0; j < DPL; ++j) vf[j] = (float)vb[j] * sv;
+#pragma unroll
+        for (int g = 0; g < G; ++g) {
+          const float pgt = __expf(sc_s[i * G + g] - M[g]);
+          l[g] += pgt;
+#pragma unroll
+          for (int j = 0; j < DPL; ++j) acc[g][j] = fmaf(pgt, vf[j], acc[g][j]);
+        }
+      }
+    }
+    __syncthreads();  // everyone is done with the stage before it is refilled
+    if (threadIdx.x == 0 && c_lo + CAP < t_hi) issue(c_lo + CAP);
+  }
+  if (dead) {
+    if (threadIdx.x == 0) atomicExch(error_word, 3);
+    return;
+  }
+  __syncthreads();
+  if (owner) {  // the new token, from shared memory: every lane joins the shuffles
+    float snew[G];
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+      float d = 0.f;
+#pragma unroll
+      for (int j = 0; j < DPL; ++j) d = fmaf(q_s[g][sub * DPL + j], knew_s[sub * DPL + j], d);
+      d += __shfl_xor_sync(0xffffffffu, d, 1);
+      d += __shfl_xor_sync(0xffffffffu, d, 2);
+      d += __shfl_xor_sync(0xffffffffu, d, 4);
+      d += __shfl_xor_sync(0xffffffffu, d, 8);
+      snew[g] = d * newscale_s[0];
+    }
+    raise_max(snew);
+    if (grp == 0) {  // one lane group adds it
+#pragma unroll
+      for (int g = 0; g < G; ++g) {
+        const float pgt = __expf(snew[g] - M[g]);
+        l[g] += pgt;
+#pragma unroll
+        for (int j = 0; j < DPL; ++j)
+          acc[g][j] = fmaf(pgt, vnew_s[sub * DPL + j] * newscale_s[1], acc[g][j]);
+      }
+    }
+  }
+
+  ATT_STAMP(4);
+  // ---- sum the 16 lane groups of the CTA (same M everywhere; the staging area is free now)
+  if (sub == 0) {
+#pragma unroll
+    for (int g = 0; g < G; ++g) l_s[grp][g] = l[g];
+  }
+  constexpr int OUT_PER_THREAD = (G * D + NT - 1) / NT;
+  float osum[OUT_PER_THREAD];
+#pragma unroll
+  for (int k = 0; k < OUT_PER_THREAD; ++k) osum[k] = 0.f;
+  for (int halfsel = 0; halfsel < 2; ++halfsel) {
+    __syncthreads();
+    if ((grp / (NGRP / 2)) == halfsel) {
+#pragma unroll
+      for (int g = 0; g < G; ++g)
+#pragma unroll
+        for (int i = 0; i < DPL; ++i) o_s[grp % (NGRP / 2)][g][sub * DPL + i] = acc[g][i];
+    }
+    __syncthreads();
+#pragma unroll
+    for (int k = 0; k < OUT_PER_THREAD; ++k) {
+      const int i = threadIdx.x + NT * k;
+      if (i < G * D) {
+        const int g = i / D, d = i % D;
+#pragma unroll
+        for (int r = 0; r < NGRP / 2; ++r) osum[k] += o_s[r][g][d];
+      }
+    }
+  }
+  float* po = part_o + (((int64_t)b * Hq + kvh * G) * ns + split) * D;
+#pragma unroll
+  for (int k = 0; k < OUT_PER_THREAD; ++k) {
+    const int i = threadIdx.x + NT * k;
+    if (i < G * D) po[(int64_t)(i / D) * ns * D + (i % D)] = osum[k];
+  }
+  if (threadIdx.x < G) {
+    const int g = threadIdx.x;
+    float lt = 0.f;
+    for (int r = 0; r < NGRP; ++r) lt += l_s[r][g];
+    float* ml = part_ml + (((int64_t)b * Hq + kvh * G + g) * ns + split) * 2;
+    ml[0] = M[g]; ml[1] = lt;
+  }
+
+  // ---- the CTA that finishes last merges the slices
+  ATT_STAMP(5);
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const int ticket = atomicAdd(&tickets[b * Hkv + kvh], 1);
+    last_s = ticket == ns - 1;
+  }
+  __syncthreads();
+  ATT_STAMP(6);
+  if (!last_s) return;
+  __threadfence();
+  // weights of the slices: w_s[s][g] = exp(m_s - max) (shared memory reused again). Then the
+  // warps split the slices between them, every lane keeps all its loads in flight at once,
+  // and the per-warp sums meet in shared memory.
+  float* wsl = reinterpret_cast<float*>(stage);          // [ns][G]
+  float* lsum = wsl + (size_t)ns * G;                    // [G]
+  float* psum = lsum + G;                                // [8 warps][G * D]
+  for (int g = warp; g < G; g += NT / 32) {
+    const int64_t base = ((int64_t)b * Hq + kvh * G + g) * ns;
+    float mm = -INFINITY;
+    for (int s = lane; s < ns; s += 32) mm = fmaxf(mm, __ldcg(part_ml + (base + s) * 2));
+    mm = warp_max(mm);
+    float lt = 0.f;
+    for (int s = lane; s < ns; s += 32) {
+      const float ms = __ldcg(part_ml + (base + s) * 2);
+      const float ws = (ms == -INFINITY) ? 0.f : __expf(ms - mm);
+      wsl[s * G + g] = ws;
+      lt = fmaf(__ldcg(part_ml + (base + s) * 2 + 1), ws, lt);
+    }
+    lt = warp_sum(lt);
+    if (lane == 0) lsum[g] = lt;
+  }
+  __syncthreads();
+  constexpr int PER_LANE = (G * D + 31) / 32;  // outputs a lane covers for its warp's slices
+  float part[PER_LANE];
+#pragma unroll
+  for (int k = 0; k < PER_LANE; ++k) part[k] = 0.f;
+  for (int s0 = warp; s0 < ns; s0 += 4 * (NT / 32)) {  // four slices of this warp per round
+    float v[4][PER_LANE];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int s = s0 + j * (NT / 32);
+#pragma unroll
+      for (int k = 0; k < PER_LANE; ++k) {
+        const int i = lane + 32 * k;
+        const int g = i / D, d = i % D;
+        v[j][k] = (s < ns && i < G * D)
+                      ? __ldcg(part_o + (((int64_t)b * Hq + kvh * G + g) * ns + s) * D + d) : 0.f;
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int s = s0 + j * (NT / 32);
+      if (s < ns) {
+#pragma unroll
+        for (int k = 0; k < PER_LANE; ++k) {
+          const int i = lane + 32 * k;
+          if (i < G * D) part[k] = fmaf(v[j][k], wsl[s * G + i / D], part[k]);
+        }
+      }
+    }
+  }
+#pragma unroll
+  for (int k = 0; k < PER_LANE; ++k) {
+    const int i = lane + 32 * k;
+    if (i < G * D) psum[warp * (G * D) + i] = part[k];
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < G * D; i += NT) {
+    const int g = i / D, d = i % D;
+    float o = 0.f;
+#pragma unroll
+    for (int w8 = 0; w8 < NT / 32; ++w8) o += psum[w8 * (G * D) + i];
+    const float lt = lsum[g];
+    out[((int64_t)b * Hq + kvh * G + g) * D + d] = __float2bfloat16_rn(lt > 0.f ? o / lt : 0.f);
+  }
+  if (threadIdx.x == 0) tickets[b * Hkv + kvh] = 0;
+  ATT_STAMP(7);
+#undef ATT_STAMP
+}
+
+__device__ int g_attn_error = 0;
+unsigned long long* g_attn_timeline = nullptr;
+
+}  // namespace
+}  // namespace lq
+
+extern "C" void lq_attn_set_timeline(void* device_buffer) {
+  lq::g_attn_timeline = (unsigned long long*)device_buffer;
+}
+
+extern "C" int lq_attn_device_error(void) {
+  void* ptr = nullptr;
+  if (cudaGetSymbolAddress(&ptr, lq::g_attn_error) != cudaSuccess) { cudaGetLastError(); return -1; }
+  int value = 0;
+  if (cudaMemcpy(&value, ptr, sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess) return -1;
+  if (value != 0) cudaMemset(ptr, 0, sizeof(int));
+  return value;
+}
+
+extern "C" int64_t lq_attn_fused_scratch_bytes(int B, int Hq, int Hkv, int D, int splits) {
+  return (int64_t)B * Hq * splits * (D + 2) * (int64_t)sizeof(float) + (int64_t)B * Hkv * (int64_t)sizeof(int);
+}
+
+extern "C" int lq_attn_decode_fused(const void* qkv, const void* cos_table, const void* sin_table,
+                                    int8_t* k_codes, int8_t* v_codes, float* k_scales, float* v_scales,
+                                    void* out, void* scratch, int B, int Hq, int Hkv, int D, int Tmax,
+                                    int table_len, const int64_t* pos_dev, int64_t pos, int num_bits,
+                                    float scaling, int splits, int pdl, void* stream) {
+  using namespace lq;
+  LQ_REQUIRE(num_bits >= 2 && num_bits <= 8, LQ_ERR_ARG, "num_bits must be in [2, 8], got %d", num_bits);
+  LQ_REQUIRE(B > 0 && Hq > 0 && Hkv > 0 && Hq % Hkv == 0 && Tmax > 0 && table_len > 0, LQ_ERR_ARG, "bad shape");
+  LQ_REQUIRE(splits >= 1 && splits <= 1024, LQ_ERR_ARG, "splits must be in [1, 1024]");
+  LQ_REQUIRE(qkv && cos_table && sin_table && k_codes && v_codes && k_scales && v_scales && out && scratch,
+             LQ_ERR_ARG, "null tensor pointer");
+  const int G = Hq / Hkv;
+  float* part_o = (float*)scratch;
+  float* part_ml = part_o + (int64_t)B * Hq * splits * D;
+  int* tickets = (int*)(part_ml + (int64_t)B * Hq * splits * 2);
+  const float qmax = (float)((1 << (num_bits - 1)) - 1);
+  dim3 grid((unsigned)splits, (unsigned)Hkv, (unsigned)B);
+  int rc = LQ_ERR_UNSUPPORTED;
+  void* err_ptr = nullptr;
+  if (cudaGetSymbolAddress(&err_ptr, g_attn_error) != cudaSuccess) {
+    cudaGetLastError();
+    return fail(LQ_ERR_LAUNCH, "cannot resolve the device error word");
+  }
+  const size_t smem = 2 * (size_t)kFusedChunkBytes + (size_t)(kFusedChunkBytes / 64) * 8 * sizeof(float);
+#define LQ_FUSED_CASE(DD, GG)                                                                      \
+  if (D == DD && G == GG) {                                                                        \
+    static bool raised = false;                                                                    \
+    if (!raised) {                                                                                 \
+      cudaFuncSetAttribute(attn_fused_kernel<DD, GG>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+      raised = true;                                                                               \
+    }                                                                                              \
+    rc = launch_pdl_smem(attn_fused_kernel<DD, GG>, grid, dim3(kFusedThreads), smem, (cudaStream_t)stream, pdl, \
+                    "lq_attn_decode_fused", (const __nv_bfloat16*)qkv, (const __nv_bfloat16*)cos_table, \
+                    (const __nv_bfloat16*)sin_table, k_codes, v_codes, k_scales, v_scales,         \
+                    (__nv_bfloat16*)out, part_o, part_ml, tickets, Hq, Hkv, Tmax, table_len, pos_dev, \
+                    pos, scaling, -qmax - 1.f, qmax, (int*)err_ptr, g_attn_timeline);                               \
+  }
+  LQ_FUSED_CASE(64, 1) LQ_FUSED_CASE(64, 2) LQ_FUSED_CASE(64, 4) LQ_FUSED_CASE(64, 8)
+  LQ_FUSED_CASE(128, 1) LQ_FUSED_CASE(128, 2) LQ_FUSED_CASE(128, 4) LQ_FUSED_CASE(128, 8)
+#undef LQ_FUSED_CASE
+  if (rc == LQ_ERR_UNSUPPORTED)
+    return fail(LQ_ERR_UNSUPPORTED, "fused decode attention is built for head_dim 64/128 and 1/2/4/8 query heads per KV head, got %d / %d", D, G);
+  return rc;
 }

@@ -35,6 +35,7 @@ _SIGNATURES = {
     "lq_wq_gemv": [_P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P],
     "lq_stream_layout_sizes": [_I, _I, _I, _I, _I, _IP, _IP, _IP],
     "lq_gemv_device_error": [],
+    "lq_gemv_set_timeline": [_P],
     "lq_repack_stream": [_P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P],
     "lq_unrepack_stream": [_P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P],
     "lq_dequant_stream": [_P, _P, _P, _I, _I, _I, _I, _I, _I, _P],
@@ -48,7 +49,15 @@ _SIGNATURES.update({
     "lq_attn_decode_kv_i8": [_P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P, _L, _I,
                              ctypes.c_float, _I, _I, _P],
 })
-_RESTYPE = {"lq_last_error": ctypes.c_char_p, "lq_attn_decode_scratch_bytes": ctypes.c_int64}
+_SIGNATURES.update({
+    "lq_attn_fused_scratch_bytes": [_I, _I, _I, _I, _I],
+    "lq_attn_device_error": [],
+    "lq_attn_set_timeline": [_P],
+    "lq_attn_decode_fused": [_P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P, _L, _I,
+                             ctypes.c_float, _I, _I, _P],
+})
+_RESTYPE = {"lq_gemv_set_timeline": None, "lq_attn_set_timeline": None, "lq_last_error": ctypes.c_char_p, "lq_attn_decode_scratch_bytes": ctypes.c_int64,
+            "lq_attn_fused_scratch_bytes": ctypes.c_int64}
 
 
 class GemvArgs(ctypes.Structure):

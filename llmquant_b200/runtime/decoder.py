@@ -5,7 +5,7 @@ separate `wq_gemv` launch with PyTorch ops in between (RMSNorm, RoPE, cache upda
 residual adds), optionally replayed from a CUDA graph (llmquant/runtime/graph_decode.py:52-131).
 This decoder walks the same layer sequence with the library's kernels only:
 
-    per layer   GEMV[RMSNorm -> q|k|v]  ->  RoPE + int8 KV write  ->  int8-KV decode attention
+    per layer   GEMV[RMSNorm -> q|k|v]  ->  [RoPE + int8 KV write + int8-KV attention + merge]
                 -> GEMV[o_proj + residual]  ->  GEMV[RMSNorm -> gate|up -> silu*mul]
                 -> GEMV[down_proj + residual]
     then        GEMV[final RMSNorm -> lm_head]  ->  argmax  ->  embedding row of the new token
@@ -144,11 +144,11 @@ class FusedLlamaDecoder:
         self.history = torch.zeros(B, max_len + 1, dtype=torch.long, device=dev)
         want = max(1, -(-2 * 148 // (B * self.Hkv)))
         self.splits = max(1, min(want, max_len // 64 or 1))
-        nbytes = native.library().lq_attn_decode_scratch_bytes(B, self.Hq, self.D, self.splits)
-        self.scratch = torch.zeros(nbytes // 4, dtype=torch.float32, device=dev)
+        nbytes = native.library().lq_attn_fused_scratch_bytes(B, self.Hq, self.Hkv, self.D, self.splits)
+        self.scratch = torch.zeros(-(-nbytes // 4), dtype=torch.float32, device=dev)
         self.cache = KernelQuantCache(kv_bits, max_cache_len=max_len)
         self.graph = None
-        self.launches_per_step = len(self.layers) * 7 + 1
+        self.launches_per_step = len(self.layers) * 5 + 1
 
     # ------------------------------------------------------------------ one token
     def _step_kernels(self):
@@ -159,15 +159,12 @@ class FusedLlamaDecoder:
         pos_ptr = self.pos.data_ptr()
         for spec, cache in zip(self.layers, self.cache.layers):
             spec["qkv"].gemv(cur, norm_weight=spec["ln1"], norm_eps=self.eps, pdl=self.pdl, out=self.qkv)
-            native.call("lq_rope_kv_write", self.qkv.data_ptr(), self.cos.data_ptr(), self.sin.data_ptr(),
-                        self.q_rot.data_ptr(), cache.k_codes.data_ptr(), cache.v_codes.data_ptr(),
-                        cache.k_scales.data_ptr(), cache.v_scales.data_ptr(), self.B, self.Hq,
-                        self.Hkv, self.D, cache.capacity, self.cos.shape[0], pos_ptr, 0,
-                        self.kv_bits, pdl, stream)
-            native.call("lq_attn_decode_kv_i8", self.q_rot.data_ptr(), cache.k_codes.data_ptr(),
-                        cache.v_codes.data_ptr(), cache.k_scales.data_ptr(), cache.v_scales.data_ptr(),
-                        self.attn.data_ptr(), self.scratch.data_ptr(), self.B, self.Hq, self.Hkv,
-                        self.D, cache.capacity, pos_ptr, 0, 1, self.scaling, self.splits, pdl, stream)
+            native.call("lq_attn_decode_fused", self.qkv.data_ptr(), self.cos.data_ptr(),
+                        self.sin.data_ptr(), cache.k_codes.data_ptr(), cache.v_codes.data_ptr(),
+                        cache.k_scales.data_ptr(), cache.v_scales.data_ptr(), self.attn.data_ptr(),
+                        self.scratch.data_ptr(), self.B, self.Hq, self.Hkv, self.D, cache.capacity,
+                        self.cos.shape[0], pos_ptr, 0, self.kv_bits, self.scaling, self.splits,
+                        pdl, stream)
             spec["o"].gemv(self.attn, residual=cur, pdl=self.pdl, out=nxt)
             spec["gate_up"].gemv(nxt, norm_weight=spec["ln2"], norm_eps=self.eps, epilogue=1,
                                  pdl=self.pdl, out=self.act)

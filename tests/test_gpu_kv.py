@@ -118,3 +118,56 @@ def test_rope_write_and_decode_attention(hd, hq, hkv):
                 vs.data_ptr(), out2.data_ptr(), scratch.data_ptr(), B, hq, hkv, hd, Tmax, 0, T, 0,
                 hd ** -0.5, 16, 0, native.stream_ptr())
     assert torch.equal(out, out2)
+
+
+@pytest.mark.parametrize("hd,hq,hkv", [(64, 8, 2), (128, 8, 2), (128, 8, 8)])
+@pytest.mark.parametrize("splits", [1, 7])
+def test_fused_attention_block_matches_the_separate_kernels(hd, hq, hkv, splits):
+    """lq_attn_decode_fused = lq_rope_kv_write + lq_attn_decode_kv_i8 in one launch: the cache
+    it leaves behind is bit-identical, its output agrees with the oracle, and its tickets are
+    back at zero so it can be replayed."""
+    B, T, Tmax = 2, (150 if splits > 1 else 520), 600
+    g = torch.Generator().manual_seed(7 * hd + hq + splits)
+    inv_freq = 1.0 / (500000.0 ** (np.arange(0, hd, 2, dtype=np.float32) / hd))
+    cos_np, sin_np = llama_ops.rope_tables(inv_freq, np.arange(Tmax))
+    cos = torch.from_numpy(cos_np).bfloat16().cuda()
+    sin = torch.from_numpy(sin_np).bfloat16().cuda()
+
+    def fresh():
+        kc = torch.zeros(B, hkv, Tmax, hd, dtype=torch.int8, device="cuda")
+        ks = torch.zeros(B, hkv, Tmax, 1, dtype=torch.float32, device="cuda")
+        return kc, torch.zeros_like(kc), ks, torch.zeros_like(ks)
+
+    ref, fus = fresh(), fresh()
+    pos = torch.zeros(1, dtype=torch.long, device="cuda")
+    q_rot = torch.zeros(B, hq, hd, dtype=torch.bfloat16, device="cuda")
+    out_ref = torch.zeros(B, hq, hd, dtype=torch.bfloat16, device="cuda")
+    out_fus = torch.zeros_like(out_ref)
+    lib = native.library()
+    scratch_ref = torch.zeros(lib.lq_attn_decode_scratch_bytes(B, hq, hd, splits) // 4, device="cuda")
+    nbytes = lib.lq_attn_fused_scratch_bytes(B, hq, hkv, hd, splits)
+    scratch_fus = torch.zeros(-(-nbytes // 4), dtype=torch.float32, device="cuda")
+    rows = torch.randn(T, B, (hq + 2 * hkv) * hd, generator=g).bfloat16().cuda()
+    stream = native.stream_ptr()
+    for t in range(T):
+        row = rows[t]
+        kc, vc, ks, vs = ref
+        native.call("lq_rope_kv_write", row.data_ptr(), cos.data_ptr(), sin.data_ptr(), q_rot.data_ptr(),
+                    kc.data_ptr(), vc.data_ptr(), ks.data_ptr(), vs.data_ptr(), B, hq, hkv, hd, Tmax,
+                    Tmax, pos.data_ptr(), 0, 8, 0, stream)
+        native.call("lq_attn_decode_kv_i8", q_rot.data_ptr(), kc.data_ptr(), vc.data_ptr(), ks.data_ptr(),
+                    vs.data_ptr(), out_ref.data_ptr(), scratch_ref.data_ptr(), B, hq, hkv, hd, Tmax,
+                    pos.data_ptr(), 0, 1, hd ** -0.5, splits, 0, stream)
+        kc, vc, ks, vs = fus
+        native.call("lq_attn_decode_fused", row.data_ptr(), cos.data_ptr(), sin.data_ptr(), kc.data_ptr(),
+                    vc.data_ptr(), ks.data_ptr(), vs.data_ptr(), out_fus.data_ptr(), scratch_fus.data_ptr(),
+                    B, hq, hkv, hd, Tmax, Tmax, pos.data_ptr(), 0, 8, hd ** -0.5, splits, 0, stream)
+        pos.add_(1)
+        if t in (0, 1, 17, T - 1):
+            err = rel_l2(out_fus.float().cpu().numpy(), out_ref.float().cpu().numpy())
+            assert err <= 1e-2, (t, err)
+    for a, b in zip(ref, fus):
+        assert torch.equal(a, b)
+    tickets = scratch_fus.view(torch.int32)[-(B * hkv):]
+    assert int(tickets.abs().sum()) == 0
+    assert lib.lq_attn_device_error() == 0

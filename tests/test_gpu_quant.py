@@ -32,7 +32,8 @@ def test_fake_quant_matches_golden_bit_exactly(golden, fq):
         got, scale = fq(x, _args(case["bits"], case["group"]), return_scale=True)
         assert got.dtype == x.dtype and got.shape == x.shape
         assert np.array_equal(bits_of(got).view(np.uint8), blob[key + "_y"].view(np.uint8)), key
-        assert np.array_equal(bits_of(scale).view(np.uint32), blob[key + "_s"].view(np.uint32)), key
+        assert np.array_equal(bits_of(scale).view(np.uint32).reshape(-1),
+                              blob[key + "_s"].view(np.uint32).reshape(-1)), key
 
 
 @pytest.mark.parametrize("bits", [4, 8])
