@@ -188,6 +188,23 @@ int lq_attn_decode_fused(const void* qkv, const void* cos_table, const void* sin
                          int table_len, const int64_t* pos_dev, int64_t pos, int num_bits,
                          float scaling, int splits, int pdl, void* stream);
 
+/* lq_attn_decode_kv_i8 for callers that cannot provide scratch memory -- a plugin inside a
+ * process whose device memory belongs to someone else's allocator, or a host that is not
+ * allowed to call cudaMalloc. The partial results of the slices go to a fixed 4 MiB array that
+ * is part of the library image (lq_attn_decode_static_scratch_bytes; every GPU that loads
+ * the library holds it until the process exits); a call whose B * Hq * splits * (D + 2) * 4
+ * bytes exceed it is rejected with LQ_ERR_UNSUPPORTED. Nothing is allocated or freed. The
+ * first call on each device resolves the array's device address; make that call outside
+ * any stream capture. Nothing in the array has to start at zero (every slot a call reads it
+ * has written first), but all calls share it: two calls that overlap on the GPU (different
+ * streams, or graph branches) race -- serialize them. This entry point has no counterpart
+ * in the reference. */
+int64_t lq_attn_decode_static_scratch_bytes(void);
+int lq_attn_decode_kv_i8_static(const void* q, const int8_t* k_codes, const int8_t* v_codes,
+                                const float* k_scales, const float* v_scales, void* out, int B,
+                                int Hq, int Hkv, int D, int Tmax, const int64_t* len_dev, int64_t len,
+                                int len_add, float scaling, int splits, int pdl, void* stream);
+
 /* The same GEMV with the work of the neighbouring decoder-layer ops folded in. All fields
  * of lq_wq_gemv_stream, plus:
  *   norm_weight / norm_eps  bf16 [K] or NULL: RMSNorm applied to x inside the kernel

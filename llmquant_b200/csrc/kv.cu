@@ -467,6 +467,68 @@ extern "C" int lq_attn_decode_kv_i8(const void* q, const int8_t* k_codes, const 
                     (__nv_bfloat16*)out, Hq, D, splits);
 }
 
+// ---------------------------------------------------------------- decode attention without a caller-provided scratch
+// Some hosts of this library cannot hand it a scratch buffer: a plugin loaded into a
+// process whose device memory is owned by another allocator (an inference server that
+// pre-allocates the whole GPU, a sandboxed extension that is forbidden to call cudaMalloc),
+// or a caller that only ever sees the tensors of the model itself. For them the slices'
+// partial results live in a fixed array inside the library image. Every GPU that loads the
+// library carries this array until the process exits.
+namespace lq {
+namespace {
+
+constexpr size_t kStaticScratchBytes = 4u << 20;  // 4 MiB: e.g. B=8, Hq=32, D=128, 31 slices
+static __device__ __align__(256) unsigned char g_static_attn_scratch[kStaticScratchBytes];
+
+constexpr int kMaxDevices = 64;
+
+// Device address of the array on the current device, resolved once per device. The symbol
+// name is only a host-side handle; the address a kernel can use comes from the runtime.
+int static_scratch_address(void** out) {
+  static void* cached[kMaxDevices] = {nullptr};
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return fail(LQ_ERR_LAUNCH, "cudaGetDevice: %s", cudaGetErrorString(e));
+  if (dev < 0 || dev >= kMaxDevices) return fail(LQ_ERR_UNSUPPORTED, "device index %d out of range", dev);
+  void* ptr = __atomic_load_n(&cached[dev], __ATOMIC_ACQUIRE);
+  if (ptr == nullptr) {
+    e = cudaGetSymbolAddress(&ptr, g_static_attn_scratch);
+    if (e != cudaSuccess || ptr == nullptr) {
+      cudaGetLastError();
+      return fail(LQ_ERR_LAUNCH, "cannot resolve the built-in scratch array: %s", cudaGetErrorString(e));
+    }
+    __atomic_store_n(&cached[dev], ptr, __ATOMIC_RELEASE);
+  }
+  *out = ptr;
+  return LQ_OK;
+}
+
+}  // namespace
+}  // namespace lq
+
+extern "C" int64_t lq_attn_decode_static_scratch_bytes(void) {
+  return (int64_t)lq::kStaticScratchBytes;
+}
+
+extern "C" int lq_attn_decode_kv_i8_static(const void* q, const int8_t* k_codes, const int8_t* v_codes,
+                                           const float* k_scales, const float* v_scales, void* out,
+                                           int B, int Hq, int Hkv, int D, int Tmax,
+                                           const int64_t* len_dev, int64_t len, int len_add,
+                                           float scaling, int splits, int pdl, void* stream) {
+  using namespace lq;
+  LQ_REQUIRE(B > 0 && Hq > 0 && D > 0 && splits >= 1, LQ_ERR_ARG, "bad shape");
+  const int64_t need = lq_attn_decode_scratch_bytes(B, Hq, D, splits);
+  LQ_REQUIRE(need <= (int64_t)kStaticScratchBytes, LQ_ERR_UNSUPPORTED,
+             "this call needs %lld bytes of scratch but the built-in array holds %lld; use fewer "
+             "slices or lq_attn_decode_kv_i8 with your own buffer",
+             (long long)need, (long long)kStaticScratchBytes);
+  void* scratch = nullptr;
+  const int rc = static_scratch_address(&scratch);
+  if (rc) return rc;
+  return lq_attn_decode_kv_i8(q, k_codes, v_codes, k_scales, v_scales, out, scratch, B, Hq, Hkv, D,
+                              Tmax, len_dev, len, len_add, scaling, splits, pdl, stream);
+}
+
 // ---------------------------------------------------------------- one kernel per layer: RoPE + KV write + attention + merge
 // The decode step's attention block as a single launch. grid (NS, Hkv, B), 128 threads.
 // Every CTA rotates the G query heads of its KV head itself (a few hundred multiply-adds)
