@@ -71,6 +71,11 @@ int lq_unpack_int4(const uint8_t* packed, int8_t* codes, int64_t n_codes, void* 
 int lq_dequant_weight(const int8_t* canonical, const float* wscale, void* out, int dtype,
                       int N, int groups, int group_size, int out_group, void* stream);
 
+/* out[i] = bf16(bf16(sum[i]) + residual[i]) over n elements (residual bf16 or NULL): the
+ * residual add after a row-parallel linear whose fp32 partial outputs were summed over the
+ * ranks. Tensor parallelism is not in the reference; on one GPU the GEMV epilogue does this. */
+int lq_residual_add(const float* sum, const void* residual, void* out, int64_t n, int pdl, void* stream);
+
 /* ---------------------------------------------------------------- decode GEMV */
 
 /* Drop-in for wq_gemv (llmquant/cuda/csrc/wq_gemv.cu:134-185, bound at fake_quant.cpp:30-37):

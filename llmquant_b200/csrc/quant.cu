@@ -240,8 +240,45 @@ __global__ void dequant_weight_kernel(const int8_t* __restrict__ canonical,
   }
 }
 
+// out = bf16(bf16(sum) + residual): the residual add that follows a row-parallel linear whose
+// partial sums were all-reduced in fp32 (same roundings as the single-GPU GEMV epilogue).
+__global__ void residual_add_kernel(const float* __restrict__ sum, const __nv_bfloat16* __restrict__ residual,
+                                    __nv_bfloat16* __restrict__ out, int64_t n) {
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) {
+    const float y = __bfloat162float(__float2bfloat16_rn(sum[i]));
+    out[i] = __float2bfloat16_rn(residual != nullptr ? y + __bfloat162float(residual[i]) : y);
+  }
+}
+
 }  // namespace
 }  // namespace lq
+
+extern "C" int lq_residual_add(const float* sum, const void* residual, void* out, int64_t n, int pdl,
+                               void* stream) {
+  using namespace lq;
+  LQ_REQUIRE(n >= 0, LQ_ERR_ARG, "negative length");
+  if (n == 0) return LQ_OK;
+  LQ_REQUIRE(sum && out, LQ_ERR_ARG, "null tensor pointer");
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)((n + 255) / 256));
+  cfg.blockDim = dim3(256);
+  cfg.stream = (cudaStream_t)stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl ? 1 : 0;
+  cudaError_t e = cudaLaunchKernelEx(&cfg, residual_add_kernel, sum, (const __nv_bfloat16*)residual,
+                                     (__nv_bfloat16*)out, n);
+  if (e != cudaSuccess) {
+    cudaGetLastError();
+    return fail(LQ_ERR_LAUNCH, "lq_residual_add: %s", cudaGetErrorString(e));
+  }
+  return LQ_OK;
+}
 
 extern "C" int lq_fake_quant_group(const void* x, void* out, float* scale_out, int64_t groups,
                                    int group_size, int num_bits, int dtype, void* stream) {

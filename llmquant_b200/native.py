@@ -29,6 +29,7 @@ _SIGNATURES = {
     "lq_fake_quant_group": [_P, _P, _P, _L, _I, _I, _I, _P],
     "lq_quantize_group_i8": [_P, _P, _P, _L, _I, _I, _I, _P],
     "lq_quantize_weight": [_P, _I, _I, _I, _I, _I, _I, _I, _P, _P, _P],
+    "lq_residual_add": [_P, _P, _P, _L, _I, _P],
     "lq_pack_int4": [_P, _P, _L, _P],
     "lq_unpack_int4": [_P, _P, _L, _P],
     "lq_dequant_weight": [_P, _P, _P, _I, _I, _I, _I, _I, _P],

@@ -62,6 +62,11 @@ def _fuse_rows(modules, interleave=False):
                              first.in_features)
 
 
+def _unwrap(module):
+    """The KernelQuantLinear inside a tensor-parallel wrapper (or the module itself)."""
+    return getattr(module, "inner", module)
+
+
 def supports(model) -> bool:
     """Whether `model` is a Llama-layout decoder fully on kernel-mode linears."""
     try:
@@ -76,8 +81,8 @@ def supports(model) -> bool:
         attn, mlp = getattr(layer, "self_attn", None), getattr(layer, "mlp", None)
         if attn is None or mlp is None:
             return False
-        mods = [getattr(attn, n, None) for n in names]
-        mods += [getattr(mlp, n, None) for n in ("gate_proj", "up_proj", "down_proj")]
+        mods = [_unwrap(getattr(attn, n, None)) for n in names]
+        mods += [_unwrap(getattr(mlp, n, None)) for n in ("gate_proj", "up_proj", "down_proj")]
         if not all(isinstance(m, KernelQuantLinear) and m._stream for m in mods):
             return False
     head_dim = getattr(cfg, "head_dim", None) or cfg.hidden_size // cfg.num_attention_heads
@@ -89,7 +94,7 @@ class FusedLlamaDecoder:
     """Greedy decode of a kernel-mode Llama: eager prefill, then one replayed graph per token."""
 
     def __init__(self, model, max_batch: int, max_len: int, kv_bits: int = 8, use_graph: bool = True,
-                 pdl: bool = True):
+                 pdl: bool = True, tp=None):
         if not supports(model):
             raise ValueError("FusedLlamaDecoder needs a Llama-layout model whose attention and MLP "
                              "linears are KernelQuantLinear (head_dim 64/128, silu MLP)")
@@ -101,7 +106,10 @@ class FusedLlamaDecoder:
         self.B, self.max_len, self.kv_bits = max_batch, max_len, kv_bits
         self.use_graph, self.pdl = use_graph, pdl
         self.hidden = cfg.hidden_size
-        self.Hq, self.Hkv = cfg.num_attention_heads, cfg.num_key_value_heads
+        self.tp = tp if tp is not None and tp.world > 1 else None
+        world = self.tp.world if self.tp else 1
+        # under tensor parallelism every rank owns Hq/world query heads and Hkv/world KV heads
+        self.Hq, self.Hkv = cfg.num_attention_heads // world, cfg.num_key_value_heads // world
         self.D = getattr(cfg, "head_dim", None) or cfg.hidden_size // cfg.num_attention_heads
         self.eps = cfg.rms_norm_eps
         self.scaling = self.D ** -0.5
@@ -113,14 +121,14 @@ class FusedLlamaDecoder:
             attn, mlp = layer.self_attn, layer.mlp
             self.layers.append({
                 "qkv": _fuse_rows([attn.q_proj, attn.k_proj, attn.v_proj]),
-                "o": attn.o_proj,
+                "o": _unwrap(attn.o_proj),
                 "gate_up": _fuse_rows([mlp.gate_proj, mlp.up_proj], interleave=True),
-                "down": mlp.down_proj,
+                "down": _unwrap(mlp.down_proj),
                 "ln1": layer.input_layernorm.weight.detach().to(bf16).contiguous(),
                 "ln2": layer.post_attention_layernorm.weight.detach().to(bf16).contiguous(),
             })
         self.final_norm = model.model.norm.weight.detach().to(bf16).contiguous()
-        self.lm_head = model.lm_head
+        self.lm_head = _unwrap(model.lm_head)
         self.embed = model.model.embed_tokens.weight
 
         # rotary tables from the model's own module, so scaling variants come along
@@ -139,6 +147,9 @@ class FusedLlamaDecoder:
         self.attn = torch.zeros(B, self.Hq * self.D, dtype=bf16, device=dev)
         self.act = torch.zeros(B, inter, dtype=bf16, device=dev)
         self.logits = torch.zeros(B, self.vocab, dtype=bf16, device=dev)
+        if self.tp:
+            self.partial = torch.zeros(B, H, dtype=torch.float32, device=dev)
+            self.local_logits = torch.zeros(B, self.vocab // world, dtype=bf16, device=dev)
         self.tokens = torch.zeros(B, dtype=torch.long, device=dev)
         self.pos = torch.zeros(1, dtype=torch.long, device=dev)
         self.history = torch.zeros(B, max_len + 1, dtype=torch.long, device=dev)
@@ -148,7 +159,7 @@ class FusedLlamaDecoder:
         self.scratch = torch.zeros(-(-nbytes // 4), dtype=torch.float32, device=dev)
         self.cache = KernelQuantCache(kv_bits, max_cache_len=max_len)
         self.graph = None
-        self.launches_per_step = len(self.layers) * 5 + 1
+        self.launches_per_step = len(self.layers) * (7 if self.tp else 5) + 1
 
     # ------------------------------------------------------------------ one token
     def _step_kernels(self):
@@ -165,19 +176,33 @@ class FusedLlamaDecoder:
                         self.scratch.data_ptr(), self.B, self.Hq, self.Hkv, self.D, cache.capacity,
                         self.cos.shape[0], pos_ptr, 0, self.kv_bits, self.scaling, self.splits,
                         pdl, stream)
-            spec["o"].gemv(self.attn, residual=cur, pdl=self.pdl, out=nxt)
+            self._row_parallel(spec["o"], self.attn, cur, nxt)
             spec["gate_up"].gemv(nxt, norm_weight=spec["ln2"], norm_eps=self.eps, epilogue=1,
                                  pdl=self.pdl, out=self.act)
-            spec["down"].gemv(self.act, residual=nxt, pdl=self.pdl, out=cur)
+            self._row_parallel(spec["down"], self.act, nxt, cur)
         if isinstance(self.lm_head, KernelQuantLinear) and self.lm_head._stream:
+            head_out = self.local_logits if self.tp else self.logits
             self.lm_head.gemv(cur, norm_weight=self.final_norm, norm_eps=self.eps, pdl=self.pdl,
-                              out=self.logits)
+                              out=head_out)
+            if self.tp:
+                self.tp.all_gather_last_dim(self.logits, self.local_logits)
         else:
             with torch.no_grad():
                 self.logits.copy_(self.lm_head(self.model.model.norm(cur)))
         torch.argmax(self.logits, dim=-1, out=self.tokens)
         self.pos.add_(1)
         self.history.index_copy_(1, self.pos, self.tokens.unsqueeze(1))
+
+    def _row_parallel(self, linear, x, residual, out):
+        """out = residual + linear(x). One GPU: fused in the GEMV epilogue. Tensor parallel:
+        fp32 partial, all-reduce over the ranks, then the same rounding and residual add."""
+        if not self.tp:
+            linear.gemv(x, residual=residual, pdl=self.pdl, out=out)
+            return
+        linear.gemv(x, out_dtype=torch.float32, pdl=self.pdl, out=self.partial)
+        self.tp.all_reduce(self.partial)
+        native.call("lq_residual_add", self.partial.data_ptr(), residual.data_ptr(), out.data_ptr(),
+                    out.numel(), 1 if self.pdl else 0, native.stream_ptr(self.device))
 
     # ------------------------------------------------------------------ prefill / capture
     @torch.no_grad()

@@ -1,0 +1,143 @@
+"""Tensor-parallel decode over the GPUs of one node.
+
+The reference is single-GPU. Sharding follows the usual column-then-row split of a Llama
+layer, cut so that quantization is unaffected (scales are per output row and per 128-wide
+group of the reduction axis, so any cut on row or group boundaries leaves every code and
+scale exactly what the unsharded weight would get):
+
+  column-parallel (rows):      q_proj, k_proj, v_proj by heads; gate_proj, up_proj; lm_head
+  row-parallel (reduction K):  o_proj by heads, down_proj by groups of 128 -> all-reduce (sum)
+                               of the [batch, hidden] partial outputs, two per layer
+
+The KV cache and the attention are sharded by KV head with no exchange. One process per GPU;
+`torch.distributed` (NCCL over NVLink) carries the all-reduce and the logits all-gather, both
+of which are captured into the decode graph.
+"""
+
+import re
+from dataclasses import dataclass
+
+import torch
+import torch.nn as nn
+
+ROW_SPLIT = re.compile(r".*\.(self_attn\.(q|k|v)_proj|mlp\.(gate|up)_proj)$|^lm_head$")
+K_SPLIT = re.compile(r".*\.(self_attn\.o_proj|mlp\.down_proj)$")
+
+
+@dataclass
+class TPContext:
+    rank: int
+    world: int
+    group: object = None  # torch.distributed process group (None = the default group)
+
+    def all_reduce(self, tensor):
+        import torch.distributed as dist
+        dist.all_reduce(tensor, group=self.group)
+        return tensor
+
+    def all_gather_last_dim(self, out, shard):
+        """out [B, world * n] <- concatenation over ranks of shard [B, n]."""
+        import torch.distributed as dist
+        rows, n = shard.shape
+        gathered = torch.empty(self.world * rows, n, dtype=shard.dtype, device=shard.device)
+        dist.all_gather_into_tensor(gathered, shard.contiguous(), group=self.group)
+        out.view(rows, self.world, n).copy_(gathered.view(self.world, rows, n).permute(1, 0, 2))
+        return out
+
+
+def check_divisible(config, world: int, group_size: int = 128):
+    heads, kv = config.num_attention_heads, config.num_key_value_heads
+    if heads % world or kv % world:
+        raise ValueError(f"tensor parallel degree {world} must divide {heads} query and {kv} KV heads")
+    if config.intermediate_size % (world * group_size):
+        raise ValueError(f"intermediate_size {config.intermediate_size} must be a multiple of "
+                         f"{world} x {group_size} so down_proj splits on group boundaries")
+    if config.vocab_size % (4 * world):
+        raise ValueError(f"vocab_size {config.vocab_size} must be a multiple of {4 * world}")
+    head_dim = getattr(config, "head_dim", None) or config.hidden_size // heads
+    if (heads // world) * head_dim % group_size and head_dim >= group_size:
+        raise ValueError("o_proj's reduction slice must fall on group boundaries")
+
+
+def shard_weight(name: str, weight: torch.Tensor, rank: int, world: int) -> torch.Tensor:
+    """This rank's slice of a Linear weight [out, in]; replicated tensors come back whole."""
+    if world == 1:
+        return weight
+    if ROW_SPLIT.match(name):
+        n = weight.shape[0]
+        if n % world:
+            raise ValueError(f"{name}: {n} rows do not divide by {world}")
+        step = n // world
+        return weight[rank * step:(rank + 1) * step].contiguous()
+    if K_SPLIT.match(name):
+        k = weight.shape[1]
+        if k % world:
+            raise ValueError(f"{name}: reduction width {k} does not divide by {world}")
+        step = k // world
+        return weight[:, rank * step:(rank + 1) * step].contiguous()
+    return weight
+
+
+class RowParallelOutput(nn.Module):
+    """Wraps a K-sharded linear for the module-by-module (prefill) path: the partial
+    products are summed over the ranks in fp32 and rounded once."""
+
+    def __init__(self, inner, ctx: TPContext):
+        super().__init__()
+        self.inner, self.ctx = inner, ctx
+
+    def forward(self, x):
+        if x.shape[:-1].numel() <= 8 and hasattr(self.inner, "gemv"):
+            flat = x.reshape(-1, x.shape[-1])
+            partial = self.inner.gemv(flat, out_dtype=torch.float32)
+        else:
+            partial = self.inner(x).float()
+        self.ctx.all_reduce(partial)
+        return partial.to(x.dtype).reshape(*x.shape[:-1], -1)
+
+
+class GatheredOutput(nn.Module):
+    """Wraps a row-sharded lm_head: every rank ends up with the full logits."""
+
+    def __init__(self, inner, ctx: TPContext):
+        super().__init__()
+        self.inner, self.ctx = inner, ctx
+
+    def forward(self, x):
+        local = self.inner(x)
+        flat = local.reshape(-1, local.shape[-1])
+        out = torch.empty(flat.shape[0], flat.shape[1] * self.ctx.world, dtype=flat.dtype, device=flat.device)
+        self.ctx.all_gather_last_dim(out, flat)
+        return out.reshape(*local.shape[:-1], -1)
+
+
+@torch.no_grad()
+def shard_linears_(model, ctx: TPContext):
+    """Slice every nn.Linear of a Llama in place (call BEFORE quantizing it)."""
+    check_divisible(model.config, ctx.world)
+    for name, module in model.named_modules():
+        if isinstance(module, nn.Linear):
+            cut = shard_weight(name, module.weight.data, ctx.rank, ctx.world)
+            if cut.shape != module.weight.shape:
+                module.weight = nn.Parameter(cut, requires_grad=False)
+                module.out_features, module.in_features = cut.shape
+                if module.bias is not None and ROW_SPLIT.match(name):
+                    step = module.bias.shape[0] // ctx.world
+                    module.bias = nn.Parameter(
+                        module.bias.data[ctx.rank * step:(ctx.rank + 1) * step].contiguous(),
+                        requires_grad=False)
+                elif module.bias is not None and ctx.rank != 0:
+                    module.bias = None  # a row-parallel bias is added once, by rank 0
+    return model
+
+
+def wrap_for_prefill_(model, ctx: TPContext):
+    """After quantization: make the module-by-module forward (prefill) tensor-parallel by
+    wrapping o_proj / down_proj with the all-reduce and lm_head with the all-gather."""
+    if ctx.world == 1:
+        return model
+    for layer in model.model.layers:
+        layer.self_attn.o_proj = RowParallelOutput(layer.self_attn.o_proj, ctx)
+        layer.mlp.down_proj = RowParallelOutput(layer.mlp.down_proj, ctx)
+    model.lm_head = GatheredOutput(model.lm_head, ctx)
+    return model
