@@ -367,6 +367,7 @@ def run_decode(args, rank, world, device):
     ctx = tpmod.TPContext(rank, world) if world > 1 else None
     if ctx:
         tpmod.check_divisible(config, world)
+        ctx.peer_allreduce = args.allreduce == "peer"
     # every rank draws the same full weights (same seed) and keeps its slice
     model = random_quantized_llama(
         config, quant, device, seed=0,
@@ -435,7 +436,7 @@ def run_decode(args, rank, world, device):
                    "batch": batch, "prompt_tokens": prompt, "context_at_timing": context,
                    "l2_policy": f"{step_bytes / 1e6:.0f} MB of weights and KV streamed per step, larger than L2",
                    "parallelism": (f"tp{world}: column-parallel q/k/v, gate/up, lm_head; row-parallel "
-                                   f"o_proj, down_proj with an NCCL all-reduce each") if world > 1 else "single"},
+                                   f"o_proj, down_proj, all-reduce = {dec.allreduce}") if world > 1 else "single"},
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peaks["hbm_gbs"],
                      "unit": "GB/s", "frac": round(achieved / peaks["hbm_gbs"], 4),
                      "frac_of_nominal_8TBs": round(achieved / 8000.0, 4), "peak_kind": peak_kind,
@@ -446,6 +447,9 @@ def run_decode(args, rank, world, device):
         "gpu_launches": dec.launches_per_step * args.steps,
         "clocks": clocks.summary(),
     }
+    if world > 1:
+        from llmquant_b200 import native
+        line["config"]["allreduce_timeouts"] = native.library().lq_allreduce_device_error()
     if rank == 0:
         line["cpu_baseline"] = cpu_decode_baseline(spec["shape"], reps=1)
         print(json.dumps(line), flush=True)
@@ -458,6 +462,7 @@ def cpu_decode_baseline(shape_name, reps=1):
     from llmquant_b200.runtime.random_init import SHAPES
     from oracle.real_mode import RealLinear
 
+    torch.set_num_threads(os.cpu_count() or 1)  # torchrun pins OMP_NUM_THREADS=1
     shp = SHAPES[shape_name]
     h, inter, d = shp["hidden_size"], shp["intermediate_size"], shp["head_dim"]
     nq, nkv = shp["num_attention_heads"] * d, shp["num_key_value_heads"] * d
@@ -574,6 +579,7 @@ def main():
     ap.add_argument("--variant", type=int, default=0)
     ap.add_argument("--batch", type=int, default=1)
     ap.add_argument("--prompt", type=int, default=0, help="prompt tokens (0 = the workload's own)")
+    ap.add_argument("--allreduce", default="peer", choices=["peer", "nccl"])
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
 

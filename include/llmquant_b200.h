@@ -76,6 +76,23 @@ int lq_dequant_weight(const int8_t* canonical, const float* wscale, void* out, i
  * ranks. Tensor parallelism is not in the reference; on one GPU the GEMV epilogue does this. */
 int lq_residual_add(const float* sum, const void* residual, void* out, int64_t n, int pdl, void* stream);
 
+/* ---------------------------------------------------------------- tensor-parallel all-reduce
+ * out = bf16(bf16(sum over ranks of partial_r) + residual) for n elements, as one small
+ * kernel per rank over peer-mapped memory (no collective library call). Every rank owns a
+ * buffer that all ranks have mapped: float data[2][slot_floats] followed, at
+ * flag_offset_bytes, by uint32 flags[2][lq_allreduce_max_world()]; it must be zero before the
+ * first call. peer_bases_dev is a device array of the `world` base addresses (index = rank).
+ * The caller's previous kernel wrote this rank's partial into data[slot] of its own buffer;
+ * consecutive calls must alternate slot 0 / 1. seq_counter_dev is a device uint32 (start 0)
+ * the kernel advances by one per call -- every rank must make the same sequence of calls.
+ * Waiting for the peers is bounded (~2 s); on expiry lq_allreduce_device_error() becomes 1.
+ * The reference is single-GPU: no counterpart. */
+int lq_allreduce_max_world(void);
+int lq_allreduce_device_error(void);
+int lq_allreduce_residual(const uint64_t* peer_bases_dev, int rank, int world, int slot,
+                          int64_t slot_floats, int64_t flag_offset_bytes, uint32_t* seq_counter_dev,
+                          const void* residual, void* out, int n, int pdl, void* stream);
+
 /* ---------------------------------------------------------------- decode GEMV */
 
 /* Drop-in for wq_gemv (llmquant/cuda/csrc/wq_gemv.cu:134-185, bound at fake_quant.cpp:30-37):

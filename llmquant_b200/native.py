@@ -30,6 +30,9 @@ _SIGNATURES = {
     "lq_quantize_group_i8": [_P, _P, _P, _L, _I, _I, _I, _P],
     "lq_quantize_weight": [_P, _I, _I, _I, _I, _I, _I, _I, _P, _P, _P],
     "lq_residual_add": [_P, _P, _P, _L, _I, _P],
+    "lq_allreduce_max_world": [],
+    "lq_allreduce_device_error": [],
+    "lq_allreduce_residual": [_P, _I, _I, _I, _L, _L, _P, _P, _P, _I, _I, _P],
     "lq_pack_int4": [_P, _P, _L, _P],
     "lq_unpack_int4": [_P, _P, _L, _P],
     "lq_dequant_weight": [_P, _P, _P, _I, _I, _I, _I, _I, _P],

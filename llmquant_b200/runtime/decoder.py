@@ -147,7 +147,14 @@ class FusedLlamaDecoder:
         self.attn = torch.zeros(B, self.Hq * self.D, dtype=bf16, device=dev)
         self.act = torch.zeros(B, inter, dtype=bf16, device=dev)
         self.logits = torch.zeros(B, self.vocab, dtype=bf16, device=dev)
+        self.peer = None
         if self.tp:
+            if getattr(self.tp, "peer_allreduce", True) and (B * H) % 4 == 0:
+                try:
+                    from llmquant_b200.runtime.tp import PeerAllReduce
+                    self.peer = PeerAllReduce(self.tp, B * H, dev)
+                except Exception as exc:  # no symmetric memory here: stay on NCCL
+                    self.peer_error = repr(exc)
             self.partial = torch.zeros(B, H, dtype=torch.float32, device=dev)
             self.local_logits = torch.zeros(B, self.vocab // world, dtype=bf16, device=dev)
         self.tokens = torch.zeros(B, dtype=torch.long, device=dev)
@@ -160,6 +167,7 @@ class FusedLlamaDecoder:
         self.cache = KernelQuantCache(kv_bits, max_cache_len=max_len)
         self.graph = None
         self.launches_per_step = len(self.layers) * (7 if self.tp else 5) + 1
+        self.allreduce = "none" if not self.tp else ("peer-memory one-shot kernel" if self.peer is not None else "nccl")
 
     # ------------------------------------------------------------------ one token
     def _step_kernels(self):
@@ -176,10 +184,10 @@ class FusedLlamaDecoder:
                         self.scratch.data_ptr(), self.B, self.Hq, self.Hkv, self.D, cache.capacity,
                         self.cos.shape[0], pos_ptr, 0, self.kv_bits, self.scaling, self.splits,
                         pdl, stream)
-            self._row_parallel(spec["o"], self.attn, cur, nxt)
+            self._row_parallel(spec["o"], self.attn, cur, nxt, 0)
             spec["gate_up"].gemv(nxt, norm_weight=spec["ln2"], norm_eps=self.eps, epilogue=1,
                                  pdl=self.pdl, out=self.act)
-            self._row_parallel(spec["down"], self.act, nxt, cur)
+            self._row_parallel(spec["down"], self.act, nxt, cur, 1)
         if isinstance(self.lm_head, KernelQuantLinear) and self.lm_head._stream:
             head_out = self.local_logits if self.tp else self.logits
             self.lm_head.gemv(cur, norm_weight=self.final_norm, norm_eps=self.eps, pdl=self.pdl,
@@ -193,11 +201,17 @@ class FusedLlamaDecoder:
         self.pos.add_(1)
         self.history.index_copy_(1, self.pos, self.tokens.unsqueeze(1))
 
-    def _row_parallel(self, linear, x, residual, out):
+    def _row_parallel(self, linear, x, residual, out, slot):
         """out = residual + linear(x). One GPU: fused in the GEMV epilogue. Tensor parallel:
-        fp32 partial, all-reduce over the ranks, then the same rounding and residual add."""
+        fp32 partial, summed over the ranks (one-shot kernel over peer memory, or NCCL),
+        then the same rounding and residual add."""
         if not self.tp:
             linear.gemv(x, residual=residual, pdl=self.pdl, out=out)
+            return
+        if self.peer is not None:
+            linear.gemv(x, out_dtype=torch.float32, pdl=self.pdl,
+                        out=self.peer.slot(slot, out.shape[0], out.shape[1]))
+            self.peer.reduce(slot, residual, out, self.pdl)
             return
         linear.gemv(x, out_dtype=torch.float32, pdl=self.pdl, out=self.partial)
         self.tp.all_reduce(self.partial)

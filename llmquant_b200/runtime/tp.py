@@ -29,6 +29,7 @@ class TPContext:
     rank: int
     world: int
     group: object = None  # torch.distributed process group (None = the default group)
+    peer_allreduce: bool = True  # try the one-shot kernel over peer memory before NCCL
 
     def all_reduce(self, tensor):
         import torch.distributed as dist
@@ -141,3 +142,50 @@ def wrap_for_prefill_(model, ctx: TPContext):
         layer.mlp.down_proj = RowParallelOutput(layer.mlp.down_proj, ctx)
     model.lm_head = GatheredOutput(model.lm_head, ctx)
     return model
+
+
+class PeerAllReduce:
+    """The fused all-reduce + residual add over NVLink peer memory (`lq_allreduce_residual`).
+
+    Each rank allocates one symmetric buffer (two fp32 slots of `max_floats` plus the flag
+    arrays), all ranks map each other's buffers, and the row-parallel GEMV writes its partial
+    straight into the rank's own slot. Raises if symmetric memory cannot be set up; the caller
+    then stays on the NCCL path."""
+
+    def __init__(self, ctx: TPContext, max_floats: int, device):
+        import torch.distributed as dist
+        import torch.distributed._symmetric_memory as symm
+
+        from llmquant_b200 import native
+
+        lib = native.library()
+        self.ctx = ctx
+        self.slot_floats = -(-max_floats // 4) * 4
+        self.flag_off = -(-(2 * self.slot_floats * 4) // 16) * 16
+        total = self.flag_off + 2 * lib.lq_allreduce_max_world() * 4
+        self.buffer = symm.empty(total // 4, dtype=torch.float32, device=device)
+        self.buffer.zero_()
+        group = ctx.group if ctx.group is not None else dist.group.WORLD
+        self.handle = symm.rendezvous(self.buffer, group)
+        ptrs = [int(p) for p in self.handle.buffer_ptrs]
+        if len(ptrs) != ctx.world:
+            raise RuntimeError("symmetric memory rendezvous returned the wrong number of peers")
+        self.peers = torch.tensor(ptrs, dtype=torch.int64, device=device)
+        self.seq = torch.zeros(1, dtype=torch.int32, device=device)
+        torch.cuda.synchronize(device)
+        dist.barrier(group=ctx.group)  # every buffer is zeroed before anyone signals
+
+    def slot(self, index: int, rows: int, width: int) -> torch.Tensor:
+        """fp32 view [rows, width] of this rank's slot `index` (the GEMV's output buffer)."""
+        if rows * width > self.slot_floats:
+            raise ValueError("partial output larger than the all-reduce slot")
+        start = index * self.slot_floats
+        return self.buffer[start:start + rows * width].view(rows, width)
+
+    def reduce(self, index: int, residual, out, pdl: bool = True):
+        from llmquant_b200 import native
+
+        native.call("lq_allreduce_residual", self.peers.data_ptr(), self.ctx.rank, self.ctx.world,
+                    index, self.slot_floats, self.flag_off, self.seq.data_ptr(),
+                    native.ptr(residual), out.data_ptr(), out.numel(), 1 if pdl else 0,
+                    native.stream_ptr(out.device))
