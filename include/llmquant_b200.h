@@ -227,6 +227,21 @@ int lq_attn_decode_kv_i8_static(const void* q, const int8_t* k_codes, const int8
                                 int Hq, int Hkv, int D, int Tmax, const int64_t* len_dev, int64_t len,
                                 int len_add, float scaling, int splits, int pdl, void* stream);
 
+/* ---------------------------------------------------------------- prefill GEMM (tcgen05 / TMEM)
+ * out[m, n] = sum_g s_w[n, g] * s_x[m, g] * sum_{k in g} a[m, k] * q[n, k] on the streaming
+ * layout, any M (tiles of 128 tokens x 128 features), out [M, N] bf16, bias bf16 or NULL.
+ *   A16: x [M, K] bf16 (x_codes = NULL, s_x = 1): kind::f16 MMA on bf16(code), fp32 accumulate.
+ *   A8:  x_codes [M, Kd] int8 + x_scales [M, G] fp32 as lq_quantize_group_i8 produces them
+ *        (dynamic, per token per group): kind::i8 MMA, int32 accumulate -- the arithmetic of
+ *        RealQuantLinear.forward with an int8 activation scheme (quantizers/real.py:88-99).
+ * span must be 64 or 128. Replaces the dequantize-then-cuBLAS branch of
+ * KernelQuantLinear.forward (quantizers/kernel.py:68-79,90-91). lq_gemm_device_error is
+ * non-zero if a bounded wait for the tensor core ever expired (reads and clears). */
+int lq_gemm_device_error(void);
+int lq_wq_gemm_prefill(const void* x, int ldx, const int8_t* x_codes, const float* x_scales,
+                       const void* codes, const float* scale_tiles, const void* bias, void* out,
+                       int M, int N, int K, int Kd, int span, int bits, void* stream);
+
 /* The same GEMV with the work of the neighbouring decoder-layer ops folded in. All fields
  * of lq_wq_gemv_stream, plus:
  *   norm_weight / norm_eps  bf16 [K] or NULL: RMSNorm applied to x inside the kernel

@@ -1,0 +1,324 @@
+// Prefill GEMM (more than 8 activation rows) on the 5th-generation tensor cores:
+// tcgen05.mma with the accumulator in tensor memory (TMEM), operands staged in shared memory
+// in the canonical K-major core-matrix layout, dequantization of the weight codes done by the
+// CTA's threads on the way into shared memory (the integer codes are exactly representable in
+// bf16 / int8, so the tensor core multiplies exact integers), and the per-group scale applied
+// in the epilogue that drains TMEM:
+//
+//     out[m, n] = sum_g s_w[n, g] * (s_x[m, g]) * sum_{k in g} a[m, k] * q[n, k]
+//
+// which is the order of operations of the reference's real mode (quantizers/real.py:93-99):
+// one exact product sum per 128-wide group, scaled, accumulated in fp32 across groups. Two
+// operand modes: A16 (bf16 activations x codes widened to bf16, kind::f16, fp32 accumulate)
+// and A8 (activations quantized per token per group to int8 codes, kind::i8, int32
+// accumulate, both scales in the epilogue).
+//
+// Tile: 128 tokens x 128 output features per CTA, one scale group (span = 64 or 128 K
+// elements) per round: fill A and B tiles, one thread issues span/16 (bf16) or span/32 (int8)
+// MMAs and commits them to an mbarrier, all four warps drain the 128x128 accumulator
+// (tcgen05.ld, one TMEM lane = one token row per thread), scale, and add into registers.
+// Every wait is bounded; on expiry the kernel records an error word, frees its TMEM and
+// returns. This first version does not overlap the fill of the next group with the MMAs of the
+// current one.
+//
+// The reference dequantizes the whole weight to bf16 and calls cuBLAS above its row threshold
+// (quantizers/kernel.py:68-79,90-91); its own fused tensor-core prototype was rejected at
+// 0.34x cuBLAS.
+#include "common.cuh"
+
+namespace lq {
+namespace {
+
+constexpr int BM = 128, BN = 128, kThreads = 128;
+constexpr int kTmemCols = 128;
+
+__device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+  // K-major, no swizzle: 8-row x 16-byte core matrices; LBO = step between core matrices along
+  // K, SBO = step between 8-row groups; descriptor version 1 (sm_100).
+  uint64_t d = 0;
+  d |= (uint64_t)((addr & 0x3FFFFu) >> 4);
+  d |= (uint64_t)(lbo_bytes >> 4) << 16;
+  d |= (uint64_t)(sbo_bytes >> 4) << 32;
+  d |= (uint64_t)1 << 46;
+  return d;
+}
+
+// instruction descriptor: D format, A/B formats, K-major both, N/8 and M/16
+constexpr uint32_t idesc(uint32_t c_fmt, uint32_t ab_fmt) {
+  return (c_fmt << 4) | (ab_fmt << 7) | (ab_fmt << 10) | ((uint32_t)(BN >> 3) << 17) |
+         ((uint32_t)(BM >> 4) << 24);
+}
+
+__device__ __forceinline__ void mma_f16(uint32_t d_tmem, uint64_t a, uint64_t b, uint32_t id, uint32_t acc) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "l"(a), "l"(b), "r"(id), "r"(acc) : "memory");
+}
+__device__ __forceinline__ void mma_i8(uint32_t d_tmem, uint64_t a, uint64_t b, uint32_t id, uint32_t acc) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "l"(a), "l"(b), "r"(id), "r"(acc) : "memory");
+}
+__device__ __forceinline__ void mma_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar)
+               : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&v)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
+      "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+      : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
+        "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]),
+        "=r"(v[15]), "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]),
+        "=r"(v[22]), "=r"(v[23]), "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]),
+        "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+      : "r"(taddr)
+      : "memory");
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+struct GemmParams {
+  const __nv_bfloat16* x;   // [M, K] (A16) -- unused for A8
+  int ldx;
+  const int8_t* x_codes;    // [M, Kd] int8 (A8) or null
+  const float* x_scales;    // [M, G] (A8)
+  const uint8_t* codes;     // streaming layout
+  const float* scale_tiles; // [NP/4, G, 4]
+  const __nv_bfloat16* bias;
+  __nv_bfloat16* out;       // [M, N]
+  int M, N, K, Kd, span, groups, rowbytes;
+  int* error_word;
+};
+
+// ES = bytes per operand element (2: bf16 operands, 1: int8 operands)
+template <int BITS, int ES>
+__global__ void __launch_bounds__(kThreads)
+prefill_gemm_kernel(const GemmParams p) {
+  extern __shared__ __align__(128) uint8_t smem[];
+  __shared__ __align__(8) uint64_t mma_bar;
+  __shared__ uint32_t tmem_base_s;
+  __shared__ float ws_s[BN];
+  __shared__ int dead_s;
+
+  const int tid = threadIdx.x, warp = tid >> 5;
+  const int n0 = blockIdx.x * BN, m0 = blockIdx.y * BM;
+  const int KT = p.span;                        // K elements per round (one scale group)
+  constexpr int CORE_K = 16 / ES;               // K elements per core-matrix row
+  const int cores_k = KT / CORE_K;              // core matrices along K
+  const uint32_t lbo = 128, sbo = (uint32_t)cores_k * 128;
+  const int tile_bytes = BM * KT * ES;          // A tile; the B tile has the same size
+  uint8_t* a_tile = smem;
+  uint8_t* b_tile = smem + tile_bytes;
+  const uint32_t a_addr = smem_u32(a_tile), b_addr = smem_u32(b_tile);
+  const uint32_t bar = smem_u32(&mma_bar);
+
+  if (warp == 0) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                 ::"r"(smem_u32(&tmem_base_s)), "r"(kTmemCols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  if (tid == 0) {
+    mbar_init(bar, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    dead_s = 0;
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem_base = tmem_base_s;
+
+  float acc[BN];
+#pragma unroll
+  for (int c = 0; c < BN; ++c) acc[c] = 0.f;
+  const int my_m = m0 + tid;  // this thread's token row (TMEM lane tid)
+
+  constexpr uint32_t kIdesc = ES == 2 ? idesc(1, 1) : idesc(2, 1);  // f32 <- bf16 x bf16 ; s32 <- s8 x s8
+  const int pieces = BM * cores_k;  // 16-byte core-matrix rows per tile
+  uint32_t phase = 0;
+
+  for (int g = 0; g < p.groups; ++g) {
+    const int kbase = g * KT;
+    // ---- A tile: activations of this group, row r / K chunk kc -> core matrix (r/8, kc)
+    for (int idx = tid; idx < pieces; idx += kThreads) {
+      const int r = idx / cores_k, kc = idx % cores_k;
+      uint4 v = make_uint4(0, 0, 0, 0);
+      const int m = m0 + r;
+      if (m < p.M) {
+        if (ES == 2) {
+          const int k = kbase + kc * CORE_K;
+          const __nv_bfloat16* src = p.x + (int64_t)m * p.ldx + k;
+          if (k + CORE_K <= p.K && ((reinterpret_cast<uintptr_t>(src) & 15) == 0)) {
+            v = __ldg(reinterpret_cast<const uint4*>(src));
+          } else {
+            __nv_bfloat16 t[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) t[j] = k + j < p.K ? src[j] : __float2bfloat16_rn(0.f);
+            v = *reinterpret_cast<uint4*>(t);
+          }
+        } else {
+          v = __ldg(reinterpret_cast<const uint4*>(p.x_codes + (int64_t)m * p.Kd + kbase + kc * CORE_K));
+        }
+      }
+      *reinterpret_cast<uint4*>(a_tile + (r >> 3) * sbo + kc * lbo + (r & 7) * 16) = v;
+    }
+    // ---- B tile: weight codes of rows n0.. widened to the operand type (exact)
+    for (int idx = tid; idx < pieces; idx += kThreads) {
+      const int r = idx / cores_k, kc = idx % cores_k;
+      const int n = n0 + r;
+      uint4 v = make_uint4(0, 0, 0, 0);
+      if (n < p.N) {
+        const int k = kbase + kc * CORE_K;  // stored-K index
+        int8_t c[16];
+        if (BITS == 8) {
+          const uint8_t* src = p.codes + (int64_t)n * p.rowbytes + k;
+          if (CORE_K == 8) *reinterpret_cast<uint2*>(c) = __ldg(reinterpret_cast<const uint2*>(src));
+          else *reinterpret_cast<uint4*>(c) = __ldg(reinterpret_cast<const uint4*>(src));
+        } else {
+          const uint8_t* src = p.codes + (int64_t)n * p.rowbytes + (k >> 1);
+          uint8_t b[8];
+          if (CORE_K == 8) *reinterpret_cast<uint32_t*>(b) = __ldg(reinterpret_cast<const uint32_t*>(src));
+          else *reinterpret_cast<uint2*>(b) = __ldg(reinterpret_cast<const uint2*>(src));
+#pragma unroll
+          for (int j = 0; j < CORE_K / 2; ++j) {
+            c[2 * j] = (int8_t)((int)(b[j] & 0xF) - 8);
+            c[2 * j + 1] = (int8_t)((int)(b[j] >> 4) - 8);
+          }
+        }
+        if (ES == 2) {
+          __nv_bfloat16 t[8];
+#pragma unroll
+          for (int j = 0; j < 8; ++j) t[j] = __float2bfloat16_rn((float)c[j]);
+          v = *reinterpret_cast<uint4*>(t);
+        } else {
+          v = *reinterpret_cast<uint4*>(c);
+        }
+      }
+      *reinterpret_cast<uint4*>(b_tile + (r >> 3) * sbo + kc * lbo + (r & 7) * 16) = v;
+    }
+    // ---- the weight scales of this group for the tile's 128 columns
+    {
+      const int n = n0 + tid;
+      ws_s[tid] = n < p.N ? p.scale_tiles[((int64_t)(n >> 2) * p.groups + g) * 4 + (n & 3)] : 0.f;
+    }
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic stores -> async reads
+    __syncthreads();
+
+    if (tid == 0) {
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      const int steps = KT / (32 / ES);  // 32 bytes of K per MMA: 16 bf16 or 32 int8
+      for (int s = 0; s < steps; ++s) {
+        const uint64_t da = smem_desc(a_addr + s * 2 * lbo, lbo, sbo);
+        const uint64_t db = smem_desc(b_addr + s * 2 * lbo, lbo, sbo);
+        if (ES == 2) mma_f16(tmem_base, da, db, kIdesc, s > 0);
+        else mma_i8(tmem_base, da, db, kIdesc, s > 0);
+      }
+      mma_commit(bar);
+    }
+    if (!mbar_wait(bar, phase)) dead_s = 1;  // bounded; every thread waits on the same phase
+    phase ^= 1;
+    __syncthreads();
+    if (dead_s) break;
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+
+    // ---- drain: TMEM lane = token row of this thread, 4 x 32 columns
+    const float xs = (ES == 1 && my_m < p.M) ? p.x_scales[(int64_t)my_m * p.groups + g] : 1.f;
+#pragma unroll
+    for (int c0 = 0; c0 < BN; c0 += 32) {
+      uint32_t v[32];
+      tmem_ld32(tmem_base + ((uint32_t)(warp * 32) << 16) + c0, v);
+#pragma unroll
+      for (int j = 0; j < 32; ++j) {
+        const float d = ES == 2 ? __uint_as_float(v[j]) : (float)(int)v[j];
+        acc[c0 + j] = fmaf(d, ws_s[c0 + j] * xs, acc[c0 + j]);
+      }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();  // TMEM and the tiles are free for the next group
+  }
+
+  if (dead_s) {
+    if (tid == 0) atomicExch(p.error_word, 1);
+  } else if (my_m < p.M) {
+    __nv_bfloat16* dst = p.out + (int64_t)my_m * p.N + n0;
+#pragma unroll
+    for (int c = 0; c < BN; ++c) {
+      if (n0 + c < p.N) {
+        float y = acc[c];
+        if (p.bias != nullptr) y += __bfloat162float(p.bias[n0 + c]);
+        dst[c] = __float2bfloat16_rn(y);
+      }
+    }
+  }
+  __syncthreads();
+  if (warp == 0) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols)
+                 : "memory");
+  }
+}
+
+__device__ int g_gemm_error = 0;
+
+template <int BITS, int ES>
+int launch_gemm(const GemmParams& p, cudaStream_t s) {
+  auto kern = prefill_gemm_kernel<BITS, ES>;
+  const size_t smem = 2 * (size_t)BM * p.span * ES;
+  static bool raised = false;
+  if (!raised) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024) != cudaSuccess) {
+      cudaGetLastError();
+      return fail(LQ_ERR_LAUNCH, "lq_wq_gemm_prefill: cannot raise the shared memory limit");
+    }
+    raised = true;
+  }
+  dim3 grid((unsigned)((p.N + BN - 1) / BN), (unsigned)((p.M + BM - 1) / BM));
+  kern<<<grid, kThreads, smem, s>>>(p);
+  return check_launch("lq_wq_gemm_prefill");
+}
+
+}  // namespace
+}  // namespace lq
+
+extern "C" int lq_gemm_device_error(void) {
+  void* ptr = nullptr;
+  if (cudaGetSymbolAddress(&ptr, lq::g_gemm_error) != cudaSuccess) { cudaGetLastError(); return -1; }
+  int value = 0;
+  if (cudaMemcpy(&value, ptr, sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess) return -1;
+  if (value != 0) cudaMemset(ptr, 0, sizeof(int));
+  return value;
+}
+
+extern "C" int lq_wq_gemm_prefill(const void* x, int ldx, const int8_t* x_codes, const float* x_scales,
+                                  const void* codes, const float* scale_tiles, const void* bias,
+                                  void* out, int M, int N, int K, int Kd, int span, int bits,
+                                  void* stream) {
+  using namespace lq;
+  LQ_REQUIRE(bits == 4 || bits == 8, LQ_ERR_ARG, "unsupported num_bits %d, expected 4 or 8", bits);
+  LQ_REQUIRE(M >= 0 && N >= 0 && K >= 0 && Kd >= K, LQ_ERR_ARG, "bad shape M=%d N=%d K=%d Kd=%d", M, N, K, Kd);
+  if (M == 0 || N == 0) return LQ_OK;
+  LQ_REQUIRE(span == 64 || span == 128, LQ_ERR_UNSUPPORTED,
+             "the prefill GEMM is built for scale groups of 64 or 128 stored codes, got %d", span);
+  LQ_REQUIRE(Kd % span == 0, LQ_ERR_ARG, "Kd=%d is not a whole number of groups of %d", Kd, span);
+  LQ_REQUIRE(codes && scale_tiles && out, LQ_ERR_ARG, "null tensor pointer");
+  const bool a8 = x_codes != nullptr;
+  LQ_REQUIRE(a8 ? x_scales != nullptr : x != nullptr, LQ_ERR_ARG, "null activation pointer");
+  LQ_REQUIRE(a8 || ldx >= K, LQ_ERR_ARG, "x row stride %d is shorter than K=%d", ldx, K);
+  LQ_REQUIRE(!a8 || ((uintptr_t)x_codes % 16 == 0 && Kd % 16 == 0), LQ_ERR_ARG, "activation codes must be 16-byte aligned");
+  LQ_REQUIRE((uintptr_t)codes % 16 == 0, LQ_ERR_ARG, "codes must be 16-byte aligned");
+  GemmParams p;
+  p.x = (const __nv_bfloat16*)x; p.ldx = ldx; p.x_codes = x_codes; p.x_scales = x_scales;
+  p.codes = (const uint8_t*)codes; p.scale_tiles = scale_tiles; p.bias = (const __nv_bfloat16*)bias;
+  p.out = (__nv_bfloat16*)out; p.M = M; p.N = N; p.K = K; p.Kd = Kd; p.span = span;
+  p.groups = Kd / span; p.rowbytes = Kd * bits / 8;
+  void* err = nullptr;
+  if (cudaGetSymbolAddress(&err, g_gemm_error) != cudaSuccess) {
+    cudaGetLastError();
+    return fail(LQ_ERR_LAUNCH, "cannot resolve the device error word");
+  }
+  p.error_word = (int*)err;
+  cudaStream_t s = (cudaStream_t)stream;
+  if (bits == 8) return a8 ? launch_gemm<8, 1>(p, s) : launch_gemm<8, 2>(p, s);
+  return a8 ? launch_gemm<4, 1>(p, s) : launch_gemm<4, 2>(p, s);
+}

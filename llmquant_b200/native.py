@@ -30,6 +30,8 @@ _SIGNATURES = {
     "lq_quantize_group_i8": [_P, _P, _P, _L, _I, _I, _I, _P],
     "lq_quantize_weight": [_P, _I, _I, _I, _I, _I, _I, _I, _P, _P, _P],
     "lq_residual_add": [_P, _P, _P, _L, _I, _P],
+    "lq_gemm_device_error": [],
+    "lq_wq_gemm_prefill": [_P, _I, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P],
     "lq_allreduce_max_world": [],
     "lq_allreduce_device_error": [],
     "lq_allreduce_residual": [_P, _I, _I, _I, _L, _L, _P, _P, _P, _I, _I, _P],

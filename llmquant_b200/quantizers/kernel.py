@@ -26,6 +26,7 @@ from llmquant_b200.core.scheme import QuantizationScheme
 KERNEL_MAX_ROWS = 4
 DECODE_MAX_ROWS = 8
 GEMV_VARIANT = 0  # 0 = library default; see lq_wq_gemv_stream
+PREFILL_TENSOR_CORE = False  # True: more than DECODE_MAX_ROWS rows take lq_wq_gemm_prefill
 
 
 def _canonical_geometry(out_features, in_features, args):
@@ -216,6 +217,38 @@ class KernelQuantLinear(nn.Module):
             native.call("lq_wq_gemv_fused", ctypes.byref(args), native.stream_ptr(flat.device))
         return out
 
+    def gemm(self, flat, a8: bool = False):
+        """Prefill GEMM on the tensor cores for any number of rows: `[M, K]` bf16 -> `[M, N]`
+        bf16. `a8=True` quantizes the activations per token per group to int8 first (the
+        reference's dynamic activation scheme) and multiplies integers."""
+        m = flat.shape[0]
+        out = torch.empty(m, self.out_features, dtype=torch.bfloat16, device=flat.device)
+        if m == 0:
+            return out
+        flat = flat.contiguous()
+        bias = None
+        if self.bias is not None:
+            if self._bias_bf16 is None or self._bias_bf16.device != flat.device:
+                self._bias_bf16 = self.bias.detach().to(device=flat.device, dtype=torch.bfloat16).contiguous()
+            bias = self._bias_bf16
+        x_codes = x_scales = None
+        if a8:
+            if self._kd != self.in_features:
+                flat = nn.functional.pad(flat, (0, self._kd - self.in_features))
+            groups = self._kd // self._span
+            x_codes = torch.empty(m, self._kd, dtype=torch.int8, device=flat.device)
+            x_scales = torch.empty(m, groups, dtype=torch.float32, device=flat.device)
+            with torch.cuda.device(flat.device):
+                native.call("lq_quantize_group_i8", flat.data_ptr(), x_codes.data_ptr(),
+                            x_scales.data_ptr(), m * groups, self._span, 8, native.LQ_BF16,
+                            native.stream_ptr(flat.device))
+        with torch.cuda.device(flat.device):
+            native.call("lq_wq_gemm_prefill", flat.data_ptr(), flat.stride(0), native.ptr(x_codes),
+                        native.ptr(x_scales), self.codes.data_ptr(), self.scale_tiles.data_ptr(),
+                        native.ptr(bias), out.data_ptr(), m, self.out_features, self.in_features,
+                        self._kd, self._span, self.num_bits, native.stream_ptr(flat.device))
+        return out
+
     def forward(self, x):
         if not x.is_cuda:
             raise RuntimeError("x must be a CUDA tensor: the kernel path has no CPU fallback")
@@ -224,6 +257,9 @@ class KernelQuantLinear(nn.Module):
         m = flat.shape[0]
         if self._stream and m <= DECODE_MAX_ROWS and flat.dtype == torch.bfloat16:
             out = self.gemv(flat)
+        elif (self._stream and PREFILL_TENSOR_CORE and flat.dtype == torch.bfloat16
+              and self._span in (64, 128)):
+            out = self.gemm(flat)
         elif not self._stream and m <= DECODE_MAX_ROWS:
             from llmquant_b200.cuda.build import load_extension
 

@@ -1,0 +1,65 @@
+"""The tcgen05/TMEM prefill GEMM against the reference's real mode: golden outputs for the
+four weight layouts with bf16 activations (A16) and with dynamic int8 activations (A8), and
+the numpy oracle at ragged larger shapes. Tolerance: rel-L2 <= 2e-3 (bf16 output vs fp32
+reference), the bound stated for layer outputs."""
+
+import numpy as np
+import pytest
+import torch
+
+import oracle
+from gpu_util import bf16_from_bits, index_of, rel_l2, seeded
+from llmquant_b200 import native
+from llmquant_b200.core import QuantizationArgs, QuantizationScheme
+
+pytestmark = pytest.mark.gpu
+
+LAYOUTS = ["plain8", "plain4", "oproj8", "oproj4", "qproj8", "tail4"]
+TOL = 2e-3
+
+
+def _module(w, bits, **kw):
+    from llmquant_b200.quantizers import KernelQuantLinear
+
+    scheme = QuantizationScheme(
+        weights=QuantizationArgs(num_bits=bits, strategy="group", group_size=128, **kw),
+        input_activations=None)
+    linear = torch.nn.Linear(w.shape[1], w.shape[0], bias=False)
+    linear.weight.data = w
+    return KernelQuantLinear.from_linear(linear.cuda(), scheme)
+
+
+@pytest.mark.parametrize("name", LAYOUTS)
+@pytest.mark.parametrize("act", [16, 8])
+def test_prefill_gemm_against_real_mode_golden(golden, name, act):
+    blob = golden("linear")
+    spec = next(c for c in index_of(blob) if c["name"] == name)
+    w = bf16_from_bits(blob[f"{name}_w"], "cpu")
+    module = _module(w, spec["bits"], head_dim=spec.get("head_dim"), out_group=spec.get("out_group"))
+    for M in (1, 4):
+        x = bf16_from_bits(blob[f"{name}_x{M}"])
+        got = module.gemm(x, a8=(act == 8))
+        want = blob[f"{name}_y{M}_a{act}_f32"]
+        assert got.shape == want.shape and got.dtype == torch.bfloat16
+        assert rel_l2(got.float().cpu().numpy(), want) <= TOL, (name, act, M)
+    assert native.library().lq_gemm_device_error() == 0
+
+
+@pytest.mark.parametrize("bits", [4, 8])
+@pytest.mark.parametrize("shape", [(200, 300, 512), (16, 4096, 4096), (129, 1024, 1152), (512, 2048, 2048)])
+def test_prefill_gemm_against_oracle(bits, shape):
+    m, n, k = shape
+    w = seeded((n, k), 11, 0.02, torch.bfloat16)
+    x = seeded((m, k), 12, 1.0, torch.bfloat16)
+    module = _module(w, bits)
+    q, scale = oracle.quantize_weight(w.float().numpy(), bits, 128)
+    want16 = oracle.real_linear(x.float().numpy(), q, scale, bits, 128)
+    want8 = oracle.real_linear(x.float().numpy(), q, scale, bits, 128, act_bits=8)
+    got16 = module.gemm(x.cuda())
+    got8 = module.gemm(x.cuda(), a8=True)
+    assert rel_l2(got16.float().cpu().numpy(), want16) <= TOL
+    assert rel_l2(got8.float().cpu().numpy(), want8) <= TOL
+    # the prefill path and the decode GEMV agree on the same rows
+    rows = module.gemv(x[:4].cuda())
+    assert rel_l2(got16[:4].float().cpu().numpy(), rows.float().cpu().numpy()) <= TOL
+    assert native.library().lq_gemm_device_error() == 0
