@@ -329,6 +329,56 @@ def run_gemv_one(args, device):
                       "gbs": round(per_copy / us / 1e3, 1), "graph_replay": True, "pdl": args.pdl}), flush=True)
 
 
+# --------------------------------------------------------------------------- prefill GEMM shapes
+def run_gemm_sweep(args, device):
+    """BASELINE config 4: W4 group-128 weights at the Llama-3-8B shapes, M in {16, 128, 512, 2048},
+    bf16 activations quantized per token per group to int8 (A8) and left in bf16 (A16); the
+    tensor-core GEMM next to the reference's own choice (dequantize to bf16 + library GEMM)."""
+    from llmquant_b200.core import QuantizationArgs, QuantizationScheme
+    from llmquant_b200.quantizers import KernelQuantLinear
+
+    shapes = [("q_o", 4096, 4096), ("k_v", 1024, 4096), ("gate_up", 14336, 4096), ("down", 4096, 14336)]
+    scheme = QuantizationScheme(
+        weights=QuantizationArgs(num_bits=args.bits, strategy="group", group_size=128), input_activations=None)
+    g = torch.Generator(device=device).manual_seed(0)
+    peaks, peak_kind = measured_peaks()
+    rows = []
+
+    def timed(fn):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(args.steps):
+            fn()
+        b.record()
+        torch.cuda.synchronize()
+        return a.elapsed_time(b) / args.steps
+
+    for name, n, k in shapes:
+        w = (torch.randn(n, k, generator=g, device=device) * 0.02).to(torch.bfloat16)
+        lin = torch.nn.Linear(k, n, bias=False, device="meta")
+        lin.weight = torch.nn.Parameter(w, requires_grad=False)
+        mod = KernelQuantLinear.from_linear(lin, scheme)
+        del w, lin
+        for m in (16, 128, 512, 2048):
+            x = torch.randn(m, k, generator=g, device=device).to(torch.bfloat16)
+            flops = 2.0 * m * n * k
+            t8 = timed(lambda: mod.gemm(x, a8=True))
+            t16 = timed(lambda: mod.gemm(x))
+            tlib = timed(lambda: x @ mod._dequantized_weight(torch.bfloat16).T)
+            rows.append({"shape": name, "M": m, "N": n, "K": k,
+                         "a8_tflops": round(flops / t8 / 1e9, 1), "a16_tflops": round(flops / t16 / 1e9, 1),
+                         "dequant_plus_library_tflops": round(flops / tlib / 1e9, 1),
+                         "a8_ms": round(t8, 4), "a16_ms": round(t16, 4), "dequant_plus_library_ms": round(tlib, 4)})
+    best = max(r["a8_tflops"] for r in rows)
+    print(json.dumps({"workload": "prefill_gemm (BASELINE config 4)", "bits": args.bits, "rows": rows,
+                      "roofline": {"bound": "tensor", "achieved": best, "peak": peaks["bf16_tflops"],
+                                   "unit": "TFLOP/s", "frac": round(best / peaks["bf16_tflops"], 4),
+                                   "peak_kind": peak_kind + " bf16 cuBLAS burst"}}), flush=True)
+
+
 # --------------------------------------------------------------------------- decode workload
 DECODE = {
     "decode_8b": dict(shape="llama-3-8b", prompt=4096, label="BASELINE config 5: random-init Llama-3-8B"),
@@ -569,7 +619,7 @@ def main():
     ap.add_argument("--steps", type=int, default=64)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
-    ap.add_argument("--workload", default="decode_8b", choices=["decode_8b", "decode_1b", "gemv_sweep_1b", "gemv_one"])
+    ap.add_argument("--workload", default="decode_8b", choices=["decode_8b", "decode_1b", "gemv_sweep_1b", "gemv_one", "prefill_gemm"])
     ap.add_argument("--n", type=int, default=28672)
     ap.add_argument("--k", type=int, default=4096)
     ap.add_argument("--bits", type=int, default=4)
@@ -599,6 +649,8 @@ def main():
     try:
         if args.workload == "gemv_one":
             run_gemv_one(args, device)
+        elif args.workload == "prefill_gemm":
+            run_gemm_sweep(args, device)
         elif args.workload in DECODE:
             run_decode(args, rank, world, device)
         else:

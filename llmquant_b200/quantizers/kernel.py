@@ -26,7 +26,10 @@ from llmquant_b200.core.scheme import QuantizationScheme
 KERNEL_MAX_ROWS = 4
 DECODE_MAX_ROWS = 8
 GEMV_VARIANT = 0  # 0 = library default; see lq_wq_gemv_stream
-PREFILL_TENSOR_CORE = False  # True: more than DECODE_MAX_ROWS rows take lq_wq_gemm_prefill
+# Rows up to which lq_wq_gemm_prefill (tcgen05, exact integer codes) serves the prefill; its
+# first version does not yet overlap tile fills with the MMAs, and above this many rows the
+# reference's own choice (dequantize to bf16 + library GEMM) is still the faster one.
+PREFILL_TENSOR_CORE_MAX_ROWS = 128
 
 
 def _canonical_geometry(out_features, in_features, args):
@@ -257,7 +260,7 @@ class KernelQuantLinear(nn.Module):
         m = flat.shape[0]
         if self._stream and m <= DECODE_MAX_ROWS and flat.dtype == torch.bfloat16:
             out = self.gemv(flat)
-        elif (self._stream and PREFILL_TENSOR_CORE and flat.dtype == torch.bfloat16
+        elif (self._stream and m <= PREFILL_TENSOR_CORE_MAX_ROWS and flat.dtype == torch.bfloat16
               and self._span in (64, 128)):
             out = self.gemm(flat)
         elif not self._stream and m <= DECODE_MAX_ROWS:
