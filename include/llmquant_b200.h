@@ -204,6 +204,9 @@ int64_t lq_attn_fused_scratch_bytes(int B, int Hq, int Hkv, int D, int splits);
 int lq_attn_device_error(void);
 /* Diagnostics, as lq_gemv_set_timeline: 8 uint64 stamps per CTA of lq_attn_decode_fused. */
 void lq_attn_set_timeline(void* device_buffer);
+/* Which kernel serves lq_attn_decode_fused: 0 (default) = contractions on mma.sync tensor-core
+ * instructions, 1 = all-SIMT arithmetic. Same results within the attention tolerance. */
+void lq_attn_set_impl(int impl);
 int lq_attn_decode_fused(const void* qkv, const void* cos_table, const void* sin_table,
                          int8_t* k_codes, int8_t* v_codes, float* k_scales, float* v_scales,
                          void* out, void* scratch, int B, int Hq, int Hkv, int D, int Tmax,

@@ -905,11 +905,388 @@ attn_fused_kernel(const __nv_bfloat16* __restrict__ qkv, const __nv_bfloat16* __
 #undef ATT_STAMP
 }
 
+// ---------------------------------------------------------------- the same block on mma.sync
+// The SIMT kernel above spends ~20 instructions per cached byte, four times what an HBM-bound
+// stream allows when four query heads share a KV head. This version keeps the same data flow
+// (bulk-copy staging, chunked online softmax, slice merge by the last CTA) but does the two
+// contractions on the tensor cores, shaped so that the int8 codes are consumed as they are:
+//   scores  m16n8k32 s8 x s8 -> s32: A rows 0..7 hold the high byte and rows 8..15 the low byte
+//           of the query heads re-expressed as 15-bit block-floating-point integers (exact for
+//           a bf16 query up to 2^-14 of the head's maximum), B is the K codes read straight
+//           from the staged rows, so one thread ends up with both halves of a score;
+//   values  m16n8k16 bf16: A is p * v_scale in bf16 taken from the score accumulators, B the V
+//           codes of four token rows widened to bf16 in registers.
+// Staged rows are padded by 16 bytes so that both fragment access patterns are free of
+// shared-memory bank conflicts (one bulk copy per row).
+constexpr int kMmaThreads = 256;
+constexpr int kMmaCap = 192;  // tokens staged per chunk
+
+__device__ __forceinline__ void mma_s8(int (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+      : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void mma_bf16(float (&c)[4], uint32_t a0, uint32_t a2, uint32_t b0, uint32_t b1) {
+  const uint32_t zero = 0;  // rows 8..15 of A (no query head there)
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a0), "r"(zero), "r"(a2), "r"(zero), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+  const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<const uint32_t*>(&v);
+}
+
+template <int D, int G>
+__global__ void __launch_bounds__(kMmaThreads)
+attn_mma_kernel(const __nv_bfloat16* __restrict__ qkv, const __nv_bfloat16* __restrict__ cos_t,
+                const __nv_bfloat16* __restrict__ sin_t, int8_t* kc, int8_t* vc, float* ks, float* vs,
+                __nv_bfloat16* __restrict__ out, float* part_o, float* part_ml, int* tickets,
+                int Hq, int Hkv, int Tmax, int table_len, const int64_t* pos_dev, int64_t pos_host,
+                float scaling, float qmin, float qmax, int* error_word, unsigned long long* debug) {
+#define ATT_STAMP(slot) do { if (debug != nullptr && threadIdx.x == 0) { unsigned long long t_; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_)); debug[((size_t)(blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x) * 8 + (slot)] = t_; } } while (0)
+  constexpr int NT = kMmaThreads, NW = NT / 32;
+  constexpr int HALF = D / 2, CAP = kMmaCap, PK = D;  // unpadded rows: one bulk copy per chunk
+  constexpr int KS = D / 32;   // k-steps of the score MMA
+  constexpr int DT = D / 8;    // n-tiles of the value MMA
+  extern __shared__ __align__(128) uint8_t stage[];  // K rows [CAP][PK], then V rows [CAP][PK]
+  __shared__ __align__(8) uint64_t bar;
+  __shared__ float sk_s[CAP], sv_s[CAP];
+  __shared__ float q_s[G][D];                       // rotated query heads (bf16 values)
+  __shared__ __align__(16) int8_t qhi_s[G][D], qlo_s[G][D];
+  __shared__ float qunit_s[G];
+  __shared__ float knew_s[D], vnew_s[D];
+  __shared__ float newscale_s[2], snew_s[G];
+  __shared__ float mw_s[NW][8], lw_s[NW][8];
+  __shared__ int last_s;
+
+  const int ns = gridDim.x, split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int gid = lane >> 2, q4 = lane & 3;  // fragment coordinates
+  ATT_STAMP(0);
+  int64_t pos = read_pos(pos_dev, pos_host);
+  if (pos < 0) pos = 0;
+  if (pos > Tmax - 1) pos = Tmax - 1;
+  const int64_t len = pos;
+  const int per = (int)((len + ns - 1) / ns);
+  const int t_lo = split * per;
+  const int t_hi = (int)min((int64_t)(t_lo + per), len);
+  const int64_t head_row = ((int64_t)b * Hkv + kvh) * Tmax;
+  const uint32_t bar_a = smem_u32(&bar);
+  uint8_t* k_st = stage;
+  uint8_t* v_st = stage + (size_t)CAP * PK;
+
+  auto issue = [&](int c_lo) {  // warp 0: the chunk's K rows and V rows, one bulk copy each
+    const int n = min(CAP, t_hi - c_lo);
+    if (lane == 0) {
+      const uint32_t bytes = (uint32_t)n * D;
+      mbar_expect_tx(bar_a, 2u * bytes);
+      bulk_g2s(smem_u32(k_st), kc + (head_row + c_lo) * D, bytes, bar_a);
+      bulk_g2s(smem_u32(v_st), vc + (head_row + c_lo) * D, bytes, bar_a);
+    }
+    __syncwarp();
+  };
+  if (threadIdx.x == 0) {
+    mbar_init(bar_a, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncthreads();
+  // cached rows and the cursor are older than the kernel ahead of this one: prefetch first
+  if (warp == 0 && t_lo < t_hi) issue(t_lo);
+
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+
+  ATT_STAMP(1);
+  const int64_t tpos = pos < table_len ? pos : table_len - 1;
+  const int heads = Hq + 2 * Hkv;
+  const __nv_bfloat16* row = qkv + (int64_t)b * heads * D;
+  auto r16 = [](float x) { return __bfloat162float(__float2bfloat16_rn(x)); };
+
+  for (int i = threadIdx.x; i < G * HALF; i += NT) {
+    const int g = i / HALF, d = i % HALF;
+    const __nv_bfloat16* src = row + (int64_t)(kvh * G + g) * D;
+    const float a = __bfloat162float(src[d]), c = __bfloat162float(src[d + HALF]);
+    const float c0 = __bfloat162float(cos_t[tpos * D + d]), s0 = __bfloat162float(sin_t[tpos * D + d]);
+    const float c1 = __bfloat162float(cos_t[tpos * D + d + HALF]), s1 = __bfloat162float(sin_t[tpos * D + d + HALF]);
+    q_s[g][d] = r16(r16(a * c0) + r16(-c * s0));
+    q_s[g][d + HALF] = r16(r16(c * c1) + r16(a * s1));
+  }
+  const bool owner = split == ns - 1;
+  if (owner && warp >= NW - 2) {  // the last two warps (warp 0 is busy issuing copies)
+    const bool is_v = warp == NW - 1;
+    const __nv_bfloat16* src = row + (int64_t)(Hq + (is_v ? Hkv : 0) + kvh) * D;
+    float val[D / 32];
+    float amax = 0.f;
+#pragma unroll
+    for (int j = 0; j < D / 32; ++j) {
+      const int d = lane + 32 * j;
+      float x = __bfloat162float(src[d]);
+      if (!is_v) {
+        const int partner = d < HALF ? d + HALF : d - HALF;
+        const float y = __bfloat162float(src[partner]);
+        const float cc = __bfloat162float(cos_t[tpos * D + d]), ss = __bfloat162float(sin_t[tpos * D + d]);
+        x = d < HALF ? r16(r16(x * cc) + r16(-y * ss)) : r16(r16(x * cc) + r16(y * ss));
+      }
+      val[j] = x;
+      amax = fmaxf(amax, fabsf(x));
+    }
+    amax = warp_max(amax);
+    const float scale = scale_of(amax, qmax);
+    const int64_t crow = head_row + pos;
+    if (lane == 0) { (is_v ? vs : ks)[crow] = scale; newscale_s[is_v] = scale; }
+#pragma unroll
+    for (int j = 0; j < D / 32; ++j) {
+      const int d = lane + 32 * j;
+      const float code = code_of(val[j], scale, qmin, qmax);
+      (is_v ? vc : kc)[crow * D + d] = (int8_t)code;
+      (is_v ? vnew_s : knew_s)[d] = code;
+    }
+  }
+  __syncthreads();
+
+  // ---- query heads as 15-bit block-floating-point integers, split into two signed bytes
+  if (warp < G) {
+    const int g = warp;
+    float v[D / 32], amax = 0.f;
+#pragma unroll
+    for (int j = 0; j < D / 32; ++j) { v[j] = q_s[g][lane + 32 * j]; amax = fmaxf(amax, fabsf(v[j])); }
+    amax = warp_max(amax);
+    int e = (int)((__float_as_uint(amax) >> 23) & 0xFF) - 127;
+    e = max(e, -100);
+    const float up = __uint_as_float((unsigned)(127 + 13 - e) << 23);  // |m| < 2^14
+    if (lane == 0) qunit_s[g] = __uint_as_float((unsigned)(127 - 13 + e) << 23);
+#pragma unroll
+    for (int j = 0; j < D / 32; ++j) {
+      const int m = __float2int_rn(v[j] * up);
+      const int hi = (m + 128) >> 8, lo = m - hi * 256;
+      qhi_s[g][lane + 32 * j] = (int8_t)hi;
+      qlo_s[g][lane + 32 * j] = (int8_t)lo;
+    }
+  }
+  // the new token's scores on the CUDA cores (one warp per head, plain dot product)
+  if (owner && warp < G) {
+    const int g = warp;
+    float d = 0.f;
+#pragma unroll
+    for (int j = 0; j < D / 32; ++j) d = fmaf(q_s[g][lane + 32 * j], knew_s[lane + 32 * j], d);
+    d = warp_sum(d);
+    if (lane == 0) snew_s[g] = d * newscale_s[0] * scaling;
+  }
+  __syncthreads();
+  uint32_t qa[KS][4];
+#pragma unroll
+  for (int ksx = 0; ksx < KS; ++ksx) {
+    const int c = ksx * 32 + q4 * 4;
+    const bool have = gid < G;
+    qa[ksx][0] = have ? *reinterpret_cast<const uint32_t*>(&qhi_s[have ? gid : 0][c]) : 0u;
+    qa[ksx][1] = have ? *reinterpret_cast<const uint32_t*>(&qlo_s[have ? gid : 0][c]) : 0u;
+    qa[ksx][2] = have ? *reinterpret_cast<const uint32_t*>(&qhi_s[have ? gid : 0][c + 16]) : 0u;
+    qa[ksx][3] = have ? *reinterpret_cast<const uint32_t*>(&qlo_s[have ? gid : 0][c + 16]) : 0u;
+  }
+  const float qscale = (gid < G ? qunit_s[gid < G ? gid : 0] : 0.f) * scaling;
+
+  ATT_STAMP(2);
+  // ---- per-warp online softmax over blocks of 16 tokens
+  float m_run = -INFINITY, l_run = 0.f;  // row gid of this thread's quad
+  float o[DT][4];
+#pragma unroll
+  for (int dt = 0; dt < DT; ++dt) { o[dt][0] = o[dt][1] = o[dt][2] = o[dt][3] = 0.f; }
+
+  bool dead = false;
+  int phase = 0;
+  for (int c_lo = t_lo; c_lo < t_hi; c_lo += CAP) {
+    const int n = min(CAP, t_hi - c_lo);
+    for (int i = threadIdx.x; i < n; i += NT) {
+      sk_s[i] = ks[head_row + c_lo + i];
+      sv_s[i] = vs[head_row + c_lo + i];
+    }
+    __syncthreads();
+    if (!mbar_wait(bar_a, phase)) { dead = true; break; }
+    phase ^= 1;
+    if (c_lo == t_lo) ATT_STAMP(3);
+    const int blocks = (n + 15) / 16;
+    for (int blk = warp; blk < blocks; blk += NW) {
+      const int r0 = blk * 16;
+      float sc[2][2];
+#pragma unroll
+      for (int j = 0; j < 2; ++j) {
+        int c[4] = {0, 0, 0, 0};
+        const uint8_t* krow = k_st + (size_t)min(r0 + j * 8 + gid, CAP - 1) * PK + q4 * 4;
+#pragma unroll
+        for (int ksx = 0; ksx < KS; ++ksx) {
+          const uint32_t b0 = *reinterpret_cast<const uint32_t*>(krow + ksx * 32);
+          const uint32_t b1 = *reinterpret_cast<const uint32_t*>(krow + ksx * 32 + 16);
+          mma_s8(c, qa[ksx], b0, b1);
+        }
+        const int t0 = r0 + j * 8 + q4 * 2;
+        sc[j][0] = t0 < n ? (float)(c[0] * 256 + c[2]) * qscale * sk_s[t0] : -INFINITY;
+        sc[j][1] = t0 + 1 < n ? (float)(c[1] * 256 + c[3]) * qscale * sk_s[min(t0 + 1, CAP - 1)] : -INFINITY;
+      }
+      float mx = fmaxf(fmaxf(sc[0][0], sc[0][1]), fmaxf(sc[1][0], sc[1][1]));
+      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+      const float m_new = fmaxf(m_run, mx);
+      const float corr = (m_run == -INFINITY) ? 0.f : __expf(m_run - m_new);
+      float pr[2][2];
+#pragma unroll
+      for (int j = 0; j < 2; ++j)
+#pragma unroll
+        for (int e = 0; e < 2; ++e)
+          pr[j][e] = (sc[j][e] == -INFINITY || m_new == -INFINITY) ? 0.f : __expf(sc[j][e] - m_new);
+      l_run = l_run * corr + (pr[0][0] + pr[0][1] + pr[1][0] + pr[1][1]);
+      m_run = m_new;
+#pragma unroll
+      for (int dt = 0; dt < DT; ++dt) { o[dt][0] *= corr; o[dt][1] *= corr; }
+      const int ta = r0 + q4 * 2, tb = ta + 8;  // this thread's token rows in the block
+      const int ra0 = min(ta, CAP - 1), ra1 = min(ta + 1, CAP - 1), rb0 = min(tb, CAP - 1), rb1 = min(tb + 1, CAP - 1);
+      // (rows past the end of the chunk hold stale bytes and no scale: their weight is a plain 0)
+      const uint32_t a0 = pack_bf16(ta < n ? pr[0][0] * sv_s[ra0] : 0.f, ta + 1 < n ? pr[0][1] * sv_s[ra1] : 0.f);
+      const uint32_t a2 = pack_bf16(tb < n ? pr[1][0] * sv_s[rb0] : 0.f, tb + 1 < n ? pr[1][1] * sv_s[rb1] : 0.f);
+      const int8_t* va0 = reinterpret_cast<const int8_t*>(v_st) + (size_t)ra0 * PK + gid;
+      const int8_t* va1 = reinterpret_cast<const int8_t*>(v_st) + (size_t)ra1 * PK + gid;
+      const int8_t* vb0 = reinterpret_cast<const int8_t*>(v_st) + (size_t)rb0 * PK + gid;
+      const int8_t* vb1 = reinterpret_cast<const int8_t*>(v_st) + (size_t)rb1 * PK + gid;
+#pragma unroll
+      for (int dt = 0; dt < DT; ++dt) {
+        const uint32_t b0 = pack_bf16((float)va0[dt * 8], (float)va1[dt * 8]);
+        const uint32_t b1 = pack_bf16((float)vb0[dt * 8], (float)vb1[dt * 8]);
+        mma_bf16(o[dt], a0, a2, b0, b1);
+      }
+    }
+    __syncthreads();  // everyone is done with the stage before it is refilled
+    if (warp == 0 && c_lo + CAP < t_hi) issue(c_lo + CAP);
+  }
+  if (dead) {
+    if (threadIdx.x == 0) atomicExch(error_word, 4);
+    return;
+  }
+  ATT_STAMP(4);
+  l_run += __shfl_xor_sync(0xffffffffu, l_run, 1);
+  l_run += __shfl_xor_sync(0xffffffffu, l_run, 2);
+
+  // ---- merge the warps (and the new token) of the CTA; the staging area is free now
+  float (*ow_s)[G][D] = reinterpret_cast<float (*)[G][D]>(stage);  // [NW][G][D]
+  if (q4 == 0 && gid < 8) { mw_s[warp][gid] = m_run; lw_s[warp][gid] = l_run; }
+  if (gid < G) {
+#pragma unroll
+    for (int dt = 0; dt < DT; ++dt) {
+      ow_s[warp][gid][dt * 8 + q4 * 2] = o[dt][0];
+      ow_s[warp][gid][dt * 8 + q4 * 2 + 1] = o[dt][1];
+    }
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < G * D; i += NT) {
+    const int g = i / D, d = i % D;
+    float mm = owner ? snew_s[g] : -INFINITY;
+    for (int w = 0; w < NW; ++w) mm = fmaxf(mm, mw_s[w][g]);
+    float acc = 0.f;
+    for (int w = 0; w < NW; ++w) {
+      const float mw = mw_s[w][g];
+      if (mw != -INFINITY) acc = fmaf(ow_s[w][g][d], __expf(mw - mm), acc);
+    }
+    if (owner) acc = fmaf(vnew_s[d] * newscale_s[1], __expf(snew_s[g] - mm), acc);
+    part_o[(((int64_t)b * Hq + kvh * G + g) * ns + split) * D + d] = acc;
+    if (d == 0) {
+      float lt = owner ? __expf(snew_s[g] - mm) : 0.f;
+      for (int w = 0; w < NW; ++w) {
+        const float mw = mw_s[w][g];
+        if (mw != -INFINITY) lt = fmaf(lw_s[w][g], __expf(mw - mm), lt);
+      }
+      float* ml = part_ml + (((int64_t)b * Hq + kvh * G + g) * ns + split) * 2;
+      ml[0] = mm; ml[1] = lt;
+    }
+  }
+
+  // ---- the CTA that finishes last merges the slices
+  ATT_STAMP(5);
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const int ticket = atomicAdd(&tickets[b * Hkv + kvh], 1);
+    last_s = ticket == ns - 1;
+  }
+  __syncthreads();
+  ATT_STAMP(6);
+  if (!last_s) return;
+  __threadfence();
+  float* wsl = reinterpret_cast<float*>(stage);          // [ns][G]
+  float* lsum = wsl + (size_t)ns * G;                    // [G]
+  float* psum = lsum + G;                                // [NW][G * D]
+  for (int g = warp; g < G; g += NW) {
+    const int64_t base = ((int64_t)b * Hq + kvh * G + g) * ns;
+    float mm = -INFINITY;
+    for (int s = lane; s < ns; s += 32) mm = fmaxf(mm, __ldcg(part_ml + (base + s) * 2));
+    mm = warp_max(mm);
+    float lt = 0.f;
+    for (int s = lane; s < ns; s += 32) {
+      const float ms = __ldcg(part_ml + (base + s) * 2);
+      const float ws = (ms == -INFINITY) ? 0.f : __expf(ms - mm);
+      wsl[s * G + g] = ws;
+      lt = fmaf(__ldcg(part_ml + (base + s) * 2 + 1), ws, lt);
+    }
+    lt = warp_sum(lt);
+    if (lane == 0) lsum[g] = lt;
+  }
+  __syncthreads();
+  constexpr int PER_LANE = (G * D + 31) / 32;
+  float part[PER_LANE];
+#pragma unroll
+  for (int k = 0; k < PER_LANE; ++k) part[k] = 0.f;
+  for (int s0 = warp; s0 < ns; s0 += 4 * NW) {
+    float v[4][PER_LANE];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int s = s0 + j * NW;
+#pragma unroll
+      for (int k = 0; k < PER_LANE; ++k) {
+        const int i = lane + 32 * k;
+        v[j][k] = (s < ns && i < G * D)
+                      ? __ldcg(part_o + (((int64_t)b * Hq + kvh * G + i / D) * ns + s) * D + i % D) : 0.f;
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int s = s0 + j * NW;
+      if (s < ns) {
+#pragma unroll
+        for (int k = 0; k < PER_LANE; ++k) {
+          const int i = lane + 32 * k;
+          if (i < G * D) part[k] = fmaf(v[j][k], wsl[s * G + i / D], part[k]);
+        }
+      }
+    }
+  }
+#pragma unroll
+  for (int k = 0; k < PER_LANE; ++k) {
+    const int i = lane + 32 * k;
+    if (i < G * D) psum[warp * (G * D) + i] = part[k];
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < G * D; i += NT) {
+    const int g = i / D, d = i % D;
+    float ov = 0.f;
+#pragma unroll
+    for (int w8 = 0; w8 < NW; ++w8) ov += psum[w8 * (G * D) + i];
+    const float lt = lsum[g];
+    out[((int64_t)b * Hq + kvh * G + g) * D + d] = __float2bfloat16_rn(lt > 0.f ? ov / lt : 0.f);
+  }
+  if (threadIdx.x == 0) tickets[b * Hkv + kvh] = 0;
+  ATT_STAMP(7);
+#undef ATT_STAMP
+}
+
+int g_attn_impl = 0;  // host-side switch: 0 = mma.sync kernel, 1 = SIMT kernel
+
 __device__ int g_attn_error = 0;
 unsigned long long* g_attn_timeline = nullptr;
 
 }  // namespace
 }  // namespace lq
+
+extern "C" void lq_attn_set_impl(int impl) { lq::g_attn_impl = impl; }
 
 extern "C" void lq_attn_set_timeline(void* device_buffer) {
   lq::g_attn_timeline = (unsigned long long*)device_buffer;
@@ -950,6 +1327,28 @@ extern "C" int lq_attn_decode_fused(const void* qkv, const void* cos_table, cons
   if (cudaGetSymbolAddress(&err_ptr, g_attn_error) != cudaSuccess) {
     cudaGetLastError();
     return fail(LQ_ERR_LAUNCH, "cannot resolve the device error word");
+  }
+  if (g_attn_impl == 0) {
+    const size_t msmem = 2 * (size_t)kMmaCap * D;
+    LQ_REQUIRE((size_t)splits * G * 4 + (size_t)(kMmaThreads / 32 + 1) * G * D * 4 + 64 <= msmem, LQ_ERR_ARG,
+               "too many slices (%d) for the merge area of the attention kernel", splits);
+#define LQ_MMA_CASE(DD, GG)                                                                        \
+  if (D == DD && G == GG) {                                                                        \
+    static bool raised = false;                                                                    \
+    if (!raised) {                                                                                 \
+      cudaFuncSetAttribute(attn_mma_kernel<DD, GG>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)msmem); \
+      raised = true;                                                                               \
+    }                                                                                              \
+    rc = launch_pdl_smem(attn_mma_kernel<DD, GG>, grid, dim3(kMmaThreads), msmem, (cudaStream_t)stream, pdl, \
+                    "lq_attn_decode_fused", (const __nv_bfloat16*)qkv, (const __nv_bfloat16*)cos_table, \
+                    (const __nv_bfloat16*)sin_table, k_codes, v_codes, k_scales, v_scales,         \
+                    (__nv_bfloat16*)out, part_o, part_ml, tickets, Hq, Hkv, Tmax, table_len, pos_dev, \
+                    pos, scaling, -qmax - 1.f, qmax, (int*)err_ptr, g_attn_timeline);              \
+  }
+    LQ_MMA_CASE(64, 1) LQ_MMA_CASE(64, 2) LQ_MMA_CASE(64, 4) LQ_MMA_CASE(64, 8)
+    LQ_MMA_CASE(128, 1) LQ_MMA_CASE(128, 2) LQ_MMA_CASE(128, 4) LQ_MMA_CASE(128, 8)
+#undef LQ_MMA_CASE
+    if (rc != LQ_ERR_UNSUPPORTED) return rc;
   }
   const size_t smem = 2 * (size_t)kFusedChunkBytes + (size_t)(kFusedChunkBytes / 64) * 8 * sizeof(float);
 #define LQ_FUSED_CASE(DD, GG)                                                                      \

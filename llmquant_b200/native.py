@@ -60,12 +60,13 @@ _SIGNATURES.update({
     "lq_attn_fused_scratch_bytes": [_I, _I, _I, _I, _I],
     "lq_attn_device_error": [],
     "lq_attn_set_timeline": [_P],
+    "lq_attn_set_impl": [_I],
     "lq_attn_decode_fused": [_P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P, _L, _I,
                              ctypes.c_float, _I, _I, _P],
     "lq_attn_decode_kv_i8_static": [_P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P, _L, _I,
                                     ctypes.c_float, _I, _I, _P],
 })
-_RESTYPE = {"lq_gemv_set_timeline": None, "lq_attn_set_timeline": None, "lq_last_error": ctypes.c_char_p, "lq_attn_decode_scratch_bytes": ctypes.c_int64,
+_RESTYPE = {"lq_gemv_set_timeline": None, "lq_attn_set_timeline": None, "lq_attn_set_impl": None, "lq_last_error": ctypes.c_char_p, "lq_attn_decode_scratch_bytes": ctypes.c_int64,
             "lq_attn_decode_static_scratch_bytes": ctypes.c_int64,
             "lq_attn_fused_scratch_bytes": ctypes.c_int64}
 
