@@ -313,6 +313,43 @@ gemv_stream_kernel(const GemvParams p) {
     grp[j] = live ? (off * (8 / BITS)) / p.span : 0;
   }
 
+  // Column chunks that can be fetched with 128-bit loads keep their raw bf16 pairs in
+  // registers, so x is read from memory exactly once (for the norm's sum of squares and for
+  // the conversion); ragged or unaligned chunks fall back to scalar loads.
+  constexpr int PW = EPL / 2;  // packed bf16 pairs per chunk
+  bool fast[SPW];
+  int k0s[SPW];
+#pragma unroll
+  for (int j = 0; j < SPW; ++j) {
+    k0s[j] = cb[j] >= 0 ? cb[j] * (8 / BITS) : 0;
+    fast[j] = cb[j] >= 0 && k0s[j] + EPL <= p.K && (p.ldx % 8) == 0 &&
+              ((reinterpret_cast<uintptr_t>(p.x + k0s[j]) & 15) == 0);
+  }
+  // the norm weight is a constant of the model: fetch it before waiting for the producer
+  uint32_t graw[SPW][PW];
+  const bool has_norm = p.norm_weight != nullptr;
+  if (has_norm) {
+#pragma unroll
+    for (int j = 0; j < SPW; ++j) {
+      const __nv_bfloat16* gw = reinterpret_cast<const __nv_bfloat16*>(p.norm_weight) + k0s[j];
+      if (fast[j] && ((reinterpret_cast<uintptr_t>(gw) & 15) == 0)) {
+#pragma unroll
+        for (int v = 0; v < PW / 4; ++v) {
+          const uint4 raw = __ldg(reinterpret_cast<const uint4*>(gw) + v);
+          graw[j][4 * v] = raw.x; graw[j][4 * v + 1] = raw.y; graw[j][4 * v + 2] = raw.z; graw[j][4 * v + 3] = raw.w;
+        }
+      } else {
+#pragma unroll
+        for (int i = 0; i < PW; ++i) {
+          const int k = k0s[j] + 2 * i;
+          const unsigned lo = (cb[j] >= 0 && k < p.K) ? __bfloat16_as_ushort(gw[2 * i]) : 0u;
+          const unsigned hi = (cb[j] >= 0 && k + 1 < p.K) ? __bfloat16_as_ushort(gw[2 * i + 1]) : 0u;
+          graw[j][i] = lo | (hi << 16);
+        }
+      }
+    }
+  }
+
   // x is produced by the kernel before this one: wait for it (a no-op without programmatic
   // dependent launch), then let the kernel after this one start its own weight stream.
   LQ_STAMP(1);
@@ -320,35 +357,47 @@ gemv_stream_kernel(const GemvParams p) {
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   LQ_STAMP(2);
 
+  uint32_t xraw[M][SPW][PW];
+#pragma unroll
+  for (int m = 0; m < M; ++m)
+#pragma unroll
+    for (int j = 0; j < SPW; ++j) {
+      const __nv_bfloat16* xr = p.x + (int64_t)m * p.ldx + k0s[j];
+      if (fast[j] && m < p.M) {
+#pragma unroll
+        for (int v = 0; v < PW / 4; ++v) {
+          const uint4 raw = __ldg(reinterpret_cast<const uint4*>(xr) + v);
+          xraw[m][j][4 * v] = raw.x; xraw[m][j][4 * v + 1] = raw.y;
+          xraw[m][j][4 * v + 2] = raw.z; xraw[m][j][4 * v + 3] = raw.w;
+        }
+      } else {
+#pragma unroll
+        for (int i = 0; i < PW; ++i) {
+          const int k = k0s[j] + 2 * i;
+          const bool ok = cb[j] >= 0 && m < p.M;
+          const unsigned lo = (ok && k < p.K) ? __bfloat16_as_ushort(xr[2 * i]) : 0u;
+          const unsigned hi = (ok && k + 1 < p.K) ? __bfloat16_as_ushort(xr[2 * i + 1]) : 0u;
+          xraw[m][j][i] = lo | (hi << 16);
+        }
+      }
+    }
+
   // ---- optional fused RMSNorm: rstd[m] = 1 / sqrt(mean(x^2) + eps) over the whole row
   float rstd[M];
-  if (p.norm_weight != nullptr) {
+  if (has_norm) {
     float ss[M];
 #pragma unroll
     for (int m = 0; m < M; ++m) {
       ss[m] = 0.f;
 #pragma unroll
-      for (int j = 0; j < SPW; ++j) {
-        if (cb[j] < 0 || m >= p.M) continue;
-        const int k0 = cb[j] * (8 / BITS);
-        const __nv_bfloat16* xr = p.x + (int64_t)m * p.ldx + k0;
-        if (k0 + EPL <= p.K && ((reinterpret_cast<uintptr_t>(xr) & 15) == 0)) {
+      for (int j = 0; j < SPW; ++j)
 #pragma unroll
-          for (int v = 0; v < EPL / 8; ++v) {
-            const uint4 raw = __ldg(reinterpret_cast<const uint4*>(xr) + v);
-            const unsigned r[4] = {raw.x, raw.y, raw.z, raw.w};
-#pragma unroll
-            for (int t = 0; t < 4; ++t) {
-              const float lo = __uint_as_float(r[t] << 16), hi = __uint_as_float(r[t] & 0xFFFF0000u);
-              ss[m] = fmaf(lo, lo, ss[m]);
-              ss[m] = fmaf(hi, hi, ss[m]);
-            }
-          }
-        } else {
-          for (int i = 0; i < EPL; ++i)
-            if (k0 + i < p.K) { const float v = __bfloat162float(xr[i]); ss[m] = fmaf(v, v, ss[m]); }
+        for (int i = 0; i < PW; ++i) {
+          const float lo = __uint_as_float(xraw[m][j][i] << 16);
+          const float hi = __uint_as_float(xraw[m][j][i] & 0xFFFF0000u);
+          ss[m] = fmaf(lo, lo, ss[m]);
+          ss[m] = fmaf(hi, hi, ss[m]);
         }
-      }
       ss[m] = warp_sum(ss[m]);
     }
     if (KW > 1) {
@@ -372,53 +421,21 @@ gemv_stream_kernel(const GemvParams p) {
   XChunk<BITS, VAR> xc[M][SPW];
 #pragma unroll
   for (int j = 0; j < SPW; ++j) {
-    const bool live = cb[j] >= 0;
-    const int k0 = live ? cb[j] * (8 / BITS) : 0;
 #pragma unroll
     for (int m = 0; m < M; ++m) {
       float xf[EPL];
-      const __nv_bfloat16* xr = p.x + (int64_t)m * p.ldx + k0;
-      const bool full = live && m < p.M && k0 + EPL <= p.K &&
-                        ((reinterpret_cast<uintptr_t>(xr) & 15) == 0);
-      if (full) {
 #pragma unroll
-        for (int v = 0; v < EPL / 8; ++v) {
-          const uint4 raw = __ldg(reinterpret_cast<const uint4*>(xr) + v);
-          const unsigned r[4] = {raw.x, raw.y, raw.z, raw.w};
-#pragma unroll
-          for (int t = 0; t < 4; ++t) {
-            xf[v * 8 + 2 * t] = __uint_as_float(r[t] << 16);
-            xf[v * 8 + 2 * t + 1] = __uint_as_float(r[t] & 0xFFFF0000u);
-          }
-        }
-      } else {
-#pragma unroll
-        for (int i = 0; i < EPL; ++i)
-          xf[i] = (live && m < p.M && k0 + i < p.K) ? __bfloat162float(xr[i]) : 0.f;
+      for (int i = 0; i < PW; ++i) {
+        xf[2 * i] = __uint_as_float(xraw[m][j][i] << 16);
+        xf[2 * i + 1] = __uint_as_float(xraw[m][j][i] & 0xFFFF0000u);
       }
-      if (p.norm_weight != nullptr) {
+      if (has_norm) {
         // weight * bf16(x * rstd), the product rounded to bf16 again: the two roundings of
         // a bf16 RMSNorm module
-        const __nv_bfloat16* gw = reinterpret_cast<const __nv_bfloat16*>(p.norm_weight) + k0;
-        float gf[EPL];
-        if (live && k0 + EPL <= p.K && ((reinterpret_cast<uintptr_t>(gw) & 15) == 0)) {
-#pragma unroll
-          for (int v = 0; v < EPL / 8; ++v) {
-            const uint4 raw = __ldg(reinterpret_cast<const uint4*>(gw) + v);
-            const unsigned r[4] = {raw.x, raw.y, raw.z, raw.w};
-#pragma unroll
-            for (int t = 0; t < 4; ++t) {
-              gf[v * 8 + 2 * t] = __uint_as_float(r[t] << 16);
-              gf[v * 8 + 2 * t + 1] = __uint_as_float(r[t] & 0xFFFF0000u);
-            }
-          }
-        } else {
-#pragma unroll
-          for (int i = 0; i < EPL; ++i) gf[i] = (live && k0 + i < p.K) ? __bfloat162float(gw[i]) : 0.f;
-        }
 #pragma unroll
         for (int i = 0; i < EPL; ++i) {
-          const float g = gf[i];
+          const uint32_t gp = graw[j][i >> 1];
+          const float g = __uint_as_float((i & 1) ? (gp & 0xFFFF0000u) : (gp << 16));
           const float nx = __bfloat162float(__float2bfloat16_rn(xf[i] * rstd[m]));
           xf[i] = __bfloat162float(__float2bfloat16_rn(g * nx));
         }
@@ -434,6 +451,20 @@ gemv_stream_kernel(const GemvParams p) {
     const int s = it % p.stages;
     const int parity = it & 1;
     const int n0 = (b_begin + it) * kU;
+    // bias and residual of this batch's outputs do not depend on the tile: fetch them now,
+    // so their latency hides behind the wait for the tile and the dot products
+    float bias_pre = 0.f, res_pre = 0.f;
+    if (EPI == 0 && kw == 0 && lane < M * kU) {
+      const int pm = lane / kU, pn = n0 + lane % kU;
+      if (pn < p.N && pm < p.M) {
+        if (p.bias != nullptr) bias_pre = __bfloat162float(p.bias[pn]);
+        if (p.residual != nullptr) {
+          const int64_t po = (int64_t)pm * p.N + pn;
+          res_pre = p.out_f32 ? reinterpret_cast<const float*>(p.residual)[po]
+                              : __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p.residual)[po]);
+        }
+      }
+    }
     if (!mbar_wait(smem_u32(&full_bar[s]), (it / p.stages) & 1)) {
       // the KW warps wait for the same stage, so they all give up here together
       if (lane == 0) atomicExch(p.error_word, 2);
@@ -509,17 +540,13 @@ gemv_stream_kernel(const GemvParams p) {
           else reinterpret_cast<__nv_bfloat16*>(p.out)[o] = __float2bfloat16_rn(y);
         }
       } else if (lane < M * kU && n < p.N && m < p.M) {
-        if (p.bias != nullptr) total += __bfloat162float(p.bias[n]);
+        total += bias_pre;
         const int64_t o = (int64_t)m * p.N + n;
         if (p.out_f32) {
-          if (p.residual != nullptr) total += reinterpret_cast<const float*>(p.residual)[o];
-          reinterpret_cast<float*>(p.out)[o] = total;
+          reinterpret_cast<float*>(p.out)[o] = total + res_pre;
         } else {
-          if (p.residual != nullptr) {
-            // a bf16 layer output added to a bf16 residual stream: round, add, round
-            total = __bfloat162float(__float2bfloat16_rn(total)) +
-                    __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p.residual)[o]);
-          }
+          // a bf16 layer output added to a bf16 residual stream: round, add, round
+          if (p.residual != nullptr) total = __bfloat162float(__float2bfloat16_rn(total)) + res_pre;
           reinterpret_cast<__nv_bfloat16*>(p.out)[o] = __float2bfloat16_rn(total);
         }
       }
@@ -584,7 +611,7 @@ int launch_one(const GemvParams& p, int threads, cudaStream_t s) {
 // requests run as several passes over the weight.
 template <int BITS, int VAR>
 constexpr int max_rows(int spw) {
-  if (spw == 1) return (BITS == 4 && VAR != 2) ? 2 : 4;  // keep the instances free of register spills
+  if (spw == 1) return BITS == 4 ? 2 : 4;  // keep the instances free of register spills
   if (spw == 2) return BITS == 8 ? (VAR == 1 ? 1 : 2) : 1;
   return 1;
 }
