@@ -300,6 +300,10 @@ def run_gemv_one(args, device):
     n_out = n // 2 if args.epilogue else n
     out = torch.empty(args.batch, n_out, dtype=torch.bfloat16, device=device)
 
+    if args.tune:
+        from llmquant_b200 import native
+        native.library().lq_gemv_set_tuning(*[int(v) for v in args.tune.split(",")])
+
     def once():
         for m in mods:
             m.gemv(x, norm_weight=gamma, epilogue=args.epilogue, pdl=bool(args.pdl), out=out,
@@ -326,7 +330,8 @@ def run_gemv_one(args, device):
     us = start.elapsed_time(stop) * 1e3 / (args.steps * copies)
     print(json.dumps({"workload": "gemv_one", "n": n, "k": k, "bits": bits, "rows": args.batch,
                       "copies": copies, "us_per_launch": round(us, 2),
-                      "gbs": round(per_copy / us / 1e3, 1), "graph_replay": True, "pdl": args.pdl}), flush=True)
+                      "gbs": round(per_copy / us / 1e3, 1), "graph_replay": True, "pdl": args.pdl,
+                      "variant": args.variant, "tune": args.tune}), flush=True)
 
 
 # --------------------------------------------------------------------------- prefill GEMM shapes
@@ -627,6 +632,7 @@ def main():
     ap.add_argument("--norm", type=int, default=0)
     ap.add_argument("--pdl", type=int, default=1)
     ap.add_argument("--variant", type=int, default=0)
+    ap.add_argument("--tune", default="", help="gemv_one, variant 4: warps,rows-per-stage,stages (0 = default)")
     ap.add_argument("--batch", type=int, default=1)
     ap.add_argument("--prompt", type=int, default=0, help="prompt tokens (0 = the workload's own)")
     ap.add_argument("--allreduce", default="peer", choices=["peer", "nccl"])

@@ -135,7 +135,9 @@ int lq_dequant_stream(const void* codes, const float* scale_tiles, void* out, in
  * read as zero), out [M, N] of out_dtype (LQ_BF16 or LQ_F32), bias bf16 [N] or NULL,
  * residual (out_dtype, [M, N]) or NULL added after the bias.
  * variant: 0 = default, 1 = fp32 FMA arithmetic, 2 / 3 = integer dot products on 16- / 24-bit
- * block-floating-point activations.
+ * block-floating-point activations (32-column blocks), 4 = tensor-core integer products
+ * (mma.sync) on 15-bit block-floating-point activations (128-column blocks; needs span == 128
+ * and a shape lq_gemv_tensor_core_ok accepts, else LQ_ERR_UNSUPPORTED).
  * Takes the role of wq_gemv.cu:45-130 inside KernelQuantLinear.forward
  * (quantizers/kernel.py:81-95). */
 int lq_wq_gemv_stream(const void* x, int ldx, const void* codes, const float* scale_tiles,
@@ -151,6 +153,13 @@ int lq_gemv_device_error(void);
  * %globaltimer stamps of its phases there (start, barriers ready, producer kernel done,
  * activations prepared, first tile landed, end). NULL (the default) switches it off. */
 void lq_gemv_set_timeline(void* device_buffer);
+/* 1 if variant 4 of the GEMV serves M activation rows against a weight of Kd stored columns in
+ * groups of `span` at `bits` per code, else 0 (the other variants serve every shape). */
+int lq_gemv_tensor_core_ok(int M, int Kd, int span, int bits);
+/* Tuning override for variant 4 (0 = the library's choice): consumer warps per CTA (<= 16),
+ * weight rows per pipeline stage (4, 8 or 16), pipeline stages (<= 8). Process-wide; meant for
+ * benchmarking. No counterpart in the reference. */
+void lq_gemv_set_tuning(int warps, int rows, int stages);
 
 /* ---------------------------------------------------------------- quantized KV cache
  * Storage per layer: codes [B, Hkv, Tmax, D] int8, scales [B, Hkv, Tmax, ceil(D/128)] fp32.

@@ -10,6 +10,8 @@ int run_b4v2(GemvParams, const lq_gemv_args&, int, int, cudaStream_t);
 int run_b4v3(GemvParams, const lq_gemv_args&, int, int, cudaStream_t);
 int run_b8v1(GemvParams, const lq_gemv_args&, int, int, cudaStream_t);
 int run_b8v2(GemvParams, const lq_gemv_args&, int, int, cudaStream_t);
+bool mma_eligible(const lq_gemv_args& a);
+int run_mma(const lq_gemv_args& a, int* error_word, unsigned long long* debug, cudaStream_t s);
 int run_b8v3(GemvParams, const lq_gemv_args&, int, int, cudaStream_t);
 }  // namespace gemv
 
@@ -211,7 +213,15 @@ extern "C" int lq_wq_gemv_fused(const lq_gemv_args* a, void* stream) {
     LQ_REQUIRE(N % 4 == 0 && a->bias == nullptr && a->residual == nullptr, LQ_ERR_ARG,
                "the silu-mul epilogue needs N %% 4 == 0 and no bias / residual");
   int variant = a->variant == 0 ? 2 : a->variant;
-  LQ_REQUIRE(variant >= 1 && variant <= 3, LQ_ERR_ARG, "unknown arithmetic variant %d", variant);
+  LQ_REQUIRE(variant >= 1 && variant <= 4, LQ_ERR_ARG, "unknown arithmetic variant %d", variant);
+  if (variant == 4) {
+    LQ_REQUIRE(mma_eligible(*a), LQ_ERR_UNSUPPORTED,
+               "the tensor-core GEMV needs scale groups of 128 stored codes, activation planes within 64 KB and "
+               "five row stages within 200 KB (span=%d, M=%d, Kd=%d, bits=%d)", a->span, M, Kd, bits);
+    int* word = error_word();
+    LQ_REQUIRE(word != nullptr, LQ_ERR_LAUNCH, "cannot resolve the device error word");
+    return run_mma(*a, word, g_debug_timeline, (cudaStream_t)stream);
+  }
 
   GemvParams p;
   p.ldx = a->ldx; p.codes = (const uint8_t*)a->codes; p.scales = a->scale_tiles;

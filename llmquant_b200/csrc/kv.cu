@@ -1215,6 +1215,23 @@ attn_mma_kernel(const __nv_bfloat16* __restrict__ qkv, const __nv_bfloat16* __re
   float* wsl = reinterpret_cast<float*>(stage);          // [ns][G]
   float* lsum = wsl + (size_t)ns * G;                    // [G]
   float* psum = lsum + G;                                // [NW][G * D]
+  // The first batch of partial outputs is requested before the slice weights are known, so
+  // that the two trips to L2 overlap.
+  constexpr int PER_LANE = (G * D + 31) / 32;
+  float v[4][PER_LANE];
+  auto load_batch = [&](int s0) {
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int s = s0 + j * NW;
+#pragma unroll
+      for (int k = 0; k < PER_LANE; ++k) {
+        const int i = lane + 32 * k;
+        v[j][k] = (s < ns && i < G * D)
+                      ? __ldcg(part_o + (((int64_t)b * Hq + kvh * G + i / D) * ns + s) * D + i % D) : 0.f;
+      }
+    }
+  };
+  load_batch(warp);
   for (int g = warp; g < G; g += NW) {
     const int64_t base = ((int64_t)b * Hq + kvh * G + g) * ns;
     float mm = -INFINITY;
@@ -1231,22 +1248,11 @@ attn_mma_kernel(const __nv_bfloat16* __restrict__ qkv, const __nv_bfloat16* __re
     if (lane == 0) lsum[g] = lt;
   }
   __syncthreads();
-  constexpr int PER_LANE = (G * D + 31) / 32;
   float part[PER_LANE];
 #pragma unroll
   for (int k = 0; k < PER_LANE; ++k) part[k] = 0.f;
   for (int s0 = warp; s0 < ns; s0 += 4 * NW) {
-    float v[4][PER_LANE];
-#pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      const int s = s0 + j * NW;
-#pragma unroll
-      for (int k = 0; k < PER_LANE; ++k) {
-        const int i = lane + 32 * k;
-        v[j][k] = (s < ns && i < G * D)
-                      ? __ldcg(part_o + (((int64_t)b * Hq + kvh * G + i / D) * ns + s) * D + i % D) : 0.f;
-      }
-    }
+    if (s0 != warp) load_batch(s0);
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
       const int s = s0 + j * NW;

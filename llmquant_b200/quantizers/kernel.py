@@ -188,6 +188,10 @@ class KernelQuantLinear(nn.Module):
                         self._kd, self._span, self.num_bits, native.stream_ptr(dev))
         return out
 
+    def tensor_core_gemv_ok(self, m: int) -> bool:
+        """Whether GEMV variant 4 (tensor-core integer products) serves `m` rows of this layer."""
+        return bool(self._stream and native.library().lq_gemv_tensor_core_ok(m, self._kd, self._span, self.num_bits))
+
     def gemv(self, flat, out_dtype=None, residual=None, variant=None, norm_weight=None,
              norm_eps=1e-5, epilogue=0, pdl=False, out=None):
         """Streaming GEMV on `[M <= 8, K]` bf16 rows -> `[M, N]` (bf16 or fp32).
