@@ -156,8 +156,8 @@ void lq_gemv_set_timeline(void* device_buffer);
 /* 1 if variant 4 of the GEMV serves M activation rows against a weight of Kd stored columns in
  * groups of `span` at `bits` per code, else 0 (the other variants serve every shape). */
 int lq_gemv_tensor_core_ok(int M, int Kd, int span, int bits);
-/* Tuning override for variant 4 (0 = the library's choice): consumer warps per CTA (<= 16),
- * weight rows per pipeline stage (4, 8 or 16), pipeline stages (<= 8). Process-wide; meant for
+/* Tuning override for variant 4 (0 = the library's choice): consumer warps per CTA (<= 8),
+ * weight rows per pipeline stage (4, 8 or 16), pipeline stages (<= 16). Process-wide; meant for
  * benchmarking. No counterpart in the reference. */
 void lq_gemv_set_tuning(int warps, int rows, int stages);
 

@@ -25,14 +25,17 @@
 //       scaled, summed in fp32 -- quantizers/real.py:93-99, cuda/csrc/wq_gemv.cu:78-112) with
 //       the activations rounded at 2^-15 of their group maximum.
 //
-// Data movement: a producer thread streams stages of R whole rows (R = 4, 8 or 16, about
-// 32 KB; rows are contiguous in the streaming layout, so a stage is ONE bulk asynchronous copy
-// plus one for its scale tiles -- bulk copies cost about 80 ns each to issue, so they have to
-// be large) into a shared-memory ring, an mbarrier per stage counting the bytes. A 16-row MMA
-// tile spans 16 / R consecutive stages. The W consumer warps take the scale groups of the
-// rows in turn; their partial sums meet in shared memory once per tile. The first stages are
+// Data movement: stages of R whole rows (R = 4, 8 or 16, about 32 KB; rows are contiguous in
+// the streaming layout, so a stage is ONE bulk asynchronous copy plus one for its scale tiles
+// -- bulk copies cost about 80 ns each to issue, so they have to be large) stream into a
+// shared-memory ring, an mbarrier per stage counting the bytes. A 16-row MMA tile spans
+// 16 / R consecutive stages. The W warps take the scale groups of the rows in turn; their
+// partial sums meet in shared memory behind one named barrier per tile, and that barrier is
+// also the proof that every warp has read the tile's stages: right after it one thread refills
+// them, so there is no producer warp and no second set of barriers. The first stages are
 // requested before the kernel waits for its predecessor on the stream (programmatic dependent
-// launch).
+// launch). 8 warps at <= 128 registers and <= ~112 KB of shared memory are half an SM, so the
+// next kernel's CTA fits beside this one.
 //
 // Every mbarrier wait is bounded; on expiry the CTA records an error word, stops computing and
 // still walks through its named barriers, so no warp is left waiting.
@@ -43,7 +46,7 @@ namespace gemv {
 
 namespace {
 
-constexpr int kMaxW = 16;       // consumer warps per CTA (one more warp produces)
+constexpr int kMaxW = 8;        // warps per CTA
 constexpr int kMaxStagesMma = 16;
 constexpr int kTileRows = 16;
 
@@ -127,15 +130,20 @@ __device__ __forceinline__ void widen16(const uint4 (&raw)[2], float (&f)[16]) {
 
 // NB = number of B column sets (4 activation rows each); EPI as in the SIMT kernel: 0 = bias /
 // residual, 1 = silu(gate) * up over interleaved (gate, up) rows.
-template <int BITS, int NB, int EPI>
-__global__ void __launch_bounds__((kMaxW + 1) * 32, 1)
+// NSEG > 0: a warp owns at most NSEG scale groups of a row and keeps their B fragments and
+// units in registers for the whole kernel (they are the same for every tile); NSEG == 0: any
+// number of groups, B fragments fetched from shared memory per tile.
+template <int BITS, int NB, int EPI, int NSEG>
+__global__ void __launch_bounds__(kMaxW * 32, 2)
 gemv_mma_kernel(const MmaParams p) {
   constexpr int SEGB = 128 * BITS / 8;  // bytes of one scale group (128 codes) in a weight row
   constexpr int NA = BITS == 8 ? 2 : 1;  // 128-bit loads per row and group
-  constexpr int PASS = BITS == 8 ? 2 : 4;  // groups whose A fragments are in registers at once
+  constexpr int PASSMAX = BITS == 8 ? 2 : 4;  // groups whose A fragments are in registers at once
+  constexpr int PASS = (NSEG > 0 && NSEG < PASSMAX) ? NSEG : PASSMAX;
+  constexpr int NPASS = NSEG > 0 ? NSEG / PASS : 0;
   extern __shared__ __align__(128) uint8_t dyn[];
-  __shared__ __align__(8) uint64_t full_bar[kMaxStagesMma], empty_bar[kMaxStagesMma];
-  __shared__ float red[2][kMaxW][NB * 2][32];
+  __shared__ __align__(8) uint64_t full_bar[kMaxStagesMma];
+  __shared__ float red[2][kMaxW][NB * 2][33];  // 33: the sixteen warps' partials of a slot fall into distinct banks
   __shared__ float nrm[kMaxW][8];
   __shared__ volatile int dead_s;
 
@@ -152,7 +160,6 @@ gemv_mma_kernel(const MmaParams p) {
   if (threadIdx.x == 0) {
     for (int s = 0; s < p.stages; ++s) {
       mbar_init(smem_u32(&full_bar[s]), 1);
-      mbar_init(smem_u32(&empty_bar[s]), W);
     }
     dead_s = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -161,35 +168,30 @@ gemv_mma_kernel(const MmaParams p) {
 
   const uint32_t ring_base = smem_u32(dyn + p.ring_off);
 
-  // ------------------------------------------------------------------ producer warp
-  if (warp == W) {
-    if (lane == 0) {
-      const int scale_tiles_total = (p.N + 3) / 4;
-      const int nit = ntile_cta * p.H;
-      for (int it = 0; it < nit; ++it) {
-        const int s = it % p.stages;
-        if (it >= p.stages) {
-          if (!mbar_wait(smem_u32(&empty_bar[s]), ((it / p.stages) - 1) & 1)) {
-            atomicExch(p.error_word, 1);
-            break;
-          }
-        }
-        const int row0 = (t_begin + it / p.H) * kTileRows + (it % p.H) * p.R;
-        const int rows = max(0, min(p.R, p.N - row0));
-        const int nt = max(0, min(p.R / 4, scale_tiles_total - row0 / 4));
-        const uint32_t bar = smem_u32(&full_bar[s]);
-        const uint32_t dst = ring_base + (uint32_t)s * p.stage_bytes;
-        if (rows == 0) {
-          mbar_arrive(bar);  // a stage past the last row: nothing to copy
-        } else {
-          const uint32_t code_bytes = (uint32_t)rows * p.rowbytes, sc_bytes = (uint32_t)nt * p.groups * 16;
-          mbar_expect_tx(bar, code_bytes + sc_bytes);
-          bulk_g2s(dst, p.codes + (int64_t)row0 * p.rowbytes, code_bytes, bar);
-          bulk_g2s(dst + p.scale_off, p.scales + (int64_t)(row0 / 4) * p.groups * 4, sc_bytes, bar);
-        }
-      }
+  // ------------------------------------------------------------------ stage requests
+  // Stage number `it` of this CTA (tile it / H, rows (it % H) * R .. + R of it) goes to ring
+  // slot `slot`; called by one thread.
+  const int nit = ntile_cta * p.H;
+  const int scale_tiles_total = (p.N + 3) / 4;
+  auto request = [&](const int it, const int slot, const int row0) {
+    const int rows = max(0, min(p.R, p.N - row0));
+    const int nt = max(0, min(p.R / 4, scale_tiles_total - row0 / 4));
+    const uint32_t bar = smem_u32(&full_bar[slot]);
+    const uint32_t dst = ring_base + (uint32_t)slot * p.stage_bytes;
+    if (rows == 0) {
+      mbar_arrive(bar);  // a stage past the last row: nothing to copy
+    } else {
+      const uint32_t code_bytes = (uint32_t)rows * p.rowbytes, sc_bytes = (uint32_t)nt * p.groups * 16;
+      mbar_expect_tx(bar, code_bytes + sc_bytes);
+      bulk_g2s(dst, p.codes + (int64_t)row0 * p.rowbytes, code_bytes, bar);
+      bulk_g2s(dst + p.scale_off, p.scales + (int64_t)(row0 / 4) * p.groups * 4, sc_bytes, bar);
     }
-    return;
+    (void)it;
+  };
+  int next_it = 0;                        // thread 0: the next stage number to request
+  int next_row = t_begin * kTileRows;     // and its first row
+  if (threadIdx.x == 0) {
+    for (; next_it < nit && next_it < p.stages; ++next_it, next_row += p.R) request(next_it, next_it, next_row);
   }
 
   // ------------------------------------------------------------------ consumer warps
@@ -366,6 +368,28 @@ gemv_mma_kernel(const MmaParams p) {
   const uint32_t a_off = (uint32_t)((2 * g) % p.R) * p.rowbytes + t * 16;
   const uint32_t sc_off = p.scale_off + (uint32_t)(((2 * g) % p.R) >> 2) * p.groups * 16 + (g & 1) * 8;
 
+  constexpr int NREG = NSEG > 0 ? NSEG : 1;
+  unsigned breg[NREG][NB][8];
+  float ureg[NREG][NB];
+  if (NSEG > 0) {
+#pragma unroll
+    for (int j = 0; j < NREG; ++j) {
+      const int grp = warp + j * W;
+#pragma unroll
+      for (int nb = 0; nb < NB; ++nb) {
+        uint4 b01 = make_uint4(0, 0, 0, 0), b23 = b01;
+        ureg[j][nb] = 0.f;
+        if (grp < p.groups) {
+          b01 = lds128(bcol[nb] + grp * 128);
+          b23 = lds128(bcol[nb] + grp * 128 + 16);
+          ureg[j][nb] = lds32f(unit_u + (uint32_t)((t + 4 * nb) * p.groups + grp) * 4);
+        }
+        breg[j][nb][0] = b01.x; breg[j][nb][1] = b01.y; breg[j][nb][2] = b01.z; breg[j][nb][3] = b01.w;
+        breg[j][nb][4] = b23.x; breg[j][nb][5] = b23.y; breg[j][nb][6] = b23.z; breg[j][nb][7] = b23.w;
+      }
+    }
+  }
+
   float facc[NB][2];
 #pragma unroll
   for (int nb = 0; nb < NB; ++nb) facc[nb][0] = facc[nb][1] = 0.f;
@@ -374,9 +398,12 @@ gemv_mma_kernel(const MmaParams p) {
   for (int nb = 0; nb < NB; ++nb) res_pre[nb][0] = res_pre[nb][1] = 0.f;
 
   long long waited = 0, ph[3] = {0, 0, 0};  // diagnostics: SM clocks of thread 0 per phase, summed over tiles
+  int cur_stage = 0, cur_phase = 0;  // ring position of the next tile's first stage, kept without divisions
+  int n0 = t_begin * kTileRows - kTileRows;
   for (int tile_local = 0; tile_local < ntile_cta; ++tile_local) {
-    const int it0 = tile_local * p.H;  // first of the tile's stages
-    const int n0 = (t_begin + tile_local) * kTileRows;
+    n0 += kTileRows;
+    int sidx[4];  // the tile's stages (H <= 4 of them)
+    uint32_t my_stage = 0;
     // Each warp finishes the outputs of two lane positions ("slots", one per half warp) of the
     // tile: their bias and residual do not depend on the products, so fetch them early.
     const int my_slot = 2 * warp + (lane >> 4);  // slot = (g, t) of the lane that owns the pair
@@ -402,21 +429,25 @@ gemv_mma_kernel(const MmaParams p) {
     }
     bool alive = dead_s == 0;
     const long long w0 = p.debug != nullptr ? clock64() : 0;
-    for (int h = 0; h < p.H && alive; ++h) {
-      if (!mbar_wait(smem_u32(&full_bar[(it0 + h) % p.stages]), ((it0 + h) / p.stages) & 1)) {
-        dead_s = 1;
-        alive = false;
-        if (lane == 0) atomicExch(p.error_word, 2);
+#pragma unroll
+    for (int h = 0; h < 4; ++h) {
+      if (h < p.H) {
+        sidx[h] = cur_stage;
+        if (h == my_h) my_stage = ring_base + (uint32_t)cur_stage * p.stage_bytes;
+        if (alive && !mbar_wait(smem_u32(&full_bar[cur_stage]), cur_phase)) {
+          dead_s = 1;
+          alive = false;
+          if (lane == 0) atomicExch(p.error_word, 2);
+        }
+        if (++cur_stage == p.stages) { cur_stage = 0; cur_phase ^= 1; }
       }
     }
     if (p.debug != nullptr) waited += clock64() - w0;
     if (tile_local == 0) LQ_MMA_STAMP(4);
     if (alive) {
-      const uint32_t stage = ring_base + (uint32_t)((it0 + my_h) % p.stages) * p.stage_bytes;
-      // The A fragments of up to PASS scale groups go to registers first; after the loads of
-      // the warp's last groups the stages are handed back to the producer, so the ring is a
-      // transit buffer and its bytes are in flight nearly all the time.
-      for (int sg0 = warp; sg0 < p.groups; sg0 += W * PASS) {
+      const uint32_t stage = my_stage;
+      // The A fragments of up to PASS scale groups go to registers first, then their products.
+      auto do_pass = [&](const int sg0, const int jbase) {
         uint4 ra[PASS][NA], rb[PASS][NA];
         uint2 sc2[PASS];
 #pragma unroll
@@ -433,12 +464,6 @@ gemv_mma_kernel(const MmaParams p) {
             sc2[j] = lds64(stage + sc_off + sg * 16);
           }
         }
-        if (sg0 + W * PASS >= p.groups) {
-          __syncwarp();
-          if (lane == 0) {
-            for (int h = 0; h < p.H; ++h) mbar_arrive(smem_u32(&empty_bar[(it0 + h) % p.stages]));
-          }
-        }
 #pragma unroll
         for (int j = 0; j < PASS; ++j) {
           const int grp = sg0 + j * W;
@@ -447,9 +472,17 @@ gemv_mma_kernel(const MmaParams p) {
 #pragma unroll
             for (int nb = 0; nb < NB; ++nb) {
               acc[nb][0] = acc[nb][1] = acc[nb][2] = acc[nb][3] = 0;
-              const uint4 b01 = lds128(bcol[nb] + grp * 128);
-              const uint4 b23 = lds128(bcol[nb] + grp * 128 + 16);
-              const unsigned bw[8] = {b01.x, b01.y, b01.z, b01.w, b23.x, b23.y, b23.z, b23.w};
+              unsigned bw[8];
+              if (NSEG > 0) {
+                // with NSEG > 0 the pass loop runs once per PASS groups and jj is a constant
+#pragma unroll
+                for (int q = 0; q < 8; ++q) bw[q] = breg[(jbase + j) % NREG][nb][q];
+              } else {
+                const uint4 b01 = lds128(bcol[nb] + grp * 128);
+                const uint4 b23 = lds128(bcol[nb] + grp * 128 + 16);
+                bw[0] = b01.x; bw[1] = b01.y; bw[2] = b01.z; bw[3] = b01.w;
+                bw[4] = b23.x; bw[5] = b23.y; bw[6] = b23.z; bw[7] = b23.w;
+              }
               const unsigned wa[4] = {ra[j][0].x, ra[j][0].y, ra[j][0].z, ra[j][0].w};
               const unsigned wb[4] = {rb[j][0].x, rb[j][0].y, rb[j][0].z, rb[j][0].w};
               const unsigned wa2[4] = {ra[j][NA - 1].x, ra[j][NA - 1].y, ra[j][NA - 1].z, ra[j][NA - 1].w};
@@ -470,12 +503,19 @@ gemv_mma_kernel(const MmaParams p) {
             }
 #pragma unroll
             for (int nb = 0; nb < NB; ++nb) {
-              const float unit = lds32f(unit_u + (uint32_t)((t + 4 * nb) * p.groups + grp) * 4);
+              const float unit = NSEG > 0 ? ureg[(jbase + j) % NREG][nb]
+                                          : lds32f(unit_u + (uint32_t)((t + 4 * nb) * p.groups + grp) * 4);
               facc[nb][0] = fmaf((float)(acc[nb][0] * 256 + acc[nb][1]), __uint_as_float(sc2[j].x) * unit, facc[nb][0]);
               facc[nb][1] = fmaf((float)(acc[nb][2] * 256 + acc[nb][3]), __uint_as_float(sc2[j].y) * unit, facc[nb][1]);
             }
           }
         }
+      };
+      if (NSEG > 0) {
+#pragma unroll
+        for (int pass = 0; pass < NPASS; ++pass) do_pass(warp + pass * PASS * W, pass * PASS);
+      } else {
+        for (int sg0 = warp; sg0 < p.groups; sg0 += W * PASS) do_pass(sg0, 0);
       }
     }
 
@@ -490,7 +530,18 @@ gemv_mma_kernel(const MmaParams p) {
       if (p.debug != nullptr && threadIdx.x == 0) ph[0] += clock64() - w0;
       named_barrier(consumers);
       if (p.debug != nullptr && threadIdx.x == 0) ph[1] += clock64() - w0;
-      // Every warp sums the W partials of two slots per round: lane (half h, index i) reads
+      // every warp is past its loads of this tile: its stages take the next rows of the stream
+      if (threadIdx.x == 0) {
+#pragma unroll
+        for (int h = 0; h < 4; ++h) {
+          if (h < p.H && next_it < nit) {
+            request(next_it, sidx[h], next_row);
+            ++next_it;
+            next_row += p.R;
+          }
+        }
+      }
+      // Every warp sums the W (<= 8) partials of two slots per round: lane (half h, index i) reads
       // warp i's partial of slot s + h, a four-step shuffle tree adds the sixteen lanes of the
       // half (fixed order, so results are reproducible), lanes 0 and 16 write the outputs.
       if (dead_s == 0) {
@@ -573,9 +624,9 @@ struct Tuning {
 };
 Tuning g_tuning;
 
-template <int BITS, int NB, int EPI>
+template <int BITS, int NB, int EPI, int NSEG>
 int launch_mma(const MmaParams& p, size_t smem, cudaStream_t s) {
-  auto kern = gemv_mma_kernel<BITS, NB, EPI>;
+  auto kern = gemv_mma_kernel<BITS, NB, EPI, NSEG>;
   static thread_local bool attr_set = false;
   if (!attr_set) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024) != cudaSuccess) {
@@ -589,7 +640,7 @@ int launch_mma(const MmaParams& p, size_t smem, cudaStream_t s) {
   if (grid < 1) grid = 1;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3((unsigned)grid);
-  cfg.blockDim = dim3((unsigned)((p.W + 1) * 32));
+  cfg.blockDim = dim3((unsigned)(p.W * 32));
   cfg.dynamicSmemBytes = smem;
   cfg.stream = s;
   cudaLaunchAttribute attr[1];
@@ -632,7 +683,9 @@ bool make_plan(int M, int Kd, int span, int bits, Plan* out) {
   q.H = kTileRows / R;
   q.scale_off = R * rowbytes;
   q.stage_bytes = (q.scale_off + (R / 4) * groups * 16 + 127) / 128 * 128;
-  int W = g_tuning.warps > 0 ? g_tuning.warps : 16;
+  // consumer warps: as many as 8, evened out so that every warp owns the same number of groups
+  const int per = (groups + kMaxW - 1) / kMaxW;
+  int W = g_tuning.warps > 0 ? g_tuning.warps : (groups + per - 1) / per;
   if (W > groups) W = groups;
   if (W > kMaxW) W = kMaxW;
   if (W < 1) W = 1;
@@ -671,10 +724,17 @@ int run_mma(const lq_gemv_args& a, int* error_word, unsigned long long* debug, c
   p.W = q.W; p.stages = q.stages;
   p.ntiles = (a.N + kTileRows - 1) / kTileRows;
   const size_t smem = q.smem;
-#define LQ_MMA_CASE(B, NBV, E) \
-  if (a.bits == B && nb == NBV && a.epilogue == E) return launch_mma<B, NBV, E>(p, smem, s);
-  LQ_MMA_CASE(8, 1, 0) LQ_MMA_CASE(8, 1, 1) LQ_MMA_CASE(8, 2, 0) LQ_MMA_CASE(8, 2, 1)
-  LQ_MMA_CASE(4, 1, 0) LQ_MMA_CASE(4, 1, 1) LQ_MMA_CASE(4, 2, 0) LQ_MMA_CASE(4, 2, 1)
+  // groups a warp owns: up to 2 or 4 of them keep their B fragments in registers (one column
+  // set only; two sets would need too many registers)
+  const int per_warp = (p.groups + p.W - 1) / p.W;
+  const int nseg = nb == 1 ? (per_warp <= 2 ? 2 : (per_warp <= 4 ? 4 : 0)) : 0;
+#define LQ_MMA_CASE(B, NBV, E, S) \
+  if (a.bits == B && nb == NBV && a.epilogue == E && nseg == S) return launch_mma<B, NBV, E, S>(p, smem, s);
+  LQ_MMA_CASE(8, 1, 0, 2) LQ_MMA_CASE(8, 1, 0, 4) LQ_MMA_CASE(8, 1, 0, 0)
+  LQ_MMA_CASE(8, 1, 1, 2) LQ_MMA_CASE(8, 1, 1, 4) LQ_MMA_CASE(8, 1, 1, 0)
+  LQ_MMA_CASE(4, 1, 0, 2) LQ_MMA_CASE(4, 1, 0, 4) LQ_MMA_CASE(4, 1, 0, 0)
+  LQ_MMA_CASE(4, 1, 1, 2) LQ_MMA_CASE(4, 1, 1, 4) LQ_MMA_CASE(4, 1, 1, 0)
+  LQ_MMA_CASE(8, 2, 0, 0) LQ_MMA_CASE(8, 2, 1, 0) LQ_MMA_CASE(4, 2, 0, 0) LQ_MMA_CASE(4, 2, 1, 0)
 #undef LQ_MMA_CASE
   return fail(LQ_ERR_ARG, "no tensor-core GEMV instance for bits=%d epilogue=%d", a.bits, a.epilogue);
 }

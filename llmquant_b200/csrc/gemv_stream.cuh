@@ -279,10 +279,10 @@ gemv_stream_kernel(const GemvParams p) {
   // ------------------------------------------------------------ producer warp
   if (warp == KW) {
     if (lane == 0) {
+      int s = 0, wrap = 0;  // ring slot and how often the ring has wrapped, kept without divisions
       for (int it = 0; it < nb; ++it) {
-        const int s = it % p.stages;
         if (it >= p.stages) {
-          if (!mbar_wait(smem_u32(&empty_bar[s]), ((it / p.stages) - 1) & 1)) {
+          if (!mbar_wait(smem_u32(&empty_bar[s]), (wrap - 1) & 1)) {
             atomicExch(p.error_word, 1);
             break;
           }
@@ -295,6 +295,7 @@ gemv_stream_kernel(const GemvParams p) {
         mbar_expect_tx(bar, bytes + p.scale_bytes);
         bulk_g2s(dst, p.codes + (int64_t)b * kU * p.rowbytes, bytes, bar);
         bulk_g2s(dst + p.tile_bytes, p.scales + (int64_t)b * p.groups * kU, p.scale_bytes, bar);
+        if (++s == p.stages) { s = 0; ++wrap; }
       }
     }
     return;
@@ -447,8 +448,8 @@ gemv_stream_kernel(const GemvParams p) {
   LQ_STAMP(3);
   // ---- the row loop over the ring
   const uint32_t ring_base = smem_u32(ring);
+  int s = 0, phase = 0;  // ring slot and its phase bit, kept without divisions
   for (int it = 0; it < nb; ++it) {
-    const int s = it % p.stages;
     const int parity = it & 1;
     const int n0 = (b_begin + it) * kU;
     // bias and residual of this batch's outputs do not depend on the tile: fetch them now,
@@ -465,7 +466,7 @@ gemv_stream_kernel(const GemvParams p) {
         }
       }
     }
-    if (!mbar_wait(smem_u32(&full_bar[s]), (it / p.stages) & 1)) {
+    if (!mbar_wait(smem_u32(&full_bar[s]), phase)) {
       // the KW warps wait for the same stage, so they all give up here together
       if (lane == 0) atomicExch(p.error_word, 2);
       return;
@@ -486,6 +487,7 @@ gemv_stream_kernel(const GemvParams p) {
     }
     __syncwarp();
     if (lane == 0) mbar_arrive(smem_u32(&empty_bar[s]));  // the stage can be refilled
+    if (++s == p.stages) { s = 0; phase ^= 1; }
 
     float acc[M][kU];
 #pragma unroll
