@@ -166,26 +166,32 @@ struct XPlanes {
     int sh = 0, sm = 0, sl = 0;
 #pragma unroll
     for (int w = 0; w < WORDS; ++w) {
-      unsigned ph = 0, pm = 0, pl = 0;
+      // int8: word w byte b meets k = 4w+b. int4: words 0..3 are the even k of weight
+      // word w (k = 8w + 2b), words 4..7 the odd k of weight word w-4.
+      int k[4];
 #pragma unroll
       for (int b = 0; b < 4; ++b) {
-        // int8: word w byte b meets k = 4w+b. int4: words 0..3 are the even k of weight
-        // word w (k = 8w + 2b), words 4..7 the odd k of weight word w-4.
-        int k;
-        if (BITS == 8) k = 4 * w + b;
-        else k = w < 4 ? 8 * w + 2 * b : 8 * (w - 4) + 2 * b + 1;
-        const int mv = m[k];
-        const int h = PLANES == 3 ? (mv >> 16) : (mv >> 8);
-        const int mdl = (mv >> 8) & 0xFF;
-        const int l = mv & 0xFF;
-        ph |= (unsigned)(h & 0xFF) << (8 * b);
-        pm |= (unsigned)mdl << (8 * b);
-        pl |= (unsigned)l << (8 * b);
-        sh += h; sm += mdl; sl += l;
+        if (BITS == 8) k[b] = 4 * w + b;
+        else k[b] = w < 4 ? 8 * w + 2 * b : 8 * (w - 4) + 2 * b + 1;
+      }
+      // byte planes of the four mantissas by byte permutes: byte 0 = low plane, byte 1 = the
+      // high (2 planes) or middle (3 planes) one, byte 2 = the high plane of 3
+      const unsigned m0 = (unsigned)m[k[0]], m1 = (unsigned)m[k[1]], m2 = (unsigned)m[k[2]], m3 = (unsigned)m[k[3]];
+      const unsigned pl = __byte_perm(__byte_perm(m0, m1, 0x0040), __byte_perm(m2, m3, 0x0040), 0x5410);
+      const unsigned p1 = __byte_perm(__byte_perm(m0, m1, 0x0051), __byte_perm(m2, m3, 0x0051), 0x5410);
+      unsigned ph = p1, pm = 0;
+      if (PLANES == 3) {
+        pm = p1;
+        ph = __byte_perm(__byte_perm(m0, m1, 0x0062), __byte_perm(m2, m3, 0x0062), 0x5410);
       }
       hi[w] = ph;
       if (PLANES == 3) mid[w] = pm;
       lo[w] = pl;
+      if (BITS == 4) {  // byte sums for the nibble bias: the high plane is signed, the others unsigned
+        sh = dp4a_ss(ph, 0x01010101u, sh);
+        if (PLANES == 3) sm = dp4a_uu(pm, 0x01010101u, sm);
+        sl = dp4a_uu(pl, 0x01010101u, sl);
+      }
     }
     bias_hi = BITS == 4 ? -8 * sh : 0;
     bias_mid = BITS == 4 ? -8 * sm : 0;

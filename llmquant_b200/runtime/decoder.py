@@ -94,7 +94,7 @@ class FusedLlamaDecoder:
     """Greedy decode of a kernel-mode Llama: eager prefill, then one replayed graph per token."""
 
     def __init__(self, model, max_batch: int, max_len: int, kv_bits: int = 8, use_graph: bool = True,
-                 pdl: bool = True, tp=None):
+                 pdl: bool = True, tp=None, attn_splits: int = 0):
         if not supports(model):
             raise ValueError("FusedLlamaDecoder needs a Llama-layout model whose attention and MLP "
                              "linears are KernelQuantLinear (head_dim 64/128, silu MLP)")
@@ -161,6 +161,8 @@ class FusedLlamaDecoder:
         self.pos = torch.zeros(1, dtype=torch.long, device=dev)
         self.history = torch.zeros(B, max_len + 1, dtype=torch.long, device=dev)
         want = max(1, -(-2 * 148 // (B * self.Hkv)))
+        if attn_splits > 0:  # slices of the cached context per KV head (0 = two CTAs per SM)
+            want = attn_splits
         self.splits = max(1, min(want, max_len // 64 or 1))
         nbytes = native.library().lq_attn_fused_scratch_bytes(B, self.Hq, self.Hkv, self.D, self.splits)
         self.scratch = torch.zeros(-(-nbytes // 4), dtype=torch.float32, device=dev)
