@@ -250,6 +250,9 @@ int lq_attn_decode_kv_i8_static(const void* q, const int8_t* k_codes, const int8
  * KernelQuantLinear.forward (quantizers/kernel.py:68-79,90-91). lq_gemm_device_error is
  * non-zero if a bounded wait for the tensor core ever expired (reads and clears). */
 int lq_gemm_device_error(void);
+/* Which kernel serves int8-activation calls with groups of 128: 0 (default) = the pipelined
+ * kernel (fill, MMA issue and drain in separate warps), 1 = the serial kernel. Same results. */
+void lq_gemm_set_impl(int impl);
 int lq_wq_gemm_prefill(const void* x, int ldx, const int8_t* x_codes, const float* x_scales,
                        const void* codes, const float* scale_tiles, const void* bias, void* out,
                        int M, int N, int K, int Kd, int span, int bits, void* stream);

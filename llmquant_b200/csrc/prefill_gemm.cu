@@ -43,6 +43,18 @@ __device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lbo_bytes,
   return d;
 }
 
+__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t addr) {
+  // K-major rows of 128 bytes, 16-byte pieces XOR-swizzled by (row & 7) (the 128-byte swizzle
+  // mode); 8-row groups 1024 bytes apart; the tile starts on a 1024-byte boundary.
+  uint64_t d = 0;
+  d |= (uint64_t)((addr & 0x3FFFFu) >> 4);
+  d |= (uint64_t)1 << 16;
+  d |= (uint64_t)(1024 >> 4) << 32;
+  d |= (uint64_t)1 << 46;
+  d |= (uint64_t)2 << 61;
+  return d;
+}
+
 // instruction descriptor: D format, A/B formats, K-major both, N/8 and M/16
 constexpr uint32_t idesc(uint32_t c_fmt, uint32_t ab_fmt) {
   return (c_fmt << 4) | (ab_fmt << 7) | (ab_fmt << 10) | ((uint32_t)(BN >> 3) << 17) |
@@ -91,6 +103,7 @@ struct GemmParams {
   __nv_bfloat16* out;       // [M, N]
   int M, N, K, Kd, span, groups, rowbytes;
   int* error_word;
+  int probe;  // timing probes (results wrong): 2 = drain a quarter of the columns, 3 = one MMA per group
 };
 
 // ES = bytes per operand element (2: bf16 operands, 1: int8 operands)
@@ -259,6 +272,246 @@ prefill_gemm_kernel(const GemmParams p) {
   }
 }
 
+
+// ---------------------------------------------------------------------------------------------
+// Pipelined variant for int8 activations (kind::i8) and scale groups of 128 codes: three roles
+// in one CTA, so that the tensor pipe, the dequantizing fill and the scaling drain overlap.
+//
+//   warps 0-3  drain: wait for a group's accumulator in TMEM, tcgen05.ld their lanes (warp w
+//              reads TMEM lanes 32w..32w+31 = token rows), multiply by (activation scale x
+//              weight scale) and add into registers; hand the accumulator back.
+//   warps 4-7  fill: token codes and weight codes of the next group into one of two
+//              shared-memory stages in the K-major core-matrix layout; int4 nibbles become the
+//              signed byte 16 * code ((n ^ 8) << 4, exact; the 1/16 goes into the scale) and
+//              are interleaved back into K order with byte permutes.
+//   warp 8     one thread issues the group's four MMAs into one of two TMEM accumulators and
+//              commits them to two mbarriers: "stage free" for the fill warps, "accumulator
+//              ready" for the drain warps.
+//
+// Handshakes are mbarriers with bounded waits; a wait that expires marks the CTA dead, every
+// role leaves its loop, the error word is set and TMEM is freed.
+constexpr int kWsThreads = 288;
+constexpr int kWsStages = 4;   // shared-memory stages (operand tiles of one group each)
+constexpr int kWsAhead = 3;    // groups whose copies are in flight ahead of the one being handed over
+
+template <int BITS>
+__global__ void __launch_bounds__(kWsThreads)
+prefill_gemm_ws_kernel(const GemmParams p) {
+  extern __shared__ __align__(128) uint8_t smem[];
+  __shared__ __align__(8) uint64_t full_bar[kWsStages], sfree_bar[kWsStages], tfull_bar[2], tfree_bar[2];
+  __shared__ uint32_t tmem_base_s;
+  __shared__ float ws_s[8][BN];
+  __shared__ volatile int dead_s;
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int n0 = blockIdx.x * BN, m0 = blockIdx.y * BM;
+  constexpr int KT = 128;                        // one group: 128 codes = one 128-byte row per tile row
+  constexpr int TILE = BM * KT;                  // bytes of an A or B tile (int8 operands)
+  // Operand tiles: row r at r * 128, its 16-byte piece kc at ((kc ^ (r & 7)) * 16) -- the
+  // 128-byte swizzle of the MMA descriptor. Eight lanes that copy the eight pieces of one row
+  // read one 128-byte line of global memory and write all 32 banks once.
+  uint8_t* const tiles = smem + ((1024u - (smem_u32(smem) & 1023u)) & 1023u);
+  constexpr uint32_t kIdesc = idesc(2, 1);       // s32 <- s8 x s8
+
+  if (warp == 0) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                 ::"r"(smem_u32(&tmem_base_s)), "r"(2 * kTmemCols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  if (tid == 0) {
+    for (int i = 0; i < kWsStages; ++i) {
+      mbar_init(smem_u32(&full_bar[i]), 128);
+      mbar_init(smem_u32(&sfree_bar[i]), 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(smem_u32(&tfull_bar[i]), 1);
+      mbar_init(smem_u32(&tfree_bar[i]), 128);
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    dead_s = 0;
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem_base = tmem_base_s;
+  const int G = p.groups;
+
+  if (warp >= 4 && warp < 8) {
+    // ------------------------------------------------------------------ fill
+    const int ft = tid - 128;  // 0..127 among the fill threads
+    const int r = ft;          // the column whose weight scale this thread stages
+    const int n = n0 + r;
+    uint8_t* raw_base = tiles + kWsStages * 2 * TILE;  // int4: the rows' nibble bytes as they come
+    // Operands travel with cp.async (16 bytes per copy, no registers), kWsAhead groups ahead
+    // of the group being handed to the MMA thread, so the trip to L2 / HBM is off the critical
+    // path. Token codes and int8 weight codes land directly in the swizzled tile; int4 weight
+    // rows land in staging rows and are widened from there by the thread that copied them.
+    auto cp16 = [](uint32_t dst, const void* src, bool valid) {
+      const int bytes = valid ? 16 : 0;  // 0 source bytes: the 16 destination bytes are zero-filled
+      asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(bytes) : "memory");
+    };
+    auto issue = [&](const int g) -> bool {
+      const int st = g % kWsStages;
+      if (g >= kWsStages && !mbar_wait(smem_u32(&sfree_bar[st]), ((g / kWsStages) - 1) & 1)) return false;
+      const uint32_t a_tile = smem_u32(tiles + st * 2 * TILE), b_tile = a_tile + TILE;
+#pragma unroll
+      for (int it = 0; it < 8; ++it) {  // piece (row, kc) = item / 8, item % 8
+        const int item = it * 128 + ft, row = item >> 3, kc = item & 7;
+        const uint32_t dst = (uint32_t)row * 128 + ((kc ^ (row & 7)) << 4);
+        const int m = m0 + row;
+        cp16(a_tile + dst, reinterpret_cast<const uint8_t*>(p.x_codes) + (int64_t)(m < p.M ? m : 0) * p.Kd + g * KT + kc * 16,
+             m < p.M);
+        if (BITS == 8) {
+          const int nn = n0 + row;
+          cp16(b_tile + dst, p.codes + (int64_t)(nn < p.N ? nn : 0) * p.rowbytes + g * KT + kc * 16, nn < p.N);
+        }
+      }
+      if (BITS == 4) {
+#pragma unroll
+        for (int it = 0; it < 4; ++it) {  // staging piece (row, q) = item / 4, item % 4
+          const int item = it * 128 + ft, row = item >> 2, q = item & 3;
+          const int nn = n0 + row;
+          cp16(smem_u32(raw_base + st * (BN * 64) + item * 16),
+               p.codes + (int64_t)(nn < p.N ? nn : 0) * p.rowbytes + g * (KT / 2) + q * 16, nn < p.N);
+        }
+      }
+      {
+        const float* ssrc = p.scale_tiles + ((int64_t)((n < p.N ? n : 0) >> 2) * G + g) * 4 + (n & 3);
+        const int bytes = n < p.N ? 4 : 0;
+        asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;"
+                     ::"r"(smem_u32(&ws_s[g & 7][r])), "l"(ssrc), "r"(bytes) : "memory");
+      }
+      asm volatile("cp.async.commit_group;" ::: "memory");
+      return true;
+    };
+    bool ok = true;
+    for (int g = 0; g < kWsAhead && g < G && ok; ++g) ok = issue(g);
+    for (int g = 0; g < G && ok; ++g) {
+      const int st = g % kWsStages;
+      if (dead_s) break;
+      // the copies of group g are complete once at most (groups issued after g) are pending
+      const int after = min(kWsAhead - 1, G - 1 - g);
+      if (after >= 2) asm volatile("cp.async.wait_group 2;" ::: "memory");
+      else if (after == 1) asm volatile("cp.async.wait_group 1;" ::: "memory");
+      else asm volatile("cp.async.wait_group 0;" ::: "memory");
+      if (BITS == 4) {
+        uint8_t* b_tile = tiles + st * 2 * TILE + TILE;
+#pragma unroll
+        for (int it = 0; it < 4; ++it) {
+          const int item = it * 128 + ft, row = item >> 2, q = item & 3;
+          const uint4 v = *reinterpret_cast<const uint4*>(raw_base + st * (BN * 64) + item * 16);
+          const unsigned w4[4] = {v.x, v.y, v.z, v.w};
+          unsigned o[8];
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            // word of 8 nibbles (code + 8): even positions and odd positions as bytes 16 * code.
+            // A zero-filled row (beyond N) becomes bytes -128: its columns are never stored.
+            const unsigned ev = ((w4[i] << 4) & 0xF0F0F0F0u) ^ 0x80808080u;
+            const unsigned od = (w4[i] & 0xF0F0F0F0u) ^ 0x80808080u;
+            o[2 * i] = __byte_perm(ev, od, 0x5140);      // codes 0..3 of the word
+            o[2 * i + 1] = __byte_perm(ev, od, 0x7362);  // codes 4..7
+          }
+          uint8_t* rowp = b_tile + row * 128;
+          *reinterpret_cast<uint4*>(rowp + (((2 * q) ^ (row & 7)) << 4)) = make_uint4(o[0], o[1], o[2], o[3]);
+          *reinterpret_cast<uint4*>(rowp + (((2 * q + 1) ^ (row & 7)) << 4)) = make_uint4(o[4], o[5], o[6], o[7]);
+        }
+      }
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic / cp.async writes -> MMA reads
+      mbar_arrive(smem_u32(&full_bar[st]));
+      if (g + kWsAhead < G) ok = issue(g + kWsAhead);
+    }
+    if (!ok) dead_s = 1;
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+  } else if (warp == 8) {
+    // ------------------------------------------------------------------ MMA issue
+    if (lane == 0) {
+      for (int g = 0; g < G; ++g) {
+        const int st = g % kWsStages, tb = g & 1;
+        if (dead_s) break;
+        if (!mbar_wait(smem_u32(&full_bar[st]), (g / kWsStages) & 1)) { dead_s = 1; break; }
+        if (g >= 2 && !mbar_wait(smem_u32(&tfree_bar[tb]), ((g >> 1) - 1) & 1)) { dead_s = 1; break; }
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const uint32_t a_addr = smem_u32(tiles + st * 2 * TILE), b_addr = a_addr + TILE;
+#pragma unroll
+        for (int s = 0; s < 4; ++s) {
+          if (p.probe == 3 && s > 0) break;
+          // 32 bytes of K per MMA: the start address moves along the 128-byte row
+          const uint64_t da = smem_desc_sw128(a_addr + s * 32);
+          const uint64_t db = smem_desc_sw128(b_addr + s * 32);
+          mma_i8(tmem_base + tb * kTmemCols, da, db, kIdesc, s > 0);
+        }
+        mma_commit(smem_u32(&sfree_bar[st]));
+        mma_commit(smem_u32(&tfull_bar[tb]));
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ drain
+    float acc[BN];
+#pragma unroll
+    for (int c = 0; c < BN; ++c) acc[c] = 0.f;
+    const int my_m = m0 + tid;
+    bool dead = false;
+    for (int g = 0; g < G; ++g) {
+      const int st = g & 1;
+      if (dead_s) { dead = true; break; }
+      // 1/16 undoes the shift that turned int4 codes into signed bytes
+      const float xs = my_m < p.M ? p.x_scales[(int64_t)my_m * G + g] * (BITS == 4 ? 0.0625f : 1.f) : 0.f;
+      if (!mbar_wait(smem_u32(&tfull_bar[st]), (g >> 1) & 1)) { dead_s = 1; dead = true; break; }
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      const float* wsg = ws_s[g & 7];
+#pragma unroll
+      for (int c0 = 0; c0 < BN; c0 += 32) {
+        if (p.probe == 2 && c0 > 0) break;
+        uint32_t v[32];
+        tmem_ld32(tmem_base + st * kTmemCols + ((uint32_t)(warp * 32) << 16) + c0, v);
+#pragma unroll
+        for (int j = 0; j < 32; ++j) acc[c0 + j] = fmaf((float)(int)v[j] * xs, wsg[c0 + j], acc[c0 + j]);
+      }
+      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+      mbar_arrive(smem_u32(&tfree_bar[st]));
+    }
+    if (!dead && my_m < p.M) {
+      __nv_bfloat16* dst = p.out + (int64_t)my_m * p.N + n0;
+#pragma unroll
+      for (int c = 0; c < BN; ++c) {
+        if (n0 + c < p.N) {
+          float y = acc[c];
+          if (p.bias != nullptr) y += __bfloat162float(p.bias[n0 + c]);
+          dst[c] = __float2bfloat16_rn(y);
+        }
+      }
+    }
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (tid == 0 && dead_s) atomicExch(p.error_word, 2);
+  if (warp == 0) {
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(2 * kTmemCols)
+                 : "memory");
+  }
+}
+
+int g_gemm_impl = 0;  // host-side switch: 0 = pipelined kernel where it applies, 1 = serial kernel
+
+template <int BITS>
+int launch_gemm_ws(const GemmParams& p, cudaStream_t s) {
+  auto kern = prefill_gemm_ws_kernel<BITS>;
+  // operand tiles of kWsStages groups, plus (int4) the staging rows of nibble bytes
+  const size_t smem = 1024 + (size_t)kWsStages * 2 * BM * 128 + (BITS == 4 ? (size_t)kWsStages * BN * 64 : 0);
+  static bool raised = false;
+  if (!raised) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024) != cudaSuccess) {
+      cudaGetLastError();
+      return fail(LQ_ERR_LAUNCH, "lq_wq_gemm_prefill: cannot raise the shared memory limit");
+    }
+    raised = true;
+  }
+  dim3 grid((unsigned)((p.N + BN - 1) / BN), (unsigned)((p.M + BM - 1) / BM));
+  kern<<<grid, kWsThreads, smem, s>>>(p);
+  return check_launch("lq_wq_gemm_prefill");
+}
+
 __device__ int g_gemm_error = 0;
 
 template <int BITS, int ES>
@@ -280,6 +533,8 @@ int launch_gemm(const GemmParams& p, cudaStream_t s) {
 
 }  // namespace
 }  // namespace lq
+
+extern "C" void lq_gemm_set_impl(int impl) { lq::g_gemm_impl = impl; }
 
 extern "C" int lq_gemm_device_error(void) {
   void* ptr = nullptr;
@@ -319,6 +574,8 @@ extern "C" int lq_wq_gemm_prefill(const void* x, int ldx, const int8_t* x_codes,
   }
   p.error_word = (int*)err;
   cudaStream_t s = (cudaStream_t)stream;
+  p.probe = g_gemm_impl;
+  if (a8 && span == 128 && g_gemm_impl != 1) return bits == 8 ? launch_gemm_ws<8>(p, s) : launch_gemm_ws<4>(p, s);
   if (bits == 8) return a8 ? launch_gemm<8, 1>(p, s) : launch_gemm<8, 2>(p, s);
   return a8 ? launch_gemm<4, 1>(p, s) : launch_gemm<4, 2>(p, s);
 }

@@ -43,6 +43,7 @@ _SIGNATURES = {
     "lq_gemv_device_error": [],
     "lq_gemv_set_timeline": [_P],
     "lq_gemv_set_tuning": [_I, _I, _I],
+    "lq_gemm_set_impl": [_I],
     "lq_gemv_tensor_core_ok": [_I, _I, _I, _I],
     "lq_repack_stream": [_P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P],
     "lq_unrepack_stream": [_P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P],
@@ -68,7 +69,7 @@ _SIGNATURES.update({
     "lq_attn_decode_kv_i8_static": [_P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P, _L, _I,
                                     ctypes.c_float, _I, _I, _P],
 })
-_RESTYPE = {"lq_gemv_set_timeline": None, "lq_gemv_set_tuning": None, "lq_attn_set_timeline": None, "lq_attn_set_impl": None, "lq_last_error": ctypes.c_char_p, "lq_attn_decode_scratch_bytes": ctypes.c_int64,
+_RESTYPE = {"lq_gemv_set_timeline": None, "lq_gemm_set_impl": None, "lq_gemv_set_tuning": None, "lq_attn_set_timeline": None, "lq_attn_set_impl": None, "lq_last_error": ctypes.c_char_p, "lq_attn_decode_scratch_bytes": ctypes.c_int64,
             "lq_attn_decode_static_scratch_bytes": ctypes.c_int64,
             "lq_attn_fused_scratch_bytes": ctypes.c_int64}
 
