@@ -102,6 +102,18 @@ int lq_allreduce_residual(const uint64_t* peer_bases_dev, int rank, int world, i
 int lq_wq_gemv(const void* x, const int8_t* qweight, const float* wscale, void* out, int M,
                int N, int groups, int group_size, int out_group, int dtype, void* stream);
 
+/* Stacked-expert decode GEMV (Mixture-of-Experts): x [R, groups*group_size] holds the routed
+ * rows grouped by expert; block b multiplies rows block_row0[b] .. + block_rows[b] (at most
+ * lq_wq_gemv_batched_max_rows() of them) with expert block_expert[b] of qweight
+ * [E, N, groups, group_size] int8 and wscale [E, scale_rows, groups] fp32; out [R, N] in x's
+ * dtype. Rows no block covers are left untouched. Device int32 arrays of length `blocks`.
+ * Replaces wq_gemv_batched (cuda/csrc/wq_gemv_batched.cu:45-185, fake_quant.cpp:14-20,39-51). */
+int lq_wq_gemv_batched_max_rows(void);
+int lq_wq_gemv_batched(const void* x, const int8_t* qweight, const float* wscale,
+                       const int* block_expert, const int* block_row0, const int* block_rows,
+                       void* out, int R, int N, int groups, int group_size, int scale_rows,
+                       int out_group, int blocks, int dtype, void* stream);
+
 /* Device ("streaming") layout of one quantized linear, built once per layer:
  *   codes        [N, Kd] int8 (bits = 8) or [N, Kd/2] bytes of biased nibbles, low nibble
  *                first (bits = 4) -- byte-identical to the model.bin payload when no head
@@ -242,7 +254,13 @@ int lq_attn_decode_kv_i8_static(const void* q, const int8_t* k_codes, const int8
 /* ---------------------------------------------------------------- prefill GEMM (tcgen05 / TMEM)
  * out[m, n] = sum_g s_w[n, g] * s_x[m, g] * sum_{k in g} a[m, k] * q[n, k] on the streaming
  * layout, any M (tiles of 128 tokens x 128 features), out [M, N] bf16, bias bf16 or NULL.
- *   A16: x [M, K] bf16 (x_codes = NULL, s_x = 1): kind::f16 MMA on bf16(code), fp32 accumulate.
+ *   A16: x [M, K] bf16 (x_codes = NULL, s_x = 1): kind::f16 MMA on bf16(code), fp32 accumulate,
+ *        scales applied per group in fp32 (the arithmetic of the reference's real mode). With
+ *        LQ_GEMM_FOLD_SCALES in `flags` the B operand is bf16(float(code) * scale) instead -- the
+ *        weight tensor the reference's kernel mode feeds its library GEMM
+ *        (quantizers/kernel.py:68-79) -- and one accumulator runs over all of K: several
+ *        times faster, with that mode's bf16 rounding of the weights (needs K % 8 == 0 and a
+ *        16-byte aligned x, else the flag is ignored).
  *   A8:  x_codes [M, Kd] int8 + x_scales [M, G] fp32 as lq_quantize_group_i8 produces them
  *        (dynamic, per token per group): kind::i8 MMA, int32 accumulate -- the arithmetic of
  *        RealQuantLinear.forward with an int8 activation scheme (quantizers/real.py:88-99).
@@ -253,9 +271,10 @@ int lq_gemm_device_error(void);
 /* Which kernel serves int8-activation calls with groups of 128: 0 (default) = the pipelined
  * kernel (fill, MMA issue and drain in separate warps), 1 = the serial kernel. Same results. */
 void lq_gemm_set_impl(int impl);
+#define LQ_GEMM_FOLD_SCALES 1
 int lq_wq_gemm_prefill(const void* x, int ldx, const int8_t* x_codes, const float* x_scales,
                        const void* codes, const float* scale_tiles, const void* bias, void* out,
-                       int M, int N, int K, int Kd, int span, int bits, void* stream);
+                       int M, int N, int K, int Kd, int span, int bits, int flags, void* stream);
 
 /* The same GEMV with the work of the neighbouring decoder-layer ops folded in. All fields
  * of lq_wq_gemv_stream, plus:

@@ -92,6 +92,11 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&v)[32]) {
   asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
+__device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
+  const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<const uint32_t*>(&v);
+}
+
 struct GemmParams {
   const __nv_bfloat16* x;   // [M, K] (A16) -- unused for A8
   int ldx;
@@ -277,22 +282,24 @@ prefill_gemm_kernel(const GemmParams p) {
 // Pipelined variant for int8 activations (kind::i8) and scale groups of 128 codes: three roles
 // in one CTA, so that the tensor pipe, the dequantizing fill and the scaling drain overlap.
 //
-//   warps 0-3  drain: wait for a group's accumulator in TMEM, tcgen05.ld their lanes (warp w
-//              reads TMEM lanes 32w..32w+31 = token rows), multiply by (activation scale x
-//              weight scale) and add into registers; hand the accumulator back.
-//   warps 4-7  fill: token codes and weight codes of the next group into one of two
+//   warps 0-7  drain: wait for a group's accumulator in TMEM, tcgen05.ld their part (warp w
+//              reads TMEM lanes 32 (w % 4) .. + 31 = token rows, columns 64 (w / 4) .. + 63),
+//              multiply by (activation scale x weight scale) and add into registers; hand the
+//              accumulator back.
+//   warps 8-11 fill: token codes and weight codes of the next group into one of two
 //              shared-memory stages in the K-major core-matrix layout; int4 nibbles become the
 //              signed byte 16 * code ((n ^ 8) << 4, exact; the 1/16 goes into the scale) and
 //              are interleaved back into K order with byte permutes.
-//   warp 8     one thread issues the group's four MMAs into one of two TMEM accumulators and
+//   warp 12    one thread issues the group's four MMAs into one of two TMEM accumulators and
 //              commits them to two mbarriers: "stage free" for the fill warps, "accumulator
 //              ready" for the drain warps.
 //
 // Handshakes are mbarriers with bounded waits; a wait that expires marks the CTA dead, every
 // role leaves its loop, the error word is set and TMEM is freed.
-constexpr int kWsThreads = 288;
-constexpr int kWsStages = 4;   // shared-memory stages (operand tiles of one group each)
-constexpr int kWsAhead = 3;    // groups whose copies are in flight ahead of the one being handed over
+constexpr int kWsThreads = 416;  // 8 drain warps, 4 fill warps, 1 MMA warp
+constexpr int kWsStages = 5;   // shared-memory stages (operand tiles of one group each)
+constexpr int kWsAhead = 3;    // groups whose copies are in flight ahead of the one being handed over; two
+                               // fewer than the stages, so a refill waits for an MMA issued two groups ago
 
 template <int BITS>
 __global__ void __launch_bounds__(kWsThreads)
@@ -325,7 +332,7 @@ prefill_gemm_ws_kernel(const GemmParams p) {
     }
     for (int i = 0; i < 2; ++i) {
       mbar_init(smem_u32(&tfull_bar[i]), 1);
-      mbar_init(smem_u32(&tfree_bar[i]), 128);
+      mbar_init(smem_u32(&tfree_bar[i]), 256);
     }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     dead_s = 0;
@@ -336,9 +343,9 @@ prefill_gemm_ws_kernel(const GemmParams p) {
   const uint32_t tmem_base = tmem_base_s;
   const int G = p.groups;
 
-  if (warp >= 4 && warp < 8) {
+  if (warp >= 8 && warp < 12) {
     // ------------------------------------------------------------------ fill
-    const int ft = tid - 128;  // 0..127 among the fill threads
+    const int ft = tid - 256;  // 0..127 among the fill threads
     const int r = ft;          // the column whose weight scale this thread stages
     const int n = n0 + r;
     uint8_t* raw_base = tiles + kWsStages * 2 * TILE;  // int4: the rows' nibble bytes as they come
@@ -391,7 +398,8 @@ prefill_gemm_ws_kernel(const GemmParams p) {
       if (dead_s) break;
       // the copies of group g are complete once at most (groups issued after g) are pending
       const int after = min(kWsAhead - 1, G - 1 - g);
-      if (after >= 2) asm volatile("cp.async.wait_group 2;" ::: "memory");
+      if (after >= 3) asm volatile("cp.async.wait_group 3;" ::: "memory");
+      else if (after == 2) asm volatile("cp.async.wait_group 2;" ::: "memory");
       else if (after == 1) asm volatile("cp.async.wait_group 1;" ::: "memory");
       else asm volatile("cp.async.wait_group 0;" ::: "memory");
       if (BITS == 4) {
@@ -422,7 +430,7 @@ prefill_gemm_ws_kernel(const GemmParams p) {
     }
     if (!ok) dead_s = 1;
     asm volatile("cp.async.wait_group 0;" ::: "memory");
-  } else if (warp == 8) {
+  } else if (warp == 12) {
     // ------------------------------------------------------------------ MMA issue
     if (lane == 0) {
       for (int g = 0; g < G; ++g) {
@@ -446,10 +454,12 @@ prefill_gemm_ws_kernel(const GemmParams p) {
     }
   } else {
     // ------------------------------------------------------------------ drain
-    float acc[BN];
+    constexpr int HALF = BN / 2;
+    float acc[HALF];
 #pragma unroll
-    for (int c = 0; c < BN; ++c) acc[c] = 0.f;
-    const int my_m = m0 + tid;
+    for (int c = 0; c < HALF; ++c) acc[c] = 0.f;
+    const int quarter = warp & 3, cbase = (warp >> 2) * HALF;  // TMEM lanes and columns of this warp
+    const int my_m = m0 + quarter * 32 + lane;
     bool dead = false;
     for (int g = 0; g < G; ++g) {
       const int st = g & 1;
@@ -458,12 +468,12 @@ prefill_gemm_ws_kernel(const GemmParams p) {
       const float xs = my_m < p.M ? p.x_scales[(int64_t)my_m * G + g] * (BITS == 4 ? 0.0625f : 1.f) : 0.f;
       if (!mbar_wait(smem_u32(&tfull_bar[st]), (g >> 1) & 1)) { dead_s = 1; dead = true; break; }
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      const float* wsg = ws_s[g & 7];
+      const float* wsg = ws_s[g & 7] + cbase;
 #pragma unroll
-      for (int c0 = 0; c0 < BN; c0 += 32) {
+      for (int c0 = 0; c0 < HALF; c0 += 32) {
         if (p.probe == 2 && c0 > 0) break;
         uint32_t v[32];
-        tmem_ld32(tmem_base + st * kTmemCols + ((uint32_t)(warp * 32) << 16) + c0, v);
+        tmem_ld32(tmem_base + st * kTmemCols + ((uint32_t)(quarter * 32) << 16) + cbase + c0, v);
 #pragma unroll
         for (int j = 0; j < 32; ++j) acc[c0 + j] = fmaf((float)(int)v[j] * xs, wsg[c0 + j], acc[c0 + j]);
       }
@@ -471,12 +481,12 @@ prefill_gemm_ws_kernel(const GemmParams p) {
       mbar_arrive(smem_u32(&tfree_bar[st]));
     }
     if (!dead && my_m < p.M) {
-      __nv_bfloat16* dst = p.out + (int64_t)my_m * p.N + n0;
+      __nv_bfloat16* dst = p.out + (int64_t)my_m * p.N + n0 + cbase;
 #pragma unroll
-      for (int c = 0; c < BN; ++c) {
-        if (n0 + c < p.N) {
+      for (int c = 0; c < HALF; ++c) {
+        if (n0 + cbase + c < p.N) {
           float y = acc[c];
-          if (p.bias != nullptr) y += __bfloat162float(p.bias[n0 + c]);
+          if (p.bias != nullptr) y += __bfloat162float(p.bias[n0 + cbase + c]);
           dst[c] = __float2bfloat16_rn(y);
         }
       }
@@ -492,6 +502,214 @@ prefill_gemm_ws_kernel(const GemmParams p) {
   }
 }
 
+// ---------------------------------------------------------------------------------------------
+// Pipelined variant for bf16 activations (kind::f16). The weight scale is folded into the B
+// operand: a code becomes bf16(float(code) * scale) -- bit for bit the tensor the reference's
+// kernel mode builds before its library GEMM (quantizers/kernel.py:68-79,
+// `(qweight * scale).to(dtype)`) -- so the whole K axis accumulates in ONE TMEM accumulator
+// and is drained once, at the end.
+//
+//   warps 0-7  fill: bf16 token rows by cp.async into a 128-byte-swizzled tile (two 64-column
+//              halves per 128-column stage), weight codes through registers (fetched two
+//              stages ahead) -> float by mantissa injection (exact) -> times the group scale
+//              -> bf16 pairs -> the swizzled B tile. After the last stage the same warps drain
+//              the accumulator (warp w: TMEM lanes 32 (w % 4).., columns 64 (w / 4)..).
+//   warp 8     one thread issues eight MMAs (K = 16 each) per stage and commits them to the
+//              stage's "free" barrier; after the last stage to the "done" barrier.
+constexpr int kF16Threads = 288;
+constexpr int kF16Stages = 3;
+
+template <int BITS>
+__global__ void __launch_bounds__(kF16Threads)
+prefill_gemm_f16_kernel(const GemmParams p) {
+  extern __shared__ __align__(128) uint8_t smem[];
+  __shared__ __align__(8) uint64_t full_bar[kF16Stages], sfree_bar[kF16Stages], done_bar;
+  __shared__ uint32_t tmem_base_s;
+  __shared__ volatile int dead_s;
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int n0 = blockIdx.x * BN, m0 = blockIdx.y * BM;
+  constexpr int KT = 128;                 // K columns per stage
+  constexpr int ATOM = BM * 128;          // bytes of one 64-column half of a tile
+  constexpr int TILE = 2 * ATOM;          // bytes of an A or B tile (bf16 operands)
+  constexpr uint32_t kIdesc = idesc(1, 1);  // f32 <- bf16 x bf16
+  uint8_t* const tiles = smem + ((1024u - (smem_u32(smem) & 1023u)) & 1023u);
+  const int S = p.Kd / KT;                // stages of work (Kd is a multiple of 128 here)
+
+  if (warp == 0) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                 ::"r"(smem_u32(&tmem_base_s)), "r"(kTmemCols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  if (tid == 0) {
+    for (int i = 0; i < kF16Stages; ++i) {
+      mbar_init(smem_u32(&full_bar[i]), 256);
+      mbar_init(smem_u32(&sfree_bar[i]), 1);
+    }
+    mbar_init(smem_u32(&done_bar), 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    dead_s = 0;
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem_base = tmem_base_s;
+
+  if (warp < 8) {
+    // ------------------------------------------------------------------ fill
+    const int ft = tid;                       // 0..255
+    const int brow = ft & 127, half = ft >> 7;  // the weight row and 64-column half this thread widens
+    const int n = n0 + brow;
+    constexpr int NRAW = BITS == 8 ? 4 : 2;   // 16-byte pieces of 64 codes
+    uint4 raw[2][NRAW];
+    float sc[2];
+    auto fetch_b = [&](const int set, const int g) {
+#pragma unroll
+      for (int q = 0; q < NRAW; ++q) raw[set][q] = make_uint4(0, 0, 0, 0);
+      sc[set] = 0.f;  // rows beyond N: every product is zero
+      if (n < p.N && g < S) {
+        const int k0 = g * KT + half * 64;
+        const uint4* src = reinterpret_cast<const uint4*>(p.codes + (int64_t)n * p.rowbytes + k0 * BITS / 8);
+#pragma unroll
+        for (int q = 0; q < NRAW; ++q) raw[set][q] = __ldg(src + q);
+        sc[set] = p.scale_tiles[((int64_t)(n >> 2) * p.groups + k0 / p.span) * 4 + (n & 3)];
+      }
+    };
+    auto cp16 = [](uint32_t dst, const void* src, bool valid) {
+      const int bytes = valid ? 16 : 0;
+      asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(bytes) : "memory");
+    };
+    auto issue_a = [&](const int g) -> bool {
+      const int st = g % kF16Stages;
+      if (g >= kF16Stages && !mbar_wait(smem_u32(&sfree_bar[st]), ((g / kF16Stages) - 1) & 1)) return false;
+      const uint32_t a_tile = smem_u32(tiles + st * 2 * TILE);
+#pragma unroll
+      for (int it = 0; it < 8; ++it) {  // piece (row, pc) = item / 16, item % 16; 8 columns each
+        const int item = it * 256 + ft, row = item >> 4, pc = item & 15;
+        const int m = m0 + row, k = g * KT + pc * 8;
+        const bool valid = m < p.M && k < p.K;
+        const uint32_t dst = (uint32_t)(pc >> 3) * ATOM + (uint32_t)row * 128 + (((pc & 7) ^ (row & 7)) << 4);
+        cp16(a_tile + dst, p.x + (int64_t)(valid ? m : 0) * p.ldx + (valid ? k : 0), valid);
+      }
+      asm volatile("cp.async.commit_group;" ::: "memory");
+      return true;
+    };
+    auto widen_store = [&](const int set, const int g) {
+      uint8_t* rowp = tiles + (g % kF16Stages) * 2 * TILE + TILE + half * ATOM + brow * 128;
+      const float s = sc[set];
+#pragma unroll
+      for (int kc = 0; kc < 8; ++kc) {  // eight columns -> one 16-byte piece
+        float f[8];
+        if (BITS == 4) {
+          const uint4 v = raw[set][kc >> 2];
+          const unsigned w = (kc & 3) == 0 ? v.x : (kc & 3) == 1 ? v.y : (kc & 3) == 2 ? v.z : v.w;
+#pragma unroll
+          for (int j = 0; j < 8; ++j)  // nibble (code + 8) into the mantissa of 2^23: exact
+            f[j] = (__uint_as_float(((w >> (4 * j)) & 0xFu) | 0x4B000000u) - 8388616.f) * s;
+        } else {
+          const uint4 v = raw[set][kc >> 1];
+          const unsigned w0 = ((kc & 1) == 0 ? v.x : v.z) ^ 0x80808080u, w1 = ((kc & 1) == 0 ? v.y : v.w) ^ 0x80808080u;
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {  // byte (code + 128) into the mantissa of 2^23: exact
+            f[j] = (__uint_as_float(__byte_perm(w0, 0x4B000000u, 0x7440u | j)) - 8388736.f) * s;
+            f[4 + j] = (__uint_as_float(__byte_perm(w1, 0x4B000000u, 0x7440u | j)) - 8388736.f) * s;
+          }
+        }
+        uint4 o;
+        o.x = pack_bf16x2(f[0], f[1]); o.y = pack_bf16x2(f[2], f[3]);
+        o.z = pack_bf16x2(f[4], f[5]); o.w = pack_bf16x2(f[6], f[7]);
+        *reinterpret_cast<uint4*>(rowp + ((kc ^ (brow & 7)) << 4)) = o;
+      }
+    };
+    bool ok = true;
+    fetch_b(0, 0);
+    fetch_b(1, 1);
+    for (int g = 0; g < 2 && g < S && ok; ++g) ok = issue_a(g);
+    for (int g = 0; g < S && ok; ++g) {
+      const int st = g % kF16Stages;
+      if (dead_s) break;
+      if (g + 1 < S) asm volatile("cp.async.wait_group 1;" ::: "memory");
+      else asm volatile("cp.async.wait_group 0;" ::: "memory");
+      // the B half of stage st was last read by the MMAs of stage g - 3, which the A copies of
+      // this stage already waited for
+      if ((g & 1) == 0) { widen_store(0, g); fetch_b(0, g + 2); }
+      else { widen_store(1, g); fetch_b(1, g + 2); }
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      mbar_arrive(smem_u32(&full_bar[st]));
+      if (g + 2 < S) ok = issue_a(g + 2);
+    }
+    if (!ok) dead_s = 1;
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+    // ------------------------------------------------------------------ drain (once)
+    if (ok && !dead_s) {
+      if (!mbar_wait(smem_u32(&done_bar), 0)) {
+        dead_s = 1;
+      } else {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const int quarter = warp & 3, cbase = (warp >> 2) * 64;
+        const int my_m = m0 + quarter * 32 + lane;
+#pragma unroll
+        for (int c0 = 0; c0 < 64; c0 += 32) {
+          uint32_t v[32];
+          tmem_ld32(tmem_base + ((uint32_t)(quarter * 32) << 16) + cbase + c0, v);
+          if (my_m < p.M) {
+            __nv_bfloat16* dst = p.out + (int64_t)my_m * p.N + n0 + cbase + c0;
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              if (n0 + cbase + c0 + j < p.N) {
+                float y = __uint_as_float(v[j]);
+                if (p.bias != nullptr) y += __bfloat162float(p.bias[n0 + cbase + c0 + j]);
+                dst[j] = __float2bfloat16_rn(y);
+              }
+            }
+          }
+        }
+      }
+    }
+  } else if (lane == 0) {
+    // ------------------------------------------------------------------ MMA issue
+    bool ok = true;
+    for (int g = 0; g < S; ++g) {
+      const int st = g % kF16Stages;
+      if (dead_s) { ok = false; break; }
+      if (!mbar_wait(smem_u32(&full_bar[st]), (g / kF16Stages) & 1)) { dead_s = 1; ok = false; break; }
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      const uint32_t a_addr = smem_u32(tiles + st * 2 * TILE), b_addr = a_addr + TILE;
+#pragma unroll
+      for (int s = 0; s < 8; ++s) {  // 16 columns (32 bytes) per MMA, four per 64-column half
+        const uint32_t off = (uint32_t)(s >> 2) * ATOM + (s & 3) * 32;
+        mma_f16(tmem_base, smem_desc_sw128(a_addr + off), smem_desc_sw128(b_addr + off), kIdesc, (g > 0 || s > 0) ? 1u : 0u);
+      }
+      mma_commit(smem_u32(&sfree_bar[st]));
+    }
+    if (ok) mma_commit(smem_u32(&done_bar));
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (tid == 0 && dead_s) atomicExch(p.error_word, 3);
+  if (warp == 0) {
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
+  }
+}
+
+template <int BITS>
+int launch_gemm_f16(const GemmParams& p, cudaStream_t s) {
+  auto kern = prefill_gemm_f16_kernel<BITS>;
+  const size_t smem = 1024 + (size_t)kF16Stages * 4 * BM * 128;  // A and B tiles of 32 KB per stage
+  static bool raised = false;
+  if (!raised) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 210 * 1024) != cudaSuccess) {
+      cudaGetLastError();
+      return fail(LQ_ERR_LAUNCH, "lq_wq_gemm_prefill: cannot raise the shared memory limit");
+    }
+    raised = true;
+  }
+  dim3 grid((unsigned)((p.N + BN - 1) / BN), (unsigned)((p.M + BM - 1) / BM));
+  kern<<<grid, kF16Threads, smem, s>>>(p);
+  return check_launch("lq_wq_gemm_prefill");
+}
+
 int g_gemm_impl = 0;  // host-side switch: 0 = pipelined kernel where it applies, 1 = serial kernel
 
 template <int BITS>
@@ -501,7 +719,7 @@ int launch_gemm_ws(const GemmParams& p, cudaStream_t s) {
   const size_t smem = 1024 + (size_t)kWsStages * 2 * BM * 128 + (BITS == 4 ? (size_t)kWsStages * BN * 64 : 0);
   static bool raised = false;
   if (!raised) {
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024) != cudaSuccess) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 210 * 1024) != cudaSuccess) {
       cudaGetLastError();
       return fail(LQ_ERR_LAUNCH, "lq_wq_gemm_prefill: cannot raise the shared memory limit");
     }
@@ -548,7 +766,7 @@ extern "C" int lq_gemm_device_error(void) {
 extern "C" int lq_wq_gemm_prefill(const void* x, int ldx, const int8_t* x_codes, const float* x_scales,
                                   const void* codes, const float* scale_tiles, const void* bias,
                                   void* out, int M, int N, int K, int Kd, int span, int bits,
-                                  void* stream) {
+                                  int flags, void* stream) {
   using namespace lq;
   LQ_REQUIRE(bits == 4 || bits == 8, LQ_ERR_ARG, "unsupported num_bits %d, expected 4 or 8", bits);
   LQ_REQUIRE(M >= 0 && N >= 0 && K >= 0 && Kd >= K, LQ_ERR_ARG, "bad shape M=%d N=%d K=%d Kd=%d", M, N, K, Kd);
@@ -576,6 +794,10 @@ extern "C" int lq_wq_gemm_prefill(const void* x, int ldx, const int8_t* x_codes,
   cudaStream_t s = (cudaStream_t)stream;
   p.probe = g_gemm_impl;
   if (a8 && span == 128 && g_gemm_impl != 1) return bits == 8 ? launch_gemm_ws<8>(p, s) : launch_gemm_ws<4>(p, s);
+  // bf16 activations: the pipelined kernel needs 16-byte pieces of x (8 columns) to be whole
+  if (!a8 && (flags & LQ_GEMM_FOLD_SCALES) && g_gemm_impl != 1 && Kd % 128 == 0 && K % 8 == 0 && ldx % 8 == 0 &&
+      (uintptr_t)x % 16 == 0)
+    return bits == 8 ? launch_gemm_f16<8>(p, s) : launch_gemm_f16<4>(p, s);
   if (bits == 8) return a8 ? launch_gemm<8, 1>(p, s) : launch_gemm<8, 2>(p, s);
   return a8 ? launch_gemm<4, 1>(p, s) : launch_gemm<4, 2>(p, s);
 }

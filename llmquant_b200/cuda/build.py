@@ -90,12 +90,42 @@ class _Kernels:
 
     @staticmethod
     def wq_gemv_batched_max_rows():
-        return 8
+        return int(native.library().lq_wq_gemv_batched_max_rows())
 
     @staticmethod
     def wq_gemv_batched(x, qweight, wscale, block_expert, block_row0, block_rows, out_group=0):
-        raise NotImplementedError(
-            "wq_gemv_batched (stacked-expert GEMV) is not built yet in this library")
+        """Stacked-expert GEMV: rows of `x` grouped by expert, one (expert, first row, row
+        count) triple per block (llmquant/cuda/csrc/wq_gemv_batched.cu:133-185)."""
+        if not (x.is_cuda and qweight.is_cuda and wscale.is_cuda):
+            raise RuntimeError("tensors must be CUDA")
+        if qweight.dim() != 4:
+            raise RuntimeError("qweight must be [E, N, groups, group_size]")
+        if wscale.dim() != 3:
+            raise RuntimeError("wscale must be [E, scale_rows, groups]")
+        if qweight.dtype != torch.int8:
+            raise RuntimeError("qweight must be int8")
+        if wscale.dtype != torch.float32:
+            raise RuntimeError("wscale must be float32")
+        if x.dtype not in (torch.float16, torch.bfloat16):
+            raise RuntimeError("wq_gemv_batched takes float16 or bfloat16 activations")
+        xc, qw, ws = x.contiguous(), qweight.contiguous(), wscale.contiguous()
+        dev = xc.device
+        be = block_expert.to(device=dev, dtype=torch.int32).contiguous()
+        br0 = block_row0.to(device=dev, dtype=torch.int32).contiguous()
+        brn = block_rows.to(device=dev, dtype=torch.int32).contiguous()
+        rows, n, groups, gs = xc.shape[0], qw.shape[1], qw.shape[2], qw.shape[3]
+        if xc.shape[1] != groups * gs:
+            raise RuntimeError("x width must be groups * group_size")
+        if gs % 4 != 0 or gs // 4 > 32:
+            raise RuntimeError("group_size must be a multiple of 4 and at most 128")
+        out = torch.empty(rows, n, dtype=xc.dtype, device=dev)
+        if be.numel() == 0 or rows == 0:
+            return out
+        with torch.cuda.device(dev):
+            native.call("lq_wq_gemv_batched", xc.data_ptr(), qw.data_ptr(), ws.data_ptr(), be.data_ptr(),
+                        br0.data_ptr(), brn.data_ptr(), out.data_ptr(), rows, n, groups, gs, ws.shape[1],
+                        int(out_group), be.numel(), native.DTYPE_ID[xc.dtype], native.stream_ptr(dev))
+        return out
 
 
 @functools.lru_cache(maxsize=1)

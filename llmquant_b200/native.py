@@ -17,6 +17,7 @@ LIB_PATH = PKG / "libllmquant_b200.so"
 HEADER = PKG.parent / "include" / "llmquant_b200.h"
 
 LQ_F32, LQ_F16, LQ_BF16 = 0, 1, 2
+GEMM_FOLD_SCALES = 1  # lq_wq_gemm_prefill flags
 DTYPE_ID = {torch.float32: LQ_F32, torch.float16: LQ_F16, torch.bfloat16: LQ_BF16}
 
 _P, _I, _L = ctypes.c_void_p, ctypes.c_int, ctypes.c_int64
@@ -31,7 +32,7 @@ _SIGNATURES = {
     "lq_quantize_weight": [_P, _I, _I, _I, _I, _I, _I, _I, _P, _P, _P],
     "lq_residual_add": [_P, _P, _P, _L, _I, _P],
     "lq_gemm_device_error": [],
-    "lq_wq_gemm_prefill": [_P, _I, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P],
+    "lq_wq_gemm_prefill": [_P, _I, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P],
     "lq_allreduce_max_world": [],
     "lq_allreduce_device_error": [],
     "lq_allreduce_residual": [_P, _I, _I, _I, _L, _L, _P, _P, _P, _I, _I, _P],
@@ -43,6 +44,8 @@ _SIGNATURES = {
     "lq_gemv_device_error": [],
     "lq_gemv_set_timeline": [_P],
     "lq_gemv_set_tuning": [_I, _I, _I],
+    "lq_wq_gemv_batched_max_rows": [],
+    "lq_wq_gemv_batched": [_P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P],
     "lq_gemm_set_impl": [_I],
     "lq_gemv_tensor_core_ok": [_I, _I, _I, _I],
     "lq_repack_stream": [_P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P],

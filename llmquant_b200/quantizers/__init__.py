@@ -8,6 +8,7 @@ from llmquant_b200.quantizers.kernel import (
     quantize_weight_canonical,
 )
 
+from llmquant_b200.quantizers.experts import KernelQuantExperts, quantize_expert_stack
 from llmquant_b200.quantizers.kv_cache import KernelQuantCache, QuantizedKVLayer, make_cache_factory
 
 AVAILABLE_MODES = frozenset({"kernel"})
@@ -21,7 +22,8 @@ def quant_linear_for(mode: str):
 
 
 __all__ = [
-    "AVAILABLE_MODES", "DECODE_MAX_ROWS", "KERNEL_MAX_ROWS", "KernelQuantCache", "KernelQuantLinear",
+    "AVAILABLE_MODES", "DECODE_MAX_ROWS", "KERNEL_MAX_ROWS", "KernelQuantCache", "KernelQuantExperts",
+    "KernelQuantLinear", "quantize_expert_stack",
     "QuantizedKVLayer", "make_cache_factory",
     "pad_activation", "quant_linear_for", "quantize_weight_canonical",
 ]

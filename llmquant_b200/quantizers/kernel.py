@@ -26,10 +26,13 @@ from llmquant_b200.core.scheme import QuantizationScheme
 KERNEL_MAX_ROWS = 4
 DECODE_MAX_ROWS = 8
 GEMV_VARIANT = 0  # 0 = library default; see lq_wq_gemv_stream
-# Rows up to which lq_wq_gemm_prefill (tcgen05, exact integer codes) serves the prefill; its
-# first version does not yet overlap tile fills with the MMAs, and above this many rows the
-# reference's own choice (dequantize to bf16 + library GEMM) is still the faster one.
-PREFILL_TENSOR_CORE_MAX_ROWS = 128
+# Prefill rows: up to PREFILL_EXACT_MAX_ROWS the tcgen05 GEMM keeps the real mode's arithmetic
+# (exact integer sums per group, scaled in fp32); from there to PREFILL_TENSOR_CORE_MAX_ROWS it
+# multiplies by bf16(code * scale) in one pass over K -- the same weights the reference's
+# kernel mode dequantizes for its library GEMM (llmquant/quantizers/kernel.py:68-79), without
+# materialising them; above that, dequantize + library GEMM is still the faster of the two.
+PREFILL_EXACT_MAX_ROWS = 16
+PREFILL_TENSOR_CORE_MAX_ROWS = 1024
 
 
 def _canonical_geometry(out_features, in_features, args):
@@ -224,10 +227,13 @@ class KernelQuantLinear(nn.Module):
             native.call("lq_wq_gemv_fused", ctypes.byref(args), native.stream_ptr(flat.device))
         return out
 
-    def gemm(self, flat, a8: bool = False):
+    def gemm(self, flat, a8: bool = False, fold_scales: bool = False):
         """Prefill GEMM on the tensor cores for any number of rows: `[M, K]` bf16 -> `[M, N]`
         bf16. `a8=True` quantizes the activations per token per group to int8 first (the
-        reference's dynamic activation scheme) and multiplies integers."""
+        reference's dynamic activation scheme) and multiplies integers. `fold_scales=True`
+        (bf16 activations only) multiplies by `bf16(code * scale)`, the weight the reference's
+        kernel mode dequantizes for its library GEMM, instead of scaling exact integer sums
+        per group: faster, with that mode's rounding."""
         m = flat.shape[0]
         out = torch.empty(m, self.out_features, dtype=torch.bfloat16, device=flat.device)
         if m == 0:
@@ -253,7 +259,9 @@ class KernelQuantLinear(nn.Module):
             native.call("lq_wq_gemm_prefill", flat.data_ptr(), flat.stride(0), native.ptr(x_codes),
                         native.ptr(x_scales), self.codes.data_ptr(), self.scale_tiles.data_ptr(),
                         native.ptr(bias), out.data_ptr(), m, self.out_features, self.in_features,
-                        self._kd, self._span, self.num_bits, native.stream_ptr(flat.device))
+                        self._kd, self._span, self.num_bits,
+                        native.GEMM_FOLD_SCALES if (fold_scales and not a8) else 0,
+                        native.stream_ptr(flat.device))
         return out
 
     def forward(self, x):
@@ -266,7 +274,7 @@ class KernelQuantLinear(nn.Module):
             out = self.gemv(flat)
         elif (self._stream and m <= PREFILL_TENSOR_CORE_MAX_ROWS and flat.dtype == torch.bfloat16
               and self._span in (64, 128)):
-            out = self.gemm(flat)
+            out = self.gemm(flat, fold_scales=m > PREFILL_EXACT_MAX_ROWS)
         elif not self._stream and m <= DECODE_MAX_ROWS:
             from llmquant_b200.cuda.build import load_extension
 

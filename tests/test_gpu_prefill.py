@@ -63,3 +63,31 @@ def test_prefill_gemm_against_oracle(bits, shape):
     rows = module.gemv(x[:4].cuda())
     assert rel_l2(got16[:4].float().cpu().numpy(), rows.float().cpu().numpy()) <= TOL
     assert native.library().lq_gemm_device_error() == 0
+
+
+@pytest.mark.parametrize("bits", [4, 8])
+@pytest.mark.parametrize("shape", [(200, 300, 512), (48, 4096, 4096), (129, 1024, 1152), (600, 2048, 2048)])
+def test_folded_scale_gemm_is_the_reference_kernel_mode_product(bits, shape):
+    """With the scales folded into the operand the kernel multiplies by bf16(code * scale): the
+    tensor the reference's kernel mode dequantizes (quantizers/kernel.py:68-79) before its
+    library GEMM. Compared with exactly that product in fp32, and with the real-mode oracle at
+    the looser bound the weights' bf16 rounding (2^-9 per weight) implies."""
+    m, n, k = shape
+    w = seeded((n, k), 21, 0.02, torch.bfloat16)
+    x = seeded((m, k), 22, 1.0, torch.bfloat16)
+    module = _module(w, bits)
+    got = module.gemm(x.cuda(), fold_scales=True).float().cpu().numpy()
+    q, scale = oracle.quantize_weight(w.float().numpy(), bits, 128)
+    groups = scale.shape[1]
+    padded = np.zeros((n, groups * 128), dtype=np.float32)
+    padded[:, :k] = q
+    dense = (padded.reshape(n, groups, 128) * scale.reshape(n, groups, 1).astype(np.float32)).reshape(n, -1)
+    dense = torch.from_numpy(dense).bfloat16().float()[:, :k]
+    same = (x.float() @ dense.T).numpy()
+    assert rel_l2(got, same) <= 2.5e-3            # only the bf16 rounding of the output and the sum order differ
+    assert rel_l2(got, oracle.bf16_bits_to_f32(oracle.f32_to_bf16_bits(same))) <= 4e-4
+    want = oracle.real_linear(x.float().numpy(), q, scale, bits, 128)
+    assert rel_l2(got, want) <= 4e-3
+    # the module's forward takes this path above PREFILL_EXACT_MAX_ROWS rows
+    assert torch.equal(module(x.cuda()), module.gemm(x.cuda(), fold_scales=True))
+    assert native.library().lq_gemm_device_error() == 0
