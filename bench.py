@@ -474,13 +474,38 @@ def run_decode(args, rank, world, device):
     barrier()
     e2e_s = (time.perf_counter() - t0) / args.steps
 
-    times = torch.tensor([step_ms, e2e_s], dtype=torch.float64, device=device)
+    # ---- the dominant kernel by itself: every GEMV launch of a step (4 per layer + lm_head),
+    # same fusions and buffers, captured as one graph and timed with CUDA events
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        dec.gemv_launches()
+    torch.cuda.current_stream().wait_stream(side)
+    torch.cuda.synchronize()
+    gemv_graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(gemv_graph):
+        dec.gemv_launches()
+    for _ in range(3):
+        gemv_graph.replay()
+    barrier()
+    g0, g1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    g0.record()
+    for _ in range(args.steps):
+        gemv_graph.replay()
+    g1.record()
+    barrier()
+    gemv_ms = g0.elapsed_time(g1) / args.steps
+    gemv_launches = 4 * len(dec.layers) + 1
+
+    times = torch.tensor([step_ms, e2e_s, gemv_ms], dtype=torch.float64, device=device)
     if world > 1:
         dist.all_reduce(times, op=dist.ReduceOp.MAX)
-    step_ms, e2e_s = times.tolist()
+    step_ms, e2e_s, gemv_ms = times.tolist()
     peaks, peak_kind = measured_peaks()
     step_bytes = decode_step_bytes(dec, context)
-    achieved = step_bytes / (step_ms * 1e-3) / 1e9
+    step_achieved = step_bytes / (step_ms * 1e-3) / 1e9
+    gemv_bytes = dec.gemv_bytes()
+    achieved = gemv_bytes / (gemv_ms * 1e-3) / 1e9
     line = {
         "metric": "decode_tokens_per_s", "value": round(batch / (step_ms * 1e-3), 1),
         "unit": "tok/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
@@ -495,8 +520,17 @@ def run_decode(args, rank, world, device):
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peaks["hbm_gbs"],
                      "unit": "GB/s", "frac": round(achieved / peaks["hbm_gbs"], 4),
                      "frac_of_nominal_8TBs": round(achieved / 8000.0, 4), "peak_kind": peak_kind,
-                     "traffic": None, "kernel": "gemv_stream_kernel (whole decode step timed, per GPU)",
-                     "bytes_per_step": step_bytes},
+                     # ncu (profiles/gemv_stream_ncu_full.md): DRAM bytes of a launch are 1.006x
+                     # (lm_head, int8) and 1.03x (gate|up, int4) its algorithmic bytes
+                     "traffic": int(gemv_bytes * 1.02) // gemv_launches,
+                     "traffic_source": "ncu captures of two shapes (1.006x and 1.03x algorithmic), scaled",
+                     "kernel": f"gemv_stream_kernel, the {gemv_launches} launches of one step timed alone "
+                               f"as a graph (per GPU); achieved / traffic are per launch on average",
+                     "algorithmic_bytes_per_launch": gemv_bytes // gemv_launches,
+                     "us_per_launch": round(gemv_ms * 1e3 / gemv_launches, 2),
+                     "share_of_step": round(gemv_ms / step_ms, 3),
+                     "whole_step": {"bytes": step_bytes, "achieved": round(step_achieved, 1),
+                                    "frac": round(step_achieved / peaks["hbm_gbs"], 4)}},
         "e2e": {"value": round(batch / e2e_s, 1), "unit": "tok/s",
                 "h2d_bytes_per_step": batch * 8, "d2h_bytes_per_step": batch * 8},
         "gpu_launches": dec.launches_per_step * args.steps,

@@ -203,6 +203,28 @@ class FusedLlamaDecoder:
         self.pos.add_(1)
         self.history.index_copy_(1, self.pos, self.tokens.unsqueeze(1))
 
+    def gemv_launches(self):
+        """Only the GEMV launches of one step, in order and with the step's own fusions and
+        buffers (no attention, no all-reduce, no token bookkeeping): what a benchmark captures
+        to time the dominant kernel by itself. Leaves the hidden-state buffers overwritten."""
+        cur, nxt = self.h
+        for spec in self.layers:
+            spec["qkv"].gemv(cur, norm_weight=spec["ln1"], norm_eps=self.eps, pdl=self.pdl, out=self.qkv)
+            spec["o"].gemv(self.attn, residual=cur, pdl=self.pdl, out=nxt)
+            spec["gate_up"].gemv(nxt, norm_weight=spec["ln2"], norm_eps=self.eps, epilogue=1,
+                                 pdl=self.pdl, out=self.act)
+            spec["down"].gemv(self.act, residual=nxt, pdl=self.pdl, out=cur)
+        if isinstance(self.lm_head, KernelQuantLinear) and self.lm_head._stream:
+            self.lm_head.gemv(cur, norm_weight=self.final_norm, norm_eps=self.eps, pdl=self.pdl,
+                              out=self.local_logits if self.tp else self.logits)
+
+    def gemv_bytes(self):
+        """Algorithmic HBM bytes of `gemv_launches`: codes + scales of every linear."""
+        total = sum(spec[key].weight_bytes() for spec in self.layers for key in ("qkv", "o", "gate_up", "down"))
+        if isinstance(self.lm_head, KernelQuantLinear):
+            total += self.lm_head.weight_bytes()
+        return total
+
     def _row_parallel(self, linear, x, residual, out, slot):
         """out = residual + linear(x). One GPU: fused in the GEMV epilogue. Tensor parallel:
         fp32 partial, summed over the ranks (one-shot kernel over peer memory, or NCCL),
