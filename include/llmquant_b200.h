@@ -146,7 +146,8 @@ int lq_dequant_stream(const void* codes, const float* scale_tiles, void* out, in
  * x [M, K] bf16 (row stride ldx elements), K real in_features (K <= Kd; columns beyond K
  * read as zero), out [M, N] of out_dtype (LQ_BF16 or LQ_F32), bias bf16 [N] or NULL,
  * residual (out_dtype, [M, N]) or NULL added after the bias.
- * variant: 0 = default, 1 = fp32 FMA arithmetic, 2 / 3 = integer dot products on 16- / 24-bit
+ * variant: 0 = default (2, or 4 where a second pass over the weight would be needed: 3+ rows on
+ * int4, 5+ rows on int8, shapes variant 4 accepts), 1 = fp32 FMA arithmetic, 2 / 3 = integer dot products on 16- / 24-bit
  * block-floating-point activations (32-column blocks), 4 = tensor-core integer products
  * (mma.sync) on 15-bit block-floating-point activations (128-column blocks; needs span == 128
  * and a shape lq_gemv_tensor_core_ok accepts, else LQ_ERR_UNSUPPORTED).
