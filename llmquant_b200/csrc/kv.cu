@@ -1178,23 +1178,32 @@ attn_mma_kernel(const __nv_bfloat16* __restrict__ qkv, const __nv_bfloat16* __re
     }
   }
   __syncthreads();
-  for (int i = threadIdx.x; i < G * D; i += NT) {
-    const int g = i / D, d = i % D;
+  // one thread merges the two outputs (g, d) and (g, d + D/2): the warps' weights exp(m_w - m)
+  // are computed once for both
+  for (int i = threadIdx.x; i < G * (D / 2); i += NT) {
+    const int g = i / (D / 2), d = i % (D / 2);
     float mm = owner ? snew_s[g] : -INFINITY;
     for (int w = 0; w < NW; ++w) mm = fmaxf(mm, mw_s[w][g]);
-    float acc = 0.f;
+    float acc0 = 0.f, acc1 = 0.f, lt = 0.f;
     for (int w = 0; w < NW; ++w) {
       const float mw = mw_s[w][g];
-      if (mw != -INFINITY) acc = fmaf(ow_s[w][g][d], __expf(mw - mm), acc);
-    }
-    if (owner) acc = fmaf(vnew_s[d] * newscale_s[1], __expf(snew_s[g] - mm), acc);
-    part_o[(((int64_t)b * Hq + kvh * G + g) * ns + split) * D + d] = acc;
-    if (d == 0) {
-      float lt = owner ? __expf(snew_s[g] - mm) : 0.f;
-      for (int w = 0; w < NW; ++w) {
-        const float mw = mw_s[w][g];
-        if (mw != -INFINITY) lt = fmaf(lw_s[w][g], __expf(mw - mm), lt);
+      if (mw != -INFINITY) {
+        const float e = __expf(mw - mm);
+        acc0 = fmaf(ow_s[w][g][d], e, acc0);
+        acc1 = fmaf(ow_s[w][g][d + D / 2], e, acc1);
+        lt = fmaf(lw_s[w][g], e, lt);
       }
+    }
+    if (owner) {
+      const float e = __expf(snew_s[g] - mm);
+      acc0 = fmaf(vnew_s[d] * newscale_s[1], e, acc0);
+      acc1 = fmaf(vnew_s[d + D / 2] * newscale_s[1], e, acc1);
+      lt += e;
+    }
+    float* po = part_o + (((int64_t)b * Hq + kvh * G + g) * ns + split) * D;
+    po[d] = acc0;
+    po[d + D / 2] = acc1;
+    if (d == 0) {
       float* ml = part_ml + (((int64_t)b * Hq + kvh * G + g) * ns + split) * 2;
       ml[0] = mm; ml[1] = lt;
     }
@@ -1218,10 +1227,11 @@ attn_mma_kernel(const __nv_bfloat16* __restrict__ qkv, const __nv_bfloat16* __re
   // The first batch of partial outputs is requested before the slice weights are known, so
   // that the two trips to L2 overlap.
   constexpr int PER_LANE = (G * D + 31) / 32;
-  float v[4][PER_LANE];
+  constexpr int VB = PER_LANE <= 16 ? 5 : 4;  // slices per warp fetched at once (register budget)
+  float v[VB][PER_LANE];
   auto load_batch = [&](int s0) {
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
+    for (int j = 0; j < VB; ++j) {
       const int s = s0 + j * NW;
 #pragma unroll
       for (int k = 0; k < PER_LANE; ++k) {
@@ -1233,16 +1243,33 @@ attn_mma_kernel(const __nv_bfloat16* __restrict__ qkv, const __nv_bfloat16* __re
   };
   load_batch(warp);
   for (int g = warp; g < G; g += NW) {
-    const int64_t base = ((int64_t)b * Hq + kvh * G + g) * ns;
-    float mm = -INFINITY;
-    for (int s = lane; s < ns; s += 32) mm = fmaxf(mm, __ldcg(part_ml + (base + s) * 2));
+    // (max, sum) of every slice of this head: one 8-byte load per slice, kept in registers for
+    // up to 64 slices, so the maximum and the weights cost one trip to L2, not three
+    const float2* mlp = reinterpret_cast<const float2*>(part_ml) + ((int64_t)b * Hq + kvh * G + g) * ns;
+    float2 held[2];
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+      const int s = lane + 32 * j;
+      held[j] = s < ns ? __ldcg(mlp + s) : make_float2(-INFINITY, 0.f);
+    }
+    float mm = fmaxf(held[0].x, held[1].x);
+    for (int s = lane + 64; s < ns; s += 32) mm = fmaxf(mm, __ldcg(mlp + s).x);
     mm = warp_max(mm);
     float lt = 0.f;
-    for (int s = lane; s < ns; s += 32) {
-      const float ms = __ldcg(part_ml + (base + s) * 2);
-      const float ws = (ms == -INFINITY) ? 0.f : __expf(ms - mm);
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+      const int s = lane + 32 * j;
+      if (s < ns) {
+        const float ws = (held[j].x == -INFINITY) ? 0.f : __expf(held[j].x - mm);
+        wsl[s * G + g] = ws;
+        lt = fmaf(held[j].y, ws, lt);
+      }
+    }
+    for (int s = lane + 64; s < ns; s += 32) {
+      const float2 e = __ldcg(mlp + s);
+      const float ws = (e.x == -INFINITY) ? 0.f : __expf(e.x - mm);
       wsl[s * G + g] = ws;
-      lt = fmaf(__ldcg(part_ml + (base + s) * 2 + 1), ws, lt);
+      lt = fmaf(e.y, ws, lt);
     }
     lt = warp_sum(lt);
     if (lane == 0) lsum[g] = lt;
@@ -1251,10 +1278,10 @@ attn_mma_kernel(const __nv_bfloat16* __restrict__ qkv, const __nv_bfloat16* __re
   float part[PER_LANE];
 #pragma unroll
   for (int k = 0; k < PER_LANE; ++k) part[k] = 0.f;
-  for (int s0 = warp; s0 < ns; s0 += 4 * NW) {
+  for (int s0 = warp; s0 < ns; s0 += VB * NW) {
     if (s0 != warp) load_batch(s0);
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
+    for (int j = 0; j < VB; ++j) {
       const int s = s0 + j * NW;
       if (s < ns) {
 #pragma unroll
