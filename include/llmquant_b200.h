@@ -164,7 +164,8 @@ int lq_gemv_device_error(void);
 
 /* Diagnostics: when set to a device buffer of 8 * grid uint64, every GEMV CTA writes
  * %globaltimer stamps of its phases there (start, barriers ready, producer kernel done,
- * activations prepared, first tile landed, end). NULL (the default) switches it off. */
+ * activations prepared, first tile landed, end, and with a fused RMSNorm: sum of squares done,
+ * rstd done). NULL (the default) switches it off. */
 void lq_gemv_set_timeline(void* device_buffer);
 /* 1 if variant 4 of the GEMV serves M activation rows against a weight of Kd stored columns in
  * groups of `span` at `bits` per code, else 0 (the other variants serve every shape). */

@@ -407,6 +407,7 @@ gemv_stream_kernel(const GemvParams p) {
         }
       ss[m] = warp_sum(ss[m]);
     }
+    LQ_STAMP(6);
     if (KW > 1) {
       if (lane == 0) {
 #pragma unroll
@@ -422,6 +423,7 @@ gemv_stream_kernel(const GemvParams p) {
     }
 #pragma unroll
     for (int m = 0; m < M; ++m) rstd[m] = __frsqrt_rn(ss[m] / (float)p.K + p.norm_eps);
+    LQ_STAMP(7);
   }
 
   // ---- per-lane activation state
