@@ -315,7 +315,8 @@ gemv_mma_kernel(const MmaParams p) {
       for (int q = 0; q < 4; ++q) { hw[q] = 0; lw[q] = 0; }
 #pragma unroll
       for (int i = 0; i < 16; ++i) {
-        const int m = __float2int_rn(f[i] * up);
+        // round-to-nearest-even by adding 1.5 * 2^23 in the FMA (|m| < 2^15), not a conversion
+        const int m = __float_as_int(fmaf(f[i], up, 12582912.f)) - 0x4B400000;
         const int h = (m + 128) >> 8;
         const int l = m - h * 256;
         // int8: word q = columns 4q .. 4q+3. int4: word 2j = even columns of the j-th eight,

@@ -160,9 +160,15 @@ struct XPlanes {
     constexpr int MBITS = PLANES == 3 ? 22 : 14;  // |mantissa| < 2^(MBITS+1)
     const float up = __uint_as_float((unsigned)(127 + MBITS - e) << 23);
     unit = __uint_as_float((unsigned)(127 - MBITS + e) << 23);
+    // Mantissas as integers. Two planes: |m| < 2^15, so adding 1.5 * 2^23 in the same FMA
+    // leaves round-to-nearest-even(m) in the low mantissa bits (the low 16 bits of the float's
+    // pattern are m's two's complement), on the FMA pipe instead of the conversion unit, which
+    // the set-up of a whole wave of CTAs would otherwise saturate. Three planes (|m| < 2^23) do
+    // not fit that trick and convert.
     int m[EPL];
 #pragma unroll
-    for (int i = 0; i < EPL; ++i) m[i] = __float2int_rn(xf[i] * up);
+    for (int i = 0; i < EPL; ++i)
+      m[i] = PLANES == 3 ? __float2int_rn(xf[i] * up) : __float_as_int(fmaf(xf[i], up, 12582912.f));
     int sh = 0, sm = 0, sl = 0;
 #pragma unroll
     for (int w = 0; w < WORDS; ++w) {
