@@ -257,7 +257,8 @@ extern "C" int lq_wq_gemv_fused(const lq_gemv_args* a, void* stream) {
   LQ_REQUIRE((size_t)stages * p.stage_bytes <= 200 * 1024, LQ_ERR_UNSUPPORTED,
              "row tile of %d bytes does not fit the shared-memory ring", p.stage_bytes);
   p.stages = stages;
-  const int threads = (p.KW + 1) * 32;
+  // consumers + producer, and with more than one consumer warp the finisher
+  const int threads = (p.KW + (p.KW > 1 ? 2 : 1)) * 32;
   cudaStream_t s = (cudaStream_t)stream;
   if (bits == 8) {
     if (variant == 1) return run_b8v1(p, *a, spw, threads, s);

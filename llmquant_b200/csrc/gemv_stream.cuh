@@ -260,13 +260,14 @@ __device__ __forceinline__ float reduce4(const float (&v)[kU], int lane) {
 // out[m, n/2] = silu(gate) * up with the roundings of a bf16 MLP (gate, up, silu(gate) and
 // the product are each rounded to bf16).
 template <int BITS, int VAR, int M, int SPW, int EPI>
-__global__ void __launch_bounds__((kMaxWarps + 1) * 32)
+__global__ void __launch_bounds__((kMaxWarps + 2) * 32)
 gemv_stream_kernel(const GemvParams p) {
   constexpr int EPL = BITS == 8 ? 16 : 32;
   extern __shared__ __align__(128) uint8_t ring[];
   __shared__ __align__(8) uint64_t full_bar[kMaxStages], empty_bar[kMaxStages];
   __shared__ float red[2][kMaxWarps][M * kU];
   __shared__ float nrm[kMaxWarps][M];
+  __shared__ volatile int dead_s;  // a pipeline wait expired: everyone winds down
 
   const int lane = threadIdx.x & 31;
   const int warp = threadIdx.x >> 5;
@@ -284,9 +285,16 @@ gemv_stream_kernel(const GemvParams p) {
       mbar_init(smem_u32(&full_bar[s]), 1);
       mbar_init(smem_u32(&empty_bar[s]), KW);
     }
+    dead_s = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   __syncthreads();
+  // With more than one consumer warp a further warp (index KW + 1) finishes the rows: it sums
+  // the consumers' partials of a batch and runs the epilogue while they are already on the
+  // next batch. One named barrier per batch, which it shares, hands a batch over; the
+  // partials are double-buffered, and because the finisher arrives at a barrier only after
+  // it is done with the batch before, a buffer is never overwritten while it is read.
+  const int round_threads = (KW + 1) * 32;
 
   // ------------------------------------------------------------ producer warp
   if (warp == KW) {
@@ -308,6 +316,64 @@ gemv_stream_kernel(const GemvParams p) {
         bulk_g2s(dst, p.codes + (int64_t)b * kU * p.rowbytes, bytes, bar);
         bulk_g2s(dst + p.tile_bytes, p.scales + (int64_t)b * p.groups * kU, p.scale_bytes, bar);
         if (++s == p.stages) { s = 0; ++wrap; }
+      }
+    }
+    return;
+  }
+
+  // ------------------------------------------------------------ finisher warp
+  if (warp == KW + 1) {
+    asm volatile("griddepcontrol.wait;" ::: "memory");  // the residual comes from earlier kernels
+    for (int it = 0; it < nb; ++it) {
+      const int parity = it & 1;
+      const int n0 = (b_begin + it) * kU;
+      const int m = lane / kU, u = lane % kU;
+      const int n = n0 + u;
+      const bool mine = lane < M * kU && n < p.N && m < p.M;
+      // bias and residual do not depend on the products: fetch them before the hand-over
+      float bias_pre = 0.f, res_pre = 0.f;
+      if (EPI == 0 && mine) {
+        if (p.bias != nullptr) bias_pre = __bfloat162float(p.bias[n]);
+        if (p.residual != nullptr) {
+          const int64_t po = (int64_t)m * p.N + n;
+          res_pre = p.out_f32 ? reinterpret_cast<const float*>(p.residual)[po]
+                              : __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p.residual)[po]);
+        }
+      }
+      asm volatile("bar.sync 1, %0;" ::"r"(round_threads) : "memory");
+      if (dead_s) return;
+      float total = 0.f;
+      if (lane < M * kU) {
+        float t0 = 0.f, t1 = 0.f;  // two chains, so the loads of a pair are in flight together
+        int w = 0;
+        for (; w + 1 < KW; w += 2) {
+          t0 += red[parity][w][lane];
+          t1 += red[parity][w + 1][lane];
+        }
+        if (w < KW) t0 += red[parity][w][lane];
+        total = t0 + t1;
+      }
+      if (EPI == 1) {
+        const float up = __shfl_down_sync(0xffffffffu, total, 1);
+        if (lane < M * kU && (u & 1) == 0 && n + 1 < p.N && m < p.M) {
+          const float g = __bfloat162float(__float2bfloat16_rn(total));
+          const float uq = __bfloat162float(__float2bfloat16_rn(up));
+          const float sg = __bfloat162float(__float2bfloat16_rn(g / (1.f + expf(-g))));
+          const float y = sg * uq;
+          const int64_t o = (int64_t)m * (p.N / 2) + n / 2;
+          if (p.out_f32) reinterpret_cast<float*>(p.out)[o] = __bfloat162float(__float2bfloat16_rn(y));
+          else reinterpret_cast<__nv_bfloat16*>(p.out)[o] = __float2bfloat16_rn(y);
+        }
+      } else if (mine) {
+        total += bias_pre;
+        const int64_t o = (int64_t)m * p.N + n;
+        if (p.out_f32) {
+          reinterpret_cast<float*>(p.out)[o] = total + res_pre;
+        } else {
+          // a bf16 layer output added to a bf16 residual stream: round, add, round
+          if (p.residual != nullptr) total = __bfloat162float(__float2bfloat16_rn(total)) + res_pre;
+          reinterpret_cast<__nv_bfloat16*>(p.out)[o] = __float2bfloat16_rn(total);
+        }
       }
     }
     return;
@@ -419,7 +485,7 @@ gemv_stream_kernel(const GemvParams p) {
 #pragma unroll
         for (int m = 0; m < M; ++m) nrm[warp][m] = ss[m];
       }
-      asm volatile("bar.sync 1, %0;" ::"r"(barrier_threads) : "memory");
+      asm volatile("bar.sync 2, %0;" ::"r"(barrier_threads) : "memory");
 #pragma unroll
       for (int m = 0; m < M; ++m) {
         float t = 0.f;
@@ -469,7 +535,7 @@ gemv_stream_kernel(const GemvParams p) {
     // bias and residual of this batch's outputs do not depend on the tile: fetch them now,
     // so their latency hides behind the wait for the tile and the dot products
     float bias_pre = 0.f, res_pre = 0.f;
-    if (EPI == 0 && kw == 0 && lane < M * kU) {
+    if (EPI == 0 && KW == 1 && lane < M * kU) {  // with a finisher warp, that warp fetches them
       const int pm = lane / kU, pn = n0 + lane % kU;
       if (pn < p.N && pm < p.M) {
         if (p.bias != nullptr) bias_pre = __bfloat162float(p.bias[pn]);
@@ -481,8 +547,13 @@ gemv_stream_kernel(const GemvParams p) {
       }
     }
     if (!mbar_wait(smem_u32(&full_bar[s]), phase)) {
-      // the KW warps wait for the same stage, so they all give up here together
+      // the KW warps wait for the same stage, so they all give up here together; the finisher
+      // is released from its barrier and sees the flag
       if (lane == 0) atomicExch(p.error_word, 2);
+      if (KW > 1) {
+        dead_s = 1;
+        asm volatile("bar.arrive 1, %0;" ::"r"(round_threads) : "memory");
+      }
       return;
     }
     if (it == 0) LQ_STAMP(4);
@@ -527,20 +598,15 @@ gemv_stream_kernel(const GemvParams p) {
 #pragma unroll
         for (int m = 0; m < M; ++m) red[parity][warp][m * kU + lane] = tot[m];
       }
-      asm volatile("bar.sync 1, %0;" ::"r"(barrier_threads) : "memory");
-    }
-    if (kw == 0) {
+      // hand the batch to the finisher warp (which arrives once it is done with the one before)
+      asm volatile("bar.sync 1, %0;" ::"r"(round_threads) : "memory");
+    } else {
       float total = 0.f;
-      if (KW > 1) {
-        if (lane < M * kU)
-          for (int w = 0; w < KW; ++w) total += red[parity][w][lane];
-      } else {
-        // lane u (< 4) holds row u for every m: lane (m, u) fetches it (all lanes shuffle)
+      // lane u (< 4) holds row u for every m: lane (m, u) fetches it (all lanes shuffle)
 #pragma unroll
-        for (int m = 0; m < M; ++m) {
-          const float v = __shfl_sync(0xffffffffu, tot[m], lane % kU);
-          if (lane / kU == m) total = v;
-        }
+      for (int m = 0; m < M; ++m) {
+        const float v = __shfl_sync(0xffffffffu, tot[m], lane % kU);
+        if (lane / kU == m) total = v;
       }
       const int m = lane / kU, u = lane % kU;
       const int n = n0 + u;
