@@ -995,12 +995,27 @@ attn_mma_kernel(const __nv_bfloat16* __restrict__ qkv, const __nv_bfloat16* __re
   __syncthreads();
   // cached rows and the cursor are older than the kernel ahead of this one: prefetch first
   if (warp == 0 && t_lo < t_hi) issue(t_lo);
+  // so are the rotary tables and the cached rows' scales: the pieces this thread needs first
+  // are requested before the wait for the producer of q|k|v, off the dependent chain
+  const int64_t tpos = pos < table_len ? pos : table_len - 1;
+  float pre_cs[4] = {0.f, 0.f, 0.f, 0.f};
+  if ((int)threadIdx.x < G * HALF) {
+    const int d = threadIdx.x % HALF;
+    pre_cs[0] = __bfloat162float(cos_t[tpos * D + d]);
+    pre_cs[1] = __bfloat162float(sin_t[tpos * D + d]);
+    pre_cs[2] = __bfloat162float(cos_t[tpos * D + d + HALF]);
+    pre_cs[3] = __bfloat162float(sin_t[tpos * D + d + HALF]);
+  }
+  float pre_sk = 0.f, pre_sv = 0.f;
+  if ((int)threadIdx.x < min(CAP, t_hi - t_lo)) {
+    pre_sk = ks[head_row + t_lo + threadIdx.x];
+    pre_sv = vs[head_row + t_lo + threadIdx.x];
+  }
 
   asm volatile("griddepcontrol.wait;" ::: "memory");
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
   ATT_STAMP(1);
-  const int64_t tpos = pos < table_len ? pos : table_len - 1;
   const int heads = Hq + 2 * Hkv;
   const __nv_bfloat16* row = qkv + (int64_t)b * heads * D;
   auto r16 = [](float x) { return __bfloat162float(__float2bfloat16_rn(x)); };
@@ -1009,8 +1024,11 @@ attn_mma_kernel(const __nv_bfloat16* __restrict__ qkv, const __nv_bfloat16* __re
     const int g = i / HALF, d = i % HALF;
     const __nv_bfloat16* src = row + (int64_t)(kvh * G + g) * D;
     const float a = __bfloat162float(src[d]), c = __bfloat162float(src[d + HALF]);
-    const float c0 = __bfloat162float(cos_t[tpos * D + d]), s0 = __bfloat162float(sin_t[tpos * D + d]);
-    const float c1 = __bfloat162float(cos_t[tpos * D + d + HALF]), s1 = __bfloat162float(sin_t[tpos * D + d + HALF]);
+    const bool first = i == (int)threadIdx.x;  // the prefetched table entries are this d's
+    const float c0 = first ? pre_cs[0] : __bfloat162float(cos_t[tpos * D + d]);
+    const float s0 = first ? pre_cs[1] : __bfloat162float(sin_t[tpos * D + d]);
+    const float c1 = first ? pre_cs[2] : __bfloat162float(cos_t[tpos * D + d + HALF]);
+    const float s1 = first ? pre_cs[3] : __bfloat162float(sin_t[tpos * D + d + HALF]);
     q_s[g][d] = r16(r16(a * c0) + r16(-c * s0));
     q_s[g][d + HALF] = r16(r16(c * c1) + r16(a * s1));
   }
@@ -1100,8 +1118,9 @@ attn_mma_kernel(const __nv_bfloat16* __restrict__ qkv, const __nv_bfloat16* __re
   for (int c_lo = t_lo; c_lo < t_hi; c_lo += CAP) {
     const int n = min(CAP, t_hi - c_lo);
     for (int i = threadIdx.x; i < n; i += NT) {
-      sk_s[i] = ks[head_row + c_lo + i];
-      sv_s[i] = vs[head_row + c_lo + i];
+      const bool pre = c_lo == t_lo && i == (int)threadIdx.x;  // CAP <= NT: the first chunk is prefetched
+      sk_s[i] = pre ? pre_sk : ks[head_row + c_lo + i];
+      sv_s[i] = pre ? pre_sv : vs[head_row + c_lo + i];
     }
     __syncthreads();
     if (!mbar_wait(bar_a, phase)) { dead = true; break; }
