@@ -18,9 +18,11 @@
 // walks DOWN the rows. Everything that depends only on the column -- the activation values,
 // their block exponent, the nibble-bias correction -- is prepared once per lane and stays in
 // registers; per row: one 128-bit shared-memory load, a dot product, one multiply by the
-// (group, row) scale. The KW partial sums meet in shared memory behind a named barrier. No
-// tensor cores: the kernel is HBM-bound and the arithmetic is sized to stay under the
-// instruction-issue budget of a 6.5 TB/s stream.
+// (group, row) scale. The KW partial sums meet in shared memory behind a named barrier, where a
+// further warp (the finisher) picks them up: it adds them, applies bias / residual / SiLU*mul
+// and stores, while the consumers are already on the next rows -- the serial tail of a row
+// batch is off the path the stream depends on. No tensor cores: the kernel is HBM-bound and
+// the arithmetic is sized to stay under the instruction-issue budget of a 6.5 TB/s stream.
 //
 // Every wait on an mbarrier is bounded by a clock limit; on expiry the kernel records an
 // error word (lq_gemv_device_error) and returns instead of spinning.
