@@ -40,4 +40,6 @@ def main(ref_root):
 
 
 if __name__ == "__main__":
-    main(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    if len(sys.argv) < 2:
+        sys.exit("usage: python %s <path to an llm-quant checkout>" % sys.argv[0])
+    main(sys.argv[1])
