@@ -430,6 +430,9 @@ def run_decode(args, rank, world, device):
     if ctx:
         tpmod.wrap_for_prefill_(model, ctx)
     new = args.warmup + 2 * args.steps + 8
+    if args.ring:
+        from llmquant_b200 import native
+        native.library().lq_gemv_set_ring_policy(*[int(v) for v in args.ring.split(",")])
     dec = FusedLlamaDecoder(model, batch, prompt + new + 8, kv_bits=8, tp=ctx, attn_splits=args.attn_splits)
     g = torch.Generator().manual_seed(1)
     host_ids = torch.randint(0, model.config.vocab_size, (batch, prompt), generator=g).pin_memory()
@@ -666,6 +669,7 @@ def main():
     ap.add_argument("--norm", type=int, default=0)
     ap.add_argument("--pdl", type=int, default=1)
     ap.add_argument("--variant", type=int, default=0)
+    ap.add_argument("--ring", default="", help="GEMV ring policy: consumer warps per SM, KB per SM (0 = default)")
     ap.add_argument("--attn-splits", type=int, default=0, help="decode workloads: context slices per KV head (0 = default)")
     ap.add_argument("--tune", default="", help="gemv_one, variant 4: warps,rows-per-stage,stages (0 = default)")
     ap.add_argument("--batch", type=int, default=1)

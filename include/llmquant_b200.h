@@ -167,6 +167,11 @@ int lq_gemv_device_error(void);
  * activations prepared, first tile landed, end, and with a fused RMSNorm: sum of squares done,
  * rstd done). NULL (the default) switches it off. */
 void lq_gemv_set_timeline(void* device_buffer);
+/* Ring depth policy of the streaming GEMV (0 = the library's choice): consumer warps per SM to
+ * aim at (default 20) and shared memory per SM one kernel's rings may take in KB (default 112,
+ * about half an SM, so the next kernel's CTAs fit beside). Process-wide; for benchmarking.
+ * No counterpart in the reference. */
+void lq_gemv_set_ring_policy(int consumer_warps_per_sm, int kb_per_sm);
 /* 1 if variant 4 of the GEMV serves M activation rows against a weight of Kd stored columns in
  * groups of `span` at `bits` per code, else 0 (the other variants serve every shape). */
 int lq_gemv_tensor_core_ok(int M, int Kd, int span, int bits);

@@ -13,6 +13,7 @@ int run_b8v2(GemvParams, const lq_gemv_args&, int, int, cudaStream_t);
 bool mma_eligible(const lq_gemv_args& a);
 int run_mma(const lq_gemv_args& a, int* error_word, unsigned long long* debug, cudaStream_t s);
 int run_b8v3(GemvParams, const lq_gemv_args&, int, int, cudaStream_t);
+int g_ring_kb_launch = 112;
 }  // namespace gemv
 
 namespace {
@@ -119,6 +120,8 @@ int repack_common(const int8_t* canonical, const float* wscale, void* codes, flo
   return check_launch(inverse ? "lq_unrepack_stream" : "lq_repack_stream");
 }
 
+int g_ring_warps = 20;  // consumer warps per SM the ring depth policy aims at
+int g_ring_kb = 112;    // shared memory per SM the rings of one kernel may take
 __device__ int g_gemv_error = 0;
 unsigned long long* g_debug_timeline = nullptr;  // host-side: where kernels write their stamps
 
@@ -176,6 +179,12 @@ extern "C" int lq_dequant_stream(const void* codes, const float* scale_tiles, vo
                                                   Kd * bits / 8, span, Kd / span, bits);
   });
   return check_launch("lq_dequant_stream");
+}
+
+extern "C" void lq_gemv_set_ring_policy(int consumer_warps_per_sm, int kb_per_sm) {
+  lq::g_ring_warps = consumer_warps_per_sm > 0 ? consumer_warps_per_sm : 20;
+  lq::g_ring_kb = kb_per_sm > 0 ? kb_per_sm : 112;
+  lq::gemv::g_ring_kb_launch = lq::g_ring_kb;
 }
 
 extern "C" void lq_gemv_set_timeline(void* device_buffer) {
@@ -251,8 +260,8 @@ extern "C" int lq_wq_gemv_fused(const lq_gemv_args* a, void* stream) {
   // Ring depth: enough CTAs per SM for ~20 consumer warps (the dot products are dependent
   // chains and need warps to hide their latency), all rings together within ~112 KB per SM so
   // that the next kernel's CTAs can become resident early (see launch_one).
-  const int want_ctas = (20 + p.KW - 1) / p.KW;
-  int stages = (112 * 1024) / (want_ctas * p.stage_bytes);
+  const int want_ctas = (g_ring_warps + p.KW - 1) / p.KW;
+  int stages = (g_ring_kb * 1024) / (want_ctas * p.stage_bytes);
   stages = stages < 2 ? 2 : (stages > kMaxStages ? kMaxStages : stages);
   LQ_REQUIRE((size_t)stages * p.stage_bytes <= 200 * 1024, LQ_ERR_UNSUPPORTED,
              "row tile of %d bytes does not fit the shared-memory ring", p.stage_bytes);

@@ -46,6 +46,7 @@ namespace gemv {
 constexpr int kU = 4;           // output rows per batch (one float4 of scales)
 constexpr int kMaxWarps = 16;   // consumer warps per CTA (one more warp produces)
 constexpr int kMaxStages = 8;
+extern int g_ring_kb_launch;  // shared memory per SM the rings of one kernel may take (KB)
 
 struct GemvParams {
   const __nv_bfloat16* x;
@@ -668,7 +669,7 @@ int launch_one(const GemvParams& p, int threads, cudaStream_t s) {
   // NEXT kernel on the stream (programmatic dependent launch) find room to become resident
   // and fill their own rings while this kernel is still computing.
   int per_sm = occ;
-  const int by_smem = (int)((112 * 1024) / (smem > 0 ? smem : 1));
+  const int by_smem = (int)(((size_t)g_ring_kb_launch * 1024) / (smem > 0 ? smem : 1));
   if (by_smem >= 1 && per_sm > by_smem) per_sm = by_smem;
   const int cap = sm_count() * per_sm;
   int grid = p.nbatch < cap ? p.nbatch : cap;

@@ -44,6 +44,7 @@ _SIGNATURES = {
     "lq_gemv_device_error": [],
     "lq_gemv_set_timeline": [_P],
     "lq_gemv_set_tuning": [_I, _I, _I],
+    "lq_gemv_set_ring_policy": [_I, _I],
     "lq_wq_gemv_batched_max_rows": [],
     "lq_wq_gemv_batched": [_P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P],
     "lq_gemm_set_impl": [_I],
@@ -72,7 +73,7 @@ _SIGNATURES.update({
     "lq_attn_decode_kv_i8_static": [_P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P, _L, _I,
                                     ctypes.c_float, _I, _I, _P],
 })
-_RESTYPE = {"lq_gemv_set_timeline": None, "lq_gemm_set_impl": None, "lq_gemv_set_tuning": None, "lq_attn_set_timeline": None, "lq_attn_set_impl": None, "lq_last_error": ctypes.c_char_p, "lq_attn_decode_scratch_bytes": ctypes.c_int64,
+_RESTYPE = {"lq_gemv_set_timeline": None, "lq_gemv_set_ring_policy": None, "lq_gemm_set_impl": None, "lq_gemv_set_tuning": None, "lq_attn_set_timeline": None, "lq_attn_set_impl": None, "lq_last_error": ctypes.c_char_p, "lq_attn_decode_scratch_bytes": ctypes.c_int64,
             "lq_attn_decode_static_scratch_bytes": ctypes.c_int64,
             "lq_attn_fused_scratch_bytes": ctypes.c_int64}
 
