@@ -367,14 +367,16 @@ def run_gemm_sweep(args, device):
         lin.weight = torch.nn.Parameter(w, requires_grad=False)
         mod = KernelQuantLinear.from_linear(lin, scheme)
         del w, lin
-        for m in (16, 128, 512, 2048):
+        for m in ([int(v) for v in args.rows.split(',')] if args.rows else (16, 128, 512, 2048)):
             x = torch.randn(m, k, generator=g, device=device).to(torch.bfloat16)
             flops = 2.0 * m * n * k
             t8 = timed(lambda: mod.gemm(x, a8=True))
-            t16 = timed(lambda: mod.gemm(x))
+            t16 = timed(lambda: mod.gemm(x, fold_scales=True))
+            t16x = timed(lambda: mod.gemm(x))
             tlib = timed(lambda: x @ mod._dequantized_weight(torch.bfloat16).T)
             rows.append({"shape": name, "M": m, "N": n, "K": k,
                          "a8_tflops": round(flops / t8 / 1e9, 1), "a16_tflops": round(flops / t16 / 1e9, 1),
+                         "a16_exact_tflops": round(flops / t16x / 1e9, 1),
                          "dequant_plus_library_tflops": round(flops / tlib / 1e9, 1),
                          "a8_ms": round(t8, 4), "a16_ms": round(t16, 4), "dequant_plus_library_ms": round(tlib, 4)})
     best = max(r["a8_tflops"] for r in rows)
@@ -669,6 +671,7 @@ def main():
     ap.add_argument("--norm", type=int, default=0)
     ap.add_argument("--pdl", type=int, default=1)
     ap.add_argument("--variant", type=int, default=0)
+    ap.add_argument("--rows", default="", help="prefill_gemm: comma-separated token counts (default 16,128,512,2048)")
     ap.add_argument("--ring", default="", help="GEMV ring policy: consumer warps per SM, KB per SM (0 = default)")
     ap.add_argument("--attn-splits", type=int, default=0, help="decode workloads: context slices per KV head (0 = default)")
     ap.add_argument("--tune", default="", help="gemv_one, variant 4: warps,rows-per-stage,stages (0 = default)")

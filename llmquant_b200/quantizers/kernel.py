@@ -30,9 +30,12 @@ GEMV_VARIANT = 0  # 0 = library default; see lq_wq_gemv_stream
 # (exact integer sums per group, scaled in fp32); from there to PREFILL_TENSOR_CORE_MAX_ROWS it
 # multiplies by bf16(code * scale) in one pass over K -- the same weights the reference's
 # kernel mode dequantizes for its library GEMM (llmquant/quantizers/kernel.py:68-79), without
-# materialising them; above that, dequantize + library GEMM is still the faster of the two.
+# materialising them; above that, and for narrow outputs (too few 128 x 128 tiles to fill the
+# GPU), dequantize + library GEMM is still the faster of the two (measured crossover: between
+# 512 and 768 rows at the Llama-3-8B shapes; 1024 output features lose at every row count).
 PREFILL_EXACT_MAX_ROWS = 16
-PREFILL_TENSOR_CORE_MAX_ROWS = 1024
+PREFILL_TENSOR_CORE_MAX_ROWS = 512
+PREFILL_TENSOR_CORE_MIN_FEATURES = 2048
 
 
 def _canonical_geometry(out_features, in_features, args):
@@ -273,6 +276,7 @@ class KernelQuantLinear(nn.Module):
         if self._stream and m <= DECODE_MAX_ROWS and flat.dtype == torch.bfloat16:
             out = self.gemv(flat)
         elif (self._stream and m <= PREFILL_TENSOR_CORE_MAX_ROWS and flat.dtype == torch.bfloat16
+              and (self.out_features >= PREFILL_TENSOR_CORE_MIN_FEATURES or m <= PREFILL_EXACT_MAX_ROWS)
               and self._span in (64, 128)):
             out = self.gemm(flat, fold_scales=m > PREFILL_EXACT_MAX_ROWS)
         elif not self._stream and m <= DECODE_MAX_ROWS:

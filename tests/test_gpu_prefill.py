@@ -88,6 +88,14 @@ def test_folded_scale_gemm_is_the_reference_kernel_mode_product(bits, shape):
     assert rel_l2(got, oracle.bf16_bits_to_f32(oracle.f32_to_bf16_bits(same))) <= 4e-4
     want = oracle.real_linear(x.float().numpy(), q, scale, bits, 128)
     assert rel_l2(got, want) <= 4e-3
-    # the module's forward takes this path above PREFILL_EXACT_MAX_ROWS rows
-    assert torch.equal(module(x.cuda()), module.gemm(x.cuda(), fold_scales=True))
+    # the module's forward takes this path between PREFILL_EXACT_MAX_ROWS and
+    # PREFILL_TENSOR_CORE_MAX_ROWS rows when the output is wide enough to fill the GPU, and the
+    # same bf16 weights through the library GEMM otherwise
+    from llmquant_b200.quantizers import kernel as kq
+
+    fwd = module(x.cuda())
+    if m <= kq.PREFILL_TENSOR_CORE_MAX_ROWS and n >= kq.PREFILL_TENSOR_CORE_MIN_FEATURES:
+        assert torch.equal(fwd, module.gemm(x.cuda(), fold_scales=True))
+    else:
+        assert rel_l2(fwd.float().cpu().numpy(), got) <= 3e-3
     assert native.library().lq_gemm_device_error() == 0
