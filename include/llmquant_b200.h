@@ -180,6 +180,19 @@ int lq_gemv_tensor_core_ok(int M, int Kd, int span, int bits);
  * benchmarking. No counterpart in the reference. */
 void lq_gemv_set_tuning(int warps, int rows, int stages);
 
+/* ---------------------------------------------------------------- decode step bookkeeping
+ * Two small kernels that keep the token loop on the device and inside the dependent-launch
+ * chain; they take the place of the host-driven copy_ / fill_ / argmax per token of the
+ * reference's graphed decoder (runtime/graph_decode.py:40-157).
+ * lq_embed_gather: hidden[b, :] = table[tokens[b], :] (bf16 [vocab, H] -> [B, H]).
+ * lq_next_token: tokens[b] = argmax over logits[b, :V] (bf16; the lowest index among equal
+ * maxima), history[b, *pos + 1] = tokens[b] (history [B, hist_len] int64 or NULL), then *pos += 1
+ * once every row has read it. `ticket` is one device int32 holding zero between calls. */
+int lq_embed_gather(const void* table, const int64_t* tokens, void* hidden, int B, int H,
+                    int64_t vocab, int pdl, void* stream);
+int lq_next_token(const void* logits, int64_t V, int64_t* tokens, int64_t* pos, int64_t* history,
+                  int64_t hist_len, int* ticket, int B, int pdl, void* stream);
+
 /* ---------------------------------------------------------------- quantized KV cache
  * Storage per layer: codes [B, Hkv, Tmax, D] int8, scales [B, Hkv, Tmax, ceil(D/128)] fp32.
  * A position / length can be given on the host (`pos`, `len`) or through a device int64

@@ -44,6 +44,8 @@ _SIGNATURES = {
     "lq_gemv_device_error": [],
     "lq_gemv_set_timeline": [_P],
     "lq_gemv_set_tuning": [_I, _I, _I],
+    "lq_embed_gather": [_P, _P, _P, _I, _I, ctypes.c_int64, _I, _P],
+    "lq_next_token": [_P, ctypes.c_int64, _P, _P, _P, ctypes.c_int64, _P, _I, _I, _P],
     "lq_gemv_set_ring_policy": [_I, _I],
     "lq_wq_gemv_batched_max_rows": [],
     "lq_wq_gemv_batched": [_P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P],

@@ -160,6 +160,10 @@ class FusedLlamaDecoder:
         self.tokens = torch.zeros(B, dtype=torch.long, device=dev)
         self.pos = torch.zeros(1, dtype=torch.long, device=dev)
         self.history = torch.zeros(B, max_len + 1, dtype=torch.long, device=dev)
+        self.ticket = torch.zeros(1, dtype=torch.int32, device=dev)
+        # the step's bookkeeping (embedding gather, argmax, cursor, history) in the library's two
+        # small kernels when the tensors are what they expect, else with torch ops
+        self._glue = (self.embed.dtype == bf16 and self.embed.is_contiguous() and self.embed.device == dev)
         want = max(1, -(-2 * 148 // (B * self.Hkv)))
         if attn_splits > 0:  # slices of the cached context per KV head (0 = two CTAs per SM)
             want = attn_splits
@@ -168,7 +172,7 @@ class FusedLlamaDecoder:
         self.scratch = torch.zeros(-(-nbytes // 4), dtype=torch.float32, device=dev)
         self.cache = KernelQuantCache(kv_bits, max_cache_len=max_len)
         self.graph = None
-        self.launches_per_step = len(self.layers) * (7 if self.tp else 5) + 1
+        self.launches_per_step = len(self.layers) * (7 if self.tp else 5) + 1 + (2 if self._glue else 0)
         self.allreduce = "none" if not self.tp else ("peer-memory one-shot kernel" if self.peer is not None else "nccl")
 
     # ------------------------------------------------------------------ one token
@@ -176,7 +180,11 @@ class FusedLlamaDecoder:
         stream = native.stream_ptr(self.device)
         pdl = 1 if self.pdl else 0
         cur, nxt = self.h
-        cur.copy_(self.embed.index_select(0, self.tokens))
+        if self._glue:
+            native.call("lq_embed_gather", self.embed.data_ptr(), self.tokens.data_ptr(), cur.data_ptr(),
+                        self.B, self.hidden, self.embed.shape[0], pdl, stream)
+        else:
+            cur.copy_(self.embed.index_select(0, self.tokens))
         pos_ptr = self.pos.data_ptr()
         for spec, cache in zip(self.layers, self.cache.layers):
             spec["qkv"].gemv(cur, norm_weight=spec["ln1"], norm_eps=self.eps, pdl=self.pdl, out=self.qkv)
@@ -199,9 +207,14 @@ class FusedLlamaDecoder:
         else:
             with torch.no_grad():
                 self.logits.copy_(self.lm_head(self.model.model.norm(cur)))
-        torch.argmax(self.logits, dim=-1, out=self.tokens)
-        self.pos.add_(1)
-        self.history.index_copy_(1, self.pos, self.tokens.unsqueeze(1))
+        if self._glue:
+            native.call("lq_next_token", self.logits.data_ptr(), self.logits.shape[1], self.tokens.data_ptr(),
+                        pos_ptr, self.history.data_ptr(), self.history.shape[1], self.ticket.data_ptr(),
+                        self.B, pdl, stream)
+        else:
+            torch.argmax(self.logits, dim=-1, out=self.tokens)
+            self.pos.add_(1)
+            self.history.index_copy_(1, self.pos, self.tokens.unsqueeze(1))
 
     def gemv_launches(self):
         """Only the GEMV launches of one step, in order and with the step's own fusions and

@@ -140,3 +140,33 @@ def test_decoder_against_the_reference_real_mode_run(golden, tag, kw):
     assert rel_l2(fused_logits, want_logits[:, 1:]) <= 2e-2
     ok = (fused_logits.argmax(-1) == want_logits[:, 1:].argmax(-1))[decided[:, 1:]]
     assert ok.all()
+
+
+@pytest.mark.parametrize("B", [1, 3, 8])
+def test_step_bookkeeping_kernels(B):
+    """lq_embed_gather and lq_next_token against the torch ops they replace (argmax with the
+    lowest index among equal maxima, history write at the advanced cursor, one cursor step)."""
+    from llmquant_b200 import native
+
+    V, H, L = 5000, 264, 32
+    stream = native.stream_ptr(torch.device("cuda", torch.cuda.current_device()))
+    table = seeded((V, H), 71).bfloat16().cuda()
+    logits = seeded((B, V), 72).bfloat16().cuda()
+    logits[0, 4000] = 50.0
+    logits[0, 17] = 50.0          # equal maxima: the lower index wins
+    if B > 1:
+        logits[1, V - 1] = 60.0   # the last element
+    tokens = torch.full((B,), -1, dtype=torch.long, device="cuda")
+    pos = torch.tensor([9], dtype=torch.long, device="cuda")
+    history = torch.zeros(B, L, dtype=torch.long, device="cuda")
+    ticket = torch.zeros(1, dtype=torch.int32, device="cuda")
+    for rep in range(3):  # the ticket goes back to zero, so calls can follow each other
+        native.call("lq_next_token", logits.data_ptr(), V, tokens.data_ptr(), pos.data_ptr(), history.data_ptr(),
+                    L, ticket.data_ptr(), B, 0, stream)
+        want = torch.argmax(logits, dim=-1)
+        assert torch.equal(tokens, want) and int(tokens[0]) == 17
+        assert int(pos) == 10 + rep and int(ticket) == 0
+        assert torch.equal(history[:, 10 + rep], want)
+    hidden = torch.zeros(B, H, dtype=torch.bfloat16, device="cuda")
+    native.call("lq_embed_gather", table.data_ptr(), tokens.data_ptr(), hidden.data_ptr(), B, H, V, 1, stream)
+    assert torch.equal(hidden, table.index_select(0, tokens))
