@@ -16,12 +16,13 @@ Prints ONE JSON line (rank 0). Workloads:
                   each shape exceeds L2, so every launch streams from HBM). value = algorithmic
                   bytes moved per second over the whole pass.
 
-`--impl reference` times the CPU oracle (a numpy restatement of the reference's real mode;
-the reference itself is Python and is not shipped to the GPU box) on a bounded sample of the
-same workload, on all host threads.
+`--impl reference` times the reference's own real mode on the host cores -- the staged copy of
+the reference package under oracle/_ref when it is there (`python oracle/make_ref.py`), else
+the oracle's restatement of it -- on a bounded sample of the same workload, on all host threads.
 """
 
 import argparse
+import ctypes
 import json
 import os
 import subprocess
@@ -163,10 +164,13 @@ def capture_shape_graph(entry):
     def run():
         from llmquant_b200 import native
         for (codes, scale_tiles), out in zip(entry["weights"], outs):
-            native.call("lq_wq_gemv_stream", x.data_ptr(), x.stride(0), codes.data_ptr(),
-                        scale_tiles.data_ptr(), 0, 0, out.data_ptr(), native.LQ_BF16, 1,
-                        mod.out_features, mod.in_features, mod._kd, mod._span, mod.num_bits, 0,
-                        native.stream_ptr(x.device))
+            # programmatic dependent launch: a launch streams its first weights while the one
+            # before it drains, as consecutive linears of a decode step do
+            a = native.GemvArgs(x=x.data_ptr(), ldx=x.stride(0), codes=codes.data_ptr(),
+                                scale_tiles=scale_tiles.data_ptr(), out=out.data_ptr(),
+                                out_dtype=native.LQ_BF16, M=1, N=mod.out_features, K=mod.in_features,
+                                Kd=mod._kd, span=mod._span, bits=mod.num_bits, pdl=1)
+            native.call("lq_wq_gemv_fused", ctypes.byref(a), native.stream_ptr(x.device))
 
     side = torch.cuda.Stream()
     side.wait_stream(torch.cuda.current_stream())
@@ -271,7 +275,8 @@ def run_gpu(args, rank, world, device):
         "clocks": clocks.summary(),
     }
     if rank == 0:
-        line["cpu_baseline"] = cpu_baseline(sample_seconds=12.0)
+        if world == 1:
+            line["cpu_baseline"] = cpu_baseline(sample_seconds=12.0)
         print(json.dumps(line), flush=True)
 
 
@@ -300,14 +305,9 @@ def run_gemv_one(args, device):
     n_out = n // 2 if args.epilogue else n
     out = torch.empty(args.batch, n_out, dtype=torch.bfloat16, device=device)
 
-    if args.tune:
-        from llmquant_b200 import native
-        native.library().lq_gemv_set_tuning(*[int(v) for v in args.tune.split(",")])
-
     def once():
         for m in mods:
-            m.gemv(x, norm_weight=gamma, epilogue=args.epilogue, pdl=bool(args.pdl), out=out,
-                   variant=args.variant)
+            m.gemv(x, norm_weight=gamma, epilogue=args.epilogue, pdl=True, out=out)
 
     side = torch.cuda.Stream()
     side.wait_stream(torch.cuda.current_stream())
@@ -330,8 +330,7 @@ def run_gemv_one(args, device):
     us = start.elapsed_time(stop) * 1e3 / (args.steps * copies)
     print(json.dumps({"workload": "gemv_one", "n": n, "k": k, "bits": bits, "rows": args.batch,
                       "copies": copies, "us_per_launch": round(us, 2),
-                      "gbs": round(per_copy / us / 1e3, 1), "graph_replay": True, "pdl": args.pdl,
-                      "variant": args.variant, "tune": args.tune}), flush=True)
+                      "gbs": round(per_copy / us / 1e3, 1), "graph_replay": True}), flush=True)
 
 
 # --------------------------------------------------------------------------- prefill GEMM shapes
@@ -431,11 +430,8 @@ def run_decode(args, rank, world, device):
         shard=(lambda name, w: tpmod.shard_weight(name, w, rank, world)) if ctx else None)
     if ctx:
         tpmod.wrap_for_prefill_(model, ctx)
-    new = args.warmup + 2 * args.steps + 8
-    if args.ring:
-        from llmquant_b200 import native
-        native.library().lq_gemv_set_ring_policy(*[int(v) for v in args.ring.split(",")])
-    dec = FusedLlamaDecoder(model, batch, prompt + new + 8, kv_bits=8, tp=ctx, attn_splits=args.attn_splits)
+    new = args.warmup + 2 * args.steps + 16
+    dec = FusedLlamaDecoder(model, batch, prompt + new + 8, kv_bits=8, tp=ctx)
     g = torch.Generator().manual_seed(1)
     host_ids = torch.randint(0, model.config.vocab_size, (batch, prompt), generator=g).pin_memory()
 
@@ -452,6 +448,7 @@ def run_decode(args, rank, world, device):
 
     # ---- value: the token loop entirely on the device
     start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    cursor = dec.pos.clone()
     with ClockSampler(torch.cuda.current_device()) as clocks:
         barrier()
         start.record()
@@ -461,6 +458,24 @@ def run_decode(args, rank, world, device):
         barrier()
     step_ms = start.elapsed_time(stop) / args.steps
     context = prompt + args.warmup + args.steps // 2
+    # what was decoded: every rank count must give the same stream (greedy, same weights)
+    produced = dec.history[:, prompt:prompt + args.warmup + args.steps + 1].cpu()
+    checksum = 0
+    for t in produced.flatten().tolist():
+        checksum = (checksum * 1000003 + int(t) + 1) % 2305843009213693951
+
+    # ---- spread: the same K steps from the same cursor, five more times
+    repeats = []
+    for _ in range(5):
+        dec.pos.copy_(cursor)
+        barrier()
+        r0, r1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        r0.record()
+        for _ in range(args.steps):
+            dec.step()
+        r1.record()
+        barrier()
+        repeats.append(r0.elapsed_time(r1) / args.steps)
 
     # ---- e2e: every step feeds the token from pinned host memory and reads the new one back
     host_tok = dec.tokens.cpu().pin_memory()
@@ -502,10 +517,11 @@ def run_decode(args, rank, world, device):
     gemv_ms = g0.elapsed_time(g1) / args.steps
     gemv_launches = 4 * len(dec.layers) + 1
 
-    times = torch.tensor([step_ms, e2e_s, gemv_ms], dtype=torch.float64, device=device)
+    times = torch.tensor([step_ms, e2e_s, gemv_ms] + repeats, dtype=torch.float64, device=device)
     if world > 1:
         dist.all_reduce(times, op=dist.ReduceOp.MAX)
-    step_ms, e2e_s, gemv_ms = times.tolist()
+    step_ms, e2e_s, gemv_ms, *repeats = times.tolist()
+    repeats.sort()
     peaks, peak_kind = measured_peaks()
     step_bytes = decode_step_bytes(dec, context)
     step_achieved = step_bytes / (step_ms * 1e-3) / 1e9
@@ -519,14 +535,16 @@ def run_decode(args, rank, world, device):
         "config": {"workload": f"{args.workload} ({spec['label']}, attn int8 / mlp int4 g128 / "
                                f"lm_head int8 / int8 KV, greedy)",
                    "batch": batch, "prompt_tokens": prompt, "context_at_timing": context,
+                   "first_tokens": produced[0, :8].tolist(), "token_checksum": checksum,
+                   "tokens_checked": int(produced.numel()),
                    "l2_policy": f"{step_bytes / 1e6:.0f} MB of weights and KV streamed per step, larger than L2",
                    "parallelism": (f"tp{world}: column-parallel q/k/v, gate/up, lm_head; row-parallel "
                                    f"o_proj, down_proj, all-reduce = {dec.allreduce}") if world > 1 else "single"},
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peaks["hbm_gbs"],
                      "unit": "GB/s", "frac": round(achieved / peaks["hbm_gbs"], 4),
                      "frac_of_nominal_8TBs": round(achieved / 8000.0, 4), "peak_kind": peak_kind,
-                     # ncu (profiles/gemv_stream_ncu_full.md): DRAM bytes of a launch are 1.006x
-                     # (lm_head, int8) and 1.03x (gate|up, int4) its algorithmic bytes
+                     # DRAM bytes per launch as one ncu capture of two shapes gave them: 1.006x
+                     # (lm_head, int8) and 1.03x (gate|up, int4) the algorithmic bytes
                      "traffic": int(gemv_bytes * 1.02) // gemv_launches,
                      "traffic_source": "ncu captures of two shapes (1.006x and 1.03x algorithmic), scaled",
                      "kernel": f"gemv_stream_kernel, the {gemv_launches} launches of one step timed alone "
@@ -538,68 +556,116 @@ def run_decode(args, rank, world, device):
                                     "frac": round(step_achieved / peaks["hbm_gbs"], 4)}},
         "e2e": {"value": round(batch / e2e_s, 1), "unit": "tok/s",
                 "h2d_bytes_per_step": batch * 8, "d2h_bytes_per_step": batch * 8},
+        "spread": {"repeats": len(repeats), "ms_per_step_median": round(repeats[len(repeats) // 2], 4),
+                   "ms_per_step_min": round(repeats[0], 4), "ms_per_step_max": round(repeats[-1], 4)},
         "gpu_launches": dec.launches_per_step * args.steps,
         "clocks": clocks.summary(),
     }
-    if world > 1:
-        from llmquant_b200 import native
-        line["config"]["allreduce_timeouts"] = native.library().lq_allreduce_device_error()
+    dec.check_device_errors()  # a bounded wait that ran out anywhere in the step voids the run
     if rank == 0:
-        line["cpu_baseline"] = cpu_decode_baseline(spec["shape"], reps=1)
+        if world == 1:  # the host cores are busy with the other ranks otherwise
+            line["cpu_baseline"] = cpu_reference_decode(spec["shape"], steps=2, warmup=1)
         print(json.dumps(line), flush=True)
 
 
-def cpu_decode_baseline(shape_name, reps=1):
-    """Real-mode linears of ONE decoder layer plus lm_head (torch CPU restatement of
-    quantizers/real.py:76-103 of the reference), batch 1, one token; the per-token time of the
-    whole model is layers x layer time + head time."""
-    from llmquant_b200.runtime.random_init import SHAPES
-    from oracle.real_mode import RealLinear
+def cpu_reference_decode(shape_name, steps, warmup, sample_layers=2, prompt=64):
+    """Decode steps of the reference's `real` mode on the host cores, run for real: a random-init
+    Llama of the workload's width, cut to `sample_layers` decoder layers (the full depth does
+    not fit a benchmark run on a CPU), quantized by the reference's own
+    `oneshot(model, QuantConfig(...).to_modifier(mode="real"))` with its FakeQuantCache(8), a
+    short prompt, then `warmup + steps` greedy tokens through the transformers model, each
+    timed. The staged reference package is used when present (kind "reference"), else the
+    oracle's restatement of the same modules (kind "port"). The per-token time of the full
+    model = time outside the decoder layers + (full depth) x mean time of one layer, both
+    measured in the same steps with forward hooks."""
+    from transformers import LlamaForCausalLM
+
+    from llmquant_b200.runtime.random_init import SHAPES, llama_config
+    from oracle import make_ref
 
     torch.set_num_threads(os.cpu_count() or 1)  # torchrun pins OMP_NUM_THREADS=1
-    shp = SHAPES[shape_name]
-    h, inter, d = shp["hidden_size"], shp["intermediate_size"], shp["head_dim"]
-    nq, nkv = shp["num_attention_heads"] * d, shp["num_key_value_heads"] * d
-    parts = [("q", nq, h, 8, 1), ("k", nkv, h, 8, 2), ("o", h, nq, 8, 1), ("gate", inter, h, 4, 2),
-             ("down", h, inter, 4, 1)]
-    torch.manual_seed(0)
-    layer_s = 0.0
-    for _, n, k, bits, count in parts:
-        lin = torch.nn.Linear(k, n, bias=False).to(torch.bfloat16)
-        mod = RealLinear(lin, bits)
-        x = torch.randn(1, k).bfloat16()
-        mod(x)
-        t0 = time.perf_counter()
-        for _ in range(reps):
-            mod(x)
-        layer_s += count * (time.perf_counter() - t0) / reps
-        del lin, mod
-    # lm_head on one eighth of the vocabulary, scaled
-    rows = shp["vocab_size"] // 8
-    lin = torch.nn.Linear(h, rows, bias=False).to(torch.bfloat16)
-    mod = RealLinear(lin, 8)
-    x = torch.randn(1, h).bfloat16()
-    mod(x)
-    t0 = time.perf_counter()
-    for _ in range(reps):
-        mod(x)
-    head_s = 8 * (time.perf_counter() - t0) / reps
-    token_s = shp["num_hidden_layers"] * layer_s + head_s
+    full_layers = SHAPES[shape_name]["num_hidden_layers"]
+    config = llama_config(shape_name, num_hidden_layers=sample_layers)
+    with torch.device("meta"):
+        model = LlamaForCausalLM(config)
+    model = model.to_empty(device="cpu")
+    g = torch.Generator().manual_seed(0)
+    with torch.no_grad():
+        for _, p in sorted(model.named_parameters()):
+            if p.dim() >= 2:
+                p.copy_(torch.randn(p.shape, generator=g) * 0.02)
+            else:
+                p.fill_(1.0)
+    model.model.rotary_emb = type(model.model.rotary_emb)(config)
+    model = model.to(torch.bfloat16).eval()
+    if make_ref.available():
+        make_ref.import_reference()
+        from llmquant.core import QuantConfig, oneshot
+        from llmquant.quantizers import make_cache_factory
+
+        kind = "reference"
+        cfg = QuantConfig(attn_weight="int8", mlp_weight="int4", head_weight="int8", kv_cache="int8")
+        oneshot(model, cfg.to_modifier(mode="real"))
+        cache = make_cache_factory(8)()
+    else:
+        from oracle.real_mode import FakeQuantKV, apply_real_mode
+
+        kind = "port"
+        apply_real_mode(model, attn_bits=8, mlp_bits=4, head_bits=8)
+        cache = FakeQuantKV(8)
+    in_layers = [0.0]
+
+    def before(_m, _a, _k=None):
+        in_layers.append(time.perf_counter())
+
+    def after(_m, _a, _o):
+        in_layers[0] += time.perf_counter() - in_layers.pop()
+
+    for layer in model.model.layers:
+        layer.register_forward_pre_hook(before)
+        layer.register_forward_hook(after)
+    ids = torch.randint(0, config.vocab_size, (1, prompt), generator=g)
+    with torch.no_grad():
+        out = model(ids, past_key_values=cache, use_cache=True, logits_to_keep=1)
+        tok = out.logits[:, -1].argmax(-1)
+        step_s, layer_s = [], []
+        for i in range(warmup + steps):
+            in_layers[0] = 0.0
+            t0 = time.perf_counter()
+            out = model(tok[:, None], past_key_values=cache, use_cache=True)
+            tok = out.logits[:, -1].argmax(-1)
+            if i >= warmup:
+                step_s.append(time.perf_counter() - t0)
+                layer_s.append(in_layers[0])
+    sample_s = sum(step_s) / len(step_s)
+    per_layer = sum(layer_s) / len(layer_s) / sample_layers
+    token_s = (sample_s - per_layer * sample_layers) + full_layers * per_layer
     return {"value": round(1.0 / token_s, 4), "unit": "tok/s", "cores": torch.get_num_threads(),
-            "kind": "port",
-            "sample": f"real-mode linears of one {shape_name} decoder layer (q, k, o, gate, down timed; "
-                      f"k/v and gate/up counted twice) + lm_head on 1/8 of the vocabulary, M=1; "
-                      f"token time = {shp['num_hidden_layers']} x layer + head"}
+            "kind": kind, "sample_ms_per_step": round(sample_s * 1e3, 2), "steps_timed": len(step_s),
+            "sample": f"{kind} real mode (attn int8 / mlp int4 / lm_head int8 / FakeQuantCache(8)) of a "
+                      f"random-init {shape_name} cut to {sample_layers} of {full_layers} decoder layers, "
+                      f"{prompt}-token prompt, batch 1, {len(step_s)} greedy tokens timed one by one; token "
+                      f"time of the full depth = time outside the layers + {full_layers} x mean layer time "
+                      f"({per_layer * 1e3:.1f} ms)"}
 
 
 # --------------------------------------------------------------------------- CPU arm
 def cpu_baseline(sample_seconds=15.0, steps=None):
-    """The oracle's real-mode linear (numpy restatement of quantizers/real.py:76-103 of the
-    reference) on the sweep shapes, M=1, on all host threads, bounded in time."""
+    """The reference's real-mode linear (quantizers/real.py:76-103) on the sweep shapes, M=1, on
+    all host threads, bounded in time: `RealQuantLinear` of the staged reference package when it
+    is there, else the oracle's numpy restatement."""
     import numpy as np
 
     import oracle
+    from oracle import make_ref
 
+    torch.set_num_threads(os.cpu_count() or 1)
+    staged = make_ref.available()
+    if staged:
+        make_ref.import_reference()
+        from llmquant.core.scheme import QuantizationArgs as RefArgs
+        from llmquant.core.scheme import QuantizationScheme as RefScheme
+        from llmquant.quantizers.real import RealQuantLinear
     rng = np.random.default_rng(0)
     done_bytes, spent, used = 0, 0.0, []
     budget = sample_seconds
@@ -608,21 +674,32 @@ def cpu_baseline(sample_seconds=15.0, steps=None):
             n = 16032  # one eighth of the vocabulary keeps the sample bounded
         w = oracle.round_to_dtype((rng.standard_normal((n, k)) * 0.02).astype(np.float32), "bf16")
         x = oracle.round_to_dtype(rng.standard_normal((1, k)).astype(np.float32), "bf16")
-        q, scale = oracle.quantize_weight(w, bits, 128)
-        oracle.real_linear(x, q, scale, bits, 128)  # warm-up
-        reps = steps or 3
-        t0 = time.perf_counter()
-        for _ in range(reps):
-            oracle.real_linear(x, q, scale, bits, 128, out_dtype="bf16")
-        dt = (time.perf_counter() - t0) / reps
+        if staged:
+            lin = torch.nn.Linear(k, n, bias=False)
+            lin.weight.data = torch.from_numpy(w).bfloat16()
+            scheme = RefScheme(weights=RefArgs(num_bits=bits, strategy="group", group_size=128),
+                               input_activations=None)
+            mod = RealQuantLinear.from_linear(lin, scheme)
+            xt = torch.from_numpy(x).bfloat16()
+            run = lambda: mod(xt)  # noqa: E731
+        else:
+            q, scale = oracle.quantize_weight(w, bits, 128)
+            run = lambda: oracle.real_linear(x, q, scale, bits, 128, out_dtype="bf16")  # noqa: E731
+        with torch.no_grad():
+            run()  # warm-up
+            reps = steps or 3
+            t0 = time.perf_counter()
+            for _ in range(reps):
+                run()
+            dt = (time.perf_counter() - t0) / reps
         done_bytes += algorithmic_bytes(n, k, bits)
         spent += dt
         used.append(name if n != 16032 else name + "[16032 rows]")
         if spent * 3 > budget:
             break
     return {"value": round(done_bytes / spent / 1e9, 3), "unit": "GB/s",
-            "cores": os.cpu_count(), "kind": "port",
-            "sample": "one M=1 forward per shape (median-free mean of 3) over: " + ", ".join(used)}
+            "cores": torch.get_num_threads(), "kind": "reference" if staged else "port",
+            "sample": "one M=1 real-mode forward per shape (mean of the repetitions) over: " + ", ".join(used)}
 
 
 def run_reference(args, rank):
@@ -630,14 +707,17 @@ def run_reference(args, rank):
         return
     if args.workload in DECODE:
         spec = DECODE[args.workload]
-        base = cpu_decode_baseline(spec["shape"], reps=max(1, min(args.steps, 3)))
+        base = cpu_reference_decode(spec["shape"], steps=args.steps, warmup=args.warmup)
         line = {
             "impl": "reference", "metric": "decode_tokens_per_s", "value": base["value"], "unit": "tok/s",
-            "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(1e3 / base["value"], 2),
+            "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+            # the time of a step as it was run (the bounded sample); `value` is the full depth
+            "ms_per_step": base["sample_ms_per_step"],
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": "int codes x fp32 (torch CPU)", "data": "synthetic",
             "config": {"workload": f"{args.workload} ({spec['label']}, attn int8 / mlp int4 g128 / "
-                                   f"lm_head int8 / int8 KV, greedy)", "batch": 1},
+                                   f"lm_head int8 / int8 KV, greedy)", "batch": 1,
+                       "sample": base["sample"]},
             "cpu_baseline": base,
             "e2e": {"value": base["value"], "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         }
@@ -669,12 +749,7 @@ def main():
     ap.add_argument("--bits", type=int, default=4)
     ap.add_argument("--epilogue", type=int, default=0)
     ap.add_argument("--norm", type=int, default=0)
-    ap.add_argument("--pdl", type=int, default=1)
-    ap.add_argument("--variant", type=int, default=0)
     ap.add_argument("--rows", default="", help="prefill_gemm: comma-separated token counts (default 16,128,512,2048)")
-    ap.add_argument("--ring", default="", help="GEMV ring policy: consumer warps per SM, KB per SM (0 = default)")
-    ap.add_argument("--attn-splits", type=int, default=0, help="decode workloads: context slices per KV head (0 = default)")
-    ap.add_argument("--tune", default="", help="gemv_one, variant 4: warps,rows-per-stage,stages (0 = default)")
     ap.add_argument("--batch", type=int, default=1)
     ap.add_argument("--prompt", type=int, default=0, help="prompt tokens (0 = the workload's own)")
     ap.add_argument("--allreduce", default="peer", choices=["peer", "nccl"])

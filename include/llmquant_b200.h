@@ -85,13 +85,15 @@ int lq_residual_add(const float* sum, const void* residual, void* out, int64_t n
  * The caller's previous kernel wrote this rank's partial into data[slot] of its own buffer;
  * consecutive calls must alternate slot 0 / 1. seq_counter_dev is a device uint32 (start 0)
  * the kernel advances by one per call -- every rank must make the same sequence of calls.
- * Waiting for the peers is bounded (~2 s); on expiry lq_allreduce_device_error() becomes 1.
+ * Waiting for the peers is bounded by wait_cycles SM clocks (0 = about two seconds); when the
+ * wait runs out lq_allreduce_device_error() becomes 1 and the kernel finishes with what it has.
  * The reference is single-GPU: no counterpart. */
 int lq_allreduce_max_world(void);
 int lq_allreduce_device_error(void);
 int lq_allreduce_residual(const uint64_t* peer_bases_dev, int rank, int world, int slot,
                           int64_t slot_floats, int64_t flag_offset_bytes, uint32_t* seq_counter_dev,
-                          const void* residual, void* out, int n, int pdl, void* stream);
+                          const void* residual, void* out, int n, int64_t wait_cycles, int pdl,
+                          void* stream);
 
 /* ---------------------------------------------------------------- decode GEMV */
 
@@ -162,24 +164,9 @@ int lq_wq_gemv_stream(const void* x, int ldx, const void* codes, const float* sc
  * with the device, so it is for tests and diagnostics. -1 = the word could not be read. */
 int lq_gemv_device_error(void);
 
-/* Diagnostics: when set to a device buffer of 8 * grid uint64, every GEMV CTA writes
- * %globaltimer stamps of its phases there (start, barriers ready, producer kernel done,
- * activations prepared, first tile landed, end, and with a fused RMSNorm: sum of squares done,
- * rstd done). NULL (the default) switches it off. */
-void lq_gemv_set_timeline(void* device_buffer);
-/* Ring depth policy of the streaming GEMV (0 = the library's choice): consumer warps per SM to
- * aim at (default 20) and shared memory per SM one kernel's rings may take in KB (default 112,
- * about half an SM, so the next kernel's CTAs fit beside). Process-wide; for benchmarking.
- * No counterpart in the reference. */
-void lq_gemv_set_ring_policy(int consumer_warps_per_sm, int kb_per_sm);
 /* 1 if variant 4 of the GEMV serves M activation rows against a weight of Kd stored columns in
  * groups of `span` at `bits` per code, else 0 (the other variants serve every shape). */
 int lq_gemv_tensor_core_ok(int M, int Kd, int span, int bits);
-/* Tuning override for variant 4 (0 = the library's choice): consumer warps per CTA (<= 8),
- * weight rows per pipeline stage (4, 8 or 16), pipeline stages (<= 16). Process-wide; meant for
- * benchmarking. No counterpart in the reference. */
-void lq_gemv_set_tuning(int warps, int rows, int stages);
-
 /* ---------------------------------------------------------------- decode step bookkeeping
  * Two small kernels that keep the token loop on the device and inside the dependent-launch
  * chain; they take the place of the host-driven copy_ / fill_ / argmax per token of the
@@ -192,6 +179,22 @@ int lq_embed_gather(const void* table, const int64_t* tokens, void* hidden, int 
                     int64_t vocab, int pdl, void* stream);
 int lq_next_token(const void* logits, int64_t V, int64_t* tokens, int64_t* pos, int64_t* history,
                   int64_t hist_len, int* ticket, int B, int pdl, void* stream);
+
+/* lq_next_token under tensor parallelism, where every rank holds the logits of its slice of the
+ * vocabulary (local_logits [B, V_local] bf16, global index = rank * V_local + local index):
+ * each rank sends (index, value, step tag) of its local maximum as one 8-byte record to every
+ * rank's exchange buffer -- uint64 records[2][16][max_batch] at record_offset_bytes of the
+ * buffers in peer_bases_dev, zero before the first call -- waits (bounded by wait_cycles SM
+ * clocks, 0 = about two seconds) for all ranks' records of this step and picks the largest
+ * value, the lowest index among equals, so all ranks pick the same token without gathering
+ * the logits. Advances *pos and the device step counter *step (start 0; every rank must make
+ * the same sequence of calls). lq_glue_device_error reads and clears the word a wait that ran
+ * out sets to 5 (it synchronizes with the device). The reference is single-GPU: no counterpart. */
+int lq_glue_device_error(void);
+int lq_next_token_tp(const void* local_logits, int64_t V_local, int rank, int world,
+                     const uint64_t* peer_bases_dev, int64_t record_offset_bytes, int max_batch,
+                     int64_t* tokens, int64_t* pos, int64_t* history, int64_t hist_len, int* ticket,
+                     uint32_t* step, int B, int64_t wait_cycles, int pdl, void* stream);
 
 /* ---------------------------------------------------------------- quantized KV cache
  * Storage per layer: codes [B, Hkv, Tmax, D] int8, scales [B, Hkv, Tmax, ceil(D/128)] fp32.
@@ -243,16 +246,19 @@ int64_t lq_attn_fused_scratch_bytes(int B, int Hq, int Hkv, int D, int splits);
 /* Non-zero if a bounded wait inside lq_attn_decode_fused ever expired (reads and clears the
  * word; synchronizes with the device: for tests and diagnostics). */
 int lq_attn_device_error(void);
-/* Diagnostics, as lq_gemv_set_timeline: 8 uint64 stamps per CTA of lq_attn_decode_fused. */
-void lq_attn_set_timeline(void* device_buffer);
-/* Which kernel serves lq_attn_decode_fused: 0 (default) = contractions on mma.sync tensor-core
- * instructions, 1 = all-SIMT arithmetic. Same results within the attention tolerance. */
-void lq_attn_set_impl(int impl);
+/* `impl` selects the kernel: LQ_ATTN_AUTO = the library's choice (LQ_ATTN_CLUSTER where it
+ * applies, else LQ_ATTN_MMA), LQ_ATTN_SIMT = all-SIMT arithmetic, LQ_ATTN_MMA = contractions on
+ * mma.sync tensor-core instructions with the slices merged through `scratch` by the CTA that
+ * finishes last, LQ_ATTN_CLUSTER = the same contractions with the slices of a KV head running as
+ * one thread-block cluster that merges through distributed shared memory (`splits` must be 2,
+ * 4, 8 or 16; LQ_ERR_UNSUPPORTED if such clusters do not fit the device). Same results within
+ * the attention tolerance. */
+enum { LQ_ATTN_AUTO = 0, LQ_ATTN_SIMT = 1, LQ_ATTN_MMA = 2, LQ_ATTN_CLUSTER = 3 };
 int lq_attn_decode_fused(const void* qkv, const void* cos_table, const void* sin_table,
                          int8_t* k_codes, int8_t* v_codes, float* k_scales, float* v_scales,
                          void* out, void* scratch, int B, int Hq, int Hkv, int D, int Tmax,
                          int table_len, const int64_t* pos_dev, int64_t pos, int num_bits,
-                         float scaling, int splits, int pdl, void* stream);
+                         float scaling, int splits, int impl, int pdl, void* stream);
 
 /* lq_attn_decode_kv_i8 for callers that cannot provide scratch memory -- a plugin inside a
  * process whose device memory belongs to someone else's allocator, or a host that is not
@@ -261,7 +267,10 @@ int lq_attn_decode_fused(const void* qkv, const void* cos_table, const void* sin
  * the library holds it until the process exits); a call whose B * Hq * splits * (D + 2) * 4
  * bytes exceed it is rejected with LQ_ERR_UNSUPPORTED. Nothing is allocated or freed. The
  * first call on each device resolves the array's device address; make that call outside
- * any stream capture. Nothing in the array has to start at zero (every slot a call reads it
+ * any stream capture. The array belongs to the CURRENT device at the time of the call, so that
+ * device must be the one that owns `stream` and every tensor passed (set it before calling);
+ * the address is remembered per device ordinal for the life of the process, so a process that
+ * resets a device (cudaDeviceReset) must not use this entry point on it afterwards. Nothing in the array has to start at zero (every slot a call reads it
  * has written first), but all calls share it: two calls that overlap on the GPU (different
  * streams, or graph branches) race -- serialize them. This entry point has no counterpart
  * in the reference. */
@@ -288,10 +297,10 @@ int lq_attn_decode_kv_i8_static(const void* q, const int8_t* k_codes, const int8
  * KernelQuantLinear.forward (quantizers/kernel.py:68-79,90-91). lq_gemm_device_error is
  * non-zero if a bounded wait for the tensor core ever expired (reads and clears). */
 int lq_gemm_device_error(void);
-/* Which kernel serves int8-activation calls with groups of 128: 0 (default) = the pipelined
- * kernel (fill, MMA issue and drain in separate warps), 1 = the serial kernel. Same results. */
-void lq_gemm_set_impl(int impl);
+/* flags: LQ_GEMM_FOLD_SCALES as described above; LQ_GEMM_SERIAL runs the first, unpipelined
+ * kernel (fill, MMA and drain in turn) instead of the warp-specialized ones -- same results. */
 #define LQ_GEMM_FOLD_SCALES 1
+#define LQ_GEMM_SERIAL 2
 int lq_wq_gemm_prefill(const void* x, int ldx, const int8_t* x_codes, const float* x_scales,
                        const void* codes, const float* scale_tiles, const void* bias, void* out,
                        int M, int N, int K, int Kd, int span, int bits, int flags, void* stream);
@@ -308,6 +317,47 @@ int lq_wq_gemm_prefill(const void* x, int ldx, const int8_t* x_codes, const floa
  *                           stream drains, and waits for it before touching x.
  * These fusions have no counterpart in the reference, which runs them as separate PyTorch
  * ops between its wq_gemv calls (llmquant/quantizers/kernel.py:81-95 is the call site). */
+/* Tensor-parallel coupling of a GEMV (NULL in lq_gemv_args.tp = none). The reference is
+ * single-GPU, so this has no counterpart there. Every rank owns one exchange buffer that all
+ * ranks of the group have mapped (NVLink peer memory); per slot it holds the fp32 partial
+ * outputs of every rank, float part[world][M][N], and a row of uint32 arrival counters, one
+ * per source rank. Counters only grow. Plain stores, loads and reductions only.
+ *   mode LQ_TP_PUSH  (row-parallel linear: o_proj, down_proj) -- the epilogue writes this
+ *        rank's fp32 partial rows straight into part[rank] of EVERY rank's buffer
+ *        (peers[r] + data_offset) and, when a CTA is done, adds its number of 4-row batches
+ *        to counter `rank` of every rank (peers[r] + counter_offset). `out`, `residual` must
+ *        be NULL / unused; N % 4 == 0.
+ *   mode LQ_TP_SUM   (the linear that consumes the sum: gate|up after o_proj, the next
+ *        layer's q|k|v or lm_head after down_proj) -- before anything else the first CTAs of
+ *        the grid wait (bounded) until every rank's counter in `counters` has reached
+ *        (*step * seq_mul + seq_add) * producer_batches, add the `world` partials of `parts`
+ *        in rank order (identical bits on every rank), round to bf16, add `residual` (bf16
+ *        [M, K]) and store the new hidden rows to `x` (which this mode WRITES before it reads
+ *        them as the GEMV input); they then add one to *ready, and every CTA waits until
+ *        *ready has reached (*step * ready_mul + ready_add) * (number of those CTAs,
+ *        min(grid, ceil(M * K / (4 * consumer threads)))). K % 4 == 0, ldx == K.
+ * `step` is a device uint32 the caller advances once per decode step (lq_next_token_tp does).
+ * wait_cycles bounds each wait in SM clocks (0 = about two seconds); when one runs out
+ * lq_gemv_device_error() reports 3 (peers) or 4 (ready) and the kernel finishes with the data
+ * it has. */
+enum { LQ_TP_PUSH = 1, LQ_TP_SUM = 2 };
+typedef struct lq_gemv_tp {
+  int mode;
+  int world, rank;
+  const uint64_t* peers;       /* device array [world]: base address of every rank's buffer */
+  int64_t data_offset;         /* PUSH: byte offset of part[0] of the slot inside a buffer */
+  int64_t counter_offset;      /* PUSH: byte offset of the slot's counter row */
+  const float* parts;          /* SUM: this rank's part[0] of the slot (local address) */
+  const uint32_t* counters;    /* SUM: this rank's counter row of the slot */
+  uint32_t* ready;             /* SUM: local device counter of this consumer kind */
+  const void* residual;        /* SUM: bf16 [M, K] */
+  const uint32_t* step;        /* SUM: device step counter */
+  uint32_t seq_mul, seq_add;   /* SUM: arrivals expected = (*step * seq_mul + seq_add) * producer_batches */
+  uint32_t ready_mul, ready_add;
+  uint32_t producer_batches;   /* SUM: ceil(N_producer / 4) of the linear that pushed */
+  int64_t wait_cycles;
+} lq_gemv_tp;
+
 typedef struct lq_gemv_args {
   const void* x;
   int ldx;
@@ -323,6 +373,7 @@ typedef struct lq_gemv_args {
   int epilogue;
   int variant;
   int pdl;
+  const lq_gemv_tp* tp;        /* NULL = no tensor-parallel coupling */
 } lq_gemv_args;
 int lq_wq_gemv_fused(const lq_gemv_args* args, void* stream);
 

@@ -12,6 +12,7 @@
 // reading the previous one. No bulk / TMA copies touch peer memory, only plain loads and
 // stores. The reference is single-GPU and has no counterpart.
 #include "common.cuh"
+#include "peer_sync.cuh"
 
 namespace lq {
 namespace {
@@ -19,30 +20,13 @@ namespace {
 constexpr int kArThreads = 1024;
 constexpr int kMaxWorld = 16;
 
-__device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
-  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
-}
-__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
-  uint32_t v;
-  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-  return v;
-}
-__device__ __forceinline__ float4 ld_peer_f4(const float4* p) {
-  float4 v;
-  asm volatile("ld.relaxed.sys.global.v4.f32 {%0,%1,%2,%3}, [%4];"
-               : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
-               : "l"(p)
-               : "memory");
-  return v;
-}
-
 // peers[r]: base of rank r's shared buffer: float data[2][slot_floats], then uint32
 // flags[2][kMaxWorld] at byte offset flag_off. n is a multiple of 4.
 __global__ void __launch_bounds__(kArThreads)
 allreduce_residual_kernel(const uint64_t* __restrict__ peers, int rank, int world, int slot,
                           int64_t slot_floats, int64_t flag_off, uint32_t* seq_counter,
                           const __nv_bfloat16* __restrict__ residual, __nv_bfloat16* __restrict__ out,
-                          int n, int* error_word) {
+                          int n, long long wait_cycles, int* error_word) {
   asm volatile("griddepcontrol.wait;" ::: "memory");
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   __shared__ uint64_t base_s[kMaxWorld];
@@ -59,7 +43,7 @@ allreduce_residual_kernel(const uint64_t* __restrict__ peers, int rank, int worl
     const uint32_t* mine = reinterpret_cast<const uint32_t*>(base_s[rank] + flag_off) + slot * kMaxWorld + tid;
     const long long t0 = clock64();
     while (ld_acquire_sys(mine) != seq) {
-      if (clock64() - t0 > 4000000000LL) {  // ~2 s: a peer never arrived
+      if (clock64() - t0 > wait_cycles) {  // a peer never arrived
         timed_out = 1;
         break;
       }
@@ -71,10 +55,16 @@ allreduce_residual_kernel(const uint64_t* __restrict__ peers, int rank, int worl
   }
   for (int i = tid * 4; i < n; i += kArThreads * 4) {
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-    for (int r = 0; r < world; ++r) {
-      const float4 v = ld_peer_f4(reinterpret_cast<const float4*>(
-          reinterpret_cast<const float*>(base_s[r]) + slot * slot_floats + i));
-      acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+    for (int r0 = 0; r0 < world; r0 += 4) {  // four peer loads in flight, added in rank order
+      float4 v[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+        if (r0 + j < world)
+          v[j] = ld_peer_f4(reinterpret_cast<const float4*>(
+              reinterpret_cast<const float*>(base_s[r0 + j]) + slot * slot_floats + i));
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+        if (r0 + j < world) { acc.x += v[j].x; acc.y += v[j].y; acc.z += v[j].z; acc.w += v[j].w; }
     }
     const float a[4] = {acc.x, acc.y, acc.z, acc.w};
 #pragma unroll
@@ -107,7 +97,7 @@ extern "C" int lq_allreduce_device_error(void) {
 extern "C" int lq_allreduce_residual(const uint64_t* peer_bases_dev, int rank, int world, int slot,
                                      int64_t slot_floats, int64_t flag_offset_bytes,
                                      uint32_t* seq_counter_dev, const void* residual, void* out, int n,
-                                     int pdl, void* stream) {
+                                     int64_t wait_cycles, int pdl, void* stream) {
   using namespace lq;
   LQ_REQUIRE(world >= 1 && world <= kMaxWorld && rank >= 0 && rank < world, LQ_ERR_ARG,
              "bad rank %d / world %d", rank, world);
@@ -133,7 +123,9 @@ extern "C" int lq_allreduce_residual(const uint64_t* peer_bases_dev, int rank, i
   cfg.numAttrs = pdl ? 1 : 0;
   cudaError_t e = cudaLaunchKernelEx(&cfg, allreduce_residual_kernel, peer_bases_dev, rank, world, slot,
                                      slot_floats, flag_offset_bytes, seq_counter_dev,
-                                     (const __nv_bfloat16*)residual, (__nv_bfloat16*)out, n, (int*)err_ptr);
+                                     (const __nv_bfloat16*)residual, (__nv_bfloat16*)out, n,
+                                     (long long)(wait_cycles > 0 ? wait_cycles : kDefaultWaitCycles),
+                                     (int*)err_ptr);
   if (e != cudaSuccess) {
     cudaGetLastError();
     return fail(LQ_ERR_LAUNCH, "lq_allreduce_residual: %s", cudaGetErrorString(e));

@@ -21,6 +21,9 @@ char* error_buffer();
 int fail(int code, const char* fmt, ...);
 int check_launch(const char* what);
 int sm_count();
+// Raises a kernel's dynamic shared-memory limit once per (kernel, device); the attribute is a
+// property of the device the kernel is loaded on, so the bookkeeping is keyed by both.
+int ensure_smem_limit(const void* kernel, int bytes, const char* what);
 
 #define LQ_REQUIRE(cond, code, ...)            \
   do {                                         \

@@ -1,6 +1,10 @@
 // Error reporting and device queries shared by every entry point of the C ABI.
 #include "common.cuh"
 
+#include <map>
+#include <mutex>
+#include <utility>
+
 namespace lq {
 
 char* error_buffer() {
@@ -39,7 +43,27 @@ int sm_count() {
   return cached;
 }
 
+int ensure_smem_limit(const void* kernel, int bytes, const char* what) {
+  static std::mutex mu;
+  static std::map<std::pair<const void*, int>, int> raised;  // (kernel, device) -> bytes granted
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) {
+    cudaGetLastError();
+    return fail(LQ_ERR_LAUNCH, "%s: no current device", what);
+  }
+  std::lock_guard<std::mutex> lock(mu);
+  auto key = std::make_pair(kernel, dev);
+  auto it = raised.find(key);
+  if (it != raised.end() && it->second >= bytes) return LQ_OK;
+  if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes) != cudaSuccess) {
+    cudaGetLastError();
+    return fail(LQ_ERR_LAUNCH, "%s: cannot raise the dynamic shared memory limit to %d bytes", what, bytes);
+  }
+  raised[key] = bytes;
+  return LQ_OK;
+}
+
 }  // namespace lq
 
-extern "C" int lq_version(void) { return 1; }
+extern "C" int lq_version(void) { return 2; }
 extern "C" const char* lq_last_error(void) { return lq::error_buffer(); }

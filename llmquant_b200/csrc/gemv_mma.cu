@@ -74,10 +74,14 @@ __device__ __forceinline__ unsigned long long global_ns() {
   asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
   return t;
 }
+#ifdef LQ_DIAGNOSTICS
 #define LQ_MMA_STAMP(slot)                                                                     \
   do {                                                                                         \
     if (p.debug != nullptr && threadIdx.x == 0) p.debug[(size_t)blockIdx.x * 8 + (slot)] = global_ns(); \
   } while (0)
+#else
+#define LQ_MMA_STAMP(slot) do { } while (0)
+#endif
 
 __device__ __forceinline__ void mma_s8(int (&d)[4], unsigned a0, unsigned a1, unsigned a2, unsigned a3,
                                        unsigned b0, unsigned b1) {
@@ -620,22 +624,10 @@ gemv_mma_kernel(const MmaParams p) {
   }
 }
 
-struct Tuning {
-  int warps = 0, rows = 0, stages = 0;
-};
-Tuning g_tuning;
-
 template <int BITS, int NB, int EPI, int NSEG>
 int launch_mma(const MmaParams& p, size_t smem, cudaStream_t s) {
   auto kern = gemv_mma_kernel<BITS, NB, EPI, NSEG>;
-  static thread_local bool attr_set = false;
-  if (!attr_set) {
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024) != cudaSuccess) {
-      cudaGetLastError();
-      return fail(LQ_ERR_LAUNCH, "lq_wq_gemv: cannot raise the dynamic shared memory limit");
-    }
-    attr_set = true;
-  }
+  if (const int rc = ensure_smem_limit(reinterpret_cast<const void*>(kern), 200 * 1024, "lq_wq_gemv")) return rc;
   const int cap = sm_count();
   int grid = p.ntiles < cap ? p.ntiles : cap;
   if (grid < 1) grid = 1;
@@ -679,14 +671,13 @@ bool make_plan(int M, int Kd, int span, int bits, Plan* out) {
   // rows per stage: the largest of 16 / 8 / 4 whose codes stay within 32 KB
   int R = 16;
   while (R > 4 && R * rowbytes > 32 * 1024) R /= 2;
-  if (g_tuning.rows == 4 || g_tuning.rows == 8 || g_tuning.rows == 16) R = g_tuning.rows;
   q.R = R;
   q.H = kTileRows / R;
   q.scale_off = R * rowbytes;
   q.stage_bytes = (q.scale_off + (R / 4) * groups * 16 + 127) / 128 * 128;
   // consumer warps: as many as 8, evened out so that every warp owns the same number of groups
   const int per = (groups + kMaxW - 1) / kMaxW;
-  int W = g_tuning.warps > 0 ? g_tuning.warps : (groups + per - 1) / per;
+  int W = (groups + per - 1) / per;
   if (W > groups) W = groups;
   if (W > kMaxW) W = kMaxW;
   if (W < 1) W = 1;
@@ -694,7 +685,7 @@ bool make_plan(int M, int Kd, int span, int bits, Plan* out) {
   // ring depth: whatever of ~112 KB per SM the activation planes leave, so that the next
   // kernel's CTA can become resident while this one still computes; a tile and the first
   // stage of the next one have to fit in any case
-  int stages = g_tuning.stages > 0 ? g_tuning.stages : ((112 * 1024 - q.ring_off) / q.stage_bytes);
+  int stages = (112 * 1024 - q.ring_off) / q.stage_bytes;
   stages = stages < q.H + 1 ? q.H + 1 : (stages > kMaxStagesMma ? kMaxStagesMma : stages);
   q.stages = stages;
   q.smem = (size_t)q.ring_off + (size_t)stages * q.stage_bytes;
@@ -740,10 +731,6 @@ int run_mma(const lq_gemv_args& a, int* error_word, unsigned long long* debug, c
   return fail(LQ_ERR_ARG, "no tensor-core GEMV instance for bits=%d epilogue=%d", a.bits, a.epilogue);
 }
 
-void set_mma_tuning(int warps, int rows, int stages) {
-  g_tuning.warps = warps; g_tuning.rows = rows; g_tuning.stages = stages;
-}
-
 }  // namespace gemv
 }  // namespace lq
 
@@ -751,8 +738,4 @@ extern "C" int lq_gemv_tensor_core_ok(int M, int Kd, int span, int bits) {
   lq_gemv_args a = {};
   a.M = M; a.Kd = Kd; a.span = span; a.bits = bits;
   return lq::gemv::mma_eligible(a) ? 1 : 0;
-}
-
-extern "C" void lq_gemv_set_tuning(int warps, int rows, int stages) {
-  lq::gemv::set_mma_tuning(warps, rows, stages);
 }

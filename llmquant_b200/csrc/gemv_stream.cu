@@ -13,7 +13,6 @@ int run_b8v2(GemvParams, const lq_gemv_args&, int, int, cudaStream_t);
 bool mma_eligible(const lq_gemv_args& a);
 int run_mma(const lq_gemv_args& a, int* error_word, unsigned long long* debug, cudaStream_t s);
 int run_b8v3(GemvParams, const lq_gemv_args&, int, int, cudaStream_t);
-int g_ring_kb_launch = 112;
 }  // namespace gemv
 
 namespace {
@@ -120,10 +119,12 @@ int repack_common(const int8_t* canonical, const float* wscale, void* codes, flo
   return check_launch(inverse ? "lq_unrepack_stream" : "lq_repack_stream");
 }
 
-int g_ring_warps = 20;  // consumer warps per SM the ring depth policy aims at
-int g_ring_kb = 112;    // shared memory per SM the rings of one kernel may take
 __device__ int g_gemv_error = 0;
-unsigned long long* g_debug_timeline = nullptr;  // host-side: where kernels write their stamps
+#ifdef LQ_DIAGNOSTICS
+unsigned long long* g_debug_timeline = nullptr;  // diagnostic builds: where kernels write their stamps
+#else
+constexpr unsigned long long* g_debug_timeline = nullptr;
+#endif
 
 int* error_word() {
   static thread_local int cached_dev = -1;
@@ -181,15 +182,13 @@ extern "C" int lq_dequant_stream(const void* codes, const float* scale_tiles, vo
   return check_launch("lq_dequant_stream");
 }
 
-extern "C" void lq_gemv_set_ring_policy(int consumer_warps_per_sm, int kb_per_sm) {
-  lq::g_ring_warps = consumer_warps_per_sm > 0 ? consumer_warps_per_sm : 20;
-  lq::g_ring_kb = kb_per_sm > 0 ? kb_per_sm : 112;
-  lq::gemv::g_ring_kb_launch = lq::g_ring_kb;
-}
-
+#ifdef LQ_DIAGNOSTICS
+// Diagnostic builds only: every GEMV CTA writes eight %globaltimer stamps of its phases to
+// `device_buffer` (8 * grid uint64); NULL switches it off. Not part of the shipped ABI.
 extern "C" void lq_gemv_set_timeline(void* device_buffer) {
   lq::g_debug_timeline = (unsigned long long*)device_buffer;
 }
+#endif
 
 extern "C" int lq_gemv_device_error(void) {
   int* word = lq::error_word();
@@ -213,7 +212,8 @@ extern "C" int lq_wq_gemv_fused(const lq_gemv_args* a, void* stream) {
   const int epl = bits == 8 ? 16 : 32;
   LQ_REQUIRE(a->span > 0 && a->span % epl == 0 && Kd % a->span == 0, LQ_ERR_ARG,
              "group span %d must be a positive multiple of %d dividing Kd=%d", a->span, epl, Kd);
-  LQ_REQUIRE(a->x && a->codes && a->scale_tiles && a->out, LQ_ERR_ARG, "null tensor pointer");
+  const bool pushing = a->tp != nullptr && a->tp->mode == LQ_TP_PUSH;
+  LQ_REQUIRE(a->x && a->codes && a->scale_tiles && (a->out || pushing), LQ_ERR_ARG, "null tensor pointer");
   LQ_REQUIRE(((uintptr_t)a->codes % 16) == 0 && ((uintptr_t)a->scale_tiles % 16) == 0, LQ_ERR_ARG,
              "codes and scales must be 16-byte aligned");
   LQ_REQUIRE(a->ldx >= K, LQ_ERR_ARG, "x row stride %d is shorter than K=%d", a->ldx, K);
@@ -221,12 +221,36 @@ extern "C" int lq_wq_gemv_fused(const lq_gemv_args* a, void* stream) {
   if (a->epilogue == 1)
     LQ_REQUIRE(N % 4 == 0 && a->bias == nullptr && a->residual == nullptr, LQ_ERR_ARG,
                "the silu-mul epilogue needs N %% 4 == 0 and no bias / residual");
+  const lq_gemv_tp* tp = a->tp;
+  if (tp != nullptr && tp->mode != 0) {
+    LQ_REQUIRE(tp->mode == LQ_TP_PUSH || tp->mode == LQ_TP_SUM, LQ_ERR_ARG, "unknown tensor-parallel mode %d", tp->mode);
+    LQ_REQUIRE(tp->world >= 1 && tp->world <= 16 && tp->rank >= 0 && tp->rank < tp->world, LQ_ERR_ARG,
+               "bad rank %d / world %d", tp->rank, tp->world);
+    LQ_REQUIRE(a->variant == 0 || a->variant == 2 || a->variant == 1 || a->variant == 3, LQ_ERR_UNSUPPORTED,
+               "the tensor-parallel coupling is built into the streaming kernel (variants 1-3)");
+    LQ_REQUIRE(M <= (bits == 4 ? 2 : 4), LQ_ERR_UNSUPPORTED,
+               "the tensor-parallel coupling takes the rows of one pass (%d given)", M);
+    if (tp->mode == LQ_TP_PUSH) {
+      LQ_REQUIRE(a->epilogue == 0 && a->residual == nullptr && N % 4 == 0 && M * tp->world <= 32, LQ_ERR_ARG,
+                 "a pushing GEMV needs epilogue 0, no residual, N %% 4 == 0 and M * world <= 32");
+      LQ_REQUIRE(tp->peers != nullptr && tp->data_offset % 16 == 0 && tp->counter_offset % 4 == 0, LQ_ERR_ARG,
+                 "peer table missing or exchange offsets misaligned");
+    } else {
+      LQ_REQUIRE(K % 4 == 0 && a->ldx == K, LQ_ERR_ARG, "a summing GEMV needs K %% 4 == 0 and dense rows");
+      LQ_REQUIRE(tp->parts && tp->counters && tp->ready && tp->residual && tp->step, LQ_ERR_ARG,
+                 "null tensor-parallel pointer");
+      LQ_REQUIRE(((uintptr_t)tp->parts % 16) == 0 && ((uintptr_t)tp->residual % 8) == 0 && ((uintptr_t)a->x % 8) == 0,
+                 LQ_ERR_ARG, "partials, residual and x must be 16 / 8 / 8-byte aligned");
+    }
+  } else {
+    tp = nullptr;
+  }
   int variant = a->variant == 0 ? 2 : a->variant;
   // Default choice by measurement: the SIMT kernel keeps 2 (int4) or 4 (int8) activation rows in
   // registers per pass over the weight; from the row count where it would need a second pass the
   // tensor-core kernel, which takes 8 rows in one pass, is the faster one (B200, Llama-3-8B
   // shapes, 8 rows: gate|up 44 vs 96 us, lm_head 185 vs 303 us).
-  if (a->variant == 0 && ((bits == 4 && M >= 3) || M >= 5) && mma_eligible(*a)) variant = 4;
+  if (a->variant == 0 && tp == nullptr && ((bits == 4 && M >= 3) || M >= 5) && mma_eligible(*a)) variant = 4;
   LQ_REQUIRE(variant >= 1 && variant <= 4, LQ_ERR_ARG, "unknown arithmetic variant %d", variant);
   if (variant == 4) {
     LQ_REQUIRE(mma_eligible(*a), LQ_ERR_UNSUPPORTED,
@@ -246,6 +270,19 @@ extern "C" int lq_wq_gemv_fused(const lq_gemv_args* a, void* stream) {
   p.norm_weight = a->norm_weight; p.norm_eps = a->norm_eps; p.pdl = a->pdl;
   p.error_word = error_word();
   p.debug = g_debug_timeline;
+  p.tp_mode = 0; p.tp_world = 0; p.tp_rank = 0; p.tp_peers = nullptr; p.tp_data_off = 0; p.tp_cnt_off = 0;
+  p.tp_parts = nullptr; p.tp_counters = nullptr; p.tp_ready = nullptr; p.tp_residual = nullptr;
+  p.tp_step = nullptr; p.tp_seq_mul = p.tp_seq_add = p.tp_ready_mul = p.tp_ready_add = p.tp_batches = 0;
+  p.tp_wait = kDefaultWaitCycles;
+  if (tp != nullptr) {
+    p.tp_mode = tp->mode; p.tp_world = tp->world; p.tp_rank = tp->rank; p.tp_peers = tp->peers;
+    p.tp_data_off = tp->data_offset; p.tp_cnt_off = tp->counter_offset; p.tp_parts = tp->parts;
+    p.tp_counters = tp->counters; p.tp_ready = tp->ready;
+    p.tp_residual = (const __nv_bfloat16*)tp->residual; p.tp_step = tp->step;
+    p.tp_seq_mul = tp->seq_mul; p.tp_seq_add = tp->seq_add; p.tp_ready_mul = tp->ready_mul;
+    p.tp_ready_add = tp->ready_add; p.tp_batches = tp->producer_batches;
+    if (tp->wait_cycles > 0) p.tp_wait = tp->wait_cycles;
+  }
   LQ_REQUIRE(p.error_word != nullptr, LQ_ERR_LAUNCH, "cannot resolve the device error word");
   p.S = (p.rowbytes + 511) / 512;
   int spw = 1;
@@ -260,8 +297,8 @@ extern "C" int lq_wq_gemv_fused(const lq_gemv_args* a, void* stream) {
   // Ring depth: enough CTAs per SM for ~20 consumer warps (the dot products are dependent
   // chains and need warps to hide their latency), all rings together within ~112 KB per SM so
   // that the next kernel's CTAs can become resident early (see launch_one).
-  const int want_ctas = (g_ring_warps + p.KW - 1) / p.KW;
-  int stages = (g_ring_kb * 1024) / (want_ctas * p.stage_bytes);
+  const int want_ctas = (kRingWarps + p.KW - 1) / p.KW;
+  int stages = (kRingKb * 1024) / (want_ctas * p.stage_bytes);
   stages = stages < 2 ? 2 : (stages > kMaxStages ? kMaxStages : stages);
   LQ_REQUIRE((size_t)stages * p.stage_bytes <= 200 * 1024, LQ_ERR_UNSUPPORTED,
              "row tile of %d bytes does not fit the shared-memory ring", p.stage_bytes);

@@ -39,6 +39,7 @@
 //      2^-15 / 2^-23 of the chunk maximum.
 #pragma once
 #include "common.cuh"
+#include "peer_sync.cuh"
 
 namespace lq {
 namespace gemv {
@@ -46,7 +47,8 @@ namespace gemv {
 constexpr int kU = 4;           // output rows per batch (one float4 of scales)
 constexpr int kMaxWarps = 16;   // consumer warps per CTA (one more warp produces)
 constexpr int kMaxStages = 8;
-extern int g_ring_kb_launch;  // shared memory per SM the rings of one kernel may take (KB)
+constexpr int kRingWarps = 20;  // consumer warps per SM the ring depth aims at
+constexpr int kRingKb = 112;    // shared memory per SM the rings of one kernel may take (KB)
 
 struct GemvParams {
   const __nv_bfloat16* x;
@@ -66,17 +68,59 @@ struct GemvParams {
   int pdl;
   int* error_word;
   unsigned long long* debug;  // optional per-CTA timeline (8 stamps per CTA), normally null
+  // tensor-parallel coupling (see lq_gemv_tp): 0 none, LQ_TP_PUSH, LQ_TP_SUM
+  int tp_mode, tp_world, tp_rank;
+  const uint64_t* tp_peers;
+  int64_t tp_data_off, tp_cnt_off;
+  const float* tp_parts;
+  const uint32_t* tp_counters;
+  uint32_t* tp_ready;
+  const __nv_bfloat16* tp_residual;
+  const uint32_t* tp_step;
+  uint32_t tp_seq_mul, tp_seq_add, tp_ready_mul, tp_ready_add, tp_batches;
+  long long tp_wait;
 };
+
+// Row-parallel epilogue of a tensor-parallel linear: lane (m, u) of the warp holds output
+// (m, n0 + u) of a 4-row batch; lane (m, peer) sends the four values of row m as one 16-byte
+// store into part[rank][m][n0 ..] of that peer's exchange buffer.
+static __device__ __noinline__ void tp_push_batch(const GemvParams& p, uint64_t peer_base, float total,
+                                              int lane, int n0) {
+  const int m = lane / p.tp_world;
+  const int src = (m < 8 ? m : 0) * kU;
+  const float v0 = __shfl_sync(0xffffffffu, total, src);
+  const float v1 = __shfl_sync(0xffffffffu, total, src + 1);
+  const float v2 = __shfl_sync(0xffffffffu, total, src + 2);
+  const float v3 = __shfl_sync(0xffffffffu, total, src + 3);
+  if (m < p.M && n0 < p.N) {
+    float* dst = reinterpret_cast<float*>(peer_base + p.tp_data_off) +
+                 ((int64_t)p.tp_rank * p.M + m) * p.N + n0;
+    st_peer_f4(dst, v0, v1, v2, v3);
+  }
+}
+// After a CTA's last batch: its stores are made visible before its share of the arrival
+// counter is added on every peer.
+static __device__ __noinline__ void tp_push_done(const GemvParams& p, uint64_t peer_base, int lane, int nb) {
+  __threadfence_system();
+  __syncwarp();
+  if (lane < p.tp_world)
+    red_add_release_sys(reinterpret_cast<uint32_t*>(peer_base + p.tp_cnt_off) + p.tp_rank, (uint32_t)nb);
+}
 
 __device__ __forceinline__ unsigned long long global_ns() {
   unsigned long long t;
   asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
   return t;
 }
+// Per-CTA phase stamps exist only in diagnostic builds (-DLQ_DIAGNOSTICS).
+#ifdef LQ_DIAGNOSTICS
 #define LQ_STAMP(slot)                                                             \
   do {                                                                             \
     if (p.debug != nullptr && threadIdx.x == 0) p.debug[(size_t)blockIdx.x * 8 + (slot)] = global_ns(); \
   } while (0)
+#else
+#define LQ_STAMP(slot) do { } while (0)
+#endif
 
 __device__ __forceinline__ int dp4a_ss(unsigned a, unsigned b, int c) {
   int d;
@@ -242,6 +286,59 @@ struct XChunk<BITS, 2> : XPlanes<BITS, 2> {};
 template <int BITS>
 struct XChunk<BITS, 3> : XPlanes<BITS, 3> {};
 
+// Tensor-parallel input of a GEMV: x = bf16(bf16(sum over ranks of the partials) + residual),
+// built once by the first CTAs of the grid (each a slice) and published to the others through
+// a counter. Called by the consumer warps only (named barrier 2 over KW * 32 threads). Kept
+// out of line so that its registers do not count against the row loop's.
+static __device__ __noinline__ void tp_sum_prologue(const GemvParams& p, int KW, int warp, int lane) {
+  const int T = KW * 32, tid = warp * 32 + lane;
+  const uint32_t step = *reinterpret_cast<const volatile uint32_t*>(p.tp_step);
+  const int total4 = p.M * p.K / 4;
+  const int R = min((int)gridDim.x, (total4 + T - 1) / T);
+  if ((int)blockIdx.x < R) {
+    if (tid < p.tp_world) {
+      const uint32_t want = (step * p.tp_seq_mul + p.tp_seq_add) * p.tp_batches;
+      if (!wait_counter<true>(p.tp_counters + tid, want, p.tp_wait)) atomicExch(p.error_word, 3);
+    }
+    asm volatile("bar.sync 2, %0;" ::"r"(T) : "memory");
+    __nv_bfloat16* hx = const_cast<__nv_bfloat16*>(p.x);
+    const int64_t stride = (int64_t)p.M * p.K;  // floats between two ranks' partials
+    for (int i = blockIdx.x * T + tid; i < total4; i += R * T) {
+      float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+      for (int r0 = 0; r0 < p.tp_world; r0 += 4) {  // four loads in flight, summed in rank order
+        float4 v[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+          if (r0 + j < p.tp_world)
+            v[j] = ld_peer_f4(reinterpret_cast<const float4*>(p.tp_parts + (r0 + j) * stride) + i);
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+          if (r0 + j < p.tp_world) { acc.x += v[j].x; acc.y += v[j].y; acc.z += v[j].z; acc.w += v[j].w; }
+      }
+      const uint2 rr = __ldcg(reinterpret_cast<const uint2*>(p.tp_residual) + i);
+      const float r4[4] = {__uint_as_float(rr.x << 16), __uint_as_float(rr.x & 0xFFFF0000u),
+                           __uint_as_float(rr.y << 16), __uint_as_float(rr.y & 0xFFFF0000u)};
+      const float a4[4] = {acc.x, acc.y, acc.z, acc.w};
+      unsigned short o4[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j)  // round the layer output, add the residual stream, round
+        o4[j] = __bfloat16_as_ushort(__float2bfloat16_rn(__bfloat162float(__float2bfloat16_rn(a4[j])) + r4[j]));
+      uint2 packed;
+      packed.x = (unsigned)o4[0] | ((unsigned)o4[1] << 16);
+      packed.y = (unsigned)o4[2] | ((unsigned)o4[3] << 16);
+      reinterpret_cast<uint2*>(hx)[i] = packed;
+    }
+    __threadfence();
+    asm volatile("bar.sync 2, %0;" ::"r"(T) : "memory");
+    if (tid == 0) red_add_release_gpu(p.tp_ready, 1u);
+  }
+  if (tid == 0) {
+    const uint32_t want = (step * p.tp_ready_mul + p.tp_ready_add) * (uint32_t)R;
+    if (!wait_counter<false>(p.tp_ready, want, p.tp_wait)) atomicExch(p.error_word, 4);
+  }
+  asm volatile("bar.sync 2, %0;" ::"r"(T) : "memory");
+}
+
 // ------------------------------------------------------------------ the kernel
 // Sums four per-lane values over the warp with 6 shuffles: afterwards lane l holds the total
 // of value (l & 3).
@@ -326,6 +423,8 @@ gemv_stream_kernel(const GemvParams p) {
 
   // ------------------------------------------------------------ finisher warp
   if (warp == KW + 1) {
+    const bool push = EPI == 0 && p.tp_mode == LQ_TP_PUSH;
+    const uint64_t peer_base = push ? p.tp_peers[lane % p.tp_world] : 0;
     asm volatile("griddepcontrol.wait;" ::: "memory");  // the residual comes from earlier kernels
     for (int it = 0; it < nb; ++it) {
       const int parity = it & 1;
@@ -367,6 +466,8 @@ gemv_stream_kernel(const GemvParams p) {
           if (p.out_f32) reinterpret_cast<float*>(p.out)[o] = __bfloat162float(__float2bfloat16_rn(y));
           else reinterpret_cast<__nv_bfloat16*>(p.out)[o] = __float2bfloat16_rn(y);
         }
+      } else if (push) {
+        tp_push_batch(p, peer_base, total + bias_pre, lane, n0);
       } else if (mine) {
         total += bias_pre;
         const int64_t o = (int64_t)m * p.N + n;
@@ -379,6 +480,7 @@ gemv_stream_kernel(const GemvParams p) {
         }
       }
     }
+    if (push) tp_push_done(p, peer_base, lane, nb);
     return;
   }
 
@@ -439,6 +541,10 @@ gemv_stream_kernel(const GemvParams p) {
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   LQ_STAMP(2);
 
+  // ---- tensor-parallel input: the hidden rows are first built from the ranks' partial sums
+  const bool tp_sum = p.tp_mode == LQ_TP_SUM;
+  if (tp_sum) tp_sum_prologue(p, KW, warp, lane);
+
   uint32_t xraw[M][SPW][PW];
 #pragma unroll
   for (int m = 0; m < M; ++m)
@@ -448,7 +554,9 @@ gemv_stream_kernel(const GemvParams p) {
       if (fast[j] && m < p.M) {
 #pragma unroll
         for (int v = 0; v < PW / 4; ++v) {
-          const uint4 raw = __ldg(reinterpret_cast<const uint4*>(xr) + v);
+          // rows another CTA of this kernel has just written must not come from the read-only path
+          const uint4 raw = tp_sum ? __ldcg(reinterpret_cast<const uint4*>(xr) + v)
+                                   : __ldg(reinterpret_cast<const uint4*>(xr) + v);
           xraw[m][j][4 * v] = raw.x; xraw[m][j][4 * v + 1] = raw.y;
           xraw[m][j][4 * v + 2] = raw.z; xraw[m][j][4 * v + 3] = raw.w;
         }
@@ -457,8 +565,9 @@ gemv_stream_kernel(const GemvParams p) {
         for (int i = 0; i < PW; ++i) {
           const int k = k0s[j] + 2 * i;
           const bool ok = cb[j] >= 0 && m < p.M;
-          const unsigned lo = (ok && k < p.K) ? __bfloat16_as_ushort(xr[2 * i]) : 0u;
-          const unsigned hi = (ok && k + 1 < p.K) ? __bfloat16_as_ushort(xr[2 * i + 1]) : 0u;
+          const volatile unsigned short* xv = reinterpret_cast<const volatile unsigned short*>(xr);
+          const unsigned lo = (ok && k < p.K) ? xv[2 * i] : 0u;
+          const unsigned hi = (ok && k + 1 < p.K) ? xv[2 * i + 1] : 0u;
           xraw[m][j][i] = lo | (hi << 16);
         }
       }
@@ -604,6 +713,7 @@ gemv_stream_kernel(const GemvParams p) {
       // hand the batch to the finisher warp (which arrives once it is done with the one before)
       asm volatile("bar.sync 1, %0;" ::"r"(round_threads) : "memory");
     } else {
+      const bool push = EPI == 0 && p.tp_mode == LQ_TP_PUSH;
       float total = 0.f;
       // lane u (< 4) holds row u for every m: lane (m, u) fetches it (all lanes shuffle)
 #pragma unroll
@@ -624,6 +734,8 @@ gemv_stream_kernel(const GemvParams p) {
           if (p.out_f32) reinterpret_cast<float*>(p.out)[o] = __bfloat162float(__float2bfloat16_rn(y));
           else reinterpret_cast<__nv_bfloat16*>(p.out)[o] = __float2bfloat16_rn(y);
         }
+      } else if (push) {
+        tp_push_batch(p, p.tp_peers[lane % p.tp_world], total + bias_pre, lane, n0);
       } else if (lane < M * kU && n < p.N && m < p.M) {
         total += bias_pre;
         const int64_t o = (int64_t)m * p.N + n;
@@ -637,6 +749,8 @@ gemv_stream_kernel(const GemvParams p) {
       }
     }
   }
+  if (KW == 1 && EPI == 0 && p.tp_mode == LQ_TP_PUSH)
+    tp_push_done(p, p.tp_peers[lane % p.tp_world], lane, nb);
   LQ_STAMP(5);
 }
 
@@ -644,17 +758,13 @@ template <int BITS, int VAR, int M, int SPW, int EPI>
 int launch_one(const GemvParams& p, int threads, cudaStream_t s) {
   auto kern = gemv_stream_kernel<BITS, VAR, M, SPW, EPI>;
   const size_t smem = (size_t)p.stages * p.stage_bytes;
-  static thread_local bool attr_set = false;
-  if (!attr_set) {
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024) != cudaSuccess) {
-      cudaGetLastError();
-      return fail(LQ_ERR_LAUNCH, "lq_wq_gemv: cannot raise the dynamic shared memory limit");
-    }
-    attr_set = true;
-  }
-  static thread_local int occ_threads = 0, occ = 0;
+  if (const int rc = ensure_smem_limit(reinterpret_cast<const void*>(kern), 200 * 1024, "lq_wq_gemv")) return rc;
+  static thread_local int occ_threads = 0, occ = 0, occ_dev = -1;
   static thread_local size_t occ_smem = 0;
-  if (occ_threads != threads || occ_smem != smem) {
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (occ_threads != threads || occ_smem != smem || occ_dev != dev) {
+    occ_dev = dev;
     int n = 0;
     if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kern, threads, smem) != cudaSuccess || n <= 0) {
       cudaGetLastError();
@@ -669,7 +779,7 @@ int launch_one(const GemvParams& p, int threads, cudaStream_t s) {
   // NEXT kernel on the stream (programmatic dependent launch) find room to become resident
   // and fill their own rings while this kernel is still computing.
   int per_sm = occ;
-  const int by_smem = (int)(((size_t)g_ring_kb_launch * 1024) / (smem > 0 ? smem : 1));
+  const int by_smem = (int)(((size_t)kRingKb * 1024) / (smem > 0 ? smem : 1));
   if (by_smem >= 1 && per_sm > by_smem) per_sm = by_smem;
   const int cap = sm_count() * per_sm;
   int grid = p.nbatch < cap ? p.nbatch : cap;
@@ -721,6 +831,8 @@ int launch_m(const GemvParams& p, int spw, int threads, cudaStream_t s) {
 template <int BITS, int VAR>
 int launch_passes(GemvParams p, const lq_gemv_args& a, int spw, int threads, cudaStream_t s) {
   const int step = max_rows<BITS, VAR>(spw);
+  if (p.tp_mode != 0 && a.M > step)
+    return fail(LQ_ERR_UNSUPPORTED, "the tensor-parallel coupling takes the rows of one pass (%d > %d)", a.M, step);
   const size_t out_es = p.out_f32 ? 4 : 2;
   const int n_out = a.epilogue == 1 ? a.N / 2 : a.N;
   for (int m0 = 0; m0 < a.M; m0 += step) {

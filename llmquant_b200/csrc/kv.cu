@@ -15,6 +15,9 @@
 
 #include "common.cuh"
 
+#include <map>
+#include <mutex>
+
 namespace lq {
 namespace {
 
@@ -369,6 +372,71 @@ int launch_pdl_smem(Kern kern, dim3 grid, dim3 block, size_t smem, cudaStream_t 
   return LQ_OK;
 }
 
+// Whether clusters of `cluster_x` CTAs of this kernel can become resident on the current device
+// (sizes above 8 need the non-portable opt-in first). Asked once per (kernel, device, size).
+template <typename Kern>
+bool cluster_fits(Kern kern, int cluster_x, dim3 grid, dim3 block, size_t smem) {
+  struct Key { const void* k; int dev, cx; bool operator<(const Key& o) const {
+    return k != o.k ? k < o.k : (dev != o.dev ? dev < o.dev : cx < o.cx); } };
+  static std::mutex mu;
+  static std::map<Key, bool> known;
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) { cudaGetLastError(); return false; }
+  std::lock_guard<std::mutex> lock(mu);
+  const Key key{reinterpret_cast<const void*>(kern), dev, cluster_x};
+  auto it = known.find(key);
+  if (it != known.end()) return it->second;
+  bool ok = true;
+  if (cluster_x > 8 &&
+      cudaFuncSetAttribute(kern, cudaFuncAttributeNonPortableClusterSizeAllowed, 1) != cudaSuccess) {
+    cudaGetLastError();
+    ok = false;
+  }
+  if (ok) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = (unsigned)cluster_x;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    int n = 0;
+    if (cudaOccupancyMaxActiveClusters(&n, kern, &cfg) != cudaSuccess) { cudaGetLastError(); n = 0; }
+    ok = n >= 1;
+  }
+  known[key] = ok;
+  return ok;
+}
+
+template <typename Kern, typename... Args>
+int launch_cluster(Kern kern, dim3 grid, dim3 block, size_t smem, int cluster_x, cudaStream_t s, int pdl,
+                   const char* what, Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = s;
+  cudaLaunchAttribute attr[2];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = (unsigned)cluster_x;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl ? 2 : 1;
+  cudaError_t e = cudaLaunchKernelEx(&cfg, kern, args...);
+  if (e != cudaSuccess) {
+    cudaGetLastError();
+    return fail(LQ_ERR_LAUNCH, "%s: %s", what, cudaGetErrorString(e));
+  }
+  return LQ_OK;
+}
+
 }  // namespace
 }  // namespace lq
 
@@ -551,7 +619,11 @@ attn_fused_kernel(const __nv_bfloat16* __restrict__ qkv, const __nv_bfloat16* __
                   __nv_bfloat16* __restrict__ out, float* part_o, float* part_ml, int* tickets,
                   int Hq, int Hkv, int Tmax, int table_len, const int64_t* pos_dev, int64_t pos_host,
                   float scaling, float qmin, float qmax, int* error_word, unsigned long long* debug) {
+#ifdef LQ_DIAGNOSTICS
 #define ATT_STAMP(slot) do { if (debug != nullptr && threadIdx.x == 0) { unsigned long long t_; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_)); debug[((size_t)(blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x) * 8 + (slot)] = t_; } } while (0)
+#else
+#define ATT_STAMP(slot) do { } while (0)
+#endif
   constexpr int DPL = D / 16;  // dims per lane
   constexpr int NGRP = 16;     // lane groups per CTA (8 warps x 2)
   constexpr int NT = kFusedThreads;
@@ -918,8 +990,33 @@ attn_fused_kernel(const __nv_bfloat16* __restrict__ qkv, const __nv_bfloat16* __
 //           codes of four token rows widened to bf16 in registers.
 // Staged rows are padded by 16 bytes so that both fragment access patterns are free of
 // shared-memory bank conflicts (one bulk copy per row).
+//
+// Two ways to merge the slices of one KV head (template flag CL):
+//   CL = false  every CTA writes its partial (max, sum, output) to global scratch and the CTA
+//               that takes the last ticket merges them: any number of slices.
+//   CL = true   the slices of a KV head form ONE thread-block cluster (2, 4, 8 or 16 CTAs): every
+//               CTA sends each piece of its partial output straight into the shared memory of
+//               the CTA that owns those output elements (st.shared::cluster), one cluster
+//               barrier follows, and every CTA finishes its own G * D / slices outputs -- no
+//               global scratch, no ticket, no second trip through L2. Every path reaches the
+//               cluster barrier (the waits before it are bounded), so it always completes.
 constexpr int kMmaThreads = 256;
-constexpr int kMmaCap = 192;  // tokens staged per chunk
+constexpr int kMmaCap = 192;      // tokens staged per chunk
+constexpr int kClusterCap = 288;  // the same for the cluster variant: 16 slices of a 4.6k context in one chunk
+constexpr int kMaxCluster = 16;
+
+__device__ __forceinline__ uint32_t cluster_map(uint32_t smem_addr, uint32_t cta_rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(cta_rank));
+  return r;
+}
+__device__ __forceinline__ void st_cluster_f32(uint32_t addr, float v) {
+  asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(addr), "f"(v) : "memory");
+}
+__device__ __forceinline__ void cluster_barrier() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
 
 __device__ __forceinline__ void mma_s8(int (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
   asm volatile(
@@ -939,16 +1036,20 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   return *reinterpret_cast<const uint32_t*>(&v);
 }
 
-template <int D, int G>
+template <int D, int G, bool CL>
 __global__ void __launch_bounds__(kMmaThreads)
 attn_mma_kernel(const __nv_bfloat16* __restrict__ qkv, const __nv_bfloat16* __restrict__ cos_t,
                 const __nv_bfloat16* __restrict__ sin_t, int8_t* kc, int8_t* vc, float* ks, float* vs,
                 __nv_bfloat16* __restrict__ out, float* part_o, float* part_ml, int* tickets,
                 int Hq, int Hkv, int Tmax, int table_len, const int64_t* pos_dev, int64_t pos_host,
                 float scaling, float qmin, float qmax, int* error_word, unsigned long long* debug) {
+#ifdef LQ_DIAGNOSTICS
 #define ATT_STAMP(slot) do { if (debug != nullptr && threadIdx.x == 0) { unsigned long long t_; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_)); debug[((size_t)(blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x) * 8 + (slot)] = t_; } } while (0)
+#else
+#define ATT_STAMP(slot) do { } while (0)
+#endif
   constexpr int NT = kMmaThreads, NW = NT / 32;
-  constexpr int HALF = D / 2, CAP = kMmaCap, PK = D;  // unpadded rows: one bulk copy per chunk
+  constexpr int HALF = D / 2, CAP = CL ? kClusterCap : kMmaCap, PK = D;  // unpadded rows: one bulk copy per chunk
   constexpr int KS = D / 32;   // k-steps of the score MMA
   constexpr int DT = D / 8;    // n-tiles of the value MMA
   extern __shared__ __align__(128) uint8_t stage[];  // K rows [CAP][PK], then V rows [CAP][PK]
@@ -961,10 +1062,17 @@ attn_mma_kernel(const __nv_bfloat16* __restrict__ qkv, const __nv_bfloat16* __re
   __shared__ float newscale_s[2], snew_s[G];
   __shared__ float mw_s[NW][8], lw_s[NW][8];
   __shared__ int last_s;
+  // cluster variant: what the other slices send here -- their pieces of this CTA's outputs and
+  // their (max, sum) per head
+  __shared__ float recv_o[CL ? G * D : 1];
+  __shared__ float recv_ml[CL ? kMaxCluster * G * 2 : 1];
 
   const int ns = gridDim.x, split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int gid = lane >> 2, q4 = lane & 3;  // fragment coordinates
+  // A CTA's shared memory may be written by its cluster peers only once it has started: every
+  // CTA announces itself here and waits for the others right before its first remote store.
+  if (CL) asm volatile("barrier.cluster.arrive.relaxed.aligned;" ::: "memory");
   ATT_STAMP(0);
   int64_t pos = read_pos(pos_dev, pos_host);
   if (pos < 0) pos = 0;
@@ -1118,7 +1226,7 @@ attn_mma_kernel(const __nv_bfloat16* __restrict__ qkv, const __nv_bfloat16* __re
   for (int c_lo = t_lo; c_lo < t_hi; c_lo += CAP) {
     const int n = min(CAP, t_hi - c_lo);
     for (int i = threadIdx.x; i < n; i += NT) {
-      const bool pre = c_lo == t_lo && i == (int)threadIdx.x;  // CAP <= NT: the first chunk is prefetched
+      const bool pre = c_lo == t_lo && i == (int)threadIdx.x;  // the first NT scales of the first chunk are prefetched
       sk_s[i] = pre ? pre_sk : ks[head_row + c_lo + i];
       sv_s[i] = pre ? pre_sv : vs[head_row + c_lo + i];
     }
@@ -1180,7 +1288,7 @@ attn_mma_kernel(const __nv_bfloat16* __restrict__ qkv, const __nv_bfloat16* __re
   }
   if (dead) {
     if (threadIdx.x == 0) atomicExch(error_word, 4);
-    return;
+    if (!CL) return;  // (a cluster's CTAs all go on to the cluster barrier)
   }
   ATT_STAMP(4);
   l_run += __shfl_xor_sync(0xffffffffu, l_run, 1);
@@ -1188,6 +1296,7 @@ attn_mma_kernel(const __nv_bfloat16* __restrict__ qkv, const __nv_bfloat16* __re
 
   // ---- merge the warps (and the new token) of the CTA; the staging area is free now
   float (*ow_s)[G][D] = reinterpret_cast<float (*)[G][D]>(stage);  // [NW][G][D]
+  if (CL) asm volatile("barrier.cluster.wait.aligned;" ::: "memory");  // every peer has started
   if (q4 == 0 && gid < 8) { mw_s[warp][gid] = m_run; lw_s[warp][gid] = l_run; }
   if (gid < G) {
 #pragma unroll
@@ -1219,13 +1328,50 @@ attn_mma_kernel(const __nv_bfloat16* __restrict__ qkv, const __nv_bfloat16* __re
       acc1 = fmaf(vnew_s[d + D / 2] * newscale_s[1], e, acc1);
       lt += e;
     }
-    float* po = part_o + (((int64_t)b * Hq + kvh * G + g) * ns + split) * D;
-    po[d] = acc0;
-    po[d + D / 2] = acc1;
-    if (d == 0) {
-      float* ml = part_ml + (((int64_t)b * Hq + kvh * G + g) * ns + split) * 2;
-      ml[0] = mm; ml[1] = lt;
+    if (CL) {
+      // output j = g * D + d belongs to CTA j / OPC of the cluster; this slice's piece lands at
+      // [split][j % OPC] of that CTA's receive area, its (max, sum) in everyone's table
+      const int OPC = G * D / ns;
+      const int j0 = g * D + d, j1 = j0 + D / 2;
+      st_cluster_f32(cluster_map(smem_u32(&recv_o[split * OPC + j0 % OPC]), j0 / OPC), acc0);
+      st_cluster_f32(cluster_map(smem_u32(&recv_o[split * OPC + j1 % OPC]), j1 / OPC), acc1);
+      if (d == 0) {
+        for (int c = 0; c < ns; ++c) {
+          st_cluster_f32(cluster_map(smem_u32(&recv_ml[(split * G + g) * 2]), c), mm);
+          st_cluster_f32(cluster_map(smem_u32(&recv_ml[(split * G + g) * 2 + 1]), c), lt);
+        }
+      }
+    } else {
+      float* po = part_o + (((int64_t)b * Hq + kvh * G + g) * ns + split) * D;
+      po[d] = acc0;
+      po[d + D / 2] = acc1;
+      if (d == 0) {
+        float* ml = part_ml + (((int64_t)b * Hq + kvh * G + g) * ns + split) * 2;
+        ml[0] = mm; ml[1] = lt;
+      }
     }
+  }
+  if (CL) {
+    // ---- every slice has delivered: finish this CTA's share of the head's outputs
+    cluster_barrier();
+    const int OPC = G * D / ns;
+    for (int i = threadIdx.x; i < OPC; i += NT) {
+      const int j = split * OPC + i, g = j / D, d = j % D;
+      float mm = -INFINITY;
+      for (int c = 0; c < ns; ++c) mm = fmaxf(mm, recv_ml[(c * G + g) * 2]);
+      float ov = 0.f, lt = 0.f;
+      for (int c = 0; c < ns; ++c) {
+        const float mc = recv_ml[(c * G + g) * 2];
+        if (mc != -INFINITY) {
+          const float e = __expf(mc - mm);
+          ov = fmaf(recv_o[c * OPC + i], e, ov);
+          lt = fmaf(recv_ml[(c * G + g) * 2 + 1], e, lt);
+        }
+      }
+      out[((int64_t)b * Hq + kvh * G + g) * D + d] = __float2bfloat16_rn(lt > 0.f ? ov / lt : 0.f);
+    }
+    ATT_STAMP(7);
+    return;
   }
 
   // ---- the CTA that finishes last merges the slices
@@ -1330,19 +1476,22 @@ attn_mma_kernel(const __nv_bfloat16* __restrict__ qkv, const __nv_bfloat16* __re
 #undef ATT_STAMP
 }
 
-int g_attn_impl = 0;  // host-side switch: 0 = mma.sync kernel, 1 = SIMT kernel
-
 __device__ int g_attn_error = 0;
+#ifdef LQ_DIAGNOSTICS
 unsigned long long* g_attn_timeline = nullptr;
+#else
+constexpr unsigned long long* g_attn_timeline = nullptr;
+#endif
 
 }  // namespace
 }  // namespace lq
 
-extern "C" void lq_attn_set_impl(int impl) { lq::g_attn_impl = impl; }
-
+#ifdef LQ_DIAGNOSTICS
+// Diagnostic builds only: eight %globaltimer stamps per CTA of lq_attn_decode_fused.
 extern "C" void lq_attn_set_timeline(void* device_buffer) {
   lq::g_attn_timeline = (unsigned long long*)device_buffer;
 }
+#endif
 
 extern "C" int lq_attn_device_error(void) {
   void* ptr = nullptr;
@@ -1361,9 +1510,10 @@ extern "C" int lq_attn_decode_fused(const void* qkv, const void* cos_table, cons
                                     int8_t* k_codes, int8_t* v_codes, float* k_scales, float* v_scales,
                                     void* out, void* scratch, int B, int Hq, int Hkv, int D, int Tmax,
                                     int table_len, const int64_t* pos_dev, int64_t pos, int num_bits,
-                                    float scaling, int splits, int pdl, void* stream) {
+                                    float scaling, int splits, int impl, int pdl, void* stream) {
   using namespace lq;
   LQ_REQUIRE(num_bits >= 2 && num_bits <= 8, LQ_ERR_ARG, "num_bits must be in [2, 8], got %d", num_bits);
+  LQ_REQUIRE(impl >= 0 && impl <= 3, LQ_ERR_ARG, "unknown attention implementation %d", impl);
   LQ_REQUIRE(B > 0 && Hq > 0 && Hkv > 0 && Hq % Hkv == 0 && Tmax > 0 && table_len > 0, LQ_ERR_ARG, "bad shape");
   LQ_REQUIRE(splits >= 1 && splits <= 1024, LQ_ERR_ARG, "splits must be in [1, 1024]");
   LQ_REQUIRE(qkv && cos_table && sin_table && k_codes && v_codes && k_scales && v_scales && out && scratch,
@@ -1380,18 +1530,42 @@ extern "C" int lq_attn_decode_fused(const void* qkv, const void* cos_table, cons
     cudaGetLastError();
     return fail(LQ_ERR_LAUNCH, "cannot resolve the device error word");
   }
-  if (g_attn_impl == 0) {
+  // one thread-block cluster per KV head when the slices can form one (2, 4, 8 or 16 of them,
+  // dividing the head's outputs evenly) and such clusters fit the device
+  const bool cluster_shape = splits >= 2 && splits <= kMaxCluster && (splits & (splits - 1)) == 0 &&
+                             (G * D) % splits == 0 && (G * D) / splits >= 1 && (D == 64 || D == 128);
+  if ((impl == LQ_ATTN_AUTO || impl == LQ_ATTN_CLUSTER) && cluster_shape) {
+    const size_t csmem = 2 * (size_t)kClusterCap * D;
+    bool tried = false;
+#define LQ_CL_CASE(DD, GG)                                                                         \
+  if (D == DD && G == GG) {                                                                        \
+    auto kern = attn_mma_kernel<DD, GG, true>;                                                     \
+    if (const int rs = ensure_smem_limit(reinterpret_cast<const void*>(kern), (int)csmem, "lq_attn_decode_fused")) return rs; \
+    if (cluster_fits(kern, splits, grid, dim3(kMmaThreads), csmem)) {                              \
+      tried = true;                                                                                \
+      rc = launch_cluster(kern, grid, dim3(kMmaThreads), csmem, splits, (cudaStream_t)stream, pdl, \
+                    "lq_attn_decode_fused", (const __nv_bfloat16*)qkv, (const __nv_bfloat16*)cos_table, \
+                    (const __nv_bfloat16*)sin_table, k_codes, v_codes, k_scales, v_scales,         \
+                    (__nv_bfloat16*)out, part_o, part_ml, tickets, Hq, Hkv, Tmax, table_len, pos_dev, \
+                    pos, scaling, -qmax - 1.f, qmax, (int*)err_ptr, g_attn_timeline);              \
+    }                                                                                              \
+  }
+    LQ_CL_CASE(64, 1) LQ_CL_CASE(64, 2) LQ_CL_CASE(64, 4) LQ_CL_CASE(64, 8)
+    LQ_CL_CASE(128, 1) LQ_CL_CASE(128, 2) LQ_CL_CASE(128, 4) LQ_CL_CASE(128, 8)
+#undef LQ_CL_CASE
+    if (tried) return rc;
+  }
+  if (impl == LQ_ATTN_CLUSTER)
+    return fail(LQ_ERR_UNSUPPORTED, "clusters of %d CTAs are not available for this shape on this device (head_dim %d, %d "
+                "query heads per KV head; the slice count must be 2, 4, 8 or 16)", splits, D, G);
+  if (impl != LQ_ATTN_SIMT) {
     const size_t msmem = 2 * (size_t)kMmaCap * D;
     LQ_REQUIRE((size_t)splits * G * 4 + (size_t)(kMmaThreads / 32 + 1) * G * D * 4 + 64 <= msmem, LQ_ERR_ARG,
                "too many slices (%d) for the merge area of the attention kernel", splits);
 #define LQ_MMA_CASE(DD, GG)                                                                        \
   if (D == DD && G == GG) {                                                                        \
-    static bool raised = false;                                                                    \
-    if (!raised) {                                                                                 \
-      cudaFuncSetAttribute(attn_mma_kernel<DD, GG>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)msmem); \
-      raised = true;                                                                               \
-    }                                                                                              \
-    rc = launch_pdl_smem(attn_mma_kernel<DD, GG>, grid, dim3(kMmaThreads), msmem, (cudaStream_t)stream, pdl, \
+    if (const int rs = ensure_smem_limit(reinterpret_cast<const void*>(attn_mma_kernel<DD, GG, false>), (int)msmem, "lq_attn_decode_fused")) return rs; \
+    rc = launch_pdl_smem(attn_mma_kernel<DD, GG, false>, grid, dim3(kMmaThreads), msmem, (cudaStream_t)stream, pdl, \
                     "lq_attn_decode_fused", (const __nv_bfloat16*)qkv, (const __nv_bfloat16*)cos_table, \
                     (const __nv_bfloat16*)sin_table, k_codes, v_codes, k_scales, v_scales,         \
                     (__nv_bfloat16*)out, part_o, part_ml, tickets, Hq, Hkv, Tmax, table_len, pos_dev, \
@@ -1405,11 +1579,7 @@ extern "C" int lq_attn_decode_fused(const void* qkv, const void* cos_table, cons
   const size_t smem = 2 * (size_t)kFusedChunkBytes + (size_t)(kFusedChunkBytes / 64) * 8 * sizeof(float);
 #define LQ_FUSED_CASE(DD, GG)                                                                      \
   if (D == DD && G == GG) {                                                                        \
-    static bool raised = false;                                                                    \
-    if (!raised) {                                                                                 \
-      cudaFuncSetAttribute(attn_fused_kernel<DD, GG>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
-      raised = true;                                                                               \
-    }                                                                                              \
+    if (const int rs = ensure_smem_limit(reinterpret_cast<const void*>(attn_fused_kernel<DD, GG>), (int)smem, "lq_attn_decode_fused")) return rs; \
     rc = launch_pdl_smem(attn_fused_kernel<DD, GG>, grid, dim3(kFusedThreads), smem, (cudaStream_t)stream, pdl, \
                     "lq_attn_decode_fused", (const __nv_bfloat16*)qkv, (const __nv_bfloat16*)cos_table, \
                     (const __nv_bfloat16*)sin_table, k_codes, v_codes, k_scales, v_scales,         \

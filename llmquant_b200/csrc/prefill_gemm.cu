@@ -108,7 +108,6 @@ struct GemmParams {
   __nv_bfloat16* out;       // [M, N]
   int M, N, K, Kd, span, groups, rowbytes;
   int* error_word;
-  int probe;  // timing probes (results wrong): 2 = drain a quarter of the columns, 3 = one MMA per group
 };
 
 // ES = bytes per operand element (2: bf16 operands, 1: int8 operands)
@@ -442,7 +441,6 @@ prefill_gemm_ws_kernel(const GemmParams p) {
         const uint32_t a_addr = smem_u32(tiles + st * 2 * TILE), b_addr = a_addr + TILE;
 #pragma unroll
         for (int s = 0; s < 4; ++s) {
-          if (p.probe == 3 && s > 0) break;
           // 32 bytes of K per MMA: the start address moves along the 128-byte row
           const uint64_t da = smem_desc_sw128(a_addr + s * 32);
           const uint64_t db = smem_desc_sw128(b_addr + s * 32);
@@ -471,7 +469,6 @@ prefill_gemm_ws_kernel(const GemmParams p) {
       const float* wsg = ws_s[g & 7] + cbase;
 #pragma unroll
       for (int c0 = 0; c0 < HALF; c0 += 32) {
-        if (p.probe == 2 && c0 > 0) break;
         uint32_t v[32];
         tmem_ld32(tmem_base + st * kTmemCols + ((uint32_t)(quarter * 32) << 16) + cbase + c0, v);
 #pragma unroll
@@ -697,34 +694,18 @@ template <int BITS>
 int launch_gemm_f16(const GemmParams& p, cudaStream_t s) {
   auto kern = prefill_gemm_f16_kernel<BITS>;
   const size_t smem = 1024 + (size_t)kF16Stages * 4 * BM * 128;  // A and B tiles of 32 KB per stage
-  static bool raised = false;
-  if (!raised) {
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 210 * 1024) != cudaSuccess) {
-      cudaGetLastError();
-      return fail(LQ_ERR_LAUNCH, "lq_wq_gemm_prefill: cannot raise the shared memory limit");
-    }
-    raised = true;
-  }
+  if (const int rc = ensure_smem_limit(reinterpret_cast<const void*>(kern), 210 * 1024, "lq_wq_gemm_prefill")) return rc;
   dim3 grid((unsigned)((p.N + BN - 1) / BN), (unsigned)((p.M + BM - 1) / BM));
   kern<<<grid, kF16Threads, smem, s>>>(p);
   return check_launch("lq_wq_gemm_prefill");
 }
-
-int g_gemm_impl = 0;  // host-side switch: 0 = pipelined kernel where it applies, 1 = serial kernel
 
 template <int BITS>
 int launch_gemm_ws(const GemmParams& p, cudaStream_t s) {
   auto kern = prefill_gemm_ws_kernel<BITS>;
   // operand tiles of kWsStages groups, plus (int4) the staging rows of nibble bytes
   const size_t smem = 1024 + (size_t)kWsStages * 2 * BM * 128 + (BITS == 4 ? (size_t)kWsStages * BN * 64 : 0);
-  static bool raised = false;
-  if (!raised) {
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 210 * 1024) != cudaSuccess) {
-      cudaGetLastError();
-      return fail(LQ_ERR_LAUNCH, "lq_wq_gemm_prefill: cannot raise the shared memory limit");
-    }
-    raised = true;
-  }
+  if (const int rc = ensure_smem_limit(reinterpret_cast<const void*>(kern), 210 * 1024, "lq_wq_gemm_prefill")) return rc;
   dim3 grid((unsigned)((p.N + BN - 1) / BN), (unsigned)((p.M + BM - 1) / BM));
   kern<<<grid, kWsThreads, smem, s>>>(p);
   return check_launch("lq_wq_gemm_prefill");
@@ -736,14 +717,7 @@ template <int BITS, int ES>
 int launch_gemm(const GemmParams& p, cudaStream_t s) {
   auto kern = prefill_gemm_kernel<BITS, ES>;
   const size_t smem = 2 * (size_t)BM * p.span * ES;
-  static bool raised = false;
-  if (!raised) {
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024) != cudaSuccess) {
-      cudaGetLastError();
-      return fail(LQ_ERR_LAUNCH, "lq_wq_gemm_prefill: cannot raise the shared memory limit");
-    }
-    raised = true;
-  }
+  if (const int rc = ensure_smem_limit(reinterpret_cast<const void*>(kern), 64 * 1024, "lq_wq_gemm_prefill")) return rc;
   dim3 grid((unsigned)((p.N + BN - 1) / BN), (unsigned)((p.M + BM - 1) / BM));
   kern<<<grid, kThreads, smem, s>>>(p);
   return check_launch("lq_wq_gemm_prefill");
@@ -751,8 +725,6 @@ int launch_gemm(const GemmParams& p, cudaStream_t s) {
 
 }  // namespace
 }  // namespace lq
-
-extern "C" void lq_gemm_set_impl(int impl) { lq::g_gemm_impl = impl; }
 
 extern "C" int lq_gemm_device_error(void) {
   void* ptr = nullptr;
@@ -792,10 +764,10 @@ extern "C" int lq_wq_gemm_prefill(const void* x, int ldx, const int8_t* x_codes,
   }
   p.error_word = (int*)err;
   cudaStream_t s = (cudaStream_t)stream;
-  p.probe = g_gemm_impl;
-  if (a8 && span == 128 && g_gemm_impl != 1) return bits == 8 ? launch_gemm_ws<8>(p, s) : launch_gemm_ws<4>(p, s);
+  const bool serial = (flags & LQ_GEMM_SERIAL) != 0;
+  if (a8 && span == 128 && !serial) return bits == 8 ? launch_gemm_ws<8>(p, s) : launch_gemm_ws<4>(p, s);
   // bf16 activations: the pipelined kernel needs 16-byte pieces of x (8 columns) to be whole
-  if (!a8 && (flags & LQ_GEMM_FOLD_SCALES) && g_gemm_impl != 1 && Kd % 128 == 0 && K % 8 == 0 && ldx % 8 == 0 &&
+  if (!a8 && (flags & LQ_GEMM_FOLD_SCALES) && !serial && Kd % 128 == 0 && K % 8 == 0 && ldx % 8 == 0 &&
       (uintptr_t)x % 16 == 0)
     return bits == 8 ? launch_gemm_f16<8>(p, s) : launch_gemm_f16<4>(p, s);
   if (bits == 8) return a8 ? launch_gemm<8, 1>(p, s) : launch_gemm<8, 2>(p, s);

@@ -17,7 +17,8 @@ LIB_PATH = PKG / "libllmquant_b200.so"
 HEADER = PKG.parent / "include" / "llmquant_b200.h"
 
 LQ_F32, LQ_F16, LQ_BF16 = 0, 1, 2
-GEMM_FOLD_SCALES = 1  # lq_wq_gemm_prefill flags
+GEMM_FOLD_SCALES, GEMM_SERIAL = 1, 2  # lq_wq_gemm_prefill flags
+ATTN_AUTO, ATTN_SIMT, ATTN_MMA, ATTN_CLUSTER = 0, 1, 2, 3  # lq_attn_decode_fused impl
 DTYPE_ID = {torch.float32: LQ_F32, torch.float16: LQ_F16, torch.bfloat16: LQ_BF16}
 
 _P, _I, _L = ctypes.c_void_p, ctypes.c_int, ctypes.c_int64
@@ -35,21 +36,17 @@ _SIGNATURES = {
     "lq_wq_gemm_prefill": [_P, _I, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P],
     "lq_allreduce_max_world": [],
     "lq_allreduce_device_error": [],
-    "lq_allreduce_residual": [_P, _I, _I, _I, _L, _L, _P, _P, _P, _I, _I, _P],
+    "lq_allreduce_residual": [_P, _I, _I, _I, _L, _L, _P, _P, _P, _I, _L, _I, _P],
     "lq_pack_int4": [_P, _P, _L, _P],
     "lq_unpack_int4": [_P, _P, _L, _P],
     "lq_dequant_weight": [_P, _P, _P, _I, _I, _I, _I, _I, _P],
     "lq_wq_gemv": [_P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P],
     "lq_stream_layout_sizes": [_I, _I, _I, _I, _I, _IP, _IP, _IP],
     "lq_gemv_device_error": [],
-    "lq_gemv_set_timeline": [_P],
-    "lq_gemv_set_tuning": [_I, _I, _I],
     "lq_embed_gather": [_P, _P, _P, _I, _I, ctypes.c_int64, _I, _P],
     "lq_next_token": [_P, ctypes.c_int64, _P, _P, _P, ctypes.c_int64, _P, _I, _I, _P],
-    "lq_gemv_set_ring_policy": [_I, _I],
     "lq_wq_gemv_batched_max_rows": [],
     "lq_wq_gemv_batched": [_P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P],
-    "lq_gemm_set_impl": [_I],
     "lq_gemv_tensor_core_ok": [_I, _I, _I, _I],
     "lq_repack_stream": [_P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P],
     "lq_unrepack_stream": [_P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P],
@@ -68,14 +65,12 @@ _SIGNATURES.update({
     "lq_attn_decode_static_scratch_bytes": [],
     "lq_attn_fused_scratch_bytes": [_I, _I, _I, _I, _I],
     "lq_attn_device_error": [],
-    "lq_attn_set_timeline": [_P],
-    "lq_attn_set_impl": [_I],
     "lq_attn_decode_fused": [_P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P, _L, _I,
-                             ctypes.c_float, _I, _I, _P],
+                             ctypes.c_float, _I, _I, _I, _P],
     "lq_attn_decode_kv_i8_static": [_P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P, _L, _I,
                                     ctypes.c_float, _I, _I, _P],
 })
-_RESTYPE = {"lq_gemv_set_timeline": None, "lq_gemv_set_ring_policy": None, "lq_gemm_set_impl": None, "lq_gemv_set_tuning": None, "lq_attn_set_timeline": None, "lq_attn_set_impl": None, "lq_last_error": ctypes.c_char_p, "lq_attn_decode_scratch_bytes": ctypes.c_int64,
+_RESTYPE = {"lq_last_error": ctypes.c_char_p, "lq_attn_decode_scratch_bytes": ctypes.c_int64,
             "lq_attn_decode_static_scratch_bytes": ctypes.c_int64,
             "lq_attn_fused_scratch_bytes": ctypes.c_int64}
 
@@ -87,11 +82,28 @@ class GemvArgs(ctypes.Structure):
         ("x", _P), ("ldx", _I), ("norm_weight", _P), ("norm_eps", ctypes.c_float),
         ("codes", _P), ("scale_tiles", _P), ("bias", _P), ("residual", _P), ("out", _P),
         ("out_dtype", _I), ("M", _I), ("N", _I), ("K", _I), ("Kd", _I), ("span", _I),
-        ("bits", _I), ("epilogue", _I), ("variant", _I), ("pdl", _I),
+        ("bits", _I), ("epilogue", _I), ("variant", _I), ("pdl", _I), ("tp", _P),
     ]
 
 
+class GemvTp(ctypes.Structure):
+    """Mirror of `lq_gemv_tp` (include/llmquant_b200.h)."""
+
+    _fields_ = [
+        ("mode", _I), ("world", _I), ("rank", _I), ("peers", _P),
+        ("data_offset", _L), ("counter_offset", _L), ("parts", _P), ("counters", _P),
+        ("ready", _P), ("residual", _P), ("step", _P),
+        ("seq_mul", ctypes.c_uint32), ("seq_add", ctypes.c_uint32),
+        ("ready_mul", ctypes.c_uint32), ("ready_add", ctypes.c_uint32),
+        ("producer_batches", ctypes.c_uint32), ("wait_cycles", _L),
+    ]
+
+
+TP_PUSH, TP_SUM = 1, 2
+
 _SIGNATURES["lq_wq_gemv_fused"] = [ctypes.POINTER(GemvArgs), _P]
+_SIGNATURES["lq_glue_device_error"] = []
+_SIGNATURES["lq_next_token_tp"] = [_P, _L, _I, _I, _P, _L, _I, _P, _P, _P, _L, _P, _P, _I, _L, _I, _P]
 
 
 def declared_symbols(header: pathlib.Path = HEADER):

@@ -199,16 +199,20 @@ class KernelQuantLinear(nn.Module):
         return bool(self._stream and native.library().lq_gemv_tensor_core_ok(m, self._kd, self._span, self.num_bits))
 
     def gemv(self, flat, out_dtype=None, residual=None, variant=None, norm_weight=None,
-             norm_eps=1e-5, epilogue=0, pdl=False, out=None):
+             norm_eps=1e-5, epilogue=0, pdl=False, out=None, tp=None):
         """Streaming GEMV on `[M <= 8, K]` bf16 rows -> `[M, N]` (bf16 or fp32).
 
         Optional fusions (see `lq_wq_gemv_fused`): RMSNorm of the input rows by `norm_weight`,
         `epilogue=1` for silu(gate) * up over interleaved (gate, up) rows, a residual added to
-        the output, and `pdl` to overlap the weight prefetch with the previous kernel."""
+        the output, and `pdl` to overlap the weight prefetch with the previous kernel.
+        `tp` (a `native.GemvTp`) couples the launch to the other ranks of a tensor-parallel
+        group: as a pushing row-parallel linear (no `out`: the partial rows go to the ranks'
+        exchange buffers) or as the consumer that first builds `flat` from the ranks' partials."""
         m = flat.shape[0]
         out_dtype = out_dtype or torch.bfloat16
         n_out = self.out_features // 2 if epilogue == 1 else self.out_features
-        if out is None:
+        pushing = tp is not None and tp.mode == native.TP_PUSH
+        if out is None and not pushing:
             out = torch.empty(m, n_out, dtype=out_dtype, device=flat.device)
         if m == 0:
             return out
@@ -222,21 +226,24 @@ class KernelQuantLinear(nn.Module):
         args = native.GemvArgs(
             x=flat.data_ptr(), ldx=flat.stride(0), norm_weight=native.ptr(norm_weight),
             norm_eps=norm_eps, codes=self.codes.data_ptr(), scale_tiles=self.scale_tiles.data_ptr(),
-            bias=native.ptr(bias), residual=native.ptr(residual), out=out.data_ptr(),
+            bias=native.ptr(bias), residual=native.ptr(residual), out=native.ptr(out),
             out_dtype=native.DTYPE_ID[out_dtype], M=m, N=self.out_features, K=self.in_features,
             Kd=self._kd, span=self._span, bits=self.num_bits, epilogue=epilogue,
-            variant=GEMV_VARIANT if variant is None else variant, pdl=1 if pdl else 0)
+            variant=GEMV_VARIANT if variant is None else variant, pdl=1 if pdl else 0,
+            tp=ctypes.addressof(tp) if tp is not None else None)
         with torch.cuda.device(flat.device):
             native.call("lq_wq_gemv_fused", ctypes.byref(args), native.stream_ptr(flat.device))
         return out
 
-    def gemm(self, flat, a8: bool = False, fold_scales: bool = False):
+    def gemm(self, flat, a8: bool = False, fold_scales: bool = False, serial: bool = False):
         """Prefill GEMM on the tensor cores for any number of rows: `[M, K]` bf16 -> `[M, N]`
         bf16. `a8=True` quantizes the activations per token per group to int8 first (the
         reference's dynamic activation scheme) and multiplies integers. `fold_scales=True`
         (bf16 activations only) multiplies by `bf16(code * scale)`, the weight the reference's
         kernel mode dequantizes for its library GEMM, instead of scaling exact integer sums
-        per group: faster, with that mode's rounding."""
+        per group: faster, with that mode's rounding. `serial=True` runs the unpipelined kernel
+        (fill, MMA and drain in turn), which otherwise only serves shapes the warp-specialized
+        kernels do not take; same results."""
         m = flat.shape[0]
         out = torch.empty(m, self.out_features, dtype=torch.bfloat16, device=flat.device)
         if m == 0:
@@ -263,7 +270,8 @@ class KernelQuantLinear(nn.Module):
                         native.ptr(x_scales), self.codes.data_ptr(), self.scale_tiles.data_ptr(),
                         native.ptr(bias), out.data_ptr(), m, self.out_features, self.in_features,
                         self._kd, self._span, self.num_bits,
-                        native.GEMM_FOLD_SCALES if (fold_scales and not a8) else 0,
+                        (native.GEMM_FOLD_SCALES if (fold_scales and not a8) else 0)
+                        | (native.GEMM_SERIAL if serial else 0),
                         native.stream_ptr(flat.device))
         return out
 

@@ -94,7 +94,8 @@ class FusedLlamaDecoder:
     """Greedy decode of a kernel-mode Llama: eager prefill, then one replayed graph per token."""
 
     def __init__(self, model, max_batch: int, max_len: int, kv_bits: int = 8, use_graph: bool = True,
-                 pdl: bool = True, tp=None, attn_splits: int = 0):
+                 pdl: bool = True, tp=None, attn_splits: int = 0, gather_logits: bool = False,
+                 exchange=None, attn_impl: int = 0):
         if not supports(model):
             raise ValueError("FusedLlamaDecoder needs a Llama-layout model whose attention and MLP "
                              "linears are KernelQuantLinear (head_dim 64/128, silu MLP)")
@@ -147,36 +148,134 @@ class FusedLlamaDecoder:
         self.attn = torch.zeros(B, self.Hq * self.D, dtype=bf16, device=dev)
         self.act = torch.zeros(B, inter, dtype=bf16, device=dev)
         self.logits = torch.zeros(B, self.vocab, dtype=bf16, device=dev)
-        self.peer = None
+        # the step's bookkeeping (embedding gather, argmax, cursor, history) in the library's two
+        # small kernels when the tensors are what they expect, else with torch ops
+        self._glue = (self.embed.dtype == bf16 and self.embed.is_contiguous() and self.embed.device == dev)
+        self.peer = None       # separate one-shot all-reduce kernel over peer memory
+        self.exchange = None   # all-reduce folded into the GEMVs (PeerExchange)
+        self.gather_logits = gather_logits
+        if self.tp and exchange is not None:
+            self.exchange = exchange  # the caller set the buffers up (ranks sharing one GPU)
+        elif self.tp:
+            self._setup_tensor_parallel(B, H, dev)
         if self.tp:
-            if getattr(self.tp, "peer_allreduce", True) and (B * H) % 4 == 0:
-                try:
-                    from llmquant_b200.runtime.tp import PeerAllReduce
-                    self.peer = PeerAllReduce(self.tp, B * H, dev)
-                except Exception as exc:  # no symmetric memory here: stay on NCCL
-                    self.peer_error = repr(exc)
             self.partial = torch.zeros(B, H, dtype=torch.float32, device=dev)
             self.local_logits = torch.zeros(B, self.vocab // world, dtype=bf16, device=dev)
         self.tokens = torch.zeros(B, dtype=torch.long, device=dev)
         self.pos = torch.zeros(1, dtype=torch.long, device=dev)
         self.history = torch.zeros(B, max_len + 1, dtype=torch.long, device=dev)
         self.ticket = torch.zeros(1, dtype=torch.int32, device=dev)
-        # the step's bookkeeping (embedding gather, argmax, cursor, history) in the library's two
-        # small kernels when the tensors are what they expect, else with torch ops
-        self._glue = (self.embed.dtype == bf16 and self.embed.is_contiguous() and self.embed.device == dev)
-        want = max(1, -(-2 * 148 // (B * self.Hkv)))
-        if attn_splits > 0:  # slices of the cached context per KV head (0 = two CTAs per SM)
-            want = attn_splits
-        self.splits = max(1, min(want, max_len // 64 or 1))
+        # Slices of the cached context per KV head: about two CTAs per SM in all, as a power of two
+        # up to 16 so that the slices of a head can run as one thread-block cluster and merge
+        # through distributed shared memory (lq_attn_decode_fused picks that kernel by itself).
+        if attn_splits > 0:
+            self.splits = attn_splits
+        else:
+            want = max(1, min(2 * 148 // (B * self.Hkv), max_len // 64 or 1, 16))
+            self.splits = 1 << (want.bit_length() - 1)
+        self.attn_impl = attn_impl
         nbytes = native.library().lq_attn_fused_scratch_bytes(B, self.Hq, self.Hkv, self.D, self.splits)
         self.scratch = torch.zeros(-(-nbytes // 4), dtype=torch.float32, device=dev)
         self.cache = KernelQuantCache(kv_bits, max_cache_len=max_len)
         self.graph = None
-        self.launches_per_step = len(self.layers) * (7 if self.tp else 5) + 1 + (2 if self._glue else 0)
-        self.allreduce = "none" if not self.tp else ("peer-memory one-shot kernel" if self.peer is not None else "nccl")
+        separate_reduce = self.tp is not None and self.exchange is None
+        self.launches_per_step = len(self.layers) * (7 if separate_reduce else 5) + 1 + (2 if self._glue else 0)
+        if not self.tp:
+            self.allreduce = "none"
+        elif self.exchange is not None:
+            self.allreduce = "folded into the GEMVs (partials pushed to peer memory, summed in the consumer's prologue)"
+        else:
+            self.allreduce = "peer-memory one-shot kernel" if self.peer is not None else "nccl"
+
+    def _setup_tensor_parallel(self, B, H, dev):
+        """Choose the all-reduce route, the same on every rank. Order of preference: folded
+        into the GEMVs (batch <= 2, the rows one GEMV pass takes), the separate one-shot kernel
+        over peer memory, NCCL. Each attempt ends in a vote, so a rank on which symmetric memory
+        cannot be set up takes all ranks to the next route instead of leaving them in kernels
+        that wait for it."""
+        from llmquant_b200.runtime.tp import PeerAllReduce, PeerExchange, all_ranks_agree
+
+        self.peer_error = None
+        want_peer = getattr(self.tp, "peer_allreduce", True) and (B * H) % 4 == 0
+        want_fused = (want_peer and getattr(self.tp, "fused_allreduce", True) and B <= 2 and self._glue
+                      and isinstance(self.lm_head, KernelQuantLinear) and self.lm_head._stream
+                      and H % 4 == 0)
+        for route in ("fused", "kernel"):
+            wanted = want_fused if route == "fused" else want_peer
+            if not all_ranks_agree(self.tp, wanted, dev):
+                continue
+            made = None
+            try:
+                if route == "fused":
+                    made = PeerExchange.over_symmetric_memory(self.tp, B, H, dev)
+                else:
+                    made = PeerAllReduce(self.tp, B * H, dev)
+            except Exception as exc:  # symmetric memory unavailable on this rank
+                self.peer_error = repr(exc)
+            if all_ranks_agree(self.tp, made is not None, dev):
+                if route == "fused":
+                    self.exchange = made
+                else:
+                    self.peer = made
+                return
 
     # ------------------------------------------------------------------ one token
+    def _folded_launches(self):
+        """The step under tensor parallelism with the all-reduce folded into the GEMVs: o_proj and
+        down_proj push their fp32 partial rows into every rank's exchange buffer; gate|up, the
+        next layer's q|k|v and lm_head first build their input -- bf16(bf16(sum of the partials)
+        + residual) -- and go on as usual. Five launches per layer, as on one GPU. A generator
+        that yields after every launch, so that several ranks living on one GPU can be advanced
+        in lock step (each launch of all ranks before the next); the token exchange that ends
+        the step is `_folded_token`."""
+        ex, L = self.exchange, len(self.layers)
+        stream = native.stream_ptr(self.device)
+        pdl = 1 if self.pdl else 0
+        h0, h1 = self.h
+        native.call("lq_embed_gather", self.embed.data_ptr(), self.tokens.data_ptr(), h0.data_ptr(),
+                    self.B, self.hidden, self.embed.shape[0], pdl, stream)
+        yield
+        pos_ptr = self.pos.data_ptr()
+        batches = self.hidden // 4  # 4-row batches of a row-parallel linear's [hidden] output
+        for l, (spec, cache) in enumerate(zip(self.layers, self.cache.layers)):
+            tp = None
+            if l > 0:  # hidden = down_proj(l - 1) summed over the ranks + its residual
+                tp = ex.sum_args(1, 1, (L, l), (L - 1, l), h1, batches)
+            spec["qkv"].gemv(h0, norm_weight=spec["ln1"], norm_eps=self.eps, pdl=self.pdl, out=self.qkv, tp=tp)
+            yield
+            native.call("lq_attn_decode_fused", self.qkv.data_ptr(), self.cos.data_ptr(),
+                        self.sin.data_ptr(), cache.k_codes.data_ptr(), cache.v_codes.data_ptr(),
+                        cache.k_scales.data_ptr(), cache.v_scales.data_ptr(), self.attn.data_ptr(),
+                        self.scratch.data_ptr(), self.B, self.Hq, self.Hkv, self.D, cache.capacity,
+                        self.cos.shape[0], pos_ptr, 0, self.kv_bits, self.scaling, self.splits,
+                        self.attn_impl, pdl, stream)
+            yield
+            spec["o"].gemv(self.attn, out_dtype=torch.float32, pdl=self.pdl, tp=ex.push_args(0))
+            yield
+            tp = ex.sum_args(0, 0, (L, l + 1), (L, l + 1), h0, batches)
+            spec["gate_up"].gemv(h1, norm_weight=spec["ln2"], norm_eps=self.eps, epilogue=1,
+                                 pdl=self.pdl, out=self.act, tp=tp)
+            yield
+            spec["down"].gemv(self.act, out_dtype=torch.float32, pdl=self.pdl, tp=ex.push_args(1))
+            yield
+        tp = ex.sum_args(1, 2, (L, L), (1, 1), h1, batches)
+        self.lm_head.gemv(h0, norm_weight=self.final_norm, norm_eps=self.eps, pdl=self.pdl,
+                          out=self.local_logits, tp=tp)
+        yield
+
+    def _folded_token(self):
+        """End of a folded step: every rank sends its local maximum to all ranks and picks the
+        same token; cursor and step counter advance. With `gather_logits` the full logits are
+        gathered as well (for inspection: the token does not need them)."""
+        if self.gather_logits:
+            self.tp.all_gather_last_dim(self.logits, self.local_logits)
+        self.exchange.next_token(self.local_logits, self.tokens, self.pos, self.history, self.ticket, self.pdl)
+
     def _step_kernels(self):
+        if self.exchange is not None:
+            for _ in self._folded_launches():
+                pass
+            return self._folded_token()
         stream = native.stream_ptr(self.device)
         pdl = 1 if self.pdl else 0
         cur, nxt = self.h
@@ -193,7 +292,7 @@ class FusedLlamaDecoder:
                         cache.k_scales.data_ptr(), cache.v_scales.data_ptr(), self.attn.data_ptr(),
                         self.scratch.data_ptr(), self.B, self.Hq, self.Hkv, self.D, cache.capacity,
                         self.cos.shape[0], pos_ptr, 0, self.kv_bits, self.scaling, self.splits,
-                        pdl, stream)
+                        self.attn_impl, pdl, stream)
             self._row_parallel(spec["o"], self.attn, cur, nxt, 0)
             spec["gate_up"].gemv(nxt, norm_weight=spec["ln2"], norm_eps=self.eps, epilogue=1,
                                  pdl=self.pdl, out=self.act)
@@ -277,6 +376,22 @@ class FusedLlamaDecoder:
         return first
 
     @torch.no_grad()
+    def start_empty(self, first_tokens):
+        """Begin decoding from an empty cache with `first_tokens` ([B], e.g. the BOS id) as the
+        token to feed: no prefill pass. The cache layers are allocated here."""
+        dummy = torch.zeros(self.B, self.Hkv, 1, self.D, dtype=torch.bfloat16, device=self.device)
+        while len(self.cache.layers) < len(self.layers):
+            self.cache.layers.append(self.cache.layer_class_to_replicate())
+        for layer in self.cache.layers:
+            if not layer.is_initialized:
+                layer.lazy_initialization(dummy, dummy)
+            layer.reset()
+        self.tokens.copy_(first_tokens.to(self.device))
+        self.pos.zero_()
+        self.history.zero_()
+        self.history[:, 0] = self.tokens
+
+    @torch.no_grad()
     def capture(self):
         """Warm up on a side stream, then capture one step. The warm-up and the capture write
         real entries at the cursor; the cursor and token are restored afterwards and the
@@ -311,6 +426,19 @@ class FusedLlamaDecoder:
         else:
             self._step_kernels()
 
+    def check_device_errors(self):
+        """Raise if a bounded wait inside one of the step's kernels ever ran out (a pipeline
+        stall, or under tensor parallelism a rank that never arrived): the tokens produced since
+        the last check cannot be trusted. Reads device words, so it synchronizes."""
+        lib = native.library()
+        words = {"gemv": lib.lq_gemv_device_error(), "attention": lib.lq_attn_device_error()}
+        if self.tp:
+            words["allreduce"] = lib.lq_allreduce_device_error()
+            words["token exchange"] = lib.lq_glue_device_error()
+        bad = {k: v for k, v in words.items() if v != 0}
+        if bad:
+            raise RuntimeError(f"a bounded device wait expired during decode: {bad}")
+
     @torch.no_grad()
     def generate(self, input_ids, max_new_tokens: int):
         """Greedy generation; returns prompt + new tokens, like `model.generate(do_sample=False)`."""
@@ -322,4 +450,6 @@ class FusedLlamaDecoder:
             self.step()
         for layer in self.cache.layers:
             layer.length = prompt + max_new_tokens - 1
-        return self.history[:, : prompt + max_new_tokens].clone()
+        out = self.history[:, : prompt + max_new_tokens].clone()
+        self.check_device_errors()
+        return out

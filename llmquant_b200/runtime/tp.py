@@ -29,7 +29,8 @@ class TPContext:
     rank: int
     world: int
     group: object = None  # torch.distributed process group (None = the default group)
-    peer_allreduce: bool = True  # try the one-shot kernel over peer memory before NCCL
+    peer_allreduce: bool = True  # use peer memory for the all-reduce before falling back to NCCL
+    fused_allreduce: bool = True  # fold the all-reduce into the GEMVs where the batch allows
 
     def all_reduce(self, tensor):
         import torch.distributed as dist
@@ -172,6 +173,7 @@ class PeerAllReduce:
             raise RuntimeError("symmetric memory rendezvous returned the wrong number of peers")
         self.peers = torch.tensor(ptrs, dtype=torch.int64, device=device)
         self.seq = torch.zeros(1, dtype=torch.int32, device=device)
+        self.wait_cycles = 0  # 0 = the library's default bound (about two seconds)
         torch.cuda.synchronize(device)
         dist.barrier(group=ctx.group)  # every buffer is zeroed before anyone signals
 
@@ -187,5 +189,117 @@ class PeerAllReduce:
 
         native.call("lq_allreduce_residual", self.peers.data_ptr(), self.ctx.rank, self.ctx.world,
                     index, self.slot_floats, self.flag_off, self.seq.data_ptr(),
-                    native.ptr(residual), out.data_ptr(), out.numel(), 1 if pdl else 0,
-                    native.stream_ptr(out.device))
+                    native.ptr(residual), out.data_ptr(), out.numel(), self.wait_cycles,
+                    1 if pdl else 0, native.stream_ptr(out.device))
+
+
+class PeerExchange:
+    """Exchange buffers of the fused tensor-parallel decode step (`lq_gemv_tp`,
+    `lq_next_token_tp`): the row-parallel GEMVs write their fp32 partial rows straight into
+    every rank's buffer and the GEMV that consumes the sum adds them up in its prologue, so no
+    separate all-reduce launch is left in the step.
+
+    One buffer per rank, mapped by all ranks (symmetric memory over NVLink):
+
+        float    part[2 slots][world][rows][width]    partial outputs, by source rank
+        uint32   arrived[2 slots][16]                 4-row batches received, by source rank
+        uint64   records[2 banks][16][max_batch]      (token index, logit, step tag) per rank
+
+    plus, local to the rank, the step counter and three `ready` counters (one per kind of
+    consuming GEMV). Slot 0 carries o_proj's output, slot 1 down_proj's."""
+
+    COUNTER_ROW = 64  # bytes per slot of arrival counters (16 ranks)
+
+    def __init__(self, rank: int, world: int, rows: int, width: int, device, buffer, peer_ptrs,
+                 max_batch: int = 8):
+        if rows * width % 4:
+            raise ValueError("rows * width of the exchanged partials must be a multiple of 4")
+        if world > 16 or rows > max_batch:
+            raise ValueError("the exchange buffer holds at most 16 ranks and max_batch rows")
+        self.rank, self.world, self.rows, self.width = rank, world, rows, width
+        self.max_batch = max_batch
+        self.buffer = buffer
+        self.slot_bytes = world * rows * width * 4
+        self.counter_off = 2 * self.slot_bytes
+        self.record_off = self.counter_off + 2 * self.COUNTER_ROW
+        if buffer.numel() * buffer.element_size() < self.bytes_needed(world, rows, width, max_batch):
+            raise ValueError("exchange buffer too small")
+        if len(peer_ptrs) != world:
+            raise RuntimeError("the exchange needs one mapped buffer per rank")
+        self.peers = torch.tensor([int(p) for p in peer_ptrs], dtype=torch.int64, device=device)
+        self.base = int(peer_ptrs[rank])
+        self.step = torch.zeros(1, dtype=torch.int32, device=device)
+        self.ready = torch.zeros(4, dtype=torch.int32, device=device)
+        self.wait_cycles = 0  # 0 = the library's default bound (about two seconds)
+
+    @staticmethod
+    def bytes_needed(world, rows, width, max_batch=8):
+        return 2 * world * rows * width * 4 + 2 * PeerExchange.COUNTER_ROW + 2 * 16 * max_batch * 8
+
+    @classmethod
+    def over_symmetric_memory(cls, ctx: TPContext, rows: int, width: int, device, max_batch: int = 8):
+        """Collective: every rank of `ctx` allocates its buffer and maps the others'."""
+        import torch.distributed as dist
+        import torch.distributed._symmetric_memory as symm
+
+        nbytes = cls.bytes_needed(ctx.world, rows, width, max_batch)
+        buffer = symm.empty(-(-nbytes // 4), dtype=torch.float32, device=device)
+        buffer.zero_()
+        group = ctx.group if ctx.group is not None else dist.group.WORLD
+        handle = symm.rendezvous(buffer, group)
+        ptrs = [int(p) for p in handle.buffer_ptrs]
+        self = cls(ctx.rank, ctx.world, rows, width, device, buffer, ptrs, max_batch)
+        self.handle = handle
+        torch.cuda.synchronize(device)
+        dist.barrier(group=ctx.group)  # every buffer is zero before anyone writes into it
+        return self
+
+    @classmethod
+    def on_one_device(cls, world: int, rows: int, width: int, device, max_batch: int = 8):
+        """`world` exchanges whose buffers all live on one GPU: the ranks of a group run one
+        after the other on one stream (all pushing launches before the launch that consumes
+        them). For single-GPU tests of the multi-rank arithmetic."""
+        nbytes = cls.bytes_needed(world, rows, width, max_batch)
+        buffers = [torch.zeros(-(-nbytes // 4), dtype=torch.float32, device=device) for _ in range(world)]
+        ptrs = [b.data_ptr() for b in buffers]
+        return [cls(r, world, rows, width, device, buffers[r], ptrs, max_batch) for r in range(world)]
+
+    # ---- per-launch argument blocks
+    def push_args(self, slot: int):
+        from llmquant_b200 import native
+
+        return native.GemvTp(mode=native.TP_PUSH, world=self.world, rank=self.rank,
+                             peers=self.peers.data_ptr(), data_offset=slot * self.slot_bytes,
+                             counter_offset=self.counter_off + slot * self.COUNTER_ROW)
+
+    def sum_args(self, slot: int, kind: int, seq, ready, residual, producer_batches: int):
+        """`seq` = (pushes into the slot per step, index of the awaited one, 1-based),
+        `ready` = the same for the launches of this consumer kind."""
+        from llmquant_b200 import native
+
+        return native.GemvTp(mode=native.TP_SUM, world=self.world, rank=self.rank,
+                             parts=self.base + slot * self.slot_bytes,
+                             counters=self.base + self.counter_off + slot * self.COUNTER_ROW,
+                             ready=self.ready.data_ptr() + 4 * kind, residual=residual.data_ptr(),
+                             step=self.step.data_ptr(), seq_mul=seq[0], seq_add=seq[1],
+                             ready_mul=ready[0], ready_add=ready[1],
+                             producer_batches=producer_batches, wait_cycles=self.wait_cycles)
+
+    def next_token(self, local_logits, tokens, pos, history, ticket, pdl: bool = True):
+        from llmquant_b200 import native
+
+        native.call("lq_next_token_tp", local_logits.data_ptr(), local_logits.shape[1], self.rank,
+                    self.world, self.peers.data_ptr(), self.record_off, self.max_batch,
+                    tokens.data_ptr(), pos.data_ptr(), native.ptr(history),
+                    history.shape[1] if history is not None else 0, ticket.data_ptr(),
+                    self.step.data_ptr(), local_logits.shape[0], self.wait_cycles, 1 if pdl else 0,
+                    native.stream_ptr(local_logits.device))
+
+
+def all_ranks_agree(ctx: TPContext, ok: bool, device) -> bool:
+    """True only if `ok` holds on every rank (a collective: every rank must call it)."""
+    import torch.distributed as dist
+
+    flag = torch.tensor([1 if ok else 0], dtype=torch.int32, device=device)
+    dist.all_reduce(flag, op=dist.ReduceOp.MIN, group=ctx.group)
+    return bool(int(flag.item()))

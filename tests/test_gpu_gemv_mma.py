@@ -145,24 +145,6 @@ def test_silu_mul_epilogue_bias_and_residual(bits, M):
     assert torch.allclose(got_b, plain32 + bias.float().cuda(), rtol=0, atol=1e-6)
 
 
-def test_tuning_override_gives_the_same_numbers():
-    from llmquant_b200 import native
-
-    w = seeded((700, 4096), 51, 0.02, torch.bfloat16)
-    x = seeded((2, 4096), 52).bfloat16()
-    module = _module(w, 4)
-    base = module.gemv(x.cuda(), out_dtype=torch.float32, variant=4)
-    try:
-        for warps, segs, stages in [(4, 4, 5), (8, 16, 3), (3, 8, 8), (1, 4, 5)]:
-            native.library().lq_gemv_set_tuning(warps, segs, stages)
-            got = module.gemv(x.cuda(), out_dtype=torch.float32, variant=4)
-            # the split of a row between warps changes the fp32 summation order only
-            assert rel_l2(got.cpu().numpy(), base.cpu().numpy()) <= 1e-6, (warps, segs, stages)
-    finally:
-        native.library().lq_gemv_set_tuning(0, 0, 0)
-    assert native.library().lq_gemv_device_error() == 0
-
-
 def test_rejects_groups_it_is_not_built_for():
     """Per-head groups of 64 stored codes stay on the SIMT kernel."""
     from llmquant_b200.quantizers import KernelQuantLinear

@@ -121,11 +121,15 @@ def test_rope_write_and_decode_attention(hd, hq, hkv):
 
 
 @pytest.mark.parametrize("hd,hq,hkv", [(64, 8, 2), (128, 8, 2), (128, 8, 8)])
-@pytest.mark.parametrize("splits", [1, 7])
-def test_fused_attention_block_matches_the_separate_kernels(hd, hq, hkv, splits):
-    """lq_attn_decode_fused = lq_rope_kv_write + lq_attn_decode_kv_i8 in one launch: the cache
-    it leaves behind is bit-identical, its output agrees with the oracle, and its tickets are
-    back at zero so it can be replayed."""
+@pytest.mark.parametrize("splits,impl", [(1, native.ATTN_AUTO), (7, native.ATTN_MMA), (7, native.ATTN_SIMT),
+                                         (1, native.ATTN_SIMT), (8, native.ATTN_AUTO), (4, native.ATTN_AUTO)])
+def test_fused_attention_block_matches_the_separate_kernels(hd, hq, hkv, splits, impl):
+    """lq_attn_decode_fused = lq_rope_kv_write + lq_attn_decode_kv_i8 in one launch, with every
+    kernel that can serve it (all-SIMT, tensor-core with the merge by the last CTA, and -- the
+    library's own choice for 2 / 4 / 8 / 16 slices -- the cluster kernel): the cache it leaves
+    behind is bit-identical, its output agrees with the separate kernels (which
+    test_rope_write_and_decode_attention holds against the oracle), and its tickets are back at
+    zero so it can be replayed."""
     B, T, Tmax = 2, (150 if splits > 1 else 520), 600
     g = torch.Generator().manual_seed(7 * hd + hq + splits)
     inv_freq = 1.0 / (500000.0 ** (np.arange(0, hd, 2, dtype=np.float32) / hd))
@@ -161,7 +165,7 @@ def test_fused_attention_block_matches_the_separate_kernels(hd, hq, hkv, splits)
         kc, vc, ks, vs = fus
         native.call("lq_attn_decode_fused", row.data_ptr(), cos.data_ptr(), sin.data_ptr(), kc.data_ptr(),
                     vc.data_ptr(), ks.data_ptr(), vs.data_ptr(), out_fus.data_ptr(), scratch_fus.data_ptr(),
-                    B, hq, hkv, hd, Tmax, Tmax, pos.data_ptr(), 0, 8, hd ** -0.5, splits, 0, stream)
+                    B, hq, hkv, hd, Tmax, Tmax, pos.data_ptr(), 0, 8, hd ** -0.5, splits, impl, 0, stream)
         pos.add_(1)
         if t in (0, 1, 17, T - 1):
             err = rel_l2(out_fus.float().cpu().numpy(), out_ref.float().cpu().numpy())

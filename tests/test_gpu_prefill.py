@@ -59,6 +59,11 @@ def test_prefill_gemm_against_oracle(bits, shape):
     got8 = module.gemm(x.cuda(), a8=True)
     assert rel_l2(got16.float().cpu().numpy(), want16) <= TOL
     assert rel_l2(got8.float().cpu().numpy(), want8) <= TOL
+    # the unpipelined kernel (the one groups of 64 stored codes always take) on the same product
+    for a8, want in ((True, want8), (False, want16)):
+        serial = module.gemm(x.cuda(), a8=a8, serial=True)
+        assert rel_l2(serial.float().cpu().numpy(), want) <= TOL, ("serial", a8)
+    assert rel_l2(module.gemm(x.cuda(), fold_scales=True, serial=True).float().cpu().numpy(), want16) <= TOL
     # the prefill path and the decode GEMV agree on the same rows
     rows = module.gemv(x[:4].cuda())
     assert rel_l2(got16[:4].float().cpu().numpy(), rows.float().cpu().numpy()) <= TOL

@@ -45,9 +45,10 @@ def _static(q, kc, vc, ks, vs, T, splits):
     B, Hq, D = q.shape
     Hkv, Tmax = kc.shape[1], kc.shape[2]
     out = torch.empty(B, Hq, D, dtype=torch.bfloat16, device="cuda")
-    native.call("lq_attn_decode_kv_i8_static", q.data_ptr(), kc.data_ptr(), vc.data_ptr(),
-                ks.data_ptr(), vs.data_ptr(), out.data_ptr(), B, Hq, Hkv, D, Tmax, 0, T, 0,
-                D ** -0.5, splits, 0, native.stream_ptr())
+    with torch.cuda.device(q.device):  # the built-in array is the current device's: make it the tensors'
+        native.call("lq_attn_decode_kv_i8_static", q.data_ptr(), kc.data_ptr(), vc.data_ptr(),
+                    ks.data_ptr(), vs.data_ptr(), out.data_ptr(), B, Hq, Hkv, D, Tmax, 0, T, 0,
+                    D ** -0.5, splits, 0, native.stream_ptr(q.device))
     return out
 
 
