@@ -20,6 +20,10 @@ MLP_RE = re.compile(r".*\.mlp\..*_proj$")
 O_PROJ_RE = re.compile(r".*\.self_attn\.o_proj$")
 QKV_RE = re.compile(r".*\.self_attn\.(q|k|v|qkv)_proj$")
 
+# stacked Mixture-of-Experts weights: one Parameter per projection holding every expert
+# (llmquant/core/modifier.py:24-38 of the reference); the router is left alone
+MOE_EXPERT_RE = re.compile(r".*\.experts\.(gate_up_proj|down_proj|w1|w2|w3)$")
+
 SchemeLike = Union[str, QuantizationScheme, None]
 AVAILABLE_MODES = frozenset({"kernel"})
 
@@ -38,6 +42,29 @@ def _listed(name: str, patterns) -> bool:
         elif name == pattern:
             return True
     return False
+
+
+def stacked_expert_blocks(model):
+    """(name, module) of every module that directly owns stacked expert weights, found by
+    structure rather than class name (llmquant/core/modifier.py:66-90 of the reference). A
+    block that lacks what the quantized expert module mirrors is refused, not half-converted."""
+    owners = []
+    for name, param in model.named_parameters():
+        if param.ndim >= 2 and MOE_EXPERT_RE.match(name):
+            parent = name.rpartition(".")[0]
+            if parent not in owners:
+                owners.append(parent)
+    blocks = []
+    for name in owners:
+        module = model.get_submodule(name)
+        missing = [a for a in ("gate_up_proj", "down_proj", "act_fn") if not hasattr(module, a)]
+        if missing:
+            raise NotImplementedError(
+                f"{name} ({type(module).__name__}) holds stacked expert weights but is missing "
+                f"{missing}. The quantized expert module mirrors the Mixtral/OLMoE block; this "
+                f"architecture needs its own.")
+        blocks.append((name, module))
+    return blocks
 
 
 @dataclass
@@ -89,12 +116,19 @@ class QuantizationModifier:
             raise ValueError(
                 f"unsupported mode {self.mode!r}: this library only carries the deployed "
                 f"'kernel' path (the reference's 'fake' and 'real' modes are its own CPU/torch paths)")
-        from llmquant_b200.quantizers import KernelQuantLinear
+        from llmquant_b200.quantizers import KernelQuantExperts, KernelQuantLinear
 
         self.resolve(model)
         swaps = []
+        expert_blocks = set()
+        if self.mlp_scheme is not None:
+            # stacked experts are the MLP of a Mixture-of-Experts block: they take the mlp scheme
+            # and are swapped as one module (llmquant/core/modifier.py:176-185 of the reference)
+            for name, module in stacked_expert_blocks(model):
+                expert_blocks.add(name)
+                swaps.append((name, KernelQuantExperts.from_experts(module, _resolve(self.mlp_scheme))))
         for name, module in model.named_modules():
-            if type(module).__name__ not in self.targets:
+            if name in expert_blocks or type(module).__name__ not in self.targets:
                 continue
             scheme = self.scheme_for(name)
             if scheme is not None:

@@ -226,8 +226,8 @@ extern "C" int lq_wq_gemv_fused(const lq_gemv_args* a, void* stream) {
     LQ_REQUIRE(tp->mode == LQ_TP_PUSH || tp->mode == LQ_TP_SUM, LQ_ERR_ARG, "unknown tensor-parallel mode %d", tp->mode);
     LQ_REQUIRE(tp->world >= 1 && tp->world <= 16 && tp->rank >= 0 && tp->rank < tp->world, LQ_ERR_ARG,
                "bad rank %d / world %d", tp->rank, tp->world);
-    LQ_REQUIRE(a->variant == 0 || a->variant == 2 || a->variant == 1 || a->variant == 3, LQ_ERR_UNSUPPORTED,
-               "the tensor-parallel coupling is built into the streaming kernel (variants 1-3)");
+    LQ_REQUIRE(a->variant == 0 || a->variant == 2, LQ_ERR_UNSUPPORTED,
+               "the tensor-parallel coupling is built into the streaming kernel's default arithmetic (variant 2)");
     LQ_REQUIRE(M <= (bits == 4 ? 2 : 4), LQ_ERR_UNSUPPORTED,
                "the tensor-parallel coupling takes the rows of one pass (%d given)", M);
     if (tp->mode == LQ_TP_PUSH) {

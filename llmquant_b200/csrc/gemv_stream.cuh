@@ -84,7 +84,7 @@ struct GemvParams {
 // Row-parallel epilogue of a tensor-parallel linear: lane (m, u) of the warp holds output
 // (m, n0 + u) of a 4-row batch; lane (m, peer) sends the four values of row m as one 16-byte
 // store into part[rank][m][n0 ..] of that peer's exchange buffer.
-static __device__ __noinline__ void tp_push_batch(const GemvParams& p, uint64_t peer_base, float total,
+__device__ __forceinline__ void tp_push_batch(const GemvParams& p, uint64_t peer_base, float total,
                                               int lane, int n0) {
   const int m = lane / p.tp_world;
   const int src = (m < 8 ? m : 0) * kU;
@@ -100,7 +100,7 @@ static __device__ __noinline__ void tp_push_batch(const GemvParams& p, uint64_t 
 }
 // After a CTA's last batch: its stores are made visible before its share of the arrival
 // counter is added on every peer.
-static __device__ __noinline__ void tp_push_done(const GemvParams& p, uint64_t peer_base, int lane, int nb) {
+__device__ __forceinline__ void tp_push_done(const GemvParams& p, uint64_t peer_base, int lane, int nb) {
   __threadfence_system();
   __syncwarp();
   if (lane < p.tp_world)
@@ -288,9 +288,8 @@ struct XChunk<BITS, 3> : XPlanes<BITS, 3> {};
 
 // Tensor-parallel input of a GEMV: x = bf16(bf16(sum over ranks of the partials) + residual),
 // built once by the first CTAs of the grid (each a slice) and published to the others through
-// a counter. Called by the consumer warps only (named barrier 2 over KW * 32 threads). Kept
-// out of line so that its registers do not count against the row loop's.
-static __device__ __noinline__ void tp_sum_prologue(const GemvParams& p, int KW, int warp, int lane) {
+// a counter. Called by the consumer warps only (named barrier 2 over KW * 32 threads).
+__device__ __forceinline__ void tp_sum_prologue(const GemvParams& p, int KW, int warp, int lane) {
   const int T = KW * 32, tid = warp * 32 + lane;
   const uint32_t step = *reinterpret_cast<const volatile uint32_t*>(p.tp_step);
   const int total4 = p.M * p.K / 4;
@@ -359,7 +358,9 @@ __device__ __forceinline__ float reduce4(const float (&v)[kU], int lane) {
 // EPI 0: out[m, n] = acc (+ bias) (+ residual).  EPI 1: rows come in (gate, up) pairs and
 // out[m, n/2] = silu(gate) * up with the roundings of a bf16 MLP (gate, up, silu(gate) and
 // the product are each rounded to bf16).
-template <int BITS, int VAR, int M, int SPW, int EPI>
+// TP: 0 = no tensor-parallel coupling (the kernel every single-GPU launch uses, with none of
+// the coupling's code in it), LQ_TP_PUSH, LQ_TP_SUM.
+template <int BITS, int VAR, int M, int SPW, int EPI, int TP>
 __global__ void __launch_bounds__((kMaxWarps + 2) * 32)
 gemv_stream_kernel(const GemvParams p) {
   constexpr int EPL = BITS == 8 ? 16 : 32;
@@ -423,8 +424,9 @@ gemv_stream_kernel(const GemvParams p) {
 
   // ------------------------------------------------------------ finisher warp
   if (warp == KW + 1) {
-    const bool push = EPI == 0 && p.tp_mode == LQ_TP_PUSH;
-    const uint64_t peer_base = push ? p.tp_peers[lane % p.tp_world] : 0;
+    constexpr bool push = EPI == 0 && TP == LQ_TP_PUSH;
+    uint64_t peer_base = 0;
+    if constexpr (push) peer_base = p.tp_peers[lane % p.tp_world];
     asm volatile("griddepcontrol.wait;" ::: "memory");  // the residual comes from earlier kernels
     for (int it = 0; it < nb; ++it) {
       const int parity = it & 1;
@@ -466,7 +468,7 @@ gemv_stream_kernel(const GemvParams p) {
           if (p.out_f32) reinterpret_cast<float*>(p.out)[o] = __bfloat162float(__float2bfloat16_rn(y));
           else reinterpret_cast<__nv_bfloat16*>(p.out)[o] = __float2bfloat16_rn(y);
         }
-      } else if (push) {
+      } else if constexpr (push) {
         tp_push_batch(p, peer_base, total + bias_pre, lane, n0);
       } else if (mine) {
         total += bias_pre;
@@ -480,7 +482,7 @@ gemv_stream_kernel(const GemvParams p) {
         }
       }
     }
-    if (push) tp_push_done(p, peer_base, lane, nb);
+    if constexpr (push) tp_push_done(p, peer_base, lane, nb);
     return;
   }
 
@@ -542,8 +544,8 @@ gemv_stream_kernel(const GemvParams p) {
   LQ_STAMP(2);
 
   // ---- tensor-parallel input: the hidden rows are first built from the ranks' partial sums
-  const bool tp_sum = p.tp_mode == LQ_TP_SUM;
-  if (tp_sum) tp_sum_prologue(p, KW, warp, lane);
+  constexpr bool tp_sum = TP == LQ_TP_SUM;
+  if constexpr (tp_sum) tp_sum_prologue(p, KW, warp, lane);
 
   uint32_t xraw[M][SPW][PW];
 #pragma unroll
@@ -565,9 +567,15 @@ gemv_stream_kernel(const GemvParams p) {
         for (int i = 0; i < PW; ++i) {
           const int k = k0s[j] + 2 * i;
           const bool ok = cb[j] >= 0 && m < p.M;
-          const volatile unsigned short* xv = reinterpret_cast<const volatile unsigned short*>(xr);
-          const unsigned lo = (ok && k < p.K) ? xv[2 * i] : 0u;
-          const unsigned hi = (ok && k + 1 < p.K) ? xv[2 * i + 1] : 0u;
+          unsigned lo, hi;
+          if constexpr (tp_sum) {  // rows written by another CTA of this kernel: no cached path
+            const volatile unsigned short* xv = reinterpret_cast<const volatile unsigned short*>(xr);
+            lo = (ok && k < p.K) ? xv[2 * i] : 0u;
+            hi = (ok && k + 1 < p.K) ? xv[2 * i + 1] : 0u;
+          } else {
+            lo = (ok && k < p.K) ? __bfloat16_as_ushort(xr[2 * i]) : 0u;
+            hi = (ok && k + 1 < p.K) ? __bfloat16_as_ushort(xr[2 * i + 1]) : 0u;
+          }
           xraw[m][j][i] = lo | (hi << 16);
         }
       }
@@ -713,7 +721,7 @@ gemv_stream_kernel(const GemvParams p) {
       // hand the batch to the finisher warp (which arrives once it is done with the one before)
       asm volatile("bar.sync 1, %0;" ::"r"(round_threads) : "memory");
     } else {
-      const bool push = EPI == 0 && p.tp_mode == LQ_TP_PUSH;
+      constexpr bool push = EPI == 0 && TP == LQ_TP_PUSH;
       float total = 0.f;
       // lane u (< 4) holds row u for every m: lane (m, u) fetches it (all lanes shuffle)
 #pragma unroll
@@ -734,7 +742,7 @@ gemv_stream_kernel(const GemvParams p) {
           if (p.out_f32) reinterpret_cast<float*>(p.out)[o] = __bfloat162float(__float2bfloat16_rn(y));
           else reinterpret_cast<__nv_bfloat16*>(p.out)[o] = __float2bfloat16_rn(y);
         }
-      } else if (push) {
+      } else if constexpr (push) {
         tp_push_batch(p, p.tp_peers[lane % p.tp_world], total + bias_pre, lane, n0);
       } else if (lane < M * kU && n < p.N && m < p.M) {
         total += bias_pre;
@@ -749,14 +757,15 @@ gemv_stream_kernel(const GemvParams p) {
       }
     }
   }
-  if (KW == 1 && EPI == 0 && p.tp_mode == LQ_TP_PUSH)
-    tp_push_done(p, p.tp_peers[lane % p.tp_world], lane, nb);
+  if constexpr (EPI == 0 && TP == LQ_TP_PUSH) {
+    if (KW == 1) tp_push_done(p, p.tp_peers[lane % p.tp_world], lane, nb);
+  }
   LQ_STAMP(5);
 }
 
-template <int BITS, int VAR, int M, int SPW, int EPI>
-int launch_one(const GemvParams& p, int threads, cudaStream_t s) {
-  auto kern = gemv_stream_kernel<BITS, VAR, M, SPW, EPI>;
+template <int BITS, int VAR, int M, int SPW, int EPI, int TP = 0>
+int launch_tp(const GemvParams& p, int threads, cudaStream_t s) {
+  auto kern = gemv_stream_kernel<BITS, VAR, M, SPW, EPI, TP>;
   const size_t smem = (size_t)p.stages * p.stage_bytes;
   if (const int rc = ensure_smem_limit(reinterpret_cast<const void*>(kern), 200 * 1024, "lq_wq_gemv")) return rc;
   static thread_local int occ_threads = 0, occ = 0, occ_dev = -1;
@@ -800,6 +809,20 @@ int launch_one(const GemvParams& p, int threads, cudaStream_t s) {
     return fail(LQ_ERR_LAUNCH, "lq_wq_gemv: %s", cudaGetErrorString(e));
   }
   return LQ_OK;
+}
+
+// The tensor-parallel instances exist for the default arithmetic (variant 2) only.
+template <int BITS, int VAR, int M, int SPW, int EPI>
+int launch_one(const GemvParams& p, int threads, cudaStream_t s) {
+  if (p.tp_mode == 0) return launch_tp<BITS, VAR, M, SPW, EPI, 0>(p, threads, s);
+  if constexpr (VAR == 2 && SPW <= 2) {
+    if (p.tp_mode == LQ_TP_SUM) return launch_tp<BITS, VAR, M, SPW, EPI, LQ_TP_SUM>(p, threads, s);
+    if constexpr (EPI == 0) {
+      if (p.tp_mode == LQ_TP_PUSH) return launch_tp<BITS, VAR, M, SPW, EPI, LQ_TP_PUSH>(p, threads, s);
+    }
+  }
+  return fail(LQ_ERR_UNSUPPORTED, "no tensor-parallel GEMV instance for this variant / shape (variant %d, %d column "
+              "chunks per lane, epilogue %d)", VAR, SPW, EPI);
 }
 
 // Activation rows one pass can keep in registers next to SPW column chunks per lane; wider

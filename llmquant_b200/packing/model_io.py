@@ -14,6 +14,7 @@ import torch.nn as nn
 from llmquant_b200.core.scheme import QuantizationArgs, QuantizationScheme
 from llmquant_b200.packing.format import read_header, read_packed, write_packed
 from llmquant_b200.packing.packing import pack_weight, unpack_weight
+from llmquant_b200.quantizers.experts import KernelQuantExperts
 from llmquant_b200.quantizers.kernel import KernelQuantLinear
 
 _ARG_FIELDS = ("num_bits", "strategy", "group_size", "head_dim", "out_group", "symmetric", "dynamic")
@@ -33,8 +34,9 @@ def save_packed_model(model: nn.Module, path, model_id: str, kv_cache_bits=None,
         if not isinstance(module, KernelQuantLinear):
             continue
         args = module.scheme.weights
-        tensors[f"{name}.qweight"] = pack_weight(module.qweight, args.num_bits)
-        tensors[f"{name}.wscale"] = module.wscale
+        qweight, wscale = module.canonical_tensors()  # one un-repack per layer
+        tensors[f"{name}.qweight"] = pack_weight(qweight, args.num_bits)
+        tensors[f"{name}.wscale"] = wscale
         layers[name] = {
             "in_features": module.in_features,
             "out_features": module.out_features,
@@ -46,7 +48,29 @@ def save_packed_model(model: nn.Module, path, model_id: str, kv_cache_bits=None,
         if module.bias is not None:
             tensors[f"{name}.bias"] = module.bias
 
-    owned = tuple(f"{layer}." for layer in layers)
+    # a Mixture-of-Experts block is one module holding every expert: one record with its two
+    # stacked tensors, packed along the group axis like a single weight
+    # (llmquant/packing/model_io.py:67-95 of the reference)
+    experts = {}
+    for name, module in model.named_modules():
+        if not isinstance(module, KernelQuantExperts):
+            continue
+        args = module.scheme.weights
+        tensors[f"{name}.qgate_up"] = pack_weight(module.qgate_up, args.num_bits)
+        tensors[f"{name}.sgate_up"] = module.sgate_up
+        tensors[f"{name}.qdown"] = pack_weight(module.qdown, args.num_bits)
+        tensors[f"{name}.sdown"] = module.sdown
+        experts[name] = {
+            "num_experts": module.num_experts,
+            "hidden_dim": module.hidden_dim,
+            "intermediate_dim": module.intermediate_dim,
+            "gate_up_shape": list(module.qgate_up.shape),
+            "down_shape": list(module.qdown.shape),
+            "weights": _args_to_dict(args),
+            "input_activations": _args_to_dict(module.scheme.input_activations),
+        }
+
+    owned = tuple(f"{layer}." for layer in (*layers, *experts))
     state = model.state_dict()
     for name, tensor in state.items():
         if (owned and name.startswith(owned)) or name in tensors:
@@ -63,7 +87,7 @@ def save_packed_model(model: nn.Module, path, model_id: str, kv_cache_bits=None,
     meta = {
         "model_id": model_id,
         "layers": layers,
-        "experts": {},
+        "experts": experts,
         "non_persistent_buffers": non_persistent,
         "kv_cache_bits": kv_cache_bits,
         **(extra or {}),
@@ -123,10 +147,23 @@ def load_packed_model(path, device="cuda", dtype=torch.bfloat16, config=None):
                                     tensors.get(f"{name}.bias"), device, dtype)
         _replace(model, name, module)
 
+    for name, spec in (meta.get("experts") or {}).items():
+        args = _args_from_dict(spec["weights"])
+        scheme = QuantizationScheme(weights=args,
+                                    input_activations=_args_from_dict(spec["input_activations"]))
+        qgate_up = unpack_weight(tensors[f"{name}.qgate_up"].to(device), args.num_bits)
+        qdown = unpack_weight(tensors[f"{name}.qdown"].to(device), args.num_bits)
+        # the activation is architecture, not weights: take it from the block being replaced
+        module = KernelQuantExperts(
+            qgate_up.reshape(spec["gate_up_shape"]), tensors[f"{name}.sgate_up"].to(device),
+            qdown.reshape(spec["down_shape"]), tensors[f"{name}.sdown"].to(device), scheme,
+            spec["hidden_dim"], spec["intermediate_dim"], model.get_submodule(name).act_fn)
+        _replace(model, name, module)
+
     provided = set(tensors)
     _materialize_remaining(model, device, dtype, provided)
     non_persistent = set(meta.get("non_persistent_buffers", []))
-    owned = tuple(f"{layer}." for layer in meta["layers"])
+    owned = tuple(f"{layer}." for layer in (*meta["layers"], *(meta.get("experts") or {})))
     remaining = {
         name: tensor.to(device=device, dtype=dtype)
         for name, tensor in tensors.items()
@@ -172,6 +209,7 @@ def describe_packed(path) -> dict:
     return {
         "model_id": header["meta"]["model_id"],
         "quantized_layers": len(header["meta"]["layers"]),
+        "expert_blocks": len(header["meta"].get("experts") or {}),
         "tensors": len(entries),
         "bytes": sum(e["nbytes"] for e in entries.values()),
     }

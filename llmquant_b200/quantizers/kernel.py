@@ -159,6 +159,11 @@ class KernelQuantLinear(nn.Module):
                         native.stream_ptr(dev))
         return qweight, wscale
 
+    def canonical_tensors(self):
+        """(qweight, wscale) in the reference's layout with one pass of the inverse repack (the
+        two properties below each run it)."""
+        return self._unrepack() if self._stream else (self._qweight, self._wscale)
+
     @property
     def qweight(self):
         """Canonical `[N, groups, group_size]` int8 codes (what model.bin stores)."""

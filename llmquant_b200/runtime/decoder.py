@@ -367,6 +367,7 @@ class FusedLlamaDecoder:
         for layer in self.cache.layers:
             layer.reset()
         out = self.model(input_ids, past_key_values=self.cache, use_cache=True, logits_to_keep=1)
+        self.logits.copy_(out.logits[:, -1])  # the prompt's last position, for callers that inspect it
         first = out.logits[:, -1].argmax(-1)
         self.tokens.copy_(first)
         self.pos.fill_(prompt)

@@ -70,3 +70,25 @@ def kv_store(states, num_bits=8):
     """What the quantized cache holds for new K or V [..., head_dim]: the reference's
     FakeQuantCache values (llmquant/quantizers/fake.py:46-55)."""
     return kv_fake_quantize(states, num_bits, 128, dtype="bf16")
+
+
+def attention_decode_exact(q, k_codes, k_scales, v_codes, v_scales, scaling):
+    """The rounding-free value of the same attention: float64 over the stored integers times
+    their fp32 scales, q [Hq, D], codes [Hkv, T, D] int8, scales [Hkv, T, 1] -> [Hq, D].
+
+    NOT the reference's arithmetic (that is `attention_decode`, which rounds scores,
+    probabilities and the output to bf16 like transformers' eager path and reads bf16-rounded
+    cache values): it is the quantity both of them approximate. The bf16 path is itself about
+    1e-2 (relative L2) away from it at a few hundred tokens, so a kernel that accumulates in
+    fp32 is held to a tight bound against this value and to the bf16 path's own noise against
+    `attention_decode`."""
+    q = np.asarray(q, dtype=np.float64)
+    k = np.asarray(k_codes, dtype=np.float64) * np.asarray(k_scales, dtype=np.float64)
+    v = np.asarray(v_codes, dtype=np.float64) * np.asarray(v_scales, dtype=np.float64)
+    rep = q.shape[0] // k.shape[0]
+    k = np.repeat(k, rep, axis=0)
+    v = np.repeat(v, rep, axis=0)
+    scores = np.einsum("hd,htd->ht", q, k) * float(scaling)
+    p = np.exp(scores - scores.max(axis=-1, keepdims=True))
+    p /= p.sum(axis=-1, keepdims=True)
+    return np.einsum("ht,htd->hd", p, v)

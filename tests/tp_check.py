@@ -1,9 +1,13 @@
 """Run under torchrun with 2+ ranks (see test_gpu_tp.py): tensor-parallel fused decode of a
-seeded tiny Llama against the single-GPU fused decoder. Prints TP_CHECK_OK on rank 0."""
+seeded tiny Llama, with every all-reduce route (folded into the GEMVs, the separate kernel over
+peer memory, NCCL), against the single-GPU fused decoder and against the reference's real-mode
+logits (tests/golden/tiny_llama.npz, when the group size divides the golden model's heads).
+Prints TP_CHECK_OK on rank 0."""
 
 import os
 import sys
 
+import numpy as np
 import torch
 import torch.distributed as dist
 
@@ -25,50 +29,87 @@ def main():
     device = torch.device("cuda", torch.cuda.current_device())
     dist.init_process_group("nccl", device_id=device)
     quant = QuantConfig(attn_weight="int8", mlp_weight="int4", head_weight="int8", kv_cache="int8")
-    kw = dict(head_dim=128, hidden=1024, inter=2048, heads=8, kv_heads=world if world > 2 else 2,
-              vocab=512)
-    g = torch.Generator().manual_seed(3)
-    prompt = torch.randint(0, 512, (2, 20), generator=g).cuda()
-    new = 12
+    blob = dict(np.load(os.path.join(ROOT, "tests", "golden", "tiny_llama.npz")))
+    golden_ok = world == 2  # the golden model: 4 query heads, 2 KV heads
+    if golden_ok:
+        kw = dict(head_dim=128, hidden=512, inter=1024)
+        ids = torch.from_numpy(blob["hd128_tokens"]).to(device)
+        n_prompt = blob["hd128_prompt"].shape[1]
+        want_logits = blob["hd128_logits"]
+    else:
+        kw = dict(head_dim=128, hidden=1024, inter=2048, heads=8, kv_heads=world, vocab=512)
+        g = torch.Generator().manual_seed(3)
+        ids = torch.randint(0, 512, (2, 36), generator=g).to(device)
+        n_prompt = 20
+    B, total = ids.shape
+    new = total - n_prompt
 
-    # single-GPU reference on rank 0, its tokens broadcast for teacher forcing
-    ref_tokens = torch.zeros(2, new, dtype=torch.long, device=device)
+    # single-GPU fused decoder on rank 0, teacher-forced with `ids`
     ref_logits = []
     if rank == 0:
         full = oneshot(tiny_llama(seed=0, **kw).cuda(), quant.to_modifier(mode="kernel"))
-        ref = FusedLlamaDecoder(full, 2, 64, kv_bits=8, use_graph=False)
-        ref.prefill(prompt)
-        for i in range(new):
-            ref_tokens[:, i] = ref.tokens
+        ref = FusedLlamaDecoder(full, B, total + 2, kv_bits=8, use_graph=False)
+        ref.prefill(ids[:, :n_prompt])
+        for i in range(new - 1):
+            ref.tokens.copy_(ids[:, n_prompt + i])
             ref.step()
             ref_logits.append(ref.logits.float().cpu().numpy().copy())
         del ref, full
-    dist.broadcast(ref_tokens, src=0)
 
     ok = True
-    for use_peer in (True, False):
-        ctx = tp.TPContext(rank, world, peer_allreduce=use_peer)
-        sharded = tp.shard_linears_(tiny_llama(seed=0, **kw), ctx).cuda()
-        oneshot(sharded, quant.to_modifier(mode="kernel"))
-        tp.wrap_for_prefill_(sharded, ctx)
-        dec = FusedLlamaDecoder(sharded, 2, 64, kv_bits=8, tp=ctx)
-        if use_peer and dec.peer is None:
-            print(f"rank {rank}: peer all-reduce unavailable: {getattr(dec, 'peer_error', '?')}", flush=True)
-        dec.prefill(prompt)
-        produced = []
-        for i in range(new):
-            dec.tokens.copy_(ref_tokens[:, i])
-            dec.step()
-            produced.append(dec.tokens.clone())
+    notes = []
+    routes = [("folded", dict(fused_allreduce=True, peer_allreduce=True)),
+              ("kernel", dict(fused_allreduce=False, peer_allreduce=True)),
+              ("nccl", dict(fused_allreduce=False, peer_allreduce=False))]
+    for name, flags in routes:
+        for use_graph in ((False, True) if name == "folded" else (True,)):
+            ctx = tp.TPContext(rank, world, **flags)
+            sharded = tp.shard_linears_(tiny_llama(seed=0, **kw), ctx).cuda()
+            oneshot(sharded, quant.to_modifier(mode="kernel"))
+            tp.wrap_for_prefill_(sharded, ctx)
+            dec = FusedLlamaDecoder(sharded, B, total + 2, kv_bits=8, tp=ctx, use_graph=use_graph,
+                                    gather_logits=True)
+            got_route = "folded" if dec.exchange is not None else ("kernel" if dec.peer is not None else "nccl")
+            if got_route != name:
+                notes.append(f"rank {rank}: wanted {name}, got {got_route}: {dec.peer_error}")
+                ok &= name != "folded" or got_route == "folded"
+            dec.prefill(ids[:, :n_prompt])
+            produced, logits = [], []
+            for i in range(new - 1):
+                dec.tokens.copy_(ids[:, n_prompt + i])
+                dec.step()
+                produced.append(dec.tokens.clone())
+                logits.append(dec.logits.float().cpu().numpy().copy())
+            mine = torch.stack(produced)
+            theirs = [torch.empty_like(mine) for _ in range(world)]
+            dist.all_gather(theirs, mine)
+            same = all(torch.equal(theirs[0], t) for t in theirs)  # every rank decodes the same tokens
+            ok &= same
             if rank == 0:
-                err = rel_l2(dec.logits.float().cpu().numpy(), ref_logits[i])
-                ok &= err <= 2e-2
-        mine = torch.stack(produced)
-        theirs = [torch.empty_like(mine) for _ in range(world)]
-        dist.all_gather(theirs, mine)
-        ok &= all(torch.equal(theirs[0], t) for t in theirs)  # every rank decodes the same tokens
-        ok &= native.library().lq_allreduce_device_error() == 0
-        del dec, sharded
+                logits = np.stack(logits, 1)
+                # the token the exchange picked is the argmax of the gathered logits
+                picked = mine.T.cpu().numpy()
+                ok &= bool((picked == logits.argmax(-1)).all())
+                err = rel_l2(logits, np.stack(ref_logits, 1))
+                ok &= err <= 1e-2
+                line = f"{name} graph={use_graph}: ranks agree={same} rel-L2 vs one GPU {err:.2e}"
+                if golden_ok:
+                    want = want_logits[:, 1:new]
+                    gerr = rel_l2(logits, want)
+                    top2 = np.sort(want, -1)[..., -2:]
+                    decided = (top2[..., 1] - top2[..., 0]) > 4 * np.abs(logits - want).max(-1)
+                    agree = bool((logits.argmax(-1) == want.argmax(-1))[decided].all())
+                    ok &= gerr <= 2e-2 and agree
+                    line += f", vs the reference's real mode {gerr:.2e} (argmax where decided: {agree})"
+                print(line, flush=True)
+            try:
+                dec.check_device_errors()
+            except RuntimeError as exc:
+                notes.append(f"rank {rank}: {exc}")
+                ok = False
+            del dec, sharded
+    for n in notes:
+        print(n, flush=True)
     flag = torch.tensor([1 if ok else 0], device=device)
     dist.all_reduce(flag, op=dist.ReduceOp.MIN)
     if rank == 0:
