@@ -246,8 +246,8 @@ int64_t lq_attn_fused_scratch_bytes(int B, int Hq, int Hkv, int D, int splits);
 /* Non-zero if a bounded wait inside lq_attn_decode_fused ever expired (reads and clears the
  * word; synchronizes with the device: for tests and diagnostics). */
 int lq_attn_device_error(void);
-/* `impl` selects the kernel: LQ_ATTN_AUTO = the library's choice (LQ_ATTN_CLUSTER where it
- * applies, else LQ_ATTN_MMA), LQ_ATTN_SIMT = all-SIMT arithmetic, LQ_ATTN_MMA = contractions on
+/* `impl` selects the kernel: LQ_ATTN_AUTO = the library's choice (LQ_ATTN_MMA for every shape
+ * it is built for), LQ_ATTN_SIMT = all-SIMT arithmetic, LQ_ATTN_MMA = contractions on
  * mma.sync tensor-core instructions with the slices merged through `scratch` by the CTA that
  * finishes last, LQ_ATTN_CLUSTER = the same contractions with the slices of a KV head running as
  * one thread-block cluster that merges through distributed shared memory (`splits` must be 2,

@@ -137,4 +137,10 @@ class QuantizationModifier:
             parent_name, _, child = name.rpartition(".")
             parent = model.get_submodule(parent_name) if parent_name else model
             setattr(parent, child, module)
+        if self.kv_cache_bits and hasattr(model, "set_attn_implementation"):
+            # a recipe with an integer KV cache also selects the attention that reads one as
+            # integers (it behaves like transformers' SDPA for every other cache)
+            from llmquant_b200.quantizers.kv_cache import enable_fused_kv_attention
+
+            enable_fused_kv_attention(model)
         return model

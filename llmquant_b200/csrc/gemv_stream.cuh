@@ -333,7 +333,9 @@ __device__ __forceinline__ void tp_sum_prologue(const GemvParams& p, int KW, int
   }
   if (tid == 0) {
     const uint32_t want = (step * p.tp_ready_mul + p.tp_ready_add) * (uint32_t)R;
-    if (!wait_counter<false>(p.tp_ready, want, p.tp_wait)) atomicExch(p.error_word, 4);
+    // twice the peers' limit: when the partials never arrive the first CTAs give up first, publish
+    // what they have, and only their error is recorded
+    if (!wait_counter<false>(p.tp_ready, want, 2 * p.tp_wait)) atomicExch(p.error_word, 4);
   }
   asm volatile("bar.sync 2, %0;" ::"r"(T) : "memory");
 }

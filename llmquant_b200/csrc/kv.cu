@@ -1534,7 +1534,10 @@ extern "C" int lq_attn_decode_fused(const void* qkv, const void* cos_table, cons
   // dividing the head's outputs evenly) and such clusters fit the device
   const bool cluster_shape = splits >= 2 && splits <= kMaxCluster && (splits & (splits - 1)) == 0 &&
                              (G * D) % splits == 0 && (G * D) / splits >= 1 && (D == 64 || D == 128);
-  if ((impl == LQ_ATTN_AUTO || impl == LQ_ATTN_CLUSTER) && cluster_shape) {
+  // (on request only: measured on B200 at a 4k context the cluster variant is no faster than the
+  // merge by the last CTA -- 13.4 us with 16 slices against 10.9 us with 37 -- because a CTA of
+  // a 16-slice cluster walks 2.3 times the tokens and the cluster launch itself is slower)
+  if (impl == LQ_ATTN_CLUSTER && cluster_shape) {
     const size_t csmem = 2 * (size_t)kClusterCap * D;
     bool tried = false;
 #define LQ_CL_CASE(DD, GG)                                                                         \

@@ -9,7 +9,12 @@ from llmquant_b200.quantizers.kernel import (
 )
 
 from llmquant_b200.quantizers.experts import KernelQuantExperts, quantize_expert_stack
-from llmquant_b200.quantizers.kv_cache import KernelQuantCache, QuantizedKVLayer, make_cache_factory
+from llmquant_b200.quantizers.kv_cache import (
+    KernelQuantCache,
+    QuantizedKVLayer,
+    enable_fused_kv_attention,
+    make_cache_factory,
+)
 
 AVAILABLE_MODES = frozenset({"kernel"})
 
@@ -24,6 +29,6 @@ def quant_linear_for(mode: str):
 __all__ = [
     "AVAILABLE_MODES", "DECODE_MAX_ROWS", "KERNEL_MAX_ROWS", "KernelQuantCache", "KernelQuantExperts",
     "KernelQuantLinear", "quantize_expert_stack",
-    "QuantizedKVLayer", "make_cache_factory",
+    "QuantizedKVLayer", "enable_fused_kv_attention", "make_cache_factory",
     "pad_activation", "quant_linear_for", "quantize_weight_canonical",
 ]

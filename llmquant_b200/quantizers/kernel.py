@@ -205,7 +205,7 @@ class KernelQuantLinear(nn.Module):
 
     def gemv(self, flat, out_dtype=None, residual=None, variant=None, norm_weight=None,
              norm_eps=1e-5, epilogue=0, pdl=False, out=None, tp=None):
-        """Streaming GEMV on `[M <= 8, K]` bf16 rows -> `[M, N]` (bf16 or fp32).
+        """Streaming GEMV on `[M, K]` bf16 rows -> `[M, N]` (bf16 or fp32), 8 rows per launch.
 
         Optional fusions (see `lq_wq_gemv_fused`): RMSNorm of the input rows by `norm_weight`,
         `epilogue=1` for silu(gate) * up over interleaved (gate, up) rows, a residual added to
@@ -220,6 +220,18 @@ class KernelQuantLinear(nn.Module):
         if out is None and not pushing:
             out = torch.empty(m, n_out, dtype=out_dtype, device=flat.device)
         if m == 0:
+            return out
+        if m > DECODE_MAX_ROWS:
+            # more rows than one launch takes: blocks of DECODE_MAX_ROWS rows, one launch each.
+            # The passes after the first find most of a layer's weight in L2 (a Llama-3-8B
+            # linear is 17 to 59 MB).
+            if tp is not None:
+                raise RuntimeError(f"the tensor-parallel coupling takes the rows of one pass ({m} given)")
+            for m0 in range(0, m, DECODE_MAX_ROWS):
+                rows = slice(m0, min(m0 + DECODE_MAX_ROWS, m))
+                self.gemv(flat[rows], out_dtype=out_dtype, residual=None if residual is None else residual[rows],
+                          variant=variant, norm_weight=norm_weight, norm_eps=norm_eps, epilogue=epilogue,
+                          pdl=pdl, out=out[rows])
             return out
         bias = None
         if self.bias is not None:

@@ -8,6 +8,13 @@ reference would have stored (an integer cannot keep the sign of a zero, nothing 
 differs). Tokens already in the cache are never re-quantized. The fused decoder
 (`llmquant_b200.runtime.decoder`) reads the same storage directly with the decode-attention
 kernel instead of going through the dequantized copy.
+
+So can transformers' own `generate`: `enable_fused_kv_attention(model)` registers an attention
+function with transformers' `AttentionInterface` and selects it for the model; a cache made by
+`make_cache_factory(bits, model=model)` then hands that function its integer storage instead
+of a dequantized copy, and a decode step (one query token) runs the dequantize-on-read
+attention kernel over the codes. Prefill, padded batches and shapes the kernel is not built
+for dequantize once and take transformers' SDPA path, as before.
 """
 
 import ctypes
@@ -19,6 +26,43 @@ from transformers.cache_utils import Cache, CacheLayerMixin
 from llmquant_b200 import native
 
 KV_GROUP = 128
+ATTENTION_NAME = "llmquant_b200_int_kv"
+
+
+def int_kv_attention(module, query, key, value, attention_mask, dropout=0.0, scaling=None, **kwargs):
+    """Attention function for transformers' `AttentionInterface`. `key` / `value` are what
+    `Cache.update` returned: int8 code views tagged with their cache layer when the cache was
+    made for fused reading, ordinary tensors otherwise."""
+    from transformers.integrations.sdpa_attention import sdpa_attention_forward
+
+    layer = getattr(key, "lq_layer", None)
+    if layer is None:
+        return sdpa_attention_forward(module, query, key, value, attention_mask, dropout=dropout,
+                                      scaling=scaling, **kwargs)
+    batch, heads, q_len, head_dim = query.shape
+    groups = heads // layer.heads if heads % layer.heads == 0 else 0
+    fused = (q_len == 1 and query.dtype == torch.bfloat16 and head_dim in (64, 128) and groups in (1, 2, 4, 8)
+             and (attention_mask is None or batch == 1) and layer.num_bits <= 8 and not dropout)
+    if fused:
+        scale = head_dim ** -0.5 if scaling is None else scaling
+        out = layer.attend(query.reshape(batch, heads, head_dim), scale)
+        return out.view(batch, 1, heads, head_dim), None
+    k, v = layer.dequantized()
+    return sdpa_attention_forward(module, query, k, v, attention_mask, dropout=dropout, scaling=scaling, **kwargs)
+
+
+def enable_fused_kv_attention(model):
+    """Select the dequantize-on-read attention for `model` (any transformers model whose
+    attention goes through `AttentionInterface`). Safe with every cache: only a cache made
+    with `make_cache_factory(bits, model=model)` is read as integers."""
+    from transformers import AttentionInterface, AttentionMaskInterface
+    from transformers.masking_utils import sdpa_mask
+
+    if ATTENTION_NAME not in AttentionInterface.valid_keys():
+        AttentionInterface.register(ATTENTION_NAME, int_kv_attention)
+        AttentionMaskInterface.register(ATTENTION_NAME, sdpa_mask)
+    model.set_attn_implementation(ATTENTION_NAME)
+    return model
 
 
 class QuantizedKVLayer(CacheLayerMixin):
@@ -27,10 +71,13 @@ class QuantizedKVLayer(CacheLayerMixin):
     is_sliding = False
     is_compileable = False
 
-    def __init__(self, num_bits: int = 8, max_cache_len=None):
+    def __init__(self, num_bits: int = 8, max_cache_len=None, fused_read: bool = False):
         super().__init__()
         self.num_bits = num_bits
         self.max_cache_len = max_cache_len
+        self.fused_read = fused_read
+        self.dequant_calls = self.fused_reads = 0  # how the cache has been read so far
+        self._scratch = None
         self.length = 0
         self.capacity = 0
         self.k_codes = self.v_codes = self.k_scales = self.v_scales = None
@@ -84,6 +131,7 @@ class QuantizedKVLayer(CacheLayerMixin):
     def dequantized(self, length=None):
         """(K, V) in the model dtype, [B, H, length, D]."""
         length = self.length if length is None else length
+        self.dequant_calls += 1
         outs = []
         for codes, scales in ((self.k_codes, self.k_scales), (self.v_codes, self.v_scales)):
             out = torch.empty(self.batch, self.heads, length, self.head_dim, dtype=self.dtype,
@@ -97,7 +145,31 @@ class QuantizedKVLayer(CacheLayerMixin):
 
     def update(self, key_states, value_states, *args, **kwargs):
         self.append(key_states, value_states)
-        return self.dequantized()
+        if not self.fused_read:
+            return self.dequantized()
+        # the integer storage itself, tagged so that int_kv_attention knows what it was given
+        k, v = self.k_codes[:, :, : self.length], self.v_codes[:, :, : self.length]
+        k.lq_layer = v.lq_layer = self
+        return k, v
+
+    def attend(self, q, scaling):
+        """softmax(q k^T * scaling) v for one query token per sequence over the stored codes:
+        q [B, Hq, D] bf16 -> [B, Hq, D] bf16 (`lq_attn_decode_kv_i8`)."""
+        batch, heads, head_dim = q.shape
+        splits = max(1, min(-(-2 * 148 // (batch * self.heads)), self.length // 64 or 1))
+        lib = native.library()
+        need = lib.lq_attn_decode_scratch_bytes(batch, heads, head_dim, splits) // 4
+        if self._scratch is None or self._scratch.numel() < need:
+            self._scratch = torch.empty(need, dtype=torch.float32, device=self.device)
+        q = q.contiguous()
+        out = torch.empty_like(q)
+        with torch.cuda.device(self.device):
+            native.call("lq_attn_decode_kv_i8", q.data_ptr(), self.k_codes.data_ptr(), self.v_codes.data_ptr(),
+                        self.k_scales.data_ptr(), self.v_scales.data_ptr(), out.data_ptr(),
+                        self._scratch.data_ptr(), batch, heads, self.heads, head_dim, self.capacity, 0,
+                        self.length, 0, float(scaling), splits, 0, native.stream_ptr(self.device))
+        self.fused_reads += 1
+        return out
 
     def get_mask_sizes(self, query_length: int):
         return self.get_seq_length() + query_length, 0
@@ -134,20 +206,24 @@ class KernelQuantCache(Cache):
     `make_cache_factory(8)()` returns; `max_cache_len` fixes the capacity up front (needed
     when a captured graph is going to write into it)."""
 
-    def __init__(self, num_bits: int = 8, max_cache_len=None):
+    def __init__(self, num_bits: int = 8, max_cache_len=None, fused_read: bool = False):
         super().__init__(layer_class_to_replicate=functools.partial(
-            QuantizedKVLayer, num_bits, max_cache_len))
+            QuantizedKVLayer, num_bits, max_cache_len, fused_read))
         self.num_bits = num_bits
         self.capacity_limit = max_cache_len
+        self.fused_read = fused_read
 
     def crop(self, max_length: int):
         for layer in self.layers:
             layer.crop(max_length)
 
 
-def make_cache_factory(num_bits, max_cache_len=None):
+def make_cache_factory(num_bits, max_cache_len=None, model=None):
     """Zero-arg factory for `generate(past_key_values=...)`, or None to keep the bf16 cache
-    (same contract as llmquant/quantizers/fake.py:58-62)."""
+    (same contract as llmquant/quantizers/fake.py:58-62). With `model` given and switched to
+    the dequantize-on-read attention (`enable_fused_kv_attention`), the caches it makes are
+    read as integers by that model's decode steps instead of being dequantized whole."""
     if num_bits is None:
         return None
-    return lambda: KernelQuantCache(num_bits, max_cache_len)
+    fused = model is not None and getattr(getattr(model, "config", None), "_attn_implementation", None) == ATTENTION_NAME
+    return lambda: KernelQuantCache(num_bits, max_cache_len, fused_read=fused)

@@ -28,6 +28,9 @@ from llmquant_b200.quantizers.kernel import KernelQuantLinear
 from llmquant_b200.quantizers.kv_cache import KernelQuantCache
 
 
+MAX_BATCH = 64
+
+
 def _fuse_rows(modules, interleave=False):
     """One KernelQuantLinear holding the rows of several (same geometry, same scheme)."""
     first = modules[0]
@@ -99,8 +102,9 @@ class FusedLlamaDecoder:
         if not supports(model):
             raise ValueError("FusedLlamaDecoder needs a Llama-layout model whose attention and MLP "
                              "linears are KernelQuantLinear (head_dim 64/128, silu MLP)")
-        if max_batch > 8:
-            raise ValueError("the decode GEMV takes at most 8 rows; batch > 8 is not built yet")
+        if max_batch > MAX_BATCH:
+            raise ValueError(f"the fused decoder serves up to {MAX_BATCH} sequences (the decode GEMV takes 8 rows "
+                             f"per launch; larger batches run as several launches per linear)")
         cfg = model.config
         self.model = model
         self.device = next(model.parameters()).device
@@ -165,14 +169,9 @@ class FusedLlamaDecoder:
         self.pos = torch.zeros(1, dtype=torch.long, device=dev)
         self.history = torch.zeros(B, max_len + 1, dtype=torch.long, device=dev)
         self.ticket = torch.zeros(1, dtype=torch.int32, device=dev)
-        # Slices of the cached context per KV head: about two CTAs per SM in all, as a power of two
-        # up to 16 so that the slices of a head can run as one thread-block cluster and merge
-        # through distributed shared memory (lq_attn_decode_fused picks that kernel by itself).
-        if attn_splits > 0:
-            self.splits = attn_splits
-        else:
-            want = max(1, min(2 * 148 // (B * self.Hkv), max_len // 64 or 1, 16))
-            self.splits = 1 << (want.bit_length() - 1)
+        # slices of the cached context per KV head: about two CTAs per SM in all
+        want = attn_splits if attn_splits > 0 else max(1, -(-2 * 148 // (B * self.Hkv)))
+        self.splits = max(1, min(want, max_len // 64 or 1))
         self.attn_impl = attn_impl
         nbytes = native.library().lq_attn_fused_scratch_bytes(B, self.Hq, self.Hkv, self.D, self.splits)
         self.scratch = torch.zeros(-(-nbytes // 4), dtype=torch.float32, device=dev)

@@ -2,7 +2,8 @@
 
 `can_graph`, `GraphedDecoder` and `graphed_generate` keep the names and call shapes of
 llmquant/runtime/graph_decode.py:40-157. Two things are lifted: a quantized KV cache can be
-graphed (its write cursor lives in device memory), and so can a batch of up to 8 sequences.
+graphed (its write cursor lives in device memory), and so can a batch of sequences (up to
+`decoder.MAX_BATCH`).
 A kernel-mode Llama takes the fused decoder (`runtime/decoder.py`); anything else that sits
 on a CUDA device takes the transformers `StaticCache` route the reference uses.
 """
@@ -26,8 +27,18 @@ def can_graph(model, cache_factory=None) -> bool:
         return False
     if not on_cuda:
         return False
+    # Callers written for the reference ask `can_graph(model, cache_factory)` and then call
+    # `graphed_generate(model, ids, n)` without saying which cache they meant
+    # (llmquant/eval/evaluate.py:186-199). The answer given here is therefore remembered on the
+    # model: the next graphed_generate without an explicit `kv_cache_bits` uses that cache.
+    bits = None
     if cache_factory is not None:
-        return fused.supports(model)  # the integer cache is graphed by the fused decoder only
+        if not fused.supports(model):
+            return False  # the integer cache is graphed by the fused decoder only
+        bits = getattr(cache_factory() if callable(cache_factory) else cache_factory, "num_bits", None)
+        if bits is None:
+            return False  # some other cache class: not one this library can capture
+    model.__dict__["_graph_kv_cache_bits"] = bits
     return True
 
 
@@ -94,9 +105,17 @@ class GraphedDecoder:
 def graphed_generate(model, input_ids, max_new_tokens: int, kv_cache_bits=None):
     """Greedy generation with the decode step replayed; None if it cannot be graphed.
 
-    `kv_cache_bits` selects the integer KV cache (fused decoder); None keeps bf16 KV."""
-    factory = object() if kv_cache_bits else None
-    if not can_graph(model, factory):
+    `kv_cache_bits` selects the integer KV cache (fused decoder); None means the cache the last
+    `can_graph(model, cache_factory)` call was asked about, bf16 KV if there was none."""
+    if kv_cache_bits is None:
+        kv_cache_bits = model.__dict__.get("_graph_kv_cache_bits")  # what can_graph was asked about
+    if kv_cache_bits:
+        from llmquant_b200.quantizers.kv_cache import make_cache_factory
+
+        ok = can_graph(model, make_cache_factory(kv_cache_bits))
+    else:
+        ok = can_graph(model)
+    if not ok:
         return None
     prompt = input_ids.shape[1]
     if kv_cache_bits:

@@ -39,14 +39,16 @@ def _filled_cache(B, hkv, T, Tmax, hd, seed):
 
 
 @pytest.mark.parametrize("hd,hq,hkv,B,T,splits,impl", [
-    (128, 32, 8, 1, 4096, 37, native.ATTN_MMA),       # the 8B decode step, merge by the last CTA
-    (128, 32, 8, 1, 4096, 16, native.ATTN_AUTO),      # the same step as the decoder launches it
+    (128, 32, 8, 1, 4096, 37, native.ATTN_AUTO),      # the 8B decode step as the decoder launches it
+    (128, 32, 8, 1, 4096, 16, native.ATTN_CLUSTER),   # the same with one cluster per KV head
     (128, 32, 8, 1, 4096, 16, native.ATTN_SIMT),
-    (128, 4, 1, 1, 4100, 16, native.ATTN_AUTO),       # one KV head per GPU (tensor parallel over 8)
-    (128, 32, 8, 2, 1030, 8, native.ATTN_AUTO),
-    (64, 32, 8, 1, 600, 16, native.ATTN_AUTO),        # the 1B decode step past 512 tokens
-    (64, 32, 8, 1, 600, 37, native.ATTN_MMA),
-    (64, 32, 8, 1, 2040, 16, native.ATTN_AUTO),
+    (128, 4, 1, 1, 4100, 64, native.ATTN_AUTO),       # one KV head per GPU (tensor parallel over 8)
+    (128, 4, 1, 1, 4100, 16, native.ATTN_CLUSTER),
+    (128, 32, 8, 2, 1030, 8, native.ATTN_CLUSTER),
+    (128, 32, 8, 8, 1030, 5, native.ATTN_AUTO),       # batch 8
+    (64, 32, 8, 1, 600, 37, native.ATTN_AUTO),        # the 1B decode step past 512 tokens
+    (64, 32, 8, 1, 600, 16, native.ATTN_CLUSTER),
+    (64, 32, 8, 1, 2040, 32, native.ATTN_AUTO),
 ])
 def test_fused_attention_at_benchmark_contexts(hd, hq, hkv, B, T, splits, impl):
     steps, Tmax = 4, T + 16

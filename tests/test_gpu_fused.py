@@ -170,3 +170,41 @@ def test_step_bookkeeping_kernels(B):
     hidden = torch.zeros(B, H, dtype=torch.bfloat16, device="cuda")
     native.call("lq_embed_gather", table.data_ptr(), tokens.data_ptr(), hidden.data_ptr(), B, H, V, 1, stream)
     assert torch.equal(hidden, table.index_select(0, tokens))
+
+
+@pytest.mark.parametrize("B", [12, 32])
+def test_batches_above_eight_rows_decode_like_the_module_path(B):
+    """More sequences than one GEMV launch takes (8 rows): the fused decoder runs every linear
+    as several row-block launches. Its logits, step by step, against the transformers
+    module-by-module path with the integer cache fed the same tokens, and the graphed loop
+    against the eager one."""
+    from llmquant_b200.quantizers import make_cache_factory
+    from llmquant_b200.runtime.decoder import FusedLlamaDecoder
+
+    model = _kernel_model(dict(head_dim=128, hidden=512, inter=1024))
+    g = torch.Generator().manual_seed(B)
+    prompt = torch.randint(0, 512, (B, 20), generator=g).cuda()
+    new = 6
+    streams = []
+    for use_graph in (False, True):
+        dec = FusedLlamaDecoder(model, B, 20 + new + 1, kv_bits=8, use_graph=use_graph)
+        streams.append(dec.generate(prompt, new))
+    assert torch.equal(streams[0], streams[1])
+    tokens = streams[0]
+    dec = FusedLlamaDecoder(model, B, 20 + new + 1, kv_bits=8, use_graph=False)
+    dec.prefill(prompt)
+    cache = make_cache_factory(8)()
+    with torch.no_grad():
+        model(tokens[:, :20], past_key_values=cache, use_cache=True)
+    for i in range(new - 1):
+        dec.tokens.copy_(tokens[:, 20 + i])
+        dec.step()
+        with torch.no_grad():
+            want = model(tokens[:, 20 + i:21 + i], past_key_values=cache, use_cache=True).logits[:, -1]
+        got = dec.logits.float().cpu().numpy()
+        want = want.float().cpu().numpy()
+        assert rel_l2(got, want) <= 2e-2, i
+        top2 = np.sort(want, -1)[:, -2:]
+        decided = (top2[:, 1] - top2[:, 0]) > 4 * np.abs(got - want).max(-1)
+        assert (got.argmax(-1) == want.argmax(-1))[decided].all()
+    dec.check_device_errors()

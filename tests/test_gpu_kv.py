@@ -122,11 +122,11 @@ def test_rope_write_and_decode_attention(hd, hq, hkv):
 
 @pytest.mark.parametrize("hd,hq,hkv", [(64, 8, 2), (128, 8, 2), (128, 8, 8)])
 @pytest.mark.parametrize("splits,impl", [(1, native.ATTN_AUTO), (7, native.ATTN_MMA), (7, native.ATTN_SIMT),
-                                         (1, native.ATTN_SIMT), (8, native.ATTN_AUTO), (4, native.ATTN_AUTO)])
+                                         (1, native.ATTN_SIMT), (8, native.ATTN_CLUSTER), (4, native.ATTN_CLUSTER)])
 def test_fused_attention_block_matches_the_separate_kernels(hd, hq, hkv, splits, impl):
     """lq_attn_decode_fused = lq_rope_kv_write + lq_attn_decode_kv_i8 in one launch, with every
-    kernel that can serve it (all-SIMT, tensor-core with the merge by the last CTA, and -- the
-    library's own choice for 2 / 4 / 8 / 16 slices -- the cluster kernel): the cache it leaves
+    kernel that can serve it (all-SIMT, tensor-core with the merge by the last CTA -- the
+    library's own choice -- and the cluster kernel for 2 / 4 / 8 / 16 slices): the cache it leaves
     behind is bit-identical, its output agrees with the separate kernels (which
     test_rope_write_and_decode_attention holds against the oracle), and its tickets are back at
     zero so it can be replayed."""
@@ -175,3 +175,40 @@ def test_fused_attention_block_matches_the_separate_kernels(hd, hq, hkv, splits,
     tickets = scratch_fus.view(torch.int32)[-(B * hkv):]
     assert int(tickets.abs().sum()) == 0
     assert lib.lq_attn_device_error() == 0
+
+
+@pytest.mark.parametrize("kw", [dict(head_dim=64), dict(head_dim=128, hidden=512, inter=1024)])
+def test_generate_reads_the_integer_cache_without_dequantizing_it(kw):
+    """transformers' own `generate` on a model switched to the dequantize-on-read attention:
+    after the prompt, no decode step dequantizes the cache (the reference's route materialises
+    the whole bf16 cache at every step), and the logits agree with the dequantizing route."""
+    from llmquant_b200.core import QuantConfig, oneshot
+    from llmquant_b200.quantizers import kv_cache, make_cache_factory
+    from oracle.real_mode import tiny_llama
+
+    cfg = QuantConfig(attn_weight="int8", mlp_weight="int4", head_weight="int8", kv_cache="int8")
+    model = oneshot(tiny_llama(seed=0, **kw).cuda(), cfg.to_modifier(mode="kernel"))
+    assert model.config._attn_implementation == kv_cache.ATTENTION_NAME
+    g = torch.Generator().manual_seed(4)
+    ids = torch.randint(0, 512, (1, 40), generator=g).cuda()
+    fused, plain = make_cache_factory(8, model=model)(), make_cache_factory(8)()
+    assert fused.fused_read and not plain.fused_read
+    new = 10
+    out = model.generate(ids, attention_mask=torch.ones_like(ids), max_new_tokens=new, do_sample=False,
+                         pad_token_id=0, past_key_values=fused)
+    assert out.shape == (1, 40 + new)
+    layers = len(model.model.layers)
+    assert [l.dequant_calls for l in fused.layers] == [1] * layers          # the prompt only
+    assert [l.fused_reads for l in fused.layers] == [new - 1] * layers
+    # teacher-forced over the generated tokens: fused reads against whole-cache dequantization
+    a, b = make_cache_factory(8, model=model)(), make_cache_factory(8)()
+    with torch.no_grad():
+        model(out[:, :40], past_key_values=a, use_cache=True)
+        model(out[:, :40], past_key_values=b, use_cache=True)
+        for i in range(40, 40 + new - 1):
+            la = model(out[:, i:i + 1], past_key_values=a, use_cache=True).logits[:, -1]
+            lb = model(out[:, i:i + 1], past_key_values=b, use_cache=True).logits[:, -1]
+            assert rel_l2(la.float().cpu().numpy(), lb.float().cpu().numpy()) <= 1e-2, i
+    assert b.layers[0].dequant_calls == new and b.layers[0].fused_reads == 0
+    for la_, lb_ in zip(a.layers, b.layers):  # both routes store the same integers
+        assert torch.equal(la_.k_codes[:, :, : la_.length], lb_.k_codes[:, :, : lb_.length])

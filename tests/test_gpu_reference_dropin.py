@@ -110,3 +110,96 @@ def test_reference_prefill_branch_and_model_level_oneshot(ref):
     toks_k, logits_k = greedy(kernel_model, prompt, 8, cache=make_cache_factory(8)())
     toks_r, logits_r = greedy(real_model, prompt, 8, cache=make_cache_factory(8)())
     assert rel_l2(logits_k.cpu().numpy(), logits_r.cpu().numpy()) <= 2e-2
+
+
+class _StubTokenizer:
+    vocab_size, eos_token_id = 512, 1
+
+
+def test_reference_latency_harness_measures_this_librarys_graphed_int8_decode(ref):
+    """The reference's `measure_latency` (llmquant/eval/evaluate.py:167-223) -- the body of its
+    run.py latency report -- called as it is, on a model quantized by THIS library with THIS
+    library's integer cache factory, its `llmquant.runtime` graph entry points replaced by
+    this library's: `can_graph` admits the integer cache, so the harness times the fused
+    graphed decoder; without graphs it drives transformers' generate with the integer cache."""
+    import llmquant.runtime as ref_runtime
+    from llmquant.eval.evaluate import measure_latency
+
+    from llmquant_b200.core import QuantConfig, oneshot
+    from llmquant_b200.quantizers import make_cache_factory
+    from llmquant_b200.runtime import can_graph, graphed_generate
+    from oracle.real_mode import tiny_llama
+
+    cfg = QuantConfig(attn_weight="int8", mlp_weight="int4", head_weight="int8", kv_cache="int8")
+    model = oneshot(tiny_llama(seed=0, head_dim=64).cuda(), cfg.to_modifier(mode="kernel"))
+    saved = (ref_runtime.can_graph, ref_runtime.graphed_generate)
+    ref_runtime.can_graph, ref_runtime.graphed_generate = can_graph, graphed_generate
+    try:
+        row = measure_latency(model, _StubTokenizer(), prompt_tokens=48, new_tokens=8, iters=1,
+                              cache_factory=make_cache_factory(8), use_cuda_graph=True)
+        assert row["cuda_graph"] is True and row["decode_tps"] > 0 and row["ttft_ms"] > 0
+        assert model.__dict__["_graph_kv_cache_bits"] == 8
+        eager = measure_latency(model, _StubTokenizer(), prompt_tokens=48, new_tokens=8, iters=1,
+                                cache_factory=make_cache_factory(8), use_cuda_graph=False)
+        assert eager["cuda_graph"] is False and eager["decode_tps"] > 0
+    finally:
+        ref_runtime.can_graph, ref_runtime.graphed_generate = saved
+
+
+def _save_tokenizer(directory):
+    """A word-level tokenizer with a chat template, made offline (no checkpoint on this machine)."""
+    from tokenizers import Tokenizer, models, pre_tokenizers
+    from transformers import PreTrainedTokenizerFast
+
+    vocab = {"<unk>": 0, "<eos>": 1, "system": 2, "user": 3, "assistant": 4}
+    vocab.update({f"w{i}": i for i in range(5, 512)})
+    tok = Tokenizer(models.WordLevel(vocab, unk_token="<unk>"))
+    tok.pre_tokenizer = pre_tokenizers.Whitespace()
+    fast = PreTrainedTokenizerFast(tokenizer_object=tok, unk_token="<unk>", eos_token="<eos>", pad_token="<eos>")
+    fast.chat_template = ("{% for m in messages %}{{ m['role'] }} {{ m['content'] }} {% endfor %}"
+                          "{% if add_generation_prompt %}assistant {% endif %}")
+    fast.save_pretrained(directory)
+
+
+def test_chat_on_a_packed_file_with_the_reference_session_and_with_this_librarys(ref, tmp_path):
+    """`examples/chat.py --load-packed` in two ways: the reference's `load_for_chat` +
+    `ChatSession` (its own modules on this library's kernels) reading a file THIS library
+    wrote, and this library's `load_for_chat` + `ChatSession` on the same file. Both carry the
+    integer KV cache across turns."""
+    from llmquant.runtime.chat import ChatSession as RefSession
+    from llmquant.runtime.chat import load_for_chat as ref_load_for_chat
+
+    from llmquant_b200.core import QuantConfig, oneshot
+    from llmquant_b200.packing import save_packed_model
+    from llmquant_b200.quantizers import KernelQuantCache
+    from llmquant_b200.runtime import ChatSession, load_for_chat
+    from oracle.real_mode import tiny_llama
+
+    cfg = QuantConfig(attn_weight="int8", mlp_weight="int4", head_weight="int8", kv_cache="int8")
+    model = oneshot(tiny_llama(seed=0, head_dim=64).cuda(), cfg.to_modifier(mode="kernel"))
+    model_id = tmp_path / "tiny-llama"
+    model.config.save_pretrained(model_id)
+    _save_tokenizer(model_id)
+    path = save_packed_model(model, tmp_path / "model.bin", str(model_id), kv_cache_bits=8)
+
+    ours_model, ours_tok, ours_factory = load_for_chat(str(path))
+    assert isinstance(ours_factory(), KernelQuantCache)
+    session = ChatSession(ours_model, ours_tok, max_new_tokens=6, cache_factory=ours_factory)
+    first = session.ask("w7 w8 w9")
+    second = session.ask("w10 w11")
+    assert len(session.history) == 4 and len(session.last_reply_ids) == 6 and session._cache is not None
+    assert session._cache.get_seq_length() > 10  # the cache was carried across the turns
+
+    ref_model, ref_tok, ref_factory = ref_load_for_chat(str(path))
+    ref_session = RefSession(ref_model, ref_tok, max_new_tokens=6, cache_factory=ref_factory)
+    ref_first, ref_second = ref_session.ask("w7 w8 w9"), ref_session.ask("w10 w11")
+    # (both are greedy decodes of the same weights; on a random-init model a near-tie may send
+    # them different ways, so only the shape of the conversation is compared)
+    assert len(ref_session.last_reply_ids) == 6 and len(ref_session.history) == 4
+    assert all(isinstance(r, str) and r for r in (first, second, ref_first, ref_second))
+    # a context limit drops whole turns and the stale cache with them
+    tight = ChatSession(ours_model, ours_tok, max_new_tokens=6, cache_factory=ours_factory,
+                        max_context_tokens=24, system_prompt=None)
+    for turn in range(4):
+        tight.ask("w20 w21 w22")
+    assert len(tight.history) < 8
