@@ -10,6 +10,10 @@ Prints ONE JSON line (rank 0). Workloads:
                   (one CUDA-graph replay). value = decoded tokens per second.
   decode_1b       BASELINE config 3: the same for the Llama-3.2-1B shape, 512-token prompt.
 
+  gemv_one / attn_one / prefill_gemm
+                  one GEMV shape, one attention shape, the prefill GEMM shapes (BASELINE config 4):
+                  the small cases kernel profiles are taken on; each prints its own JSON line.
+
   gemv_sweep_1b   BASELINE config 2: the Llama-3.2-1B linear shapes at M=1 (q/o, k/v, gate/up,
                   down as int4 and int8, lm_head int8), bf16 activations, group 128. A step is
                   one pass over a pool of distinct weight copies of every shape (the pool of
@@ -333,6 +337,71 @@ def run_gemv_one(args, device):
                       "gbs": round(per_copy / us / 1e3, 1), "graph_replay": True}), flush=True)
 
 
+# --------------------------------------------------------------------------- one attention shape
+def run_attn_one(args, device):
+    """The fused decode-attention block by itself at one shape and context (the small case for
+    kernel profiles): `layers` caches of random codes (together larger than L2), one launch per
+    cache in a CUDA graph with dependent launches. Prints a short JSON line of its own."""
+    from llmquant_b200 import native
+
+    lib = native.library()
+    B, D, T = args.batch, args.head_dim, args.prompt or 4111
+    Hq, Hkv = args.heads, args.kv_heads
+    tmax = T + 64
+    per_layer = 2 * B * Hkv * T * (D + 4)
+    layers = max(2, -(-int(1.5 * L2_BYTES) // per_layer))
+    g = torch.Generator(device=device).manual_seed(0)
+    caches = []
+    for _ in range(layers):
+        kc = torch.randint(-127, 128, (B, Hkv, tmax, D), dtype=torch.int8, device=device, generator=g)
+        vc = torch.randint(-127, 128, (B, Hkv, tmax, D), dtype=torch.int8, device=device, generator=g)
+        ks = torch.rand(B, Hkv, tmax, 1, device=device, generator=g) * 0.02 + 0.001
+        vs = torch.rand(B, Hkv, tmax, 1, device=device, generator=g) * 0.02 + 0.001
+        caches.append((kc, vc, ks, vs))
+    qkv = torch.randn(B, (Hq + 2 * Hkv) * D, device=device, generator=g).to(torch.bfloat16)
+    cos = torch.randn(tmax, D, device=device, generator=g).to(torch.bfloat16)
+    sin = torch.randn(tmax, D, device=device, generator=g).to(torch.bfloat16)
+    out = torch.zeros(B, Hq, D, dtype=torch.bfloat16, device=device)
+    pos = torch.tensor([T], dtype=torch.long, device=device)
+    splits = args.splits or max(1, -(-2 * 148 // (B * Hkv)))
+    nbytes = lib.lq_attn_fused_scratch_bytes(B, Hq, Hkv, D, splits)
+    scratch = torch.zeros(-(-nbytes // 4), dtype=torch.float32, device=device)
+
+    def once():
+        stream = native.stream_ptr(device)
+        for kc, vc, ks, vs in caches:
+            native.call("lq_attn_decode_fused", qkv.data_ptr(), cos.data_ptr(), sin.data_ptr(), kc.data_ptr(),
+                        vc.data_ptr(), ks.data_ptr(), vs.data_ptr(), out.data_ptr(), scratch.data_ptr(), B, Hq,
+                        Hkv, D, tmax, tmax, pos.data_ptr(), 0, 8, D ** -0.5, splits, args.attn_impl, 1, stream)
+
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        for _ in range(args.warmup):
+            once()
+    torch.cuda.current_stream().wait_stream(side)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        once()
+    graph.replay()
+    torch.cuda.synchronize()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for _ in range(args.steps):
+        graph.replay()
+    stop.record()
+    torch.cuda.synchronize()
+    us = start.elapsed_time(stop) * 1e3 / (args.steps * layers)
+    peaks, _ = measured_peaks()
+    print(json.dumps({"workload": "attn_one", "batch": B, "heads": Hq, "kv_heads": Hkv, "head_dim": D,
+                      "context": T, "slices": splits, "impl": args.attn_impl, "caches": layers,
+                      "us_per_launch": round(us, 2), "algorithmic_bytes": per_layer,
+                      "gbs": round(per_layer / us / 1e3, 1),
+                      "frac_of_measured_hbm_peak": round(per_layer / us / 1e3 / peaks["hbm_gbs"], 4),
+                      "device_error": lib.lq_attn_device_error()}), flush=True)
+
+
 # --------------------------------------------------------------------------- prefill GEMM shapes
 def run_gemm_sweep(args, device):
     """BASELINE config 4: W4 group-128 weights at the Llama-3-8B shapes, M in {16, 128, 512, 2048},
@@ -405,6 +474,20 @@ def decode_step_bytes(dec, context):
         total += dec.lm_head.weight.numel() * 2
     kv = 2 * dec.B * dec.Hkv * context * (dec.D + 4)
     return total + kv * len(dec.layers) + dec.B * dec.hidden * 2
+
+
+def decode_margins(dec, ids, n):
+    """Top-2 logit margin (bf16 logits, sequence 0) of the first `n` generated tokens, decoded
+    again from the prompt with eager launches and the logits gathered on every rank."""
+    dec.use_graph, dec.graph, dec.gather_logits = False, None, True
+    dec.prefill(ids)
+    margins = []
+    for i in range(n):
+        top = dec.logits[0].float().topk(2).values
+        margins.append(round(float(top[0] - top[1]), 4))
+        if i + 1 < n:
+            dec.step()
+    return margins
 
 
 def run_decode(args, rank, world, device):
@@ -562,6 +645,11 @@ def run_decode(args, rank, world, device):
         "clocks": clocks.summary(),
     }
     dec.check_device_errors()  # a bounded wait that ran out anywhere in the step voids the run
+    # the same stream once more with the full logits at hand (gathered over the ranks): the
+    # top-2 margin of every step, so that streams decoded on different numbers of GPUs can be
+    # compared -- where they part, the margin says whether a near-tie decided it
+    line["config"]["tokens"] = produced[0].tolist()
+    line["config"]["top2_margin"] = decode_margins(dec, host_ids.to(device), produced.shape[1])
     if rank == 0:
         if world == 1:  # the host cores are busy with the other ranks otherwise
             line["cpu_baseline"] = cpu_reference_decode(spec["shape"], steps=2, warmup=1)
@@ -743,7 +831,13 @@ def main():
     ap.add_argument("--steps", type=int, default=64)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
-    ap.add_argument("--workload", default="decode_8b", choices=["decode_8b", "decode_1b", "gemv_sweep_1b", "gemv_one", "prefill_gemm"])
+    ap.add_argument("--workload", default="decode_8b",
+                    choices=["decode_8b", "decode_1b", "gemv_sweep_1b", "gemv_one", "attn_one", "prefill_gemm"])
+    ap.add_argument("--heads", type=int, default=32, help="attn_one: query heads")
+    ap.add_argument("--kv-heads", type=int, default=8, help="attn_one: KV heads")
+    ap.add_argument("--head-dim", type=int, default=128, help="attn_one: head width")
+    ap.add_argument("--splits", type=int, default=0, help="attn_one: context slices per KV head (0 = the decoder's choice)")
+    ap.add_argument("--attn-impl", type=int, default=0, help="attn_one: 0 library's choice, 1 SIMT, 2 mma, 3 cluster")
     ap.add_argument("--n", type=int, default=28672)
     ap.add_argument("--k", type=int, default=4096)
     ap.add_argument("--bits", type=int, default=4)
@@ -772,6 +866,8 @@ def main():
     try:
         if args.workload == "gemv_one":
             run_gemv_one(args, device)
+        elif args.workload == "attn_one":
+            run_attn_one(args, device)
         elif args.workload == "prefill_gemm":
             run_gemm_sweep(args, device)
         elif args.workload in DECODE:

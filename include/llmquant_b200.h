@@ -320,41 +320,36 @@ int lq_wq_gemm_prefill(const void* x, int ldx, const int8_t* x_codes, const floa
 /* Tensor-parallel coupling of a GEMV (NULL in lq_gemv_args.tp = none). The reference is
  * single-GPU, so this has no counterpart there. Every rank owns one exchange buffer that all
  * ranks of the group have mapped (NVLink peer memory); per slot it holds the fp32 partial
- * outputs of every rank, float part[world][M][N], and a row of uint32 arrival counters, one
- * per source rank. Counters only grow. Plain stores, loads and reductions only.
+ * outputs of every rank, float part[world][M][N]. A 32-bit word of it -- and of the bf16
+ * hidden-state rows named below -- holds the bit pattern 0xFFFFFFFF ("empty": NaNs nothing here
+ * computes) while no value is there, so data that arrives is its own signal: a reader re-reads
+ * a 16-byte piece until none of its words is empty. Plain stores and loads only; no flags,
+ * fences, counters or copies.
  *   mode LQ_TP_PUSH  (row-parallel linear: o_proj, down_proj) -- the epilogue writes this
  *        rank's fp32 partial rows straight into part[rank] of EVERY rank's buffer
- *        (peers[r] + data_offset) and, when a CTA is done, adds its number of 4-row batches
- *        to counter `rank` of every rank (peers[r] + counter_offset). `out`, `residual` must
- *        be NULL / unused; N % 4 == 0.
+ *        (peers[r] + data_offset). `out` and `residual` must be NULL / unused; N % 4 == 0.
  *   mode LQ_TP_SUM   (the linear that consumes the sum: gate|up after o_proj, the next
- *        layer's q|k|v or lm_head after down_proj) -- before anything else the first CTAs of
- *        the grid wait (bounded) until every rank's counter in `counters` has reached
- *        (*step * seq_mul + seq_add) * producer_batches, add the `world` partials of `parts`
- *        in rank order (identical bits on every rank), round to bf16, add `residual` (bf16
- *        [M, K]) and store the new hidden rows to `x` (which this mode WRITES before it reads
- *        them as the GEMV input); they then add one to *ready, and every CTA waits until
- *        *ready has reached (*step * ready_mul + ready_add) * (number of those CTAs,
- *        min(grid, ceil(M * K / (4 * consumer threads)))). K % 4 == 0, ldx == K.
- * `step` is a device uint32 the caller advances once per decode step (lq_next_token_tp does).
- * wait_cycles bounds each wait in SM clocks (0 = about two seconds); when one runs out
- * lq_gemv_device_error() reports 3 (peers) or 4 (ready) and the kernel finishes with the data
- * it has. */
+ *        layer's q|k|v or lm_head after down_proj) -- the first CTAs of the grid read the
+ *        `world` partials of `parts` (waiting, bounded, for words still empty), add them in
+ *        rank order (identical bits on every rank), round to bf16, add `residual` (bf16 [M, K])
+ *        and store the new hidden rows to `x`, which must be EMPTY when the kernel starts;
+ *        every CTA then reads x as the GEMV input, waiting for the pieces it needs. The CTAs
+ *        that sum put "empty" back into the partial words and into the `residual` rows they
+ *        have read -- so the caller alternates two hidden-state buffers between consecutive
+ *        summing GEMVs (this one's `residual` is the next one's `x`) and fills the first `x`
+ *        and the whole exchange buffer with 0xFF bytes before the first step.
+ *        K a multiple of 16 (int8) / 32 (int4) codes, ldx == K, 16-byte aligned pointers.
+ * wait_cycles bounds each wait in SM clocks (0 = about two seconds; rows are given twice
+ * that); when one runs out lq_gemv_device_error() reports 3 (partials) or 4 (rows) and the
+ * kernel finishes with the data it has. */
 enum { LQ_TP_PUSH = 1, LQ_TP_SUM = 2 };
 typedef struct lq_gemv_tp {
   int mode;
   int world, rank;
-  const uint64_t* peers;       /* device array [world]: base address of every rank's buffer */
+  const uint64_t* peers;       /* PUSH: device array [world], base address of every rank's buffer */
   int64_t data_offset;         /* PUSH: byte offset of part[0] of the slot inside a buffer */
-  int64_t counter_offset;      /* PUSH: byte offset of the slot's counter row */
-  const float* parts;          /* SUM: this rank's part[0] of the slot (local address) */
-  const uint32_t* counters;    /* SUM: this rank's counter row of the slot */
-  uint32_t* ready;             /* SUM: local device counter of this consumer kind */
-  const void* residual;        /* SUM: bf16 [M, K] */
-  const uint32_t* step;        /* SUM: device step counter */
-  uint32_t seq_mul, seq_add;   /* SUM: arrivals expected = (*step * seq_mul + seq_add) * producer_batches */
-  uint32_t ready_mul, ready_add;
-  uint32_t producer_batches;   /* SUM: ceil(N_producer / 4) of the linear that pushed */
+  float* parts;                /* SUM: this rank's part[0] of the slot (local address) */
+  void* residual;              /* SUM: bf16 [M, K]; left empty */
   int64_t wait_cycles;
 } lq_gemv_tp;
 

@@ -3,6 +3,8 @@
 // (code width, arithmetic variant) in gemv_stream_b*v*.cu.
 #include "gemv_stream.cuh"
 
+#include <cstdlib>
+
 namespace lq {
 namespace gemv {
 int run_b4v1(GemvParams, const lq_gemv_args&, int, int, cudaStream_t);
@@ -233,14 +235,14 @@ extern "C" int lq_wq_gemv_fused(const lq_gemv_args* a, void* stream) {
     if (tp->mode == LQ_TP_PUSH) {
       LQ_REQUIRE(a->epilogue == 0 && a->residual == nullptr && N % 4 == 0 && M * tp->world <= 32, LQ_ERR_ARG,
                  "a pushing GEMV needs epilogue 0, no residual, N %% 4 == 0 and M * world <= 32");
-      LQ_REQUIRE(tp->peers != nullptr && tp->data_offset % 16 == 0 && tp->counter_offset % 4 == 0, LQ_ERR_ARG,
-                 "peer table missing or exchange offsets misaligned");
+      LQ_REQUIRE(tp->peers != nullptr && tp->data_offset % 16 == 0, LQ_ERR_ARG,
+                 "peer table missing or exchange offset misaligned");
     } else {
-      LQ_REQUIRE(K % 4 == 0 && a->ldx == K, LQ_ERR_ARG, "a summing GEMV needs K %% 4 == 0 and dense rows");
-      LQ_REQUIRE(tp->parts && tp->counters && tp->ready && tp->residual && tp->step, LQ_ERR_ARG,
-                 "null tensor-parallel pointer");
-      LQ_REQUIRE(((uintptr_t)tp->parts % 16) == 0 && ((uintptr_t)tp->residual % 8) == 0 && ((uintptr_t)a->x % 8) == 0,
-                 LQ_ERR_ARG, "partials, residual and x must be 16 / 8 / 8-byte aligned");
+      LQ_REQUIRE(K % (bits == 8 ? 16 : 32) == 0 && a->ldx == K, LQ_ERR_ARG,
+                 "a summing GEMV needs dense rows of a whole number of 16-byte code pieces");
+      LQ_REQUIRE(tp->parts && tp->residual, LQ_ERR_ARG, "null tensor-parallel pointer");
+      LQ_REQUIRE(((uintptr_t)tp->parts % 16) == 0 && ((uintptr_t)tp->residual % 16) == 0 && ((uintptr_t)a->x % 16) == 0,
+                 LQ_ERR_ARG, "partials, residual and x must be 16-byte aligned");
     }
   } else {
     tp = nullptr;
@@ -270,23 +272,26 @@ extern "C" int lq_wq_gemv_fused(const lq_gemv_args* a, void* stream) {
   p.norm_weight = a->norm_weight; p.norm_eps = a->norm_eps; p.pdl = a->pdl;
   p.error_word = error_word();
   p.debug = g_debug_timeline;
-  p.tp_mode = 0; p.tp_world = 0; p.tp_rank = 0; p.tp_peers = nullptr; p.tp_data_off = 0; p.tp_cnt_off = 0;
-  p.tp_parts = nullptr; p.tp_counters = nullptr; p.tp_ready = nullptr; p.tp_residual = nullptr;
-  p.tp_step = nullptr; p.tp_seq_mul = p.tp_seq_add = p.tp_ready_mul = p.tp_ready_add = p.tp_batches = 0;
+  p.tp_mode = 0; p.tp_world = 0; p.tp_rank = 0; p.tp_peers = nullptr; p.tp_data_off = 0;
+  p.tp_parts = nullptr; p.tp_residual = nullptr;
   p.tp_wait = kDefaultWaitCycles;
   if (tp != nullptr) {
     p.tp_mode = tp->mode; p.tp_world = tp->world; p.tp_rank = tp->rank; p.tp_peers = tp->peers;
-    p.tp_data_off = tp->data_offset; p.tp_cnt_off = tp->counter_offset; p.tp_parts = tp->parts;
-    p.tp_counters = tp->counters; p.tp_ready = tp->ready;
-    p.tp_residual = (const __nv_bfloat16*)tp->residual; p.tp_step = tp->step;
-    p.tp_seq_mul = tp->seq_mul; p.tp_seq_add = tp->seq_add; p.tp_ready_mul = tp->ready_mul;
-    p.tp_ready_add = tp->ready_add; p.tp_batches = tp->producer_batches;
+    p.tp_data_off = tp->data_offset; p.tp_parts = tp->parts;
+    p.tp_residual = (__nv_bfloat16*)tp->residual;
     if (tp->wait_cycles > 0) p.tp_wait = tp->wait_cycles;
   }
   LQ_REQUIRE(p.error_word != nullptr, LQ_ERR_LAUNCH, "cannot resolve the device error word");
   p.S = (p.rowbytes + 511) / 512;
   int spw = 1;
   while (spw <= 4 && (p.S + spw - 1) / spw > kMaxWarps) spw *= 2;
+#ifdef LQ_DIAGNOSTICS
+  if (const char* e = getenv("LQ_X_SPW")) {  // diagnostic builds: column chunks per lane
+    const int want = atoi(e);
+    if ((want == 2 || want == 4) && want > spw && M <= (bits == 8 && want == 2 ? 2 : 1) && !(want == 4 && a->epilogue == 1))
+      spw = want;
+  }
+#endif
   LQ_REQUIRE(spw <= 4, LQ_ERR_UNSUPPORTED, "reduction axis too long for the streaming GEMV (Kd=%d)", Kd);
   LQ_REQUIRE(!(spw == 4 && a->epilogue == 1), LQ_ERR_UNSUPPORTED, "reduction axis too long for the fused epilogue");
   p.KW = (p.S + spw - 1) / spw;
@@ -299,6 +304,9 @@ extern "C" int lq_wq_gemv_fused(const lq_gemv_args* a, void* stream) {
   // that the next kernel's CTAs can become resident early (see launch_one).
   const int want_ctas = (kRingWarps + p.KW - 1) / p.KW;
   int stages = (kRingKb * 1024) / (want_ctas * p.stage_bytes);
+#ifdef LQ_DIAGNOSTICS
+  if (const char* e = getenv("LQ_X_STAGES")) stages = atoi(e);
+#endif
   stages = stages < 2 ? 2 : (stages > kMaxStages ? kMaxStages : stages);
   LQ_REQUIRE((size_t)stages * p.stage_bytes <= 200 * 1024, LQ_ERR_UNSUPPORTED,
              "row tile of %d bytes does not fit the shared-memory ring", p.stage_bytes);

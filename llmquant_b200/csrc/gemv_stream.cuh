@@ -41,6 +41,8 @@
 #include "common.cuh"
 #include "peer_sync.cuh"
 
+#include <cstdlib>
+
 namespace lq {
 namespace gemv {
 
@@ -71,13 +73,9 @@ struct GemvParams {
   // tensor-parallel coupling (see lq_gemv_tp): 0 none, LQ_TP_PUSH, LQ_TP_SUM
   int tp_mode, tp_world, tp_rank;
   const uint64_t* tp_peers;
-  int64_t tp_data_off, tp_cnt_off;
-  const float* tp_parts;
-  const uint32_t* tp_counters;
-  uint32_t* tp_ready;
-  const __nv_bfloat16* tp_residual;
-  const uint32_t* tp_step;
-  uint32_t tp_seq_mul, tp_seq_add, tp_ready_mul, tp_ready_add, tp_batches;
+  int64_t tp_data_off;
+  float* tp_parts;
+  __nv_bfloat16* tp_residual;
   long long tp_wait;
 };
 
@@ -98,15 +96,6 @@ __device__ __forceinline__ void tp_push_batch(const GemvParams& p, uint64_t peer
     st_peer_f4(dst, v0, v1, v2, v3);
   }
 }
-// After a CTA's last batch: its stores are made visible before its share of the arrival
-// counter is added on every peer.
-__device__ __forceinline__ void tp_push_done(const GemvParams& p, uint64_t peer_base, int lane, int nb) {
-  __threadfence_system();
-  __syncwarp();
-  if (lane < p.tp_world)
-    red_add_release_sys(reinterpret_cast<uint32_t*>(peer_base + p.tp_cnt_off) + p.tp_rank, (uint32_t)nb);
-}
-
 __device__ __forceinline__ unsigned long long global_ns() {
   unsigned long long t;
   asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
@@ -287,57 +276,99 @@ template <int BITS>
 struct XChunk<BITS, 3> : XPlanes<BITS, 3> {};
 
 // Tensor-parallel input of a GEMV: x = bf16(bf16(sum over ranks of the partials) + residual),
-// built once by the first CTAs of the grid (each a slice) and published to the others through
-// a counter. Called by the consumer warps only (named barrier 2 over KW * 32 threads).
+// built once by the first CTAs of the grid (each a slice of the row) and read by all of them.
+//
+// Both hand-overs -- partials from the other GPUs to the CTAs that sum, summed rows from those
+// CTAs to every CTA of the grid -- carry their own arrival signal: a 32-bit word of the exchange
+// buffer (an fp32 partial) or of a hidden-state row (a pair of bf16) holds the bit pattern
+// kTpEmpty (NaNs no computation here produces) until a value is stored there, and a reader
+// re-reads a 16-byte piece until none of its words is empty. No flag, no fence, no counter,
+// and no second trip over NVLink behind the data. Whoever consumes a buffer for the last time
+// before its next use puts kTpEmpty back: the summing thread into the partial words it has
+// read and into the residual row it has read (the hidden-state buffers alternate, so that row
+// is the next one to be rebuilt). The next write to either is at least one kernel of every
+// rank away.
+constexpr uint32_t kTpEmpty = 0xFFFFFFFFu;
+__device__ __forceinline__ bool tp_piece_missing(const float4& v) {
+  return __float_as_uint(v.x) == kTpEmpty || __float_as_uint(v.y) == kTpEmpty ||
+         __float_as_uint(v.z) == kTpEmpty || __float_as_uint(v.w) == kTpEmpty;
+}
+__device__ __forceinline__ bool tp_piece_missing(const uint4& v) {
+  return v.x == kTpEmpty || v.y == kTpEmpty || v.z == kTpEmpty || v.w == kTpEmpty;
+}
+__device__ __forceinline__ uint4 ld_volatile_u4(const void* p) {
+  uint4 v;
+  asm volatile("ld.volatile.global.v4.u32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(p)
+               : "memory");
+  return v;
+}
+// 16 bytes of a hidden-state row that other CTAs of this kernel are still writing.
+__device__ __forceinline__ uint4 tp_wait_row_piece(const GemvParams& p, const void* src) {
+  uint4 v = ld_volatile_u4(src);
+  if (tp_piece_missing(v)) {
+    const long long t0 = clock64();
+    do {
+      v = ld_volatile_u4(src);
+      if (clock64() - t0 > 2 * p.tp_wait) {  // (twice the partials' limit: their error is the one recorded)
+        atomicCAS(p.error_word, 0, 4);
+        break;
+      }
+    } while (tp_piece_missing(v));
+  }
+  return v;
+}
 __device__ __forceinline__ void tp_sum_prologue(const GemvParams& p, int KW, int warp, int lane) {
   const int T = KW * 32, tid = warp * 32 + lane;
-  const uint32_t step = *reinterpret_cast<const volatile uint32_t*>(p.tp_step);
   const int total4 = p.M * p.K / 4;
   const int R = min((int)gridDim.x, (total4 + T - 1) / T);
-  if ((int)blockIdx.x < R) {
-    if (tid < p.tp_world) {
-      const uint32_t want = (step * p.tp_seq_mul + p.tp_seq_add) * p.tp_batches;
-      if (!wait_counter<true>(p.tp_counters + tid, want, p.tp_wait)) atomicExch(p.error_word, 3);
-    }
-    asm volatile("bar.sync 2, %0;" ::"r"(T) : "memory");
-    __nv_bfloat16* hx = const_cast<__nv_bfloat16*>(p.x);
-    const int64_t stride = (int64_t)p.M * p.K;  // floats between two ranks' partials
-    for (int i = blockIdx.x * T + tid; i < total4; i += R * T) {
-      float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-      for (int r0 = 0; r0 < p.tp_world; r0 += 4) {  // four loads in flight, summed in rank order
-        float4 v[4];
+  if ((int)blockIdx.x >= R) return;
+  __nv_bfloat16* hx = const_cast<__nv_bfloat16*>(p.x);
+  const int64_t stride = (int64_t)p.M * p.K;  // floats between two ranks' partials
+  const float empty = __uint_as_float(kTpEmpty);
+  bool late = false;
+  for (int i = blockIdx.x * T + tid; i < total4; i += R * T) {
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int r0 = 0; r0 < p.tp_world; r0 += 4) {  // four loads in flight, summed in rank order
+      float4 v[4];
 #pragma unroll
-        for (int j = 0; j < 4; ++j)
-          if (r0 + j < p.tp_world)
-            v[j] = ld_peer_f4(reinterpret_cast<const float4*>(p.tp_parts + (r0 + j) * stride) + i);
+      for (int j = 0; j < 4; ++j)
+        if (r0 + j < p.tp_world)
+          v[j] = ld_peer_f4(reinterpret_cast<const float4*>(p.tp_parts + (r0 + j) * stride) + i);
 #pragma unroll
-        for (int j = 0; j < 4; ++j)
-          if (r0 + j < p.tp_world) { acc.x += v[j].x; acc.y += v[j].y; acc.z += v[j].z; acc.w += v[j].w; }
+      for (int j = 0; j < 4; ++j) {
+        if (r0 + j < p.tp_world) {
+          float4* src = reinterpret_cast<float4*>(p.tp_parts + (r0 + j) * stride) + i;
+          if (tp_piece_missing(v[j])) {  // not there yet: wait for it (bounded)
+            const long long t0 = clock64();
+            do {
+              v[j] = ld_peer_f4(src);
+              if (clock64() - t0 > p.tp_wait) { late = true; break; }
+            } while (tp_piece_missing(v[j]));
+          }
+          acc.x += v[j].x; acc.y += v[j].y; acc.z += v[j].z; acc.w += v[j].w;
+          st_peer_f4(reinterpret_cast<float*>(src), empty, empty, empty, empty);
+        }
       }
-      const uint2 rr = __ldcg(reinterpret_cast<const uint2*>(p.tp_residual) + i);
-      const float r4[4] = {__uint_as_float(rr.x << 16), __uint_as_float(rr.x & 0xFFFF0000u),
-                           __uint_as_float(rr.y << 16), __uint_as_float(rr.y & 0xFFFF0000u)};
-      const float a4[4] = {acc.x, acc.y, acc.z, acc.w};
-      unsigned short o4[4];
-#pragma unroll
-      for (int j = 0; j < 4; ++j)  // round the layer output, add the residual stream, round
-        o4[j] = __bfloat16_as_ushort(__float2bfloat16_rn(__bfloat162float(__float2bfloat16_rn(a4[j])) + r4[j]));
-      uint2 packed;
-      packed.x = (unsigned)o4[0] | ((unsigned)o4[1] << 16);
-      packed.y = (unsigned)o4[2] | ((unsigned)o4[3] << 16);
-      reinterpret_cast<uint2*>(hx)[i] = packed;
     }
-    __threadfence();
-    asm volatile("bar.sync 2, %0;" ::"r"(T) : "memory");
-    if (tid == 0) red_add_release_gpu(p.tp_ready, 1u);
+    uint2* res = reinterpret_cast<uint2*>(p.tp_residual) + i;
+    const uint2 rr = __ldcg(res);
+    const float r4[4] = {__uint_as_float(rr.x << 16), __uint_as_float(rr.x & 0xFFFF0000u),
+                         __uint_as_float(rr.y << 16), __uint_as_float(rr.y & 0xFFFF0000u)};
+    const float a4[4] = {acc.x, acc.y, acc.z, acc.w};
+    unsigned short o4[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j)  // round the layer output, add the residual stream, round
+      o4[j] = __bfloat16_as_ushort(__float2bfloat16_rn(__bfloat162float(__float2bfloat16_rn(a4[j])) + r4[j]));
+    uint2 packed;
+    packed.x = (unsigned)o4[0] | ((unsigned)o4[1] << 16);
+    packed.y = (unsigned)o4[2] | ((unsigned)o4[3] << 16);
+    asm volatile("st.volatile.global.v2.u32 [%0], {%1,%2};" ::"l"(reinterpret_cast<uint2*>(hx) + i), "r"(packed.x),
+                 "r"(packed.y) : "memory");
+    *res = make_uint2(kTpEmpty, kTpEmpty);  // this row is the next one to be rebuilt
   }
-  if (tid == 0) {
-    const uint32_t want = (step * p.tp_ready_mul + p.tp_ready_add) * (uint32_t)R;
-    // twice the peers' limit: when the partials never arrive the first CTAs give up first, publish
-    // what they have, and only their error is recorded
-    if (!wait_counter<false>(p.tp_ready, want, 2 * p.tp_wait)) atomicExch(p.error_word, 4);
-  }
-  asm volatile("bar.sync 2, %0;" ::"r"(T) : "memory");
+  if (late) atomicCAS(p.error_word, 0, 3);
 }
 
 // ------------------------------------------------------------------ the kernel
@@ -484,7 +515,6 @@ gemv_stream_kernel(const GemvParams p) {
         }
       }
     }
-    if constexpr (push) tp_push_done(p, peer_base, lane, nb);
     return;
   }
 
@@ -558,9 +588,10 @@ gemv_stream_kernel(const GemvParams p) {
       if (fast[j] && m < p.M) {
 #pragma unroll
         for (int v = 0; v < PW / 4; ++v) {
-          // rows another CTA of this kernel has just written must not come from the read-only path
-          const uint4 raw = tp_sum ? __ldcg(reinterpret_cast<const uint4*>(xr) + v)
-                                   : __ldg(reinterpret_cast<const uint4*>(xr) + v);
+          // rows other CTAs of this kernel are writing: wait for each piece to be there
+          uint4 raw;
+          if constexpr (tp_sum) raw = tp_wait_row_piece(p, reinterpret_cast<const uint4*>(xr) + v);
+          else raw = __ldg(reinterpret_cast<const uint4*>(xr) + v);
           xraw[m][j][4 * v] = raw.x; xraw[m][j][4 * v + 1] = raw.y;
           xraw[m][j][4 * v + 2] = raw.z; xraw[m][j][4 * v + 3] = raw.w;
         }
@@ -759,9 +790,6 @@ gemv_stream_kernel(const GemvParams p) {
       }
     }
   }
-  if constexpr (EPI == 0 && TP == LQ_TP_PUSH) {
-    if (KW == 1) tp_push_done(p, p.tp_peers[lane % p.tp_world], lane, nb);
-  }
   LQ_STAMP(5);
 }
 
@@ -792,6 +820,12 @@ int launch_tp(const GemvParams& p, int threads, cudaStream_t s) {
   int per_sm = occ;
   const int by_smem = (int)(((size_t)kRingKb * 1024) / (smem > 0 ? smem : 1));
   if (by_smem >= 1 && per_sm > by_smem) per_sm = by_smem;
+#ifdef LQ_DIAGNOSTICS
+  if (const char* e = getenv("LQ_X_PERSM")) {  // diagnostic builds: resident CTAs per SM
+    const int want = atoi(e);
+    if (want >= 1 && want <= occ) per_sm = want;
+  }
+#endif
   const int cap = sm_count() * per_sm;
   int grid = p.nbatch < cap ? p.nbatch : cap;
   if (grid < 1) grid = 1;

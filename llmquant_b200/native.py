@@ -7,13 +7,15 @@ from the library is raised as a RuntimeError carrying the library's message.
 
 import ctypes
 import functools
+import os
 import pathlib
 import re
 
 import torch
 
 PKG = pathlib.Path(__file__).resolve().parent
-LIB_PATH = PKG / "libllmquant_b200.so"
+# LLMQUANT_B200_LIBRARY points at another build of the same sources (a diagnostic build, say)
+LIB_PATH = pathlib.Path(os.environ.get("LLMQUANT_B200_LIBRARY") or PKG / "libllmquant_b200.so")
 HEADER = PKG.parent / "include" / "llmquant_b200.h"
 
 LQ_F32, LQ_F16, LQ_BF16 = 0, 1, 2
@@ -90,12 +92,8 @@ class GemvTp(ctypes.Structure):
     """Mirror of `lq_gemv_tp` (include/llmquant_b200.h)."""
 
     _fields_ = [
-        ("mode", _I), ("world", _I), ("rank", _I), ("peers", _P),
-        ("data_offset", _L), ("counter_offset", _L), ("parts", _P), ("counters", _P),
-        ("ready", _P), ("residual", _P), ("step", _P),
-        ("seq_mul", ctypes.c_uint32), ("seq_add", ctypes.c_uint32),
-        ("ready_mul", ctypes.c_uint32), ("ready_add", ctypes.c_uint32),
-        ("producer_batches", ctypes.c_uint32), ("wait_cycles", _L),
+        ("mode", _I), ("world", _I), ("rank", _I), ("peers", _P), ("data_offset", _L),
+        ("parts", _P), ("residual", _P), ("wait_cycles", _L),
     ]
 
 

@@ -57,8 +57,9 @@ def enable_fused_kv_attention(model):
     with `make_cache_factory(bits, model=model)` is read as integers."""
     from transformers import AttentionInterface, AttentionMaskInterface
     from transformers.masking_utils import sdpa_mask
+    from transformers.modeling_utils import ALL_ATTENTION_FUNCTIONS
 
-    if ATTENTION_NAME not in AttentionInterface.valid_keys():
+    if ATTENTION_NAME not in ALL_ATTENTION_FUNCTIONS.valid_keys():
         AttentionInterface.register(ATTENTION_NAME, int_kv_attention)
         AttentionMaskInterface.register(ATTENTION_NAME, sdpa_mask)
     model.set_attn_implementation(ATTENTION_NAME)

@@ -235,11 +235,10 @@ class FusedLlamaDecoder:
                     self.B, self.hidden, self.embed.shape[0], pdl, stream)
         yield
         pos_ptr = self.pos.data_ptr()
-        batches = self.hidden // 4  # 4-row batches of a row-parallel linear's [hidden] output
         for l, (spec, cache) in enumerate(zip(self.layers, self.cache.layers)):
             tp = None
             if l > 0:  # hidden = down_proj(l - 1) summed over the ranks + its residual
-                tp = ex.sum_args(1, 1, (L, l), (L - 1, l), h1, batches)
+                tp = ex.sum_args(1, h1)
             spec["qkv"].gemv(h0, norm_weight=spec["ln1"], norm_eps=self.eps, pdl=self.pdl, out=self.qkv, tp=tp)
             yield
             native.call("lq_attn_decode_fused", self.qkv.data_ptr(), self.cos.data_ptr(),
@@ -251,13 +250,13 @@ class FusedLlamaDecoder:
             yield
             spec["o"].gemv(self.attn, out_dtype=torch.float32, pdl=self.pdl, tp=ex.push_args(0))
             yield
-            tp = ex.sum_args(0, 0, (L, l + 1), (L, l + 1), h0, batches)
+            tp = ex.sum_args(0, h0)
             spec["gate_up"].gemv(h1, norm_weight=spec["ln2"], norm_eps=self.eps, epilogue=1,
                                  pdl=self.pdl, out=self.act, tp=tp)
             yield
             spec["down"].gemv(self.act, out_dtype=torch.float32, pdl=self.pdl, tp=ex.push_args(1))
             yield
-        tp = ex.sum_args(1, 2, (L, L), (1, 1), h1, batches)
+        tp = ex.sum_args(1, h1)
         self.lm_head.gemv(h0, norm_weight=self.final_norm, norm_eps=self.eps, pdl=self.pdl,
                           out=self.local_logits, tp=tp)
         yield
@@ -368,12 +367,20 @@ class FusedLlamaDecoder:
         out = self.model(input_ids, past_key_values=self.cache, use_cache=True, logits_to_keep=1)
         self.logits.copy_(out.logits[:, -1])  # the prompt's last position, for callers that inspect it
         first = out.logits[:, -1].argmax(-1)
+        self._begin_sequence()
         self.tokens.copy_(first)
         self.pos.fill_(prompt)
         self.history.zero_()
         self.history[:, :prompt] = input_ids
         self.history[:, prompt] = first
         return first
+
+    def _begin_sequence(self):
+        """State the folded tensor-parallel step expects at its first launch: the second
+        hidden-state buffer empty (its rows are rebuilt by the first summing GEMV and read by
+        CTAs that wait for them to appear)."""
+        if self.exchange is not None:
+            self.exchange.mark_empty(self.h[1])
 
     @torch.no_grad()
     def start_empty(self, first_tokens):
@@ -386,6 +393,7 @@ class FusedLlamaDecoder:
             if not layer.is_initialized:
                 layer.lazy_initialization(dummy, dummy)
             layer.reset()
+        self._begin_sequence()
         self.tokens.copy_(first_tokens.to(self.device))
         self.pos.zero_()
         self.history.zero_()

@@ -201,14 +201,13 @@ class PeerExchange:
 
     One buffer per rank, mapped by all ranks (symmetric memory over NVLink):
 
-        float    part[2 slots][world][rows][width]    partial outputs, by source rank
-        uint32   arrived[2 slots][16]                 4-row batches received, by source rank
+        float    part[2 slots][world][rows][width]    partial outputs, by source rank; a word
+                                                      holds 0xFFFFFFFF while no value is there
         uint64   records[2 banks][16][max_batch]      (token index, logit, step tag) per rank
 
-    plus, local to the rank, the step counter and three `ready` counters (one per kind of
-    consuming GEMV). Slot 0 carries o_proj's output, slot 1 down_proj's."""
-
-    COUNTER_ROW = 64  # bytes per slot of arrival counters (16 ranks)
+    plus, local to the rank, the step counter that tags the records. Slot 0 carries o_proj's
+    output, slot 1 down_proj's. The hidden-state rows the consuming GEMVs rebuild follow the
+    same convention (`empty_rows`): empty until written, emptied again by their last reader."""
 
     def __init__(self, rank: int, world: int, rows: int, width: int, device, buffer, peer_ptrs,
                  max_batch: int = 8):
@@ -220,8 +219,7 @@ class PeerExchange:
         self.max_batch = max_batch
         self.buffer = buffer
         self.slot_bytes = world * rows * width * 4
-        self.counter_off = 2 * self.slot_bytes
-        self.record_off = self.counter_off + 2 * self.COUNTER_ROW
+        self.record_off = 2 * self.slot_bytes
         if buffer.numel() * buffer.element_size() < self.bytes_needed(world, rows, width, max_batch):
             raise ValueError("exchange buffer too small")
         if len(peer_ptrs) != world:
@@ -229,12 +227,19 @@ class PeerExchange:
         self.peers = torch.tensor([int(p) for p in peer_ptrs], dtype=torch.int64, device=device)
         self.base = int(peer_ptrs[rank])
         self.step = torch.zeros(1, dtype=torch.int32, device=device)
-        self.ready = torch.zeros(4, dtype=torch.int32, device=device)
         self.wait_cycles = 0  # 0 = the library's default bound (about two seconds)
 
     @staticmethod
     def bytes_needed(world, rows, width, max_batch=8):
-        return 2 * world * rows * width * 4 + 2 * PeerExchange.COUNTER_ROW + 2 * 16 * max_batch * 8
+        return 2 * world * rows * width * 4 + 2 * 16 * max_batch * 8
+
+    @staticmethod
+    def clear(buffer, world, rows, width):
+        """The state before the first step: every partial word empty, every record zero."""
+        words = buffer.view(torch.int32)
+        n = 2 * world * rows * width
+        words[:n] = -1
+        words[n:] = 0
 
     @classmethod
     def over_symmetric_memory(cls, ctx: TPContext, rows: int, width: int, device, max_batch: int = 8):
@@ -244,14 +249,14 @@ class PeerExchange:
 
         nbytes = cls.bytes_needed(ctx.world, rows, width, max_batch)
         buffer = symm.empty(-(-nbytes // 4), dtype=torch.float32, device=device)
-        buffer.zero_()
+        cls.clear(buffer, ctx.world, rows, width)
         group = ctx.group if ctx.group is not None else dist.group.WORLD
         handle = symm.rendezvous(buffer, group)
         ptrs = [int(p) for p in handle.buffer_ptrs]
         self = cls(ctx.rank, ctx.world, rows, width, device, buffer, ptrs, max_batch)
         self.handle = handle
         torch.cuda.synchronize(device)
-        dist.barrier(group=ctx.group)  # every buffer is zero before anyone writes into it
+        dist.barrier(group=ctx.group)  # every buffer is cleared before anyone writes into it
         return self
 
     @classmethod
@@ -261,6 +266,8 @@ class PeerExchange:
         them). For single-GPU tests of the multi-rank arithmetic."""
         nbytes = cls.bytes_needed(world, rows, width, max_batch)
         buffers = [torch.zeros(-(-nbytes // 4), dtype=torch.float32, device=device) for _ in range(world)]
+        for b in buffers:
+            cls.clear(b, world, rows, width)
         ptrs = [b.data_ptr() for b in buffers]
         return [cls(r, world, rows, width, device, buffers[r], ptrs, max_batch) for r in range(world)]
 
@@ -269,21 +276,23 @@ class PeerExchange:
         from llmquant_b200 import native
 
         return native.GemvTp(mode=native.TP_PUSH, world=self.world, rank=self.rank,
-                             peers=self.peers.data_ptr(), data_offset=slot * self.slot_bytes,
-                             counter_offset=self.counter_off + slot * self.COUNTER_ROW)
+                             peers=self.peers.data_ptr(), data_offset=slot * self.slot_bytes)
 
-    def sum_args(self, slot: int, kind: int, seq, ready, residual, producer_batches: int):
-        """`seq` = (pushes into the slot per step, index of the awaited one, 1-based),
-        `ready` = the same for the launches of this consumer kind."""
+    def sum_args(self, slot: int, residual):
         from llmquant_b200 import native
 
         return native.GemvTp(mode=native.TP_SUM, world=self.world, rank=self.rank,
-                             parts=self.base + slot * self.slot_bytes,
-                             counters=self.base + self.counter_off + slot * self.COUNTER_ROW,
-                             ready=self.ready.data_ptr() + 4 * kind, residual=residual.data_ptr(),
-                             step=self.step.data_ptr(), seq_mul=seq[0], seq_add=seq[1],
-                             ready_mul=ready[0], ready_add=ready[1],
-                             producer_batches=producer_batches, wait_cycles=self.wait_cycles)
+                             parts=self.base + slot * self.slot_bytes, residual=residual.data_ptr(),
+                             wait_cycles=self.wait_cycles)
+
+    @staticmethod
+    def empty_rows(rows: int, width: int, device):
+        """A bf16 [rows, width] hidden-state buffer in the "nothing here yet" state."""
+        return torch.full((rows, width), -1, dtype=torch.int16, device=device).view(torch.bfloat16)
+
+    @staticmethod
+    def mark_empty(tensor):
+        tensor.view(torch.int16).fill_(-1)
 
     def next_token(self, local_logits, tokens, pos, history, ticket, pdl: bool = True):
         from llmquant_b200 import native

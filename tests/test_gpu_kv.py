@@ -210,5 +210,7 @@ def test_generate_reads_the_integer_cache_without_dequantizing_it(kw):
             lb = model(out[:, i:i + 1], past_key_values=b, use_cache=True).logits[:, -1]
             assert rel_l2(la.float().cpu().numpy(), lb.float().cpu().numpy()) <= 1e-2, i
     assert b.layers[0].dequant_calls == new and b.layers[0].fused_reads == 0
-    for la_, lb_ in zip(a.layers, b.layers):  # both routes store the same integers
-        assert torch.equal(la_.k_codes[:, :, : la_.length], lb_.k_codes[:, :, : lb_.length])
+    # the first layer's keys depend on the embeddings only: both routes store the same integers
+    # there (deeper layers see hidden states that differ by the two routes' rounding)
+    assert torch.equal(a.layers[0].k_codes[:, :, : a.layers[0].length], b.layers[0].k_codes[:, :, : b.layers[0].length])
+    assert a.layers[-1].length == b.layers[-1].length == 40 + new - 1

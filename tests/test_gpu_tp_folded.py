@@ -4,7 +4,8 @@ The ranks of a group live on one device and their launches are issued in lock st
 stream (every pushing launch of all ranks before the launch that consumes the sums), so no
 kernel ever waits for a kernel that has not been launched yet: the exchange buffers are plain
 device memory mapped to themselves. What is checked is the multi-rank arithmetic and the
-counter protocol; the same kernels over NVLink peer memory are checked by tp_check.py on a
+exchange protocol (partials that signal their own arrival, slots left empty for their next
+use, the ready counters); the same kernels over NVLink peer memory are checked by tp_check.py on a
 multi-GPU box.
 
 Also here: every bounded device wait of the tensor-parallel kernels is made to run out (a flag
@@ -68,17 +69,19 @@ def test_pushed_partials_and_summing_consumer(world, M, bits, k_shard):
             for ex in exs:
                 held = ex.buffer[: world * M * hidden].view(world, M, hidden)
                 assert torch.equal(held, torch.stack(parts)), (step, use, ex.rank)
-                h = torch.zeros(M, hidden, dtype=torch.bfloat16, device="cuda")
+                h = PeerExchange.empty_rows(M, hidden, "cuda")
+                residual_in = residual.clone()  # the consumer empties the residual rows it reads
                 y = consumer.gemv(h, norm_weight=gamma, norm_eps=1e-5, pdl=True,
-                                  tp=ex.sum_args(0, 0, (uses, use + 1), (uses, use + 1), residual, hidden // 4))
+                                  tp=ex.sum_args(0, residual_in))
                 assert torch.equal(h, want_h), (step, use, ex.rank)
+                assert bool((residual_in.view(torch.int16) == -1).all())
                 assert torch.equal(y, want_y), (step, use, ex.rank)
+                # the consumer left the slot empty for its next use
+                assert bool((ex.buffer[: world * M * hidden].view(torch.int32) == -1).all())
             if step == 0 and use == 0:  # the unsplit linear of the oracle
                 q, scale = oracle.quantize_weight(w_row.float().numpy(), bits, 128)
                 ref = oracle.real_linear(x.float().cpu().numpy(), q, scale, bits, 128)
                 assert rel_l2(total.cpu().numpy(), ref) <= 1e-4
-        for ex in exs:
-            ex.step.add_(1)
     assert lib.lq_gemv_device_error() == 0
 
 
@@ -90,8 +93,8 @@ def test_summing_consumer_gives_up_when_the_partials_never_arrive():
     lib = native.library()
     assert lib.lq_gemv_device_error() == 0
     residual = torch.zeros(M, hidden, dtype=torch.bfloat16, device="cuda")
-    h = torch.zeros(M, hidden, dtype=torch.bfloat16, device="cuda")
-    consumer.gemv(h, tp=ex.sum_args(0, 0, (1, 1), (1, 1), residual, hidden // 4))  # nothing was pushed
+    h = PeerExchange.empty_rows(M, hidden, "cuda")
+    consumer.gemv(h, tp=ex.sum_args(0, residual))  # nothing was pushed
     torch.cuda.synchronize()
     assert lib.lq_gemv_device_error() == 3
     # the context is intact: a complete exchange on fresh buffers works
@@ -99,7 +102,9 @@ def test_summing_consumer_gives_up_when_the_partials_never_arrive():
     producer = _module(seeded((hidden, 256), 2, 0.02, torch.bfloat16), 8)
     x = seeded((M, 256), 3).bfloat16().cuda()
     producer.gemv(x, out_dtype=torch.float32, tp=ex2.push_args(0))
-    y = consumer.gemv(h, tp=ex2.sum_args(0, 0, (1, 1), (1, 1), residual, hidden // 4))
+    PeerExchange.mark_empty(h)
+    residual.zero_()
+    y = consumer.gemv(h, tp=ex2.sum_args(0, residual))
     want_h = producer.gemv(x, out_dtype=torch.float32).bfloat16()
     assert torch.equal(h, want_h) and torch.equal(y, consumer.gemv(want_h))
     assert lib.lq_gemv_device_error() == 0
@@ -180,7 +185,6 @@ def _lockstep(decs):
         d.logits.copy_(full)
         d.tokens.copy_(tok)
         d.pos.add_(1)
-        d.exchange.step.add_(1)
     return full
 
 
@@ -224,8 +228,9 @@ def test_folded_decode_of_a_tiny_llama_against_one_gpu_and_the_reference(golden,
         if s >= n_prompt - 1:
             got.append(logits.float().cpu().numpy())
     assert worst <= 1e-2, worst
-    for d in decs[1:]:  # every rank holds the same hidden state bit for bit
-        assert torch.equal(d.h[0], decs[0].h[0]) and torch.equal(d.h[1], decs[0].h[1])
+    for d in decs[1:]:  # every rank holds the same hidden state bit for bit (the other buffer is left empty)
+        assert torch.equal(d.h[0].view(torch.int16), decs[0].h[0].view(torch.int16))
+        assert bool((d.h[1].view(torch.int16) == -1).all())
     if compare_reference:
         got = np.stack(got, 1)
         assert rel_l2(got, want_logits) <= 2e-2

@@ -25,22 +25,23 @@ def _exchange(world=4, rows=2, width=1024, rank=1):
 def test_exchange_layout_and_argument_blocks():
     ex, ptrs = _exchange()
     slot = 4 * 2 * 1024 * 4
-    assert ex.slot_bytes == slot and ex.counter_off == 2 * slot and ex.record_off == 2 * slot + 128
+    assert ex.slot_bytes == slot and ex.record_off == 2 * slot
     assert PeerExchange.bytes_needed(4, 2, 1024) == ex.record_off + 2 * 16 * 8 * 8
+    PeerExchange.clear(ex.buffer, 4, 2, 1024)
+    words = ex.buffer.view(torch.int32)
+    assert bool((words[: 2 * slot // 4] == -1).all()) and bool((words[2 * slot // 4:] == 0).all())
     push = ex.push_args(1)
     assert (push.mode, push.world, push.rank) == (native.TP_PUSH, 4, 1)
-    assert push.data_offset == slot and push.counter_offset == 2 * slot + 64
-    assert push.peers == ex.peers.data_ptr()
+    assert push.data_offset == slot and push.peers == ex.peers.data_ptr()
     residual = torch.zeros(2, 1024, dtype=torch.bfloat16)
     ex.wait_cycles = 12345
-    summ = ex.sum_args(1, 2, (32, 32), (1, 1), residual, 1024)
+    summ = ex.sum_args(1, residual)
     assert summ.mode == native.TP_SUM and summ.parts == ptrs[1] + slot
-    assert summ.counters == ptrs[1] + 2 * slot + 64 and summ.ready == ex.ready.data_ptr() + 8
-    assert (summ.seq_mul, summ.seq_add, summ.ready_mul, summ.ready_add) == (32, 32, 1, 1)
-    assert summ.producer_batches == 1024 and summ.wait_cycles == 12345
-    assert summ.residual == residual.data_ptr() and summ.step == ex.step.data_ptr()
-    # the C struct: three ints, padding, then pointers and 64-bit offsets
-    assert native.GemvTp.peers.offset == 16 and ctypes.sizeof(native.GemvTp) == 112
+    assert summ.wait_cycles == 12345 and summ.residual == residual.data_ptr()
+    rows = PeerExchange.empty_rows(2, 8, "cpu")
+    assert rows.dtype == torch.bfloat16 and bool((rows.view(torch.int16) == -1).all())
+    # the C struct: three ints, padding, then pointers and 64-bit fields
+    assert native.GemvTp.peers.offset == 16 and ctypes.sizeof(native.GemvTp) == 56
     assert native.GemvArgs.tp.offset == ctypes.sizeof(native.GemvArgs) - 8
 
 
