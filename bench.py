@@ -53,6 +53,11 @@ SWEEP_1B = [
 ]
 
 
+# The same projections as a decode step launches them: q|k|v and gate|up as one weight each. Timed
+# and reported next to the sweep (not part of its aggregate: BASELINE config 2 names the single shapes).
+SWEEP_1B_FUSED = [("qkv.int8", 3072, 2048, 8), ("gate_up.int4", 16384, 2048, 4), ("gate_up.int8", 16384, 2048, 8)]
+
+
 def algorithmic_bytes(n, k, bits, m=1, out_bytes=2):
     """Packed codes + one fp32 scale per (row, group of 128) + bf16 x + the output."""
     return n * k * bits // 8 + n * (-(-k // 128)) * 4 + m * k * 2 + m * n * out_bytes
@@ -127,13 +132,13 @@ class ClockSampler:
 
 
 # --------------------------------------------------------------------------- GPU arm
-def build_pool(device):
+def build_pool(device, shapes=None):
     """For every shape: enough distinct quantized copies to exceed twice the L2 size."""
     from llmquant_b200.core import QuantizationArgs, QuantizationScheme
     from llmquant_b200.quantizers import KernelQuantLinear
 
     pool = []
-    for name, n, k, bits in SWEEP_1B:
+    for name, n, k, bits in (shapes or SWEEP_1B):
         scheme = QuantizationScheme(
             weights=QuantizationArgs(num_bits=bits, strategy="group", group_size=128),
             input_activations=None)
@@ -271,15 +276,35 @@ def run_gpu(args, rank, world, device):
                      "frac_of_nominal_8TBs": round(achieved / 8000.0, 4), "peak_kind": peak_kind,
                      "traffic": None, "kernel": "gemv_stream_kernel"},
         "shapes": {e["name"]: {"us_per_launch": round(ms * 1e3 / len(e["weights"]), 3),
-                               "gbs": round(e["bytes"] * len(e["weights"]) / (ms * 1e-3) / 1e9, 1)}
+                               "gbs": round(e["bytes"] * len(e["weights"]) / (ms * 1e-3) / 1e9, 1),
+                               "frac": round(e["bytes"] * len(e["weights"]) / (ms * 1e-3) / 1e9 / peaks["hbm_gbs"], 4)}
                    for e, ms in zip(pool, shape_ms)},
         "e2e": {"value": round(world * e2e_bytes / e2e_s / 1e9, 2), "unit": "GB/s",
                 "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
         "gpu_launches": launches_per_step * args.steps,
         "clocks": clocks.summary(),
     }
+    # the fused projections of a decode step, the same way (after the timed region)
+    del pool
+    torch.cuda.empty_cache()
+    fused = build_pool(device, SWEEP_1B_FUSED)
+    line["fused_shapes"] = {}
+    for entry in fused:
+        capture_shape_graph(entry)
+        for _ in range(3):
+            entry["graph"].replay()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(args.steps):
+            entry["graph"].replay()
+        e1.record()
+        torch.cuda.synchronize()
+        us = e0.elapsed_time(e1) * 1e3 / (args.steps * len(entry["weights"]))
+        line["fused_shapes"][entry["name"]] = {"us_per_launch": round(us, 3), "gbs": round(entry["bytes"] / us / 1e3, 1),
+                                               "frac": round(entry["bytes"] / us / 1e3 / peaks["hbm_gbs"], 4)}
     if rank == 0:
-        if world == 1:
+        if world == 1 and not args.skip_cpu_baseline:
             line["cpu_baseline"] = cpu_baseline(sample_seconds=12.0)
         print(json.dumps(line), flush=True)
 
@@ -490,6 +515,76 @@ def decode_margins(dec, ids, n):
     return margins
 
 
+def decode_at_batch(model, batch, prompt, host_ids, device, steps=8, warmup=3):
+    """Greedy decode of `batch` sequences (the first sequence's prompt, rotated, for each) with
+    the fused decoder: prefill, graph capture, `warmup` steps, `steps` timed steps."""
+    from llmquant_b200.runtime.decoder import FusedLlamaDecoder
+
+    dec = FusedLlamaDecoder(model, batch, prompt + warmup + steps + 16, kv_bits=8)
+    ids = torch.stack([torch.roll(host_ids[0], shifts=i) for i in range(batch)]).to(device)
+    # the prompt goes through the transformers modules: in chunks of sequences to bound memory
+    dec.prefill(ids) if batch <= 8 else prefill_in_chunks(dec, ids, 8)
+    dec.capture()
+    for _ in range(warmup):
+        dec.step()
+    torch.cuda.synchronize()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(steps):
+        dec.step()
+    b.record()
+    torch.cuda.synchronize()
+    ms = a.elapsed_time(b) / steps
+    context = prompt + warmup + steps // 2
+    out = {"tok_per_s": round(batch / (ms * 1e-3), 1), "ms_per_step": round(ms, 3), "steps": steps,
+           "context": context, "gemv_launches_per_linear": -(-batch // 8),
+           "kv_bytes_per_step": 2 * batch * dec.Hkv * context * (dec.D + 4) * len(dec.layers)}
+    dec.check_device_errors()
+    del dec
+    torch.cuda.empty_cache()
+    return out
+
+
+def prefill_in_chunks(dec, ids, chunk):
+    """Prefill a large batch a few sequences at a time: each chunk runs through the model with a
+    cache of its own, whose integer rows are then copied into the decoder's cache."""
+    from llmquant_b200.quantizers import KernelQuantCache
+
+    batch, prompt = ids.shape
+    dec._begin_sequence()
+    firsts = []
+    full = None
+    for b0 in range(0, batch, chunk):
+        part = KernelQuantCache(dec.kv_bits, max_cache_len=dec.max_len)
+        with torch.no_grad():
+            out = dec.model(ids[b0:b0 + chunk], past_key_values=part, use_cache=True, logits_to_keep=1)
+        firsts.append(out.logits[:, -1].argmax(-1))
+        if full is None:
+            full = [dict(k=torch.zeros(batch, *l.k_codes.shape[1:], dtype=torch.int8, device=ids.device),
+                         v=torch.zeros(batch, *l.v_codes.shape[1:], dtype=torch.int8, device=ids.device),
+                         ks=torch.zeros(batch, *l.k_scales.shape[1:], device=ids.device),
+                         vs=torch.zeros(batch, *l.v_scales.shape[1:], device=ids.device)) for l in part.layers]
+        for dst, l in zip(full, part.layers):
+            dst["k"][b0:b0 + chunk], dst["v"][b0:b0 + chunk] = l.k_codes, l.v_codes
+            dst["ks"][b0:b0 + chunk], dst["vs"][b0:b0 + chunk] = l.k_scales, l.v_scales
+        del part, out
+    # hand the assembled rows to the decoder's cache layers
+    proto = torch.zeros(batch, dec.Hkv, 1, dec.D, dtype=torch.bfloat16, device=ids.device)
+    while len(dec.cache.layers) < len(dec.layers):
+        dec.cache.layers.append(dec.cache.layer_class_to_replicate())
+    for layer, src in zip(dec.cache.layers, full):
+        if not layer.is_initialized:
+            layer.lazy_initialization(proto, proto)
+        layer.k_codes, layer.v_codes, layer.k_scales, layer.v_scales = src["k"], src["v"], src["ks"], src["vs"]
+        layer.capacity, layer.length = src["k"].shape[2], prompt
+    first = torch.cat(firsts)
+    dec.tokens.copy_(first)
+    dec.pos.fill_(prompt)
+    dec.history.zero_()
+    dec.history[:, :prompt] = ids
+    dec.history[:, prompt] = first
+
+
 def run_decode(args, rank, world, device):
     import torch.distributed as dist
 
@@ -650,8 +745,14 @@ def run_decode(args, rank, world, device):
     # compared -- where they part, the margin says whether a near-tie decided it
     line["config"]["tokens"] = produced[0].tolist()
     line["config"]["top2_margin"] = decode_margins(dec, host_ids.to(device), produced.shape[1])
+    if world == 1 and batch == 1 and args.workload == "decode_8b" and not args.no_batch_sweep:
+        # the workload's other batch sizes (BASELINE config 5: batch 1, 8, 32), same prompt length,
+        # a short timed loop each: whole-batch tokens per second, device-timed
+        del dec
+        torch.cuda.empty_cache()
+        line["batch_sweep"] = {str(b): decode_at_batch(model, b, prompt, host_ids, device) for b in (8, 32)}
     if rank == 0:
-        if world == 1:  # the host cores are busy with the other ranks otherwise
+        if world == 1 and not args.skip_cpu_baseline:  # (the host cores are busy with the other ranks otherwise)
             line["cpu_baseline"] = cpu_reference_decode(spec["shape"], steps=2, warmup=1)
         print(json.dumps(line), flush=True)
 
@@ -844,6 +945,10 @@ def main():
     ap.add_argument("--epilogue", type=int, default=0)
     ap.add_argument("--norm", type=int, default=0)
     ap.add_argument("--rows", default="", help="prefill_gemm: comma-separated token counts (default 16,128,512,2048)")
+    ap.add_argument("--no-batch-sweep", action="store_true",
+                    help="decode_8b: leave out the short batch-8 / batch-32 measurements")
+    ap.add_argument("--skip-cpu-baseline", action="store_true",
+                    help="leave the CPU reference sample out of the line (profiling runs)")
     ap.add_argument("--batch", type=int, default=1)
     ap.add_argument("--prompt", type=int, default=0, help="prompt tokens (0 = the workload's own)")
     ap.add_argument("--allreduce", default="peer", choices=["peer", "nccl"])

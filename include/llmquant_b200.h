@@ -369,6 +369,9 @@ typedef struct lq_gemv_args {
   int variant;
   int pdl;
   const lq_gemv_tp* tp;        /* NULL = no tensor-parallel coupling */
+  int ldo;                     /* elements between two rows of out / residual; 0 = dense (N, or N/2
+                                  with epilogue 1). Lets a launch cover a block of the output
+                                  columns: a slice of the weight's rows against all activation rows. */
 } lq_gemv_args;
 int lq_wq_gemv_fused(const lq_gemv_args* args, void* stream);
 

@@ -62,6 +62,7 @@ struct MmaParams {
   const void* norm_weight;
   float norm_eps;
   int M, N, K, Kd, rowbytes, groups;
+  int ldo;  // elements between two activation rows of out / residual
   int W, ntiles, R, H, stages, stage_bytes, scale_off;  // R rows per stage, H = 16 / R stages per tile
   int plane_stride, ncols0, ncols1, unit_off, ring_off;
   int pdl;
@@ -423,7 +424,7 @@ gemv_mma_kernel(const MmaParams p) {
             for (int nb = 0; nb < NB; ++nb) {
               const int b = (my_slot & 3) + 4 * nb;
               if (b < p.M) {
-                const int64_t o = (int64_t)b * p.N + n + r;
+                const int64_t o = (int64_t)b * p.ldo + n + r;
                 res_pre[nb][r] = p.out_f32 ? reinterpret_cast<const float*>(p.residual)[o]
                                            : __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p.residual)[o]);
               }
@@ -579,7 +580,7 @@ gemv_mma_kernel(const MmaParams p) {
                 const float uq = __bfloat162float(__float2bfloat16_rn(tot[nb][1]));
                 const float sg = __bfloat162float(__float2bfloat16_rn(gt / (1.f + expf(-gt))));
                 const float y = sg * uq;
-                const int64_t o = (int64_t)b * (p.N / 2) + n / 2;
+                const int64_t o = (int64_t)b * p.ldo + n / 2;
                 if (p.out_f32) reinterpret_cast<float*>(p.out)[o] = __bfloat162float(__float2bfloat16_rn(y));
                 else reinterpret_cast<__nv_bfloat16*>(p.out)[o] = __float2bfloat16_rn(y);
               }
@@ -587,7 +588,7 @@ gemv_mma_kernel(const MmaParams p) {
 #pragma unroll
               for (int r = 0; r < 2; ++r) {
                 if (n + r < p.N) {
-                  const int64_t o = (int64_t)b * p.N + n + r;
+                  const int64_t o = (int64_t)b * p.ldo + n + r;
                   float bias_v = bias_pre[r], res_v = res_pre[nb][r];
                   if (!pre) {
                     bias_v = p.bias != nullptr ? __bfloat162float(p.bias[n + r]) : 0.f;
@@ -707,6 +708,7 @@ int run_mma(const lq_gemv_args& a, int* error_word, unsigned long long* debug, c
   p.out = a.out; p.out_f32 = a.out_dtype == LQ_F32;
   p.norm_weight = a.norm_weight; p.norm_eps = a.norm_eps;
   p.M = a.M; p.N = a.N; p.K = a.K; p.Kd = a.Kd; p.rowbytes = a.Kd * a.bits / 8; p.groups = a.Kd / 128;
+  p.ldo = a.ldo > 0 ? a.ldo : (a.epilogue == 1 ? a.N / 2 : a.N);
   p.pdl = a.pdl; p.error_word = error_word; p.debug = debug;
   Plan q;
   LQ_REQUIRE(make_plan(a.M, a.Kd, a.span, a.bits, &q), LQ_ERR_UNSUPPORTED, "shape outside the tensor-core GEMV");

@@ -254,6 +254,8 @@ extern "C" int lq_wq_gemv_fused(const lq_gemv_args* a, void* stream) {
   // shapes, 8 rows: gate|up 44 vs 96 us, lm_head 185 vs 303 us).
   if (a->variant == 0 && tp == nullptr && ((bits == 4 && M >= 3) || M >= 5) && mma_eligible(*a)) variant = 4;
   LQ_REQUIRE(variant >= 1 && variant <= 4, LQ_ERR_ARG, "unknown arithmetic variant %d", variant);
+  LQ_REQUIRE(a->ldo == 0 || a->ldo >= (a->epilogue == 1 ? N / 2 : N), LQ_ERR_ARG, "ldo=%d is shorter than a row", a->ldo);
+  LQ_REQUIRE(a->ldo == 0 || tp == nullptr, LQ_ERR_ARG, "an output row stride and the tensor-parallel coupling exclude each other");
   if (variant == 4) {
     LQ_REQUIRE(mma_eligible(*a), LQ_ERR_UNSUPPORTED,
                "the tensor-core GEMV needs scale groups of 128 stored codes, activation planes within 64 KB and "
@@ -267,6 +269,7 @@ extern "C" int lq_wq_gemv_fused(const lq_gemv_args* a, void* stream) {
   p.ldx = a->ldx; p.codes = (const uint8_t*)a->codes; p.scales = a->scale_tiles;
   p.bias = (const __nv_bfloat16*)a->bias;
   p.out_f32 = a->out_dtype == LQ_F32;
+  p.ldo = a->ldo > 0 ? a->ldo : (a->epilogue == 1 ? N / 2 : N);
   p.N = N; p.K = K; p.Kd = Kd; p.rowbytes = Kd * bits / 8; p.span = a->span;
   p.groups = Kd / a->span;
   p.norm_weight = a->norm_weight; p.norm_eps = a->norm_eps; p.pdl = a->pdl;

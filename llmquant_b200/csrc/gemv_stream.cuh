@@ -61,6 +61,7 @@ struct GemvParams {
   const void* residual;
   void* out;
   int out_f32;
+  int ldo;  // elements between two activation rows of out / residual
   int M, N, K, Kd, rowbytes, span, groups;
   int KW, S;
   int nbatch;
@@ -472,7 +473,7 @@ gemv_stream_kernel(const GemvParams p) {
       if (EPI == 0 && mine) {
         if (p.bias != nullptr) bias_pre = __bfloat162float(p.bias[n]);
         if (p.residual != nullptr) {
-          const int64_t po = (int64_t)m * p.N + n;
+          const int64_t po = (int64_t)m * p.ldo + n;
           res_pre = p.out_f32 ? reinterpret_cast<const float*>(p.residual)[po]
                               : __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p.residual)[po]);
         }
@@ -497,7 +498,7 @@ gemv_stream_kernel(const GemvParams p) {
           const float uq = __bfloat162float(__float2bfloat16_rn(up));
           const float sg = __bfloat162float(__float2bfloat16_rn(g / (1.f + expf(-g))));
           const float y = sg * uq;
-          const int64_t o = (int64_t)m * (p.N / 2) + n / 2;
+          const int64_t o = (int64_t)m * p.ldo + n / 2;
           if (p.out_f32) reinterpret_cast<float*>(p.out)[o] = __bfloat162float(__float2bfloat16_rn(y));
           else reinterpret_cast<__nv_bfloat16*>(p.out)[o] = __float2bfloat16_rn(y);
         }
@@ -505,7 +506,7 @@ gemv_stream_kernel(const GemvParams p) {
         tp_push_batch(p, peer_base, total + bias_pre, lane, n0);
       } else if (mine) {
         total += bias_pre;
-        const int64_t o = (int64_t)m * p.N + n;
+        const int64_t o = (int64_t)m * p.ldo + n;
         if (p.out_f32) {
           reinterpret_cast<float*>(p.out)[o] = total + res_pre;
         } else {
@@ -693,7 +694,7 @@ gemv_stream_kernel(const GemvParams p) {
       if (pn < p.N && pm < p.M) {
         if (p.bias != nullptr) bias_pre = __bfloat162float(p.bias[pn]);
         if (p.residual != nullptr) {
-          const int64_t po = (int64_t)pm * p.N + pn;
+          const int64_t po = (int64_t)pm * p.ldo + pn;
           res_pre = p.out_f32 ? reinterpret_cast<const float*>(p.residual)[po]
                               : __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p.residual)[po]);
         }
@@ -771,7 +772,7 @@ gemv_stream_kernel(const GemvParams p) {
           const float uq = __bfloat162float(__float2bfloat16_rn(up));
           const float sg = __bfloat162float(__float2bfloat16_rn(g / (1.f + expf(-g))));
           const float y = sg * uq;
-          const int64_t o = (int64_t)m * (p.N / 2) + n / 2;
+          const int64_t o = (int64_t)m * p.ldo + n / 2;
           if (p.out_f32) reinterpret_cast<float*>(p.out)[o] = __bfloat162float(__float2bfloat16_rn(y));
           else reinterpret_cast<__nv_bfloat16*>(p.out)[o] = __float2bfloat16_rn(y);
         }
@@ -779,7 +780,7 @@ gemv_stream_kernel(const GemvParams p) {
         tp_push_batch(p, p.tp_peers[lane % p.tp_world], total + bias_pre, lane, n0);
       } else if (lane < M * kU && n < p.N && m < p.M) {
         total += bias_pre;
-        const int64_t o = (int64_t)m * p.N + n;
+        const int64_t o = (int64_t)m * p.ldo + n;
         if (p.out_f32) {
           reinterpret_cast<float*>(p.out)[o] = total + res_pre;
         } else {
@@ -897,8 +898,8 @@ int launch_passes(GemvParams p, const lq_gemv_args& a, int spw, int threads, cud
   for (int m0 = 0; m0 < a.M; m0 += step) {
     p.M = a.M - m0 < step ? a.M - m0 : step;
     p.x = (const __nv_bfloat16*)a.x + (int64_t)m0 * p.ldx;
-    p.out = (char*)a.out + (size_t)m0 * n_out * out_es;
-    p.residual = a.residual ? (const char*)a.residual + (size_t)m0 * n_out * out_es : nullptr;
+    p.out = (char*)a.out + (size_t)m0 * p.ldo * out_es;
+    p.residual = a.residual ? (const char*)a.residual + (size_t)m0 * p.ldo * out_es : nullptr;
     const int rc = a.epilogue == 1 ? launch_m<BITS, VAR, 1>(p, spw, threads, s)
                                    : launch_m<BITS, VAR, 0>(p, spw, threads, s);
     if (rc) return rc;

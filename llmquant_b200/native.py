@@ -84,7 +84,7 @@ class GemvArgs(ctypes.Structure):
         ("x", _P), ("ldx", _I), ("norm_weight", _P), ("norm_eps", ctypes.c_float),
         ("codes", _P), ("scale_tiles", _P), ("bias", _P), ("residual", _P), ("out", _P),
         ("out_dtype", _I), ("M", _I), ("N", _I), ("K", _I), ("Kd", _I), ("span", _I),
-        ("bits", _I), ("epilogue", _I), ("variant", _I), ("pdl", _I), ("tp", _P),
+        ("bits", _I), ("epilogue", _I), ("variant", _I), ("pdl", _I), ("tp", _P), ("ldo", _I),
     ]
 
 

@@ -71,7 +71,11 @@ def save_packed_model(model: nn.Module, path, model_id: str, kv_cache_bits=None,
         }
 
     owned = tuple(f"{layer}." for layer in (*layers, *experts))
-    state = model.state_dict()
+    KernelQuantLinear.emit_canonical_state = False  # already written above, packed
+    try:
+        state = model.state_dict()
+    finally:
+        KernelQuantLinear.emit_canonical_state = True
     for name, tensor in state.items():
         if (owned and name.startswith(owned)) or name in tensors:
             continue

@@ -33,6 +33,8 @@ GEMV_VARIANT = 0  # 0 = library default; see lq_wq_gemv_stream
 # materialising them; above that, and for narrow outputs (too few 128 x 128 tiles to fill the
 # GPU), dequantize + library GEMM is still the faster of the two (measured crossover: between
 # 512 and 768 rows at the Llama-3-8B shapes; 1024 output features lose at every row count).
+# output-row slice of a weight that the launches of one row-block sweep share through L2
+L2_SLICE_BYTES = 24 << 20
 PREFILL_EXACT_MAX_ROWS = 16
 PREFILL_TENSOR_CORE_MAX_ROWS = 512
 PREFILL_TENSOR_CORE_MIN_FEATURES = 2048
@@ -180,6 +182,44 @@ class KernelQuantLinear(nn.Module):
             return self.codes.numel() + self._scale_rows * self.canonical_shape[1] * 4
         return self._qweight.numel() + self._wscale.numel() * 4
 
+    # ---- state dict: the reference's two tensors, although they are not what is stored ----
+    # (the reference registers qweight / wscale as persistent buffers, llmquant/quantizers/
+    # kernel.py:36-37, so `model.state_dict()` carries the quantized weights there; here they are
+    # rebuilt on the way out and repacked on the way in)
+    emit_canonical_state = True  # save_packed_model switches this off: it writes them itself, packed
+
+    def _save_to_state_dict(self, destination, prefix, keep_vars):
+        super()._save_to_state_dict(destination, prefix, keep_vars)
+        if self.emit_canonical_state:
+            qweight, wscale = self.canonical_tensors()
+            destination[prefix + "qweight"] = qweight
+            destination[prefix + "wscale"] = wscale
+
+    def _load_from_state_dict(self, state_dict, prefix, local_metadata, strict, missing_keys,
+                              unexpected_keys, error_msgs):
+        qweight, wscale = state_dict.pop(prefix + "qweight", None), state_dict.pop(prefix + "wscale", None)
+        if qweight is not None and wscale is not None:
+            if tuple(qweight.shape) != self.canonical_shape or wscale.shape[0] != self._scale_rows:
+                error_msgs.append(f"{prefix}qweight / wscale: shapes {tuple(qweight.shape)} / "
+                                  f"{tuple(wscale.shape)} do not match this layer")
+            elif self._stream:
+                dev = self.codes.device
+                q = qweight.to(device=dev, dtype=torch.int8).contiguous()
+                sc = wscale.to(device=dev, dtype=torch.float32).contiguous()
+                n, groups, gs = self.canonical_shape
+                with torch.cuda.device(dev):
+                    native.call("lq_repack_stream", q.data_ptr(), sc.data_ptr(), self.codes.data_ptr(),
+                                self.scale_tiles.data_ptr(), n, groups, gs, self._weight_args.head_dim or 0,
+                                self.num_bits, self.out_group, native.stream_ptr(dev))
+                    torch.cuda.current_stream(dev).synchronize()  # q and sc are temporaries
+            else:
+                self._qweight.copy_(qweight)
+                self._wscale.copy_(wscale)
+        elif strict and (qweight is None) != (wscale is None):
+            missing_keys.append(prefix + ("qweight" if qweight is None else "wscale"))
+        super()._load_from_state_dict(state_dict, prefix, local_metadata, strict, missing_keys,
+                                      unexpected_keys, error_msgs)
+
     # ---- forward ------------------------------------------------------------------------
     def _dequantized_weight(self, dtype):
         """Dense `[out, in]` weight in the activation dtype for the library-GEMM path."""
@@ -222,17 +262,10 @@ class KernelQuantLinear(nn.Module):
         if m == 0:
             return out
         if m > DECODE_MAX_ROWS:
-            # more rows than one launch takes: blocks of DECODE_MAX_ROWS rows, one launch each.
-            # The passes after the first find most of a layer's weight in L2 (a Llama-3-8B
-            # linear is 17 to 59 MB).
             if tp is not None:
                 raise RuntimeError(f"the tensor-parallel coupling takes the rows of one pass ({m} given)")
-            for m0 in range(0, m, DECODE_MAX_ROWS):
-                rows = slice(m0, min(m0 + DECODE_MAX_ROWS, m))
-                self.gemv(flat[rows], out_dtype=out_dtype, residual=None if residual is None else residual[rows],
-                          variant=variant, norm_weight=norm_weight, norm_eps=norm_eps, epilogue=epilogue,
-                          pdl=pdl, out=out[rows])
-            return out
+            return self._gemv_row_blocks(flat, out, out_dtype, residual, variant, norm_weight, norm_eps,
+                                         epilogue, pdl)
         bias = None
         if self.bias is not None:
             if self._bias_bf16 is None or self._bias_bf16.device != flat.device:
@@ -250,6 +283,48 @@ class KernelQuantLinear(nn.Module):
             tp=ctypes.addressof(tp) if tp is not None else None)
         with torch.cuda.device(flat.device):
             native.call("lq_wq_gemv_fused", ctypes.byref(args), native.stream_ptr(flat.device))
+        return out
+
+    def _gemv_row_blocks(self, flat, out, out_dtype, residual, variant, norm_weight, norm_eps, epilogue, pdl):
+        """More activation rows than one launch takes (8): the weight is walked in slices of
+        about L2_SLICE_BYTES of its output rows, and every slice meets all the activation rows,
+        8 per launch, before the next slice is touched -- so only the first of those launches
+        streams the slice from HBM, the others find it in L2. (Walking the whole weight once per
+        row block streams it again every time: a 59 MB weight does not survive a cyclic sweep of
+        the L2.) A launch covers a block of output columns through the output row stride `ldo`."""
+        m = flat.shape[0]
+        n, rowbytes = self.out_features, self.codes.shape[1]
+        groups = self._kd // self._span
+        bias = None
+        if self.bias is not None:
+            if self._bias_bf16 is None or self._bias_bf16.device != flat.device:
+                self._bias_bf16 = self.bias.detach().to(device=flat.device, dtype=torch.bfloat16).contiguous()
+            bias = self._bias_bf16
+        if flat.stride(-1) != 1:
+            flat = flat.contiguous()
+        es = out.element_size()
+        n_out = out.shape[1]
+        slice_rows = max(16, L2_SLICE_BYTES // max(rowbytes, 1) // 16 * 16)
+        stream = native.stream_ptr(flat.device)
+        with torch.cuda.device(flat.device):
+            for n0 in range(0, n, slice_rows):
+                rows_n = min(slice_rows, n - n0)
+                col0 = n0 // 2 if epilogue == 1 else n0
+                for m0 in range(0, m, DECODE_MAX_ROWS):
+                    rows_m = min(DECODE_MAX_ROWS, m - m0)
+                    off = (m0 * n_out + col0) * es
+                    args = native.GemvArgs(
+                        x=flat.data_ptr() + m0 * flat.stride(0) * 2, ldx=flat.stride(0),
+                        norm_weight=native.ptr(norm_weight), norm_eps=norm_eps,
+                        codes=self.codes.data_ptr() + n0 * rowbytes,
+                        scale_tiles=self.scale_tiles.data_ptr() + (n0 // 4) * groups * 16,
+                        bias=(bias.data_ptr() + n0 * 2) if bias is not None else None,
+                        residual=(residual.data_ptr() + off) if residual is not None else None,
+                        out=out.data_ptr() + off, out_dtype=native.DTYPE_ID[out_dtype], M=rows_m, N=rows_n,
+                        K=self.in_features, Kd=self._kd, span=self._span, bits=self.num_bits,
+                        epilogue=epilogue, variant=GEMV_VARIANT if variant is None else variant,
+                        pdl=1 if pdl else 0, tp=None, ldo=n_out)
+                    native.call("lq_wq_gemv_fused", ctypes.byref(args), stream)
         return out
 
     def gemm(self, flat, a8: bool = False, fold_scales: bool = False, serial: bool = False):

@@ -179,3 +179,31 @@ def test_bias_residual_leading_dims_and_prefill_branch():
     small = torch.cat([module(many[i:i + 4]) for i in range(0, many.shape[0], 4)])
     assert rel_l2(big.float().cpu().numpy(), small.float().cpu().numpy()) <= 1e-2
     assert module(many[:0]).shape == (0, 512)
+
+
+def test_state_dict_carries_the_quantized_weight_like_the_reference_module():
+    """`state_dict()` holds the canonical qweight / wscale (the reference registers them as
+    persistent buffers) although the module stores the streaming layout, and loading them into
+    another module of the same geometry reproduces the layer bit for bit."""
+    from llmquant_b200.core import QuantizationArgs, QuantizationScheme
+    from llmquant_b200.quantizers import KernelQuantLinear
+
+    def build(weight, bits):
+        scheme = QuantizationScheme(
+            weights=QuantizationArgs(num_bits=bits, strategy="group", group_size=128), input_activations=None)
+        linear = torch.nn.Linear(weight.shape[1], weight.shape[0], bias=False)
+        linear.weight.data = weight
+        return KernelQuantLinear.from_linear(linear.cuda(), scheme)
+
+    w = seeded((256, 512), 31, 0.02, torch.bfloat16)
+    other = seeded((256, 512), 32, 0.02, torch.bfloat16)
+    for bits in (4, 8):
+        a, b = build(w, bits), build(other, bits)
+        state = a.state_dict()
+        assert set(state) == {"qweight", "wscale"} and state["qweight"].dtype == torch.int8
+        assert torch.equal(state["qweight"], a.qweight) and torch.equal(state["wscale"], a.wscale)
+        x = seeded((2, 512), 33).bfloat16().cuda()
+        assert not torch.equal(a(x), b(x))
+        b.load_state_dict(state)
+        assert torch.equal(a(x), b(x)) and torch.equal(a.codes, b.codes)
+        assert torch.equal(a.scale_tiles, b.scale_tiles)

@@ -42,7 +42,8 @@ def test_exchange_layout_and_argument_blocks():
     assert rows.dtype == torch.bfloat16 and bool((rows.view(torch.int16) == -1).all())
     # the C struct: three ints, padding, then pointers and 64-bit fields
     assert native.GemvTp.peers.offset == 16 and ctypes.sizeof(native.GemvTp) == 56
-    assert native.GemvArgs.tp.offset == ctypes.sizeof(native.GemvArgs) - 8
+    assert native.GemvArgs.tp.offset == 112 and native.GemvArgs.ldo.offset == 120
+    assert ctypes.sizeof(native.GemvArgs) == 128
 
 
 def test_exchange_refuses_a_missing_peer_a_small_buffer_and_ragged_rows():
