@@ -397,7 +397,7 @@ def run_attn_one(args, device):
         for kc, vc, ks, vs in caches:
             native.call("lq_attn_decode_fused", qkv.data_ptr(), cos.data_ptr(), sin.data_ptr(), kc.data_ptr(),
                         vc.data_ptr(), ks.data_ptr(), vs.data_ptr(), out.data_ptr(), scratch.data_ptr(), B, Hq,
-                        Hkv, D, tmax, tmax, pos.data_ptr(), 0, 8, D ** -0.5, splits, args.attn_impl, 1, stream)
+                        Hkv, D, tmax, tmax, pos.data_ptr(), 0, 8, D ** -0.5, splits, args.attn_impl, None, 0, 1, stream)
 
     side = torch.cuda.Stream()
     side.wait_stream(torch.cuda.current_stream())
@@ -618,7 +618,9 @@ def run_decode(args, rank, world, device):
             dist.barrier()
         torch.cuda.synchronize()
 
-    dec.prefill(host_ids.to(device, non_blocking=True))
+    # the prompt goes through the transformers modules: a large batch in chunks of sequences
+    dev_ids = host_ids.to(device, non_blocking=True)
+    dec.prefill(dev_ids) if batch <= 8 else prefill_in_chunks(dec, dev_ids, 8)
     dec.capture()
     for _ in range(args.warmup):
         dec.step()

@@ -14,6 +14,7 @@ int run_b8v1(GemvParams, const lq_gemv_args&, int, int, cudaStream_t);
 int run_b8v2(GemvParams, const lq_gemv_args&, int, int, cudaStream_t);
 bool mma_eligible(const lq_gemv_args& a);
 int run_mma(const lq_gemv_args& a, int* error_word, unsigned long long* debug, cudaStream_t s);
+int run_decode_gemm(const lq_gemv_args& a, cudaStream_t s);  // decode_gemm.cu
 int run_b8v3(GemvParams, const lq_gemv_args&, int, int, cudaStream_t);
 }  // namespace gemv
 
@@ -207,7 +208,8 @@ extern "C" int lq_wq_gemv_fused(const lq_gemv_args* a, void* stream) {
   LQ_REQUIRE(a != nullptr, LQ_ERR_ARG, "null argument block");
   const int bits = a->bits, M = a->M, N = a->N, K = a->K, Kd = a->Kd;
   LQ_REQUIRE(bits == 4 || bits == 8, LQ_ERR_ARG, "unsupported num_bits %d, expected 4 or 8", bits);
-  LQ_REQUIRE(M >= 0 && M <= 8, LQ_ERR_ARG, "the decode GEMV takes at most 8 activation rows, got %d", M);
+  LQ_REQUIRE(M >= 0 && M <= (a->variant == 5 ? 64 : 8), LQ_ERR_ARG,
+             "the decode GEMV takes at most 8 activation rows (variant 5: 64), got %d", M);
   LQ_REQUIRE(N >= 0 && K >= 0 && Kd >= K, LQ_ERR_ARG, "bad shape N=%d K=%d Kd=%d", N, K, Kd);
   LQ_REQUIRE(a->out_dtype == LQ_BF16 || a->out_dtype == LQ_F32, LQ_ERR_DTYPE, "out must be bfloat16 or float32");
   if (M == 0 || N == 0) return LQ_OK;
@@ -253,9 +255,13 @@ extern "C" int lq_wq_gemv_fused(const lq_gemv_args* a, void* stream) {
   // tensor-core kernel, which takes 8 rows in one pass, is the faster one (B200, Llama-3-8B
   // shapes, 8 rows: gate|up 44 vs 96 us, lm_head 185 vs 303 us).
   if (a->variant == 0 && tp == nullptr && ((bits == 4 && M >= 3) || M >= 5) && mma_eligible(*a)) variant = 4;
-  LQ_REQUIRE(variant >= 1 && variant <= 4, LQ_ERR_ARG, "unknown arithmetic variant %d", variant);
+  LQ_REQUIRE(variant >= 1 && variant <= 5, LQ_ERR_ARG, "unknown arithmetic variant %d", variant);
   LQ_REQUIRE(a->ldo == 0 || a->ldo >= (a->epilogue == 1 ? N / 2 : N), LQ_ERR_ARG, "ldo=%d is shorter than a row", a->ldo);
   LQ_REQUIRE(a->ldo == 0 || tp == nullptr, LQ_ERR_ARG, "an output row stride and the tensor-parallel coupling exclude each other");
+  if (variant == 5) {
+    LQ_REQUIRE(tp == nullptr, LQ_ERR_UNSUPPORTED, "the decode GEMM has no tensor-parallel coupling");
+    return run_decode_gemm(*a, (cudaStream_t)stream);
+  }
   if (variant == 4) {
     LQ_REQUIRE(mma_eligible(*a), LQ_ERR_UNSUPPORTED,
                "the tensor-core GEMV needs scale groups of 128 stored codes, activation planes within 64 KB and "
@@ -285,6 +291,7 @@ extern "C" int lq_wq_gemv_fused(const lq_gemv_args* a, void* stream) {
     if (tp->wait_cycles > 0) p.tp_wait = tp->wait_cycles;
   }
   LQ_REQUIRE(p.error_word != nullptr, LQ_ERR_LAUNCH, "cannot resolve the device error word");
+  if (const int rw = take_warm_spans(a->warm, LQ_MAX_WARM_SPANS, &p.warm, "lq_wq_gemv_fused")) return rw;
   p.S = (p.rowbytes + 511) / 512;
   int spw = 1;
   while (spw <= 4 && (p.S + spw - 1) / spw > kMaxWarps) spw *= 2;

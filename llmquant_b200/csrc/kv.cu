@@ -618,7 +618,8 @@ attn_fused_kernel(const __nv_bfloat16* __restrict__ qkv, const __nv_bfloat16* __
                   const __nv_bfloat16* __restrict__ sin_t, int8_t* kc, int8_t* vc, float* ks, float* vs,
                   __nv_bfloat16* __restrict__ out, float* part_o, float* part_ml, int* tickets,
                   int Hq, int Hkv, int Tmax, int table_len, const int64_t* pos_dev, int64_t pos_host,
-                  float scaling, float qmin, float qmax, int* error_word, unsigned long long* debug) {
+                  float scaling, float qmin, float qmax, int* error_word, unsigned long long* debug,
+                  const WarmSpans warm) {
 #ifdef LQ_DIAGNOSTICS
 #define ATT_STAMP(slot) do { if (debug != nullptr && threadIdx.x == 0) { unsigned long long t_; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_)); debug[((size_t)(blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x) * 8 + (slot)] = t_; } } while (0)
 #else
@@ -668,6 +669,11 @@ attn_fused_kernel(const __nv_bfloat16* __restrict__ qkv, const __nv_bfloat16* __
     mbar_init(bar_a, 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     if (t_lo < t_hi) issue(t_lo);
+  }
+  // weights the kernels after this one will stream: this kernel leaves HBM almost idle
+  if (warp == NT / 32 - 1) {
+    const long long cta = ((long long)blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x;
+    l2_warm(warm, cta * 32 + lane, (long long)gridDim.x * gridDim.y * gridDim.z * 32);
   }
 
   asm volatile("griddepcontrol.wait;" ::: "memory");
@@ -1042,7 +1048,8 @@ attn_mma_kernel(const __nv_bfloat16* __restrict__ qkv, const __nv_bfloat16* __re
                 const __nv_bfloat16* __restrict__ sin_t, int8_t* kc, int8_t* vc, float* ks, float* vs,
                 __nv_bfloat16* __restrict__ out, float* part_o, float* part_ml, int* tickets,
                 int Hq, int Hkv, int Tmax, int table_len, const int64_t* pos_dev, int64_t pos_host,
-                float scaling, float qmin, float qmax, int* error_word, unsigned long long* debug) {
+                float scaling, float qmin, float qmax, int* error_word, unsigned long long* debug,
+                const WarmSpans warm) {
 #ifdef LQ_DIAGNOSTICS
 #define ATT_STAMP(slot) do { if (debug != nullptr && threadIdx.x == 0) { unsigned long long t_; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_)); debug[((size_t)(blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x) * 8 + (slot)] = t_; } } while (0)
 #else
@@ -1103,6 +1110,11 @@ attn_mma_kernel(const __nv_bfloat16* __restrict__ qkv, const __nv_bfloat16* __re
   __syncthreads();
   // cached rows and the cursor are older than the kernel ahead of this one: prefetch first
   if (warp == 0 && t_lo < t_hi) issue(t_lo);
+  // weights the kernels after this one will stream: this kernel leaves HBM almost idle
+  if (warp == NW - 1) {
+    const long long cta = ((long long)blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x;
+    l2_warm(warm, cta * 32 + lane, (long long)gridDim.x * gridDim.y * gridDim.z * 32);
+  }
   // so are the rotary tables and the cached rows' scales: the pieces this thread needs first
   // are requested before the wait for the producer of q|k|v, off the dependent chain
   const int64_t tpos = pos < table_len ? pos : table_len - 1;
@@ -1510,8 +1522,11 @@ extern "C" int lq_attn_decode_fused(const void* qkv, const void* cos_table, cons
                                     int8_t* k_codes, int8_t* v_codes, float* k_scales, float* v_scales,
                                     void* out, void* scratch, int B, int Hq, int Hkv, int D, int Tmax,
                                     int table_len, const int64_t* pos_dev, int64_t pos, int num_bits,
-                                    float scaling, int splits, int impl, int pdl, void* stream) {
+                                    float scaling, int splits, int impl, const lq_span* warm, int n_warm,
+                                    int pdl, void* stream) {
   using namespace lq;
+  WarmSpans ws;
+  if (const int rw = take_warm_spans(warm, n_warm, &ws, "lq_attn_decode_fused")) return rw;
   LQ_REQUIRE(num_bits >= 2 && num_bits <= 8, LQ_ERR_ARG, "num_bits must be in [2, 8], got %d", num_bits);
   LQ_REQUIRE(impl >= 0 && impl <= 3, LQ_ERR_ARG, "unknown attention implementation %d", impl);
   LQ_REQUIRE(B > 0 && Hq > 0 && Hkv > 0 && Hq % Hkv == 0 && Tmax > 0 && table_len > 0, LQ_ERR_ARG, "bad shape");
@@ -1550,7 +1565,7 @@ extern "C" int lq_attn_decode_fused(const void* qkv, const void* cos_table, cons
                     "lq_attn_decode_fused", (const __nv_bfloat16*)qkv, (const __nv_bfloat16*)cos_table, \
                     (const __nv_bfloat16*)sin_table, k_codes, v_codes, k_scales, v_scales,         \
                     (__nv_bfloat16*)out, part_o, part_ml, tickets, Hq, Hkv, Tmax, table_len, pos_dev, \
-                    pos, scaling, -qmax - 1.f, qmax, (int*)err_ptr, g_attn_timeline);              \
+                    pos, scaling, -qmax - 1.f, qmax, (int*)err_ptr, g_attn_timeline, ws);              \
     }                                                                                              \
   }
     LQ_CL_CASE(64, 1) LQ_CL_CASE(64, 2) LQ_CL_CASE(64, 4) LQ_CL_CASE(64, 8)
@@ -1572,7 +1587,7 @@ extern "C" int lq_attn_decode_fused(const void* qkv, const void* cos_table, cons
                     "lq_attn_decode_fused", (const __nv_bfloat16*)qkv, (const __nv_bfloat16*)cos_table, \
                     (const __nv_bfloat16*)sin_table, k_codes, v_codes, k_scales, v_scales,         \
                     (__nv_bfloat16*)out, part_o, part_ml, tickets, Hq, Hkv, Tmax, table_len, pos_dev, \
-                    pos, scaling, -qmax - 1.f, qmax, (int*)err_ptr, g_attn_timeline);              \
+                    pos, scaling, -qmax - 1.f, qmax, (int*)err_ptr, g_attn_timeline, ws);              \
   }
     LQ_MMA_CASE(64, 1) LQ_MMA_CASE(64, 2) LQ_MMA_CASE(64, 4) LQ_MMA_CASE(64, 8)
     LQ_MMA_CASE(128, 1) LQ_MMA_CASE(128, 2) LQ_MMA_CASE(128, 4) LQ_MMA_CASE(128, 8)
@@ -1587,7 +1602,7 @@ extern "C" int lq_attn_decode_fused(const void* qkv, const void* cos_table, cons
                     "lq_attn_decode_fused", (const __nv_bfloat16*)qkv, (const __nv_bfloat16*)cos_table, \
                     (const __nv_bfloat16*)sin_table, k_codes, v_codes, k_scales, v_scales,         \
                     (__nv_bfloat16*)out, part_o, part_ml, tickets, Hq, Hkv, Tmax, table_len, pos_dev, \
-                    pos, scaling, -qmax - 1.f, qmax, (int*)err_ptr, g_attn_timeline);                               \
+                    pos, scaling, -qmax - 1.f, qmax, (int*)err_ptr, g_attn_timeline, ws);                               \
   }
   LQ_FUSED_CASE(64, 1) LQ_FUSED_CASE(64, 2) LQ_FUSED_CASE(64, 4) LQ_FUSED_CASE(64, 8)
   LQ_FUSED_CASE(128, 1) LQ_FUSED_CASE(128, 2) LQ_FUSED_CASE(128, 4) LQ_FUSED_CASE(128, 8)

@@ -34,7 +34,8 @@ GEMV_VARIANT = 0  # 0 = library default; see lq_wq_gemv_stream
 # GPU), dequantize + library GEMM is still the faster of the two (measured crossover: between
 # 512 and 768 rows at the Llama-3-8B shapes; 1024 output features lose at every row count).
 # output-row slice of a weight that the launches of one row-block sweep share through L2
-L2_SLICE_BYTES = 24 << 20
+L2_SLICE_BYTES = 0  # 0 = whole passes (see _gemv_row_blocks)
+DECODE_GEMM_MAX_ROWS = 64
 PREFILL_EXACT_MAX_ROWS = 16
 PREFILL_TENSOR_CORE_MAX_ROWS = 512
 PREFILL_TENSOR_CORE_MIN_FEATURES = 2048
@@ -244,7 +245,7 @@ class KernelQuantLinear(nn.Module):
         return bool(self._stream and native.library().lq_gemv_tensor_core_ok(m, self._kd, self._span, self.num_bits))
 
     def gemv(self, flat, out_dtype=None, residual=None, variant=None, norm_weight=None,
-             norm_eps=1e-5, epilogue=0, pdl=False, out=None, tp=None):
+             norm_eps=1e-5, epilogue=0, pdl=False, out=None, tp=None, warm=None, workspace=None):
         """Streaming GEMV on `[M, K]` bf16 rows -> `[M, N]` (bf16 or fp32), 8 rows per launch.
 
         Optional fusions (see `lq_wq_gemv_fused`): RMSNorm of the input rows by `norm_weight`,
@@ -252,7 +253,12 @@ class KernelQuantLinear(nn.Module):
         the output, and `pdl` to overlap the weight prefetch with the previous kernel.
         `tp` (a `native.GemvTp`) couples the launch to the other ranks of a tensor-parallel
         group: as a pushing row-parallel linear (no `out`: the partial rows go to the ranks'
-        exchange buffers) or as the consumer that first builds `flat` from the ranks' partials."""
+        exchange buffers) or as the consumer that first builds `flat` from the ranks' partials.
+        `warm`: up to two tensors of constant device memory (weights of the kernels that follow)
+        which this launch pulls into L2 while it runs.
+        More than 8 rows (or `variant=5`) go through the tensor-core decode GEMM, which streams
+        the weight once for up to 64 rows; `workspace` is its scratch (a uint8 tensor of
+        `decode_workspace_bytes(rows)`; allocated per call when absent)."""
         m = flat.shape[0]
         out_dtype = out_dtype or torch.bfloat16
         n_out = self.out_features // 2 if epilogue == 1 else self.out_features
@@ -261,9 +267,12 @@ class KernelQuantLinear(nn.Module):
             out = torch.empty(m, n_out, dtype=out_dtype, device=flat.device)
         if m == 0:
             return out
-        if m > DECODE_MAX_ROWS:
+        if m > DECODE_MAX_ROWS or variant == 5:
             if tp is not None:
                 raise RuntimeError(f"the tensor-parallel coupling takes the rows of one pass ({m} given)")
+            if self._span == 128 and variant in (None, 0, 5):
+                return self._decode_gemm(flat, out, out_dtype, residual, norm_weight, norm_eps, epilogue, pdl,
+                                         workspace)
             return self._gemv_row_blocks(flat, out, out_dtype, residual, variant, norm_weight, norm_eps,
                                          epilogue, pdl)
         bias = None
@@ -281,17 +290,58 @@ class KernelQuantLinear(nn.Module):
             Kd=self._kd, span=self._span, bits=self.num_bits, epilogue=epilogue,
             variant=GEMV_VARIANT if variant is None else variant, pdl=1 if pdl else 0,
             tp=ctypes.addressof(tp) if tp is not None else None)
+        if warm:
+            args.warm = native.spans(warm)[0]
         with torch.cuda.device(flat.device):
             native.call("lq_wq_gemv_fused", ctypes.byref(args), native.stream_ptr(flat.device))
         return out
 
+    def decode_workspace_bytes(self, rows: int) -> int:
+        """Scratch bytes of the decode GEMM for up to `rows` activation rows per call."""
+        rows = min(max(rows, 1), DECODE_GEMM_MAX_ROWS)
+        return int(native.library().lq_decode_gemm_workspace_bytes(rows, self.out_features, self._kd))
+
+    def _decode_gemm(self, flat, out, out_dtype, residual, norm_weight, norm_eps, epilogue, pdl, workspace):
+        """Rows through the tensor-core decode GEMM (variant 5 of `lq_wq_gemv_fused`), 64 per
+        call: activation planes, one pass over the weight, finish -- three launches."""
+        m = flat.shape[0]
+        bias = None
+        if self.bias is not None:
+            if self._bias_bf16 is None or self._bias_bf16.device != flat.device:
+                self._bias_bf16 = self.bias.detach().to(device=flat.device, dtype=torch.bfloat16).contiguous()
+            bias = self._bias_bf16
+        if flat.stride(-1) != 1:
+            flat = flat.contiguous()
+        need = self.decode_workspace_bytes(m)
+        if workspace is None:
+            workspace = torch.empty(need, dtype=torch.uint8, device=flat.device)
+        elif workspace.numel() * workspace.element_size() < need or workspace.device != flat.device:
+            raise ValueError(f"the decode GEMM needs {need} bytes of workspace on {flat.device}")
+        es, n_out = out.element_size(), out.shape[1]
+        stream = native.stream_ptr(flat.device)
+        with torch.cuda.device(flat.device):
+            for m0 in range(0, m, DECODE_GEMM_MAX_ROWS):
+                rows = min(DECODE_GEMM_MAX_ROWS, m - m0)
+                off = m0 * n_out * es
+                args = native.GemvArgs(
+                    x=flat.data_ptr() + m0 * flat.stride(0) * 2, ldx=flat.stride(0),
+                    norm_weight=native.ptr(norm_weight), norm_eps=norm_eps, codes=self.codes.data_ptr(),
+                    scale_tiles=self.scale_tiles.data_ptr(), bias=native.ptr(bias),
+                    residual=(residual.data_ptr() + off) if residual is not None else None,
+                    out=out.data_ptr() + off, out_dtype=native.DTYPE_ID[out_dtype], M=rows, N=self.out_features,
+                    K=self.in_features, Kd=self._kd, span=self._span, bits=self.num_bits, epilogue=epilogue,
+                    variant=5, pdl=1 if pdl else 0, tp=None, ldo=n_out, workspace=workspace.data_ptr(),
+                    workspace_bytes=workspace.numel() * workspace.element_size())
+                native.call("lq_wq_gemv_fused", ctypes.byref(args), stream)
+        return out
+
     def _gemv_row_blocks(self, flat, out, out_dtype, residual, variant, norm_weight, norm_eps, epilogue, pdl):
-        """More activation rows than one launch takes (8): the weight is walked in slices of
-        about L2_SLICE_BYTES of its output rows, and every slice meets all the activation rows,
-        8 per launch, before the next slice is touched -- so only the first of those launches
-        streams the slice from HBM, the others find it in L2. (Walking the whole weight once per
-        row block streams it again every time: a 59 MB weight does not survive a cyclic sweep of
-        the L2.) A launch covers a block of output columns through the output row stride `ldo`."""
+        """More activation rows than one GEMV launch takes (8) on a weight the decode GEMM does
+        not serve (scale groups other than 128 codes): 8 rows per launch. The weight can be
+        walked in slices of L2_SLICE_BYTES of its output rows, every slice meeting all the row
+        blocks before the next slice is touched (a launch covers a block of output columns
+        through the output row stride `ldo`); by default it is not (measured on B200: the
+        per-launch set-up costs more than the second to fourth passes save)."""
         m = flat.shape[0]
         n, rowbytes = self.out_features, self.codes.shape[1]
         groups = self._kd // self._span
@@ -304,7 +354,7 @@ class KernelQuantLinear(nn.Module):
             flat = flat.contiguous()
         es = out.element_size()
         n_out = out.shape[1]
-        slice_rows = max(16, L2_SLICE_BYTES // max(rowbytes, 1) // 16 * 16)
+        slice_rows = max(16, L2_SLICE_BYTES // max(rowbytes, 1) // 16 * 16) if L2_SLICE_BYTES else max(n, 16)
         stream = native.stream_ptr(flat.device)
         with torch.cuda.device(flat.device):
             for n0 in range(0, n, slice_rows):

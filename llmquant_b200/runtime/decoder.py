@@ -29,6 +29,9 @@ from llmquant_b200.quantizers.kv_cache import KernelQuantCache
 
 
 MAX_BATCH = 64
+WARM_POLICIES = ("none", "attn", "chain", "next")
+L2_WARM = "none"                 # which launches pull later launches' weights into L2 (see _warm)
+LM_HEAD_WARM_BYTES = 48 << 20    # of lm_head, only a first part is requested ahead
 
 
 def _fuse_rows(modules, interleave=False):
@@ -98,7 +101,7 @@ class FusedLlamaDecoder:
 
     def __init__(self, model, max_batch: int, max_len: int, kv_bits: int = 8, use_graph: bool = True,
                  pdl: bool = True, tp=None, attn_splits: int = 0, gather_logits: bool = False,
-                 exchange=None, attn_impl: int = 0):
+                 exchange=None, attn_impl: int = 0, l2_warm: str = L2_WARM):
         if not supports(model):
             raise ValueError("FusedLlamaDecoder needs a Llama-layout model whose attention and MLP "
                              "linears are KernelQuantLinear (head_dim 64/128, silu MLP)")
@@ -173,9 +176,20 @@ class FusedLlamaDecoder:
         want = attn_splits if attn_splits > 0 else max(1, -(-2 * 148 // (B * self.Hkv)))
         self.splits = max(1, min(want, max_len // 64 or 1))
         self.attn_impl = attn_impl
+        if l2_warm not in WARM_POLICIES:
+            raise ValueError(f"l2_warm must be one of {WARM_POLICIES}, got {l2_warm!r}")
+        self.l2_warm = l2_warm
         nbytes = native.library().lq_attn_fused_scratch_bytes(B, self.Hq, self.Hkv, self.D, self.splits)
         self.scratch = torch.zeros(-(-nbytes // 4), dtype=torch.float32, device=dev)
         self.cache = KernelQuantCache(kv_bits, max_cache_len=max_len)
+        # scratch of the tensor-core decode GEMM that batches above 8 rows go through
+        self.workspace = None
+        if B > 8:
+            linears = [spec[k] for spec in self.layers for k in ("qkv", "o", "gate_up", "down")]
+            if isinstance(self.lm_head, KernelQuantLinear):
+                linears.append(self.lm_head)
+            need = max(m.decode_workspace_bytes(B) for m in linears)
+            self.workspace = torch.empty(need, dtype=torch.uint8, device=dev)
         self.graph = None
         separate_reduce = self.tp is not None and self.exchange is None
         self.launches_per_step = len(self.layers) * (7 if separate_reduce else 5) + 1 + (2 if self._glue else 0)
@@ -219,6 +233,42 @@ class FusedLlamaDecoder:
                 return
 
     # ------------------------------------------------------------------ one token
+    def _warm(self, l, launch):
+        """Weights that launch `launch` ('qkv', 'attn', 'o', 'gate_up', 'down') of layer `l` pulls
+        into L2 for the launches after it (`l2_warm`): the step is a chain of kernels that wait
+        for one another, and the attention block above all leaves HBM idle. 'attn': the
+        attention launch requests its layer's o_proj and gate|up weights. 'chain': in addition
+        o_proj requests down_proj and gate|up the next layer's q|k|v (lm_head's first part after
+        the last layer). 'next': every launch requests only the weights of the launch after it."""
+        policy = self.l2_warm
+        if policy == "none":
+            return None
+        spec = self.layers[l]
+        if l + 1 < len(self.layers):
+            after = self.layers[l + 1]["qkv"].codes
+        elif isinstance(self.lm_head, KernelQuantLinear) and self.lm_head._stream:
+            after = self.lm_head.codes.view(-1)[:LM_HEAD_WARM_BYTES]
+        else:
+            after = None
+        if policy == "attn":
+            table = {"attn": [spec["o"].codes, spec["gate_up"].codes]}
+        elif policy == "chain":
+            table = {"attn": [spec["o"].codes, spec["gate_up"].codes], "o": [spec["down"].codes],
+                     "gate_up": [after]}
+        else:  # "next"
+            table = {"attn": [spec["o"].codes], "o": [spec["gate_up"].codes],
+                     "gate_up": [spec["down"].codes], "down": [after]}
+        return table.get(launch)
+
+    def _attention(self, l, cache, pos_ptr, pdl, stream):
+        warm, n_warm = native.spans(self._warm(l, "attn"))
+        native.call("lq_attn_decode_fused", self.qkv.data_ptr(), self.cos.data_ptr(),
+                    self.sin.data_ptr(), cache.k_codes.data_ptr(), cache.v_codes.data_ptr(),
+                    cache.k_scales.data_ptr(), cache.v_scales.data_ptr(), self.attn.data_ptr(),
+                    self.scratch.data_ptr(), self.B, self.Hq, self.Hkv, self.D, cache.capacity,
+                    self.cos.shape[0], pos_ptr, 0, self.kv_bits, self.scaling, self.splits,
+                    self.attn_impl, warm, n_warm, pdl, stream)
+
     def _folded_launches(self):
         """The step under tensor parallelism with the all-reduce folded into the GEMVs: o_proj and
         down_proj push their fp32 partial rows into every rank's exchange buffer; gate|up, the
@@ -239,25 +289,23 @@ class FusedLlamaDecoder:
             tp = None
             if l > 0:  # hidden = down_proj(l - 1) summed over the ranks + its residual
                 tp = ex.sum_args(1, h1)
-            spec["qkv"].gemv(h0, norm_weight=spec["ln1"], norm_eps=self.eps, pdl=self.pdl, out=self.qkv, tp=tp)
+            spec["qkv"].gemv(h0, norm_weight=spec["ln1"], norm_eps=self.eps, pdl=self.pdl, workspace=self.workspace, out=self.qkv, tp=tp,
+                             warm=self._warm(l, "qkv"))
             yield
-            native.call("lq_attn_decode_fused", self.qkv.data_ptr(), self.cos.data_ptr(),
-                        self.sin.data_ptr(), cache.k_codes.data_ptr(), cache.v_codes.data_ptr(),
-                        cache.k_scales.data_ptr(), cache.v_scales.data_ptr(), self.attn.data_ptr(),
-                        self.scratch.data_ptr(), self.B, self.Hq, self.Hkv, self.D, cache.capacity,
-                        self.cos.shape[0], pos_ptr, 0, self.kv_bits, self.scaling, self.splits,
-                        self.attn_impl, pdl, stream)
+            self._attention(l, cache, pos_ptr, pdl, stream)
             yield
-            spec["o"].gemv(self.attn, out_dtype=torch.float32, pdl=self.pdl, tp=ex.push_args(0))
+            spec["o"].gemv(self.attn, out_dtype=torch.float32, pdl=self.pdl, workspace=self.workspace, tp=ex.push_args(0),
+                           warm=self._warm(l, "o"))
             yield
             tp = ex.sum_args(0, h0)
             spec["gate_up"].gemv(h1, norm_weight=spec["ln2"], norm_eps=self.eps, epilogue=1,
-                                 pdl=self.pdl, out=self.act, tp=tp)
+                                 pdl=self.pdl, workspace=self.workspace, out=self.act, tp=tp, warm=self._warm(l, "gate_up"))
             yield
-            spec["down"].gemv(self.act, out_dtype=torch.float32, pdl=self.pdl, tp=ex.push_args(1))
+            spec["down"].gemv(self.act, out_dtype=torch.float32, pdl=self.pdl, workspace=self.workspace, tp=ex.push_args(1),
+                              warm=self._warm(l, "down"))
             yield
         tp = ex.sum_args(1, h1)
-        self.lm_head.gemv(h0, norm_weight=self.final_norm, norm_eps=self.eps, pdl=self.pdl,
+        self.lm_head.gemv(h0, norm_weight=self.final_norm, norm_eps=self.eps, pdl=self.pdl, workspace=self.workspace,
                           out=self.local_logits, tp=tp)
         yield
 
@@ -283,21 +331,17 @@ class FusedLlamaDecoder:
         else:
             cur.copy_(self.embed.index_select(0, self.tokens))
         pos_ptr = self.pos.data_ptr()
-        for spec, cache in zip(self.layers, self.cache.layers):
-            spec["qkv"].gemv(cur, norm_weight=spec["ln1"], norm_eps=self.eps, pdl=self.pdl, out=self.qkv)
-            native.call("lq_attn_decode_fused", self.qkv.data_ptr(), self.cos.data_ptr(),
-                        self.sin.data_ptr(), cache.k_codes.data_ptr(), cache.v_codes.data_ptr(),
-                        cache.k_scales.data_ptr(), cache.v_scales.data_ptr(), self.attn.data_ptr(),
-                        self.scratch.data_ptr(), self.B, self.Hq, self.Hkv, self.D, cache.capacity,
-                        self.cos.shape[0], pos_ptr, 0, self.kv_bits, self.scaling, self.splits,
-                        self.attn_impl, pdl, stream)
-            self._row_parallel(spec["o"], self.attn, cur, nxt, 0)
+        for l, (spec, cache) in enumerate(zip(self.layers, self.cache.layers)):
+            spec["qkv"].gemv(cur, norm_weight=spec["ln1"], norm_eps=self.eps, pdl=self.pdl, workspace=self.workspace, out=self.qkv,
+                             warm=self._warm(l, "qkv"))
+            self._attention(l, cache, pos_ptr, pdl, stream)
+            self._row_parallel(spec["o"], self.attn, cur, nxt, 0, warm=self._warm(l, "o"))
             spec["gate_up"].gemv(nxt, norm_weight=spec["ln2"], norm_eps=self.eps, epilogue=1,
-                                 pdl=self.pdl, out=self.act)
-            self._row_parallel(spec["down"], self.act, nxt, cur, 1)
+                                 pdl=self.pdl, workspace=self.workspace, out=self.act, warm=self._warm(l, "gate_up"))
+            self._row_parallel(spec["down"], self.act, nxt, cur, 1, warm=self._warm(l, "down"))
         if isinstance(self.lm_head, KernelQuantLinear) and self.lm_head._stream:
             head_out = self.local_logits if self.tp else self.logits
-            self.lm_head.gemv(cur, norm_weight=self.final_norm, norm_eps=self.eps, pdl=self.pdl,
+            self.lm_head.gemv(cur, norm_weight=self.final_norm, norm_eps=self.eps, pdl=self.pdl, workspace=self.workspace,
                               out=head_out)
             if self.tp:
                 self.tp.all_gather_last_dim(self.logits, self.local_logits)
@@ -318,14 +362,15 @@ class FusedLlamaDecoder:
         buffers (no attention, no all-reduce, no token bookkeeping): what a benchmark captures
         to time the dominant kernel by itself. Leaves the hidden-state buffers overwritten."""
         cur, nxt = self.h
-        for spec in self.layers:
-            spec["qkv"].gemv(cur, norm_weight=spec["ln1"], norm_eps=self.eps, pdl=self.pdl, out=self.qkv)
-            spec["o"].gemv(self.attn, residual=cur, pdl=self.pdl, out=nxt)
+        for l, spec in enumerate(self.layers):
+            spec["qkv"].gemv(cur, norm_weight=spec["ln1"], norm_eps=self.eps, pdl=self.pdl, workspace=self.workspace, out=self.qkv,
+                             warm=self._warm(l, "qkv"))
+            spec["o"].gemv(self.attn, residual=cur, pdl=self.pdl, workspace=self.workspace, out=nxt, warm=self._warm(l, "o"))
             spec["gate_up"].gemv(nxt, norm_weight=spec["ln2"], norm_eps=self.eps, epilogue=1,
-                                 pdl=self.pdl, out=self.act)
-            spec["down"].gemv(self.act, residual=nxt, pdl=self.pdl, out=cur)
+                                 pdl=self.pdl, workspace=self.workspace, out=self.act, warm=self._warm(l, "gate_up"))
+            spec["down"].gemv(self.act, residual=nxt, pdl=self.pdl, workspace=self.workspace, out=cur, warm=self._warm(l, "down"))
         if isinstance(self.lm_head, KernelQuantLinear) and self.lm_head._stream:
-            self.lm_head.gemv(cur, norm_weight=self.final_norm, norm_eps=self.eps, pdl=self.pdl,
+            self.lm_head.gemv(cur, norm_weight=self.final_norm, norm_eps=self.eps, pdl=self.pdl, workspace=self.workspace,
                               out=self.local_logits if self.tp else self.logits)
 
     def gemv_bytes(self):
@@ -335,19 +380,19 @@ class FusedLlamaDecoder:
             total += self.lm_head.weight_bytes()
         return total
 
-    def _row_parallel(self, linear, x, residual, out, slot):
+    def _row_parallel(self, linear, x, residual, out, slot, warm=None):
         """out = residual + linear(x). One GPU: fused in the GEMV epilogue. Tensor parallel:
         fp32 partial, summed over the ranks (one-shot kernel over peer memory, or NCCL),
         then the same rounding and residual add."""
         if not self.tp:
-            linear.gemv(x, residual=residual, pdl=self.pdl, out=out)
+            linear.gemv(x, residual=residual, pdl=self.pdl, workspace=self.workspace, out=out, warm=warm)
             return
         if self.peer is not None:
-            linear.gemv(x, out_dtype=torch.float32, pdl=self.pdl,
-                        out=self.peer.slot(slot, out.shape[0], out.shape[1]))
+            linear.gemv(x, out_dtype=torch.float32, pdl=self.pdl, workspace=self.workspace,
+                        out=self.peer.slot(slot, out.shape[0], out.shape[1]), warm=warm)
             self.peer.reduce(slot, residual, out, self.pdl)
             return
-        linear.gemv(x, out_dtype=torch.float32, pdl=self.pdl, out=self.partial)
+        linear.gemv(x, out_dtype=torch.float32, pdl=self.pdl, workspace=self.workspace, out=self.partial, warm=warm)
         self.tp.all_reduce(self.partial)
         native.call("lq_residual_add", self.partial.data_ptr(), residual.data_ptr(), out.data_ptr(),
                     out.numel(), 1 if self.pdl else 0, native.stream_ptr(self.device))
@@ -440,6 +485,8 @@ class FusedLlamaDecoder:
         the last check cannot be trusted. Reads device words, so it synchronizes."""
         lib = native.library()
         words = {"gemv": lib.lq_gemv_device_error(), "attention": lib.lq_attn_device_error()}
+        if self.workspace is not None:
+            words["decode gemm"] = lib.lq_decode_gemm_device_error()
         if self.tp:
             words["allreduce"] = lib.lq_allreduce_device_error()
             words["token exchange"] = lib.lq_glue_device_error()

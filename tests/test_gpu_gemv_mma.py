@@ -185,7 +185,8 @@ def test_row_blocks_over_weight_slices_equal_whole_passes(bits, k, epilogue, mon
     monkeypatch.setattr(kq, "L2_SLICE_BYTES", 160 * module.codes.shape[1])  # slices of 160 rows: 4 of them
     sliced = module.gemv(x, residual=residual, **kwargs)
     assert sliced.shape == (m, n_out) and torch.equal(sliced, whole)
-    want = _want(w, llama_ops.rmsnorm(x.float().cpu().numpy(), gamma.float().cpu().numpy(), 1e-5), bits)
+    normed = llama_ops.rmsnorm(x.float().cpu().numpy(), gamma.float().cpu().numpy(), 1e-5)
+    want = _want(w, torch.from_numpy(normed), bits)
     if epilogue == 0:
         want = want + bias.float().numpy()
         got = (module.gemv(x, out_dtype=torch.float32, **kwargs)).cpu().numpy()
