@@ -397,7 +397,7 @@ def run_attn_one(args, device):
         for kc, vc, ks, vs in caches:
             native.call("lq_attn_decode_fused", qkv.data_ptr(), cos.data_ptr(), sin.data_ptr(), kc.data_ptr(),
                         vc.data_ptr(), ks.data_ptr(), vs.data_ptr(), out.data_ptr(), scratch.data_ptr(), B, Hq,
-                        Hkv, D, tmax, tmax, pos.data_ptr(), 0, 8, D ** -0.5, splits, args.attn_impl, None, 0, 1, stream)
+                        Hkv, D, tmax, tmax, pos.data_ptr(), 0, 8, D ** -0.5, splits, args.attn_impl, 1, stream)
 
     side = torch.cuda.Stream()
     side.wait_stream(torch.cuda.current_stream())
@@ -537,7 +537,7 @@ def decode_at_batch(model, batch, prompt, host_ids, device, steps=8, warmup=3):
     ms = a.elapsed_time(b) / steps
     context = prompt + warmup + steps // 2
     out = {"tok_per_s": round(batch / (ms * 1e-3), 1), "ms_per_step": round(ms, 3), "steps": steps,
-           "context": context, "gemv_launches_per_linear": -(-batch // 8),
+           "context": context, "launches_per_linear": 3 if dec.decode_gemm else 1,
            "kv_bytes_per_step": 2 * batch * dec.Hkv * context * (dec.D + 4) * len(dec.layers)}
     dec.check_device_errors()
     del dec
@@ -727,8 +727,9 @@ def run_decode(args, rank, world, device):
                      # (lm_head, int8) and 1.03x (gate|up, int4) the algorithmic bytes
                      "traffic": int(gemv_bytes * 1.02) // gemv_launches,
                      "traffic_source": "ncu captures of two shapes (1.006x and 1.03x algorithmic), scaled",
-                     "kernel": f"gemv_stream_kernel, the {gemv_launches} launches of one step timed alone "
-                               f"as a graph (per GPU); achieved / traffic are per launch on average",
+                     "kernel": (f"{'decode_gemm_kernel (with its planes and finish launches)' if dec.decode_gemm else 'gemv_stream_kernel'}"
+                                f", the {gemv_launches} linears of one step timed alone as a graph (per GPU); "
+                                f"achieved / traffic are per linear on average"),
                      "algorithmic_bytes_per_launch": gemv_bytes // gemv_launches,
                      "us_per_launch": round(gemv_ms * 1e3 / gemv_launches, 2),
                      "share_of_step": round(gemv_ms / step_ms, 3),

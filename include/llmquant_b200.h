@@ -35,20 +35,6 @@ enum {
 int lq_version(void);
 const char* lq_last_error(void);
 
-/* A span of constant device memory -- weights -- that a kernel is asked to pull into L2
- * for the kernels launched after it. A decode step is a chain of kernels of which each
- * waits for the one before, and some of them leave HBM almost idle (the attention block,
- * the set-up and tail of every GEMV); a kernel given spans requests them
- * (cp.async.bulk.prefetch.L2) before it waits for its predecessor, its CTAs sharing the span
- * between them. The requests change no result and nothing waits for them. `ptr` 16-byte
- * aligned, memory of the launching GPU; at most LQ_MAX_WARM_SPANS per launch. No counterpart
- * in the reference. */
-#define LQ_MAX_WARM_SPANS 2
-typedef struct lq_span {
-  const void* ptr;
-  int64_t bytes;
-} lq_span;
-
 /* ---------------------------------------------------------------- quantize / dequantize */
 
 /* Fused symmetric RTN quant-dequant over groups of `group_size` along the last axis.
@@ -266,14 +252,13 @@ int lq_attn_device_error(void);
  * finishes last, LQ_ATTN_CLUSTER = the same contractions with the slices of a KV head running as
  * one thread-block cluster that merges through distributed shared memory (`splits` must be 2,
  * 4, 8 or 16; LQ_ERR_UNSUPPORTED if such clusters do not fit the device). Same results within
- * the attention tolerance. `warm` / `n_warm`: spans to pull into L2 (lq_span; NULL / 0 = none). */
+ * the attention tolerance. */
 enum { LQ_ATTN_AUTO = 0, LQ_ATTN_SIMT = 1, LQ_ATTN_MMA = 2, LQ_ATTN_CLUSTER = 3 };
 int lq_attn_decode_fused(const void* qkv, const void* cos_table, const void* sin_table,
                          int8_t* k_codes, int8_t* v_codes, float* k_scales, float* v_scales,
                          void* out, void* scratch, int B, int Hq, int Hkv, int D, int Tmax,
                          int table_len, const int64_t* pos_dev, int64_t pos, int num_bits,
-                         float scaling, int splits, int impl, const lq_span* warm, int n_warm,
-                         int pdl, void* stream);
+                         float scaling, int splits, int impl, int pdl, void* stream);
 
 /* lq_attn_decode_kv_i8 for callers that cannot provide scratch memory -- a plugin inside a
  * process whose device memory belongs to someone else's allocator, or a host that is not
@@ -387,7 +372,6 @@ typedef struct lq_gemv_args {
   int ldo;                     /* elements between two rows of out / residual; 0 = dense (N, or N/2
                                   with epilogue 1). Lets a launch cover a block of the output
                                   columns: a slice of the weight's rows against all activation rows. */
-  lq_span warm[LQ_MAX_WARM_SPANS];  /* memory to pull into L2 for later kernels; bytes 0 = unused */
   void* workspace;             /* variant 5 only: lq_decode_gemm_workspace_bytes(M, N, Kd) bytes, 256-byte aligned */
   int64_t workspace_bytes;
 } lq_gemv_args;
@@ -395,16 +379,28 @@ int lq_wq_gemv_fused(const lq_gemv_args* args, void* stream);
 
 /* variant 5 of lq_wq_gemv_fused: the decode GEMM for 1..64 activation rows (the sequences of a
  * decode step) on tcgen05 tensor cores -- the weights are streamed ONCE for all rows, where
- * the GEMV variants take 8 rows per pass. Three launches: the activation rows (through the
- * optional RMSNorm) become 15-bit block-floating-point byte planes in `workspace`; one CTA
- * per (128 weight rows, slice of the scale groups) multiplies them with kind::i8 MMAs into
- * tensor memory and applies (weight scale x activation unit) per group in fp32 -- the order
- * of operations of quantizers/real.py:93-99; a last kernel adds the slices and applies bias,
- * residual or silu(gate) * up. Needs span == 128. Same fusions and roundings as the other
- * variants; no tensor-parallel coupling. The workspace may be shared by consecutive launches on
- * one stream. lq_decode_gemm_device_error is non-zero if a bounded wait inside the kernel ever
- * expired (reads and clears the word; synchronizes: for sync points). Replaces, for batched
- * decode, the dequantize + library GEMM branch of quantizers/kernel.py:68-79,90-91. */
+ * the GEMV variants take 8 rows per pass. `codes` is the weight in the TILE-MAJOR layout of
+ * lq_tile_weight (not the streaming layout of the other variants).
+ * Three launches: the activation rows (through the optional RMSNorm) become 15-bit
+ * block-floating-point byte planes in `workspace`; one CTA per (128 weight rows, slice of the
+ * scale groups) multiplies them with kind::i8 MMAs into tensor memory and applies (weight
+ * scale x activation unit) per group in fp32 -- the order of operations of
+ * quantizers/real.py:93-99; a last kernel adds the slices and applies bias, residual or
+ * silu(gate) * up. Needs span == 128. Same fusions and roundings as the other variants; no
+ * tensor-parallel coupling. The workspace may be shared by consecutive launches on one stream.
+ * lq_decode_gemm_device_error is non-zero if a bounded wait inside the kernel ever expired
+ * (reads and clears the word; synchronizes: for sync points). Replaces, for batched decode,
+ * the dequantize + library GEMM branch of quantizers/kernel.py:68-79,90-91.
+ *
+ * lq_tile_weight: streaming layout -> tile-major: per tile of 128 weight rows and per scale
+ * group of 128 codes one contiguous block -- the codes (int8: 16 KB, already in the swizzled
+ * order the MMA reads from shared memory; int4: 8 KB of nibble bytes), then the 128 fp32 scales
+ * of the block's rows; rows beyond N are zeros -- so that a CTA fetches a group with one linear
+ * bulk copy. `out` takes lq_tile_weight_bytes(N, Kd, bits) bytes; variant 5 is given it as
+ * `codes` (its `scale_tiles` is not read). */
+int64_t lq_tile_weight_bytes(int N, int Kd, int bits);
+int lq_tile_weight(const void* codes, const float* scale_tiles, void* out, int N, int Kd, int bits,
+                   void* stream);
 int64_t lq_decode_gemm_workspace_bytes(int M, int N, int Kd);
 int lq_decode_gemm_device_error(void);
 

@@ -91,14 +91,28 @@ __device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
       : "memory");
   return done != 0;
 }
+// The same test, but the thread may be suspended for up to `ns` nanoseconds while the phase
+// is incomplete: it is woken when the phase completes and issues nothing until then.
+__device__ __forceinline__ bool mbar_try_suspend(uint32_t bar, uint32_t parity, uint32_t ns) {
+  uint32_t done;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+      "selp.b32 %0, 1, 0, p;\n\t}"
+      : "=r"(done)
+      : "r"(bar), "r"(parity), "r"(ns)
+      : "memory");
+  return done != 0;
+}
 // Bounded wait: false if the phase did not complete within ~1 s of SM clock. The clock is only
 // read once the first try has failed, so a wait on data that has already landed costs three
-// instructions.
+// instructions; after that the thread sleeps in the barrier between looks at the clock, so a
+// waiting warp leaves the issue slots to the warps that work.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
   if (mbar_try(bar, parity)) return true;
   const long long t0 = clock64();
   for (;;) {
-    if (mbar_try(bar, parity)) return true;
+    if (mbar_try_suspend(bar, parity, 20000u)) return true;
     if (clock64() - t0 > 2000000000LL) return false;
   }
 }
@@ -116,30 +130,6 @@ __device__ __forceinline__ uint4 lds128(uint32_t addr) {
   return v;
 }
 
-// ---- pulling constant memory (weights) into L2 ahead of its use
-// A kernel whose own work leaves the memory system idle -- while it waits for its predecessor,
-// in a latency-bound phase -- asks for the spans the kernels after it will stream. A prefetch
-// writes nothing and completes on nothing, so it needs no wait.
-constexpr int kMaxWarm = LQ_MAX_WARM_SPANS;
-constexpr int kWarmPiece = 128;  // bytes per request: one L2 line
-struct WarmSpans {
-  const uint8_t* ptr[kMaxWarm];
-  long long bytes[kMaxWarm];  // 0 = unused; multiples of 16 (the host rounds down)
-};
-// `unit` of `nunits` (the lanes of one warp per CTA, over all CTAs of the grid): line i of a
-// span goes to unit i % nunits, so a warp asks for 4 KB of consecutive lines per instruction
-// and the requests of one moment spread over all SMs. Plain prefetch instructions: they go
-// through the load/store path and leave the bulk-copy engine to the kernel's own streams.
-__device__ __forceinline__ void l2_warm(const WarmSpans& w, long long unit, long long nunits) {
-#pragma unroll
-  for (int s = 0; s < kMaxWarm; ++s) {
-    const long long bytes = w.bytes[s];
-    for (long long off = unit * kWarmPiece; off < bytes; off += nunits * kWarmPiece)
-      asm volatile("prefetch.global.L2 [%0];" ::"l"(w.ptr[s] + off) : "memory");
-  }
-}
-// Host side: validates and copies the caller's spans. Returns 0 or an error code.
-int take_warm_spans(const lq_span* spans, int n, WarmSpans* out, const char* what);
 
 #define LQ_DISPATCH_DTYPE(dtype, T, ...)                   \
   switch (dtype) {                                         \

@@ -63,25 +63,6 @@ int ensure_smem_limit(const void* kernel, int bytes, const char* what) {
   return LQ_OK;
 }
 
-int take_warm_spans(const lq_span* spans, int n, WarmSpans* out, const char* what) {
-  for (int i = 0; i < kMaxWarm; ++i) {
-    out->ptr[i] = nullptr;
-    out->bytes[i] = 0;
-  }
-  if (n == 0) return LQ_OK;
-  if (n < 0 || n > kMaxWarm || spans == nullptr)
-    return fail(LQ_ERR_ARG, "%s: between 0 and %d warm spans, got %d", what, kMaxWarm, n);
-  for (int i = 0; i < n; ++i) {
-    if (spans[i].bytes < 0 || (spans[i].bytes > 0 && spans[i].ptr == nullptr))
-      return fail(LQ_ERR_ARG, "%s: warm span %d has no address or a negative size", what, i);
-    if (reinterpret_cast<uintptr_t>(spans[i].ptr) & 15)
-      return fail(LQ_ERR_ARG, "%s: warm span %d must start on a 16-byte boundary", what, i);
-    out->ptr[i] = static_cast<const uint8_t*>(spans[i].ptr);
-    out->bytes[i] = spans[i].bytes & ~15LL;
-  }
-  return LQ_OK;
-}
-
 }  // namespace lq
 
 extern "C" int lq_version(void) { return 3; }

@@ -21,7 +21,7 @@
 //                       2 * TP plane rows, four tcgen05.mma kind::i8 (K = 32 each) into one of
 //                       two TMEM accumulators [128 lanes = weight rows][2 * TP columns]. Warp
 //                       roles as in the prefill kernel: 4 fill warps (cp.async into 128-byte
-//                       swizzled tiles, three groups ahead), one MMA-issuing thread, 8 drain
+//                       swizzled tiles, as many groups ahead as shared memory holds), one MMA-issuing thread, 8 drain
 //                       warps (tcgen05.ld; hi * 256 + lo; times weight scale x unit; fp32
 //                       registers). This is the reference's order of operations: one exact
 //                       product sum per group, scaled, accumulated in fp32 over the groups
@@ -37,19 +37,79 @@
 namespace lq {
 namespace {
 
-constexpr int kDgThreads = 416;  // 8 drain warps, 4 fill warps, 1 MMA warp
-constexpr int kDgStages = 5;     // shared-memory stages (operand tiles of one group each)
-constexpr int kDgAhead = 3;      // groups whose copies are in flight ahead of the one handed over
+constexpr int kDgThreads = 672;  // 8 drain warps, 8 widening warps, 2 MMA warps, 3 copy warps
+constexpr int kDgWidenWarps = 8;  // each widens every eighth group by itself
 constexpr int kDgRows = 128;     // weight rows per CTA = TMEM lanes
 constexpr int KT = 128;          // codes per scale group = bytes per operand row
+constexpr int kDgSmem = 200 * 1024;  // dynamic shared memory the rings are sized for
+constexpr int kDgRing = 16;      // slots of the small per-group rings (weight scales, units)
+
+// Shared-memory plan of an instance. A CTA streams its rows at the rate its bytes in flight allow
+// (HBM answers after about a microsecond), so the rings are as deep as shared memory permits:
+// int8 codes land directly in the A operand tiles; int4 nibbles land in a deep ring of raw bytes
+// and are widened into a short ring of A tiles. The activation planes (B tiles) have a ring of
+// their own. A group's weight scales ride behind its codes and its units behind its planes, so
+// a group costs two bulk copies: issuing one occupies the issuing thread for some hundred
+// clocks, which is why there are few of them and one thread per ring.
+constexpr int kScaleBytes = kDgRows * 4;  // the 128 weight scales of a group
+template <int BITS, int TP>
+struct DgPlan {
+  static constexpr int NCOL = 2 * TP;
+  static constexpr int A_TILE = kDgRows * KT;  // 16 KB
+  static constexpr int B_TILE = NCOL * KT;
+  static constexpr int UNIT_BYTES = (TP * 4 + 127) / 128 * 128;
+  static constexpr int B_BLOCK = B_TILE + UNIT_BYTES;   // what one copy brings: planes + units
+  static constexpr int RAW = kDgRows * (KT / 2);        // int4: a group's nibble bytes as they come
+  static constexpr int W_BLOCK = (BITS == 8 ? A_TILE : RAW) + kScaleBytes;  // codes + scales
+  // slots keep the operand tiles on 1024-byte boundaries (the 128-byte swizzle)
+  static constexpr int A_SLOT = A_TILE + (BITS == 8 ? 1024 : 0);
+  static constexpr int B_SLOT = B_TILE + 1024;
+  static constexpr int RAW_SLOT = RAW + kScaleBytes;
+  static constexpr int SA8_ = kDgSmem / (A_SLOT + B_SLOT) > 8 ? 8 : kDgSmem / (A_SLOT + B_SLOT);
+  static constexpr int SA = BITS == 8 ? (SA8_ & ~1) : (TP <= 8 ? 6 : 4);
+  static constexpr int BN = BITS == 8 ? SA : (TP <= 16 ? 8 : (TP == 32 ? 6 : 4));
+  static constexpr int RAWN = BITS == 8 ? 0 : kDgWidenWarps;
+  static constexpr size_t SMEM = (size_t)SA * A_SLOT + (size_t)BN * B_SLOT + (size_t)RAWN * RAW_SLOT + 1024;
+  // Accumulators in tensor memory: as many as its 512 columns hold, up to 8. An MMA, the
+  // commit that follows it, the drain's tensor-memory load and the hand-back are each a few
+  // hundred clocks of latency: the ring has to cover that loop.
+  static constexpr int NACC = 512 / NCOL < 8 ? 512 / NCOL : 8;
+  // Whoever tests a barrier for its n-th completion must know the (n-1)-th has happened (a
+  // test that comes a whole phase early reads as "complete"). So the rings are laid out such
+  // that all uses of one slot fall to one thread, which takes them in order: even depths for
+  // the rings walked by the even / odd thread pairs, a raw ring as deep as there are widening
+  // warps, and 16-deep barrier rings ("group multiplied", "group drained") behind rings of at
+  // most 8.
+  static_assert(SA % 2 == 0 && BN % 2 == 0 && NACC % 2 == 0, "ring depths must be even");
+  static_assert(SA <= 8 && BN <= 8 && NACC <= 8 && SA + NACC <= kDgRing, "rings deeper than the barrier rings allow");
+  static_assert(kDgRing % kDgWidenWarps == 0, "a widening warp must meet a barrier slot again after 16 groups");
+  static_assert(BITS == 8 || (size_t)SA * A_SLOT + (size_t)BN * B_SLOT + (size_t)RAWN * RAW_SLOT <= kDgSmem,
+                "the rings do not fit");
+};
 
 __device__ int g_decode_gemm_error = 0;
 
+#ifdef LQ_DIAGNOSTICS
+// Diagnostic builds: SM clocks the role leaders of CTA 0..255 spent in each part of a round,
+// summed over the rounds. [cta][slot]: widen 0 wait-copies 1 widen | mma 4 wait-operands
+// 5 wait-accumulator 6 issue | drain 8 wait 9 load+scale | 12 whole kernel
+__device__ unsigned long long g_dg_diag[256 * 16];
+// and for CTA (0, 0) the SM clock of eight events per group: 0 raw bytes seen by the widen
+// warps, 1 group widened, 2 planes requested, 3 MMA thread has its operands, 4 MMAs issued,
+// 5 drain sees the group multiplied, 6 drain done, 7 raw bytes requested
+__device__ long long g_dg_trace[128 * 8];
+#define DG_EV(j, e) do { if (blockIdx.x == 0 && blockIdx.y == 0 && (j) < 128) g_dg_trace[(j) * 8 + (e)] = clock64(); } while (0)
+#define DG_T0() const long long dg_t0_ = clock64()
+#define DG_ADD(slot) do { (void)dg_t0_; } while (0)  // (sums off: they cost a round trip to memory each, which distorts the trace)
+#else
+#define DG_T0() do { } while (0)
+#define DG_ADD(slot) do { } while (0)
+#define DG_EV(j, e) do { } while (0)
+#endif
+
 struct DgParams {
-  const uint8_t* codes;      // streaming layout [N, rowbytes]
-  const float* scale_tiles;  // [N/4, G, 4]
-  const int8_t* planes;      // [G][2 * TP][128]
-  const float* units;        // [G][TP]
+  const uint8_t* codes;      // tile-major [tiles][G] blocks: codes of 128 rows, then their 128 scales
+  const uint8_t* planes;     // [G] blocks: plane rows [2 * TP][128] swizzled as the MMA reads them, then TP units
   float* partial;            // [splits][T][N]
   int T, N, groups, rowbytes, gper;
   int* error_word;
@@ -60,31 +120,39 @@ constexpr uint32_t dg_idesc(int ncol) {
   return (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(ncol >> 3) << 17) | ((uint32_t)(kDgRows >> 4) << 24);
 }
 
+// Roles (warps): 0-7 drain, 8-15 widen (int4), 16-17 MMA issue (even / odd groups), 18 weight
+// copies, 19 plane copies.
 template <int BITS, int TP>
 __global__ void __launch_bounds__(kDgThreads)
 decode_gemm_kernel(const DgParams p) {
-  constexpr int NCOL = 2 * TP;                      // accumulator columns: high planes, low planes
-  constexpr int TMEM_COLS = 2 * NCOL < 32 ? 32 : 2 * NCOL;
-  constexpr int A_TILE = kDgRows * KT;              // 16 KB
-  constexpr int B_TILE = NCOL * KT;
-  constexpr int STAGE = A_TILE + B_TILE;
-  constexpr int RAW = kDgRows * (KT / 2);           // int4: a group's nibble bytes as they come
+  using Plan = DgPlan<BITS, TP>;
+  constexpr int NCOL = Plan::NCOL;                  // accumulator columns: high planes, low planes
+  constexpr int NACC = Plan::NACC;
+  constexpr int TMEM_COLS = NACC * NCOL < 32 ? 32 : NACC * NCOL;
+  constexpr int A_TILE = Plan::A_TILE, B_TILE = Plan::B_TILE, RAW = Plan::RAW;
+  constexpr int A_SLOT = Plan::A_SLOT, B_SLOT = Plan::B_SLOT, RAW_SLOT = Plan::RAW_SLOT;
+  constexpr int SA = Plan::SA, BN = Plan::BN, RAWN = Plan::RAWN > 0 ? Plan::RAWN : 1;
   constexpr int DW = TP >= 16 ? 8 : 4;              // drain warps in use
   constexpr int TPH = TP / (DW / 4);                // tokens per drain thread
   constexpr int CH = TPH < 16 ? 8 : 16;             // tokens per tensor-memory load
   extern __shared__ __align__(128) uint8_t smem[];
-  __shared__ __align__(8) uint64_t full_bar[kDgStages], sfree_bar[kDgStages], tfull_bar[2], tfree_bar[2];
+  __shared__ __align__(8) uint64_t a_full[SA], b_full[BN], raw_full[RAWN], raw_free[RAWN];
+  __shared__ __align__(8) uint64_t mma_done[kDgRing], drained[kDgRing];
   __shared__ uint32_t tmem_base_s;
-  __shared__ float ws_s[8][kDgRows];
-  __shared__ __align__(16) float us_s[8][TP];
+  __shared__ __align__(16) float ws_s[BITS == 4 ? kDgRing : 1][kDgRows];  // int4: scales, saved from the raw ring
   __shared__ volatile int dead_s;
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int n0 = blockIdx.x * kDgRows;
   const int g_lo = blockIdx.y * p.gper;
   const int GL = min(p.gper, p.groups - g_lo);  // groups of this CTA
-  uint8_t* const tiles = smem + ((1024u - (smem_u32(smem) & 1023u)) & 1023u);
+  uint8_t* const a_ring = smem + ((1024u - (smem_u32(smem) & 1023u)) & 1023u);
+  uint8_t* const b_ring = a_ring + SA * A_SLOT;
+  uint8_t* const raw_base = b_ring + BN * B_SLOT;
   constexpr uint32_t kIdesc = dg_idesc(NCOL);
+  // "group k has been multiplied" / "... drained": slot k % 16 of the ring, its (k / 16)-th completion
+  auto wait_done = [&](int k) { return mbar_wait(smem_u32(&mma_done[k & (kDgRing - 1)]), (k / kDgRing) & 1); };
+  auto wait_drained = [&](int k) { return mbar_wait(smem_u32(&drained[k & (kDgRing - 1)]), (k / kDgRing) & 1); };
 
   if (warp == 0) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
@@ -92,13 +160,17 @@ decode_gemm_kernel(const DgParams p) {
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
   if (tid == 0) {
-    for (int i = 0; i < kDgStages; ++i) {
-      mbar_init(smem_u32(&full_bar[i]), 128);
-      mbar_init(smem_u32(&sfree_bar[i]), 1);
+    // (arrivals are one per warp, after the warp has synchronized: an arrival is an atomic
+    // operation on the barrier word, and hundreds of them per group are what a round would cost)
+    for (int i = 0; i < SA; ++i) mbar_init(smem_u32(&a_full[i]), 1);
+    for (int i = 0; i < BN; ++i) mbar_init(smem_u32(&b_full[i]), 1);
+    for (int i = 0; i < RAWN; ++i) {
+      mbar_init(smem_u32(&raw_full[i]), 1);
+      mbar_init(smem_u32(&raw_free[i]), 1);
     }
-    for (int i = 0; i < 2; ++i) {
-      mbar_init(smem_u32(&tfull_bar[i]), 1);
-      mbar_init(smem_u32(&tfree_bar[i]), DW * 32);
+    for (int i = 0; i < kDgRing; ++i) {
+      mbar_init(smem_u32(&mma_done[i]), 1);
+      mbar_init(smem_u32(&drained[i]), DW);
     }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     dead_s = 0;
@@ -107,81 +179,73 @@ decode_gemm_kernel(const DgParams p) {
   __syncthreads();
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const uint32_t tmem_base = tmem_base_s;
-  // the planes come from the kernel before this one
-  asm volatile("griddepcontrol.wait;" ::: "memory");
-  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  DG_T0();
 
-  if (warp >= 8 && warp < 12) {
-    // ------------------------------------------------------------------ fill
-    const int ft = tid - 256;  // 0..127 among the fill threads; also the row whose scale it stages
-    const int n = n0 + ft;
-    uint8_t* const raw_base = tiles + kDgStages * STAGE;
-    auto cp16 = [](uint32_t dst, const void* src, bool valid) {
-      const int bytes = valid ? 16 : 0;  // 0 source bytes: the 16 destination bytes are zero-filled
-      asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(bytes) : "memory");
-    };
-    auto issue = [&](const int j) -> bool {  // j: group index within this CTA's slice
-      const int st = j % kDgStages, g = g_lo + j;
-      if (j >= kDgStages && !mbar_wait(smem_u32(&sfree_bar[st]), ((j / kDgStages) - 1) & 1)) return false;
-      const uint32_t a_tile = smem_u32(tiles + st * STAGE), b_tile = a_tile + A_TILE;
-      if (BITS == 8) {
-#pragma unroll
-        for (int it = 0; it < 8; ++it) {  // piece (row, kc) = item / 8, item % 8
-          const int item = it * 128 + ft, row = item >> 3, kc = item & 7;
-          const int nn = n0 + row;
-          cp16(a_tile + (uint32_t)row * 128 + ((kc ^ (row & 7)) << 4),
-               p.codes + (int64_t)(nn < p.N ? nn : 0) * p.rowbytes + g * KT + kc * 16, nn < p.N);
+  if (warp == 18 || warp == 20) {
+    // ------------------------------------------------------------------ weight copies (two threads)
+    // Weights do not depend on the kernel before this one: their copies start at once. One
+    // contiguous block per group: the codes of the 128 rows, then their scales. Issuing a bulk
+    // copy occupies a thread for about 500 clocks, more than a group's bytes take to arrive:
+    // one thread takes the even groups, another the odd ones.
+    if (lane == 0) {
+      const uint8_t* my_codes = p.codes + (int64_t)blockIdx.x * p.groups * Plan::W_BLOCK;
+      for (int j = (warp - 18) >> 1; j < GL && !dead_s; j += 2) {
+        const uint8_t* src = my_codes + (int64_t)(g_lo + j) * Plan::W_BLOCK;
+        if (BITS == 4) {
+          const int slot = j % RAWN;
+          if (j >= RAWN && !mbar_wait(smem_u32(&raw_free[slot]), ((j / RAWN) - 1) & 1)) { dead_s = 1; break; }
+          mbar_expect_tx(smem_u32(&raw_full[slot]), Plan::W_BLOCK);
+          bulk_g2s(smem_u32(raw_base + slot * RAW_SLOT), src, Plan::W_BLOCK, smem_u32(&raw_full[slot]));
+        } else {
+          // the slot's scales are read by the drain of the group that used it last
+          if (j >= SA && !wait_drained(j - SA)) { dead_s = 1; break; }
+          mbar_expect_tx(smem_u32(&a_full[j % SA]), Plan::W_BLOCK);
+          bulk_g2s(smem_u32(a_ring + (j % SA) * A_SLOT), src, Plan::W_BLOCK, smem_u32(&a_full[j % SA]));
         }
-      } else {
-#pragma unroll
-        for (int it = 0; it < 4; ++it) {  // staging piece (row, q) = item / 4, item % 4
-          const int item = it * 128 + ft, row = item >> 2, q = item & 3;
-          const int nn = n0 + row;
-          cp16(smem_u32(raw_base + st * RAW + item * 16),
-               p.codes + (int64_t)(nn < p.N ? nn : 0) * p.rowbytes + g * (KT / 2) + q * 16, nn < p.N);
-        }
+        DG_EV(j, 7);
       }
-      // the group's plane rows: contiguous in global memory, piece (row, kc) = item / 8, item % 8
-      const int8_t* psrc = p.planes + (int64_t)g * B_TILE;
-#pragma unroll
-      for (int it = 0; it < (NCOL * 8 + 127) / 128; ++it) {
-        const int item = it * 128 + ft, row = item >> 3, kc = item & 7;
-        if (NCOL * 8 >= 128 || item < NCOL * 8)
-          cp16(b_tile + (uint32_t)row * 128 + ((kc ^ (row & 7)) << 4), psrc + item * 16, true);
+    }
+  } else if (warp == 19) {
+    // ------------------------------------------------------------------ plane copies (one thread)
+    // The activation planes and units are the output of the kernel before this one.
+    if (lane == 0) {
+      asm volatile("griddepcontrol.wait;" ::: "memory");
+      for (int j = 0; j < GL && !dead_s; ++j) {
+        // the slot's units are read by the drain of the group that used it last
+        if (j >= BN && !wait_drained(j - BN)) { dead_s = 1; break; }
+        mbar_expect_tx(smem_u32(&b_full[j % BN]), Plan::B_BLOCK);
+        bulk_g2s(smem_u32(b_ring + (j % BN) * B_SLOT), p.planes + (int64_t)(g_lo + j) * Plan::B_BLOCK, Plan::B_BLOCK,
+                 smem_u32(&b_full[j % BN]));
+        DG_EV(j, 2);
       }
-      {
-        const float* ssrc = p.scale_tiles + ((int64_t)((n < p.N ? n : 0) >> 2) * p.groups + g) * 4 + (n & 3);
-        const int bytes = n < p.N ? 4 : 0;
-        asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;"
-                     ::"r"(smem_u32(&ws_s[j & 7][ft])), "l"(ssrc), "r"(bytes) : "memory");
-      }
-      if (ft < TP / 4) cp16(smem_u32(&us_s[j & 7][ft * 4]), p.units + (int64_t)g * TP + ft * 4, true);
-      asm volatile("cp.async.commit_group;" ::: "memory");
-      return true;
-    };
-    bool ok = true;
-    for (int j = 0; j < kDgAhead && j < GL && ok; ++j) ok = issue(j);
-    for (int j = 0; j < GL && ok; ++j) {
-      const int st = j % kDgStages;
-      if (dead_s) break;
-      // the copies of group j are complete once at most (groups issued after j) are pending
-      const int after = min(kDgAhead - 1, GL - 1 - j);
-      if (after >= 2) asm volatile("cp.async.wait_group 2;" ::: "memory");
-      else if (after == 1) asm volatile("cp.async.wait_group 1;" ::: "memory");
-      else asm volatile("cp.async.wait_group 0;" ::: "memory");
-      if (BITS == 4) {
-        uint8_t* a_tile = tiles + st * STAGE;
-#pragma unroll
-        for (int it = 0; it < 4; ++it) {
-          const int item = it * 128 + ft, row = item >> 2, q = item & 3;
-          const uint4 v = *reinterpret_cast<const uint4*>(raw_base + st * RAW + item * 16);
+    }
+  } else if (warp >= 8 && warp < 16) {
+    // ------------------------------------------------------------------ widen (int4 only)
+    // A group's way through a warp here is mostly latency (barrier operations, the proxy fence),
+    // so each warp widens every eighth group by itself and eight groups are under way at once.
+    if (BITS == 4) {
+      for (int j = warp - 8; j < GL; j += kDgWidenWarps) {
+        const int st = j % SA, slot = j % RAWN;
+        if (dead_s) break;
+        { DG_T0(); if (!mbar_wait(smem_u32(&raw_full[slot]), (j / RAWN) & 1)) { dead_s = 1; break; } if (lane == 0) DG_ADD(0); }
+        if (lane == 0) DG_EV(j, 0);
+        if (j >= SA && !wait_done(j - SA)) { dead_s = 1; break; }
+        DG_T0();
+        uint8_t* a_tile = a_ring + st * A_SLOT;
+        const uint8_t* raw = raw_base + slot * RAW_SLOT;  // [128 rows][64 bytes], then 128 scales
+        // the scales outlive the raw slot: the drain reads them after the MMAs
+        *reinterpret_cast<float4*>(&ws_s[j & (kDgRing - 1)][lane * 4]) = *reinterpret_cast<const float4*>(raw + RAW + lane * 16);
+#pragma unroll 4
+        for (int it = 0; it < 16; ++it) {
+          const int item = it * 32 + lane, row = item >> 2, q = item & 3;
+          const uint4 v = *reinterpret_cast<const uint4*>(raw + item * 16);
           const unsigned w4[4] = {v.x, v.y, v.z, v.w};
           unsigned o[8];
 #pragma unroll
           for (int i = 0; i < 4; ++i) {
             // word of 8 nibbles (code + 8): even positions and odd positions as bytes 16 * code,
-            // interleaved back into K order. A zero-filled row (beyond N) becomes bytes -128:
-            // its outputs are never stored.
+            // interleaved back into K order. A row beyond N arrives as zeros and becomes
+            // bytes -128: its outputs are never stored.
             const unsigned ev = ((w4[i] << 4) & 0xF0F0F0F0u) ^ 0x80808080u;
             const unsigned od = (w4[i] & 0xF0F0F0F0u) ^ 0x80808080u;
             o[2 * i] = __byte_perm(ev, od, 0x5140);      // codes 0..3 of the word
@@ -191,31 +255,39 @@ decode_gemm_kernel(const DgParams p) {
           *reinterpret_cast<uint4*>(rowp + (((2 * q) ^ (row & 7)) << 4)) = make_uint4(o[0], o[1], o[2], o[3]);
           *reinterpret_cast<uint4*>(rowp + (((2 * q + 1) ^ (row & 7)) << 4)) = make_uint4(o[4], o[5], o[6], o[7]);
         }
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic writes -> MMA reads
+        __syncwarp();
+        if (lane == 0) {
+          mbar_arrive(smem_u32(&a_full[st]));
+          mbar_arrive(smem_u32(&raw_free[slot]));
+        }
+        if (lane == 0) { DG_ADD(1); DG_EV(j, 1); }
       }
-      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic / cp.async writes -> MMA reads
-      mbar_arrive(smem_u32(&full_bar[st]));
-      if (j + kDgAhead < GL) ok = issue(j + kDgAhead);
     }
-    if (!ok) dead_s = 1;
-    asm volatile("cp.async.wait_group 0;" ::: "memory");
-  } else if (warp == 12) {
+  } else if (warp == 16 || warp == 17) {
     // ------------------------------------------------------------------ MMA issue
+    // Two issuing threads, one for the even groups and one for the odd ones (a group has an
+    // accumulator of its own): issuing a group's four MMAs and its commit takes one thread
+    // longer than the group's bytes take to arrive.
     if (lane == 0) {
-      for (int j = 0; j < GL; ++j) {
-        const int st = j % kDgStages, tb = j & 1;
+      for (int j = warp - 16; j < GL; j += 2) {
+        const int tb = j % NACC;
         if (dead_s) break;
-        if (!mbar_wait(smem_u32(&full_bar[st]), (j / kDgStages) & 1)) { dead_s = 1; break; }
-        if (j >= 2 && !mbar_wait(smem_u32(&tfree_bar[tb]), ((j >> 1) - 1) & 1)) { dead_s = 1; break; }
+        { DG_T0(); if (!mbar_wait(smem_u32(&a_full[j % SA]), (j / SA) & 1) || !mbar_wait(smem_u32(&b_full[j % BN]), (j / BN) & 1)) { dead_s = 1; break; } if (warp == 16) DG_ADD(4); }
+        { DG_T0(); if (j >= NACC && !wait_drained(j - NACC)) { dead_s = 1; break; } if (warp == 16) DG_ADD(5); }
+        DG_T0();
+        DG_EV(j, 3);
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        const uint32_t a_addr = smem_u32(tiles + st * STAGE), b_addr = a_addr + A_TILE;
+        const uint64_t da = smem_desc_sw128(smem_u32(a_ring + (j % SA) * A_SLOT));
+        const uint64_t db = smem_desc_sw128(smem_u32(b_ring + (j % BN) * B_SLOT));
 #pragma unroll
         for (int s = 0; s < 4; ++s) {
-          // 32 bytes of K per MMA: the start address moves along the 128-byte row
-          mma_i8(tmem_base + tb * NCOL, smem_desc_sw128(a_addr + s * 32), smem_desc_sw128(b_addr + s * 32),
-                 kIdesc, s > 0);
+          // 32 bytes of K per MMA: the start address (in 16-byte units) moves along the 128-byte row
+          mma_i8(tmem_base + tb * NCOL, da + 2 * s, db + 2 * s, kIdesc, s > 0);
         }
-        mma_commit(smem_u32(&sfree_bar[st]));
-        mma_commit(smem_u32(&tfull_bar[tb]));
+        mma_commit(smem_u32(&mma_done[j & (kDgRing - 1)]));
+        DG_EV(j, 4);
+        if (warp == 16) DG_ADD(6);
       }
     }
   } else if (warp < DW) {
@@ -227,12 +299,16 @@ decode_gemm_kernel(const DgParams p) {
     const int row = quarter * 32 + lane, nrow = n0 + row;
     bool dead = false;
     for (int j = 0; j < GL; ++j) {
-      const int tb = j & 1;
+      const int tb = j % NACC, ring = j & (kDgRing - 1);
       if (dead_s) { dead = true; break; }
-      if (!mbar_wait(smem_u32(&tfull_bar[tb]), (j >> 1) & 1)) { dead_s = 1; dead = true; break; }
+      { DG_T0(); if (!wait_done(j)) { dead_s = 1; dead = true; break; } if (tid == 0) DG_ADD(8); }
+      DG_T0();
+      if (tid == 0) DG_EV(j, 5);
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      // (the scales of group j were complete before its tiles were handed to the MMA thread)
-      const float wsx = ws_s[j & 7][row] * (BITS == 4 ? 0.0625f : 1.f);  // 1/16: nibbles ride as 16 * code
+      // the group's scales (behind its codes, or saved by the widening warps) and units (behind its planes)
+      const float* ws = BITS == 8 ? reinterpret_cast<const float*>(a_ring + (j % SA) * A_SLOT + A_TILE) : ws_s[BITS == 4 ? ring : 0];
+      const float* us = reinterpret_cast<const float*>(b_ring + (j % BN) * B_SLOT + B_TILE);
+      const float wsx = ws[row] * (BITS == 4 ? 0.0625f : 1.f);  // 1/16: nibbles ride as 16 * code
       const uint32_t taddr = tmem_base + tb * NCOL + ((uint32_t)(quarter * 32) << 16) + t0;
 #pragma unroll
       for (int c0 = 0; c0 < TPH; c0 += CH) {
@@ -242,7 +318,7 @@ decode_gemm_kernel(const DgParams p) {
         tmem_ld_wait();
 #pragma unroll
         for (int q = 0; q < CH; q += 4) {
-          const float4 u = *reinterpret_cast<const float4*>(&us_s[j & 7][t0 + c0 + q]);
+          const float4 u = *reinterpret_cast<const float4*>(us + t0 + c0 + q);
           const float uu[4] = {u.x, u.y, u.z, u.w};
 #pragma unroll
           for (int e = 0; e < 4; ++e)
@@ -250,8 +326,13 @@ decode_gemm_kernel(const DgParams p) {
         }
       }
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-      mbar_arrive(smem_u32(&tfree_bar[tb]));
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&drained[ring]));
+      if (tid == 0) { DG_ADD(9); DG_EV(j, 6); }
     }
+    // the buffer the sums go to may still be read by a kernel before this one: nothing of this
+    // kernel is stored before its predecessors are complete
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     if (!dead && nrow < p.N) {
       float* dst = p.partial + ((int64_t)blockIdx.y * p.T + t0) * p.N + nrow;
 #pragma unroll
@@ -261,6 +342,8 @@ decode_gemm_kernel(const DgParams p) {
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  if (tid == 0) DG_ADD(12);
   if (tid == 0 && dead_s) atomicExch(p.error_word, 1);
   if (warp == 0) {
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -292,8 +375,7 @@ __device__ __forceinline__ void ap_load16(const __nv_bfloat16* base, int k0, int
 
 __global__ void __launch_bounds__(kApThreads)
 act_planes_kernel(const __nv_bfloat16* __restrict__ x, int ldx, const __nv_bfloat16* __restrict__ norm_weight,
-                  float norm_eps, int8_t* __restrict__ planes, float* __restrict__ units, int T, int TP, int K,
-                  int groups) {
+                  float norm_eps, uint8_t* __restrict__ planes, int block_bytes, int T, int TP, int K, int groups) {
   __shared__ float red_s[kApThreads / 32];
   const int t = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int nchunk = groups * 8;  // 16-column chunks of the padded row
@@ -363,10 +445,16 @@ act_planes_kernel(const __nv_bfloat16* __restrict__ x, int ldx, const __nv_bfloa
     }
     if (valid) {
       const int g = ch >> 3, sub = ch & 7;
-      int8_t* hp = planes + ((int64_t)g * 2 * TP + t) * KT + sub * 16;
+      // a group's block: the plane rows as the MMA reads them from shared memory -- 16-byte piece
+      // `sub` of row r sits at piece (sub ^ (r & 7)), the 128-byte swizzle -- then the TP units;
+      // one linear bulk copy stages it
+      uint8_t* blk = planes + (int64_t)g * block_bytes;
+      uint8_t* hp = blk + (int64_t)t * KT + ((sub ^ (t & 7)) << 4);
       *reinterpret_cast<uint4*>(hp) = make_uint4(hw[0], hw[1], hw[2], hw[3]);
       *reinterpret_cast<uint4*>(hp + (int64_t)TP * KT) = make_uint4(lw[0], lw[1], lw[2], lw[3]);
-      if (sub == 0) units[(int64_t)g * TP + t] = live && amax > 0.f ? __uint_as_float((unsigned)(127 + e - 14) << 23) : 0.f;
+      if (sub == 0)
+        reinterpret_cast<float*>(blk + (int64_t)2 * TP * KT)[t] =
+            live && amax > 0.f ? __uint_as_float((unsigned)(127 + e - 14) << 23) : 0.f;
     }
   }
 }
@@ -417,6 +505,32 @@ decode_finish_kernel(const float* __restrict__ partial, int splits, int T, int N
   }
 }
 
+// ---------------------------------------------------------------------------------------------
+// Streaming layout -> the layout the decode GEMM reads: per tile of 128 weight rows and per
+// scale group one contiguous block, so that a CTA fetches a group with ONE linear bulk copy
+// (fetching 128 pieces of 64 or 128 bytes a whole weight row apart limits an SM to a fraction
+// of its share of the HBM bandwidth). int8 blocks are the shared-memory image the MMA reads
+// (16-byte piece kc of row r at piece kc ^ (r & 7)); int4 blocks are the nibble bytes, 64 per
+// row; rows beyond N are zeros. Scales: [tile][G][128] fp32.
+__global__ void tile_weight_kernel(const uint8_t* __restrict__ codes, const float* __restrict__ scale_tiles,
+                                   uint8_t* __restrict__ out, int N, int groups, int rowbytes, int bits) {
+  const int tile = blockIdx.x, g = blockIdx.y;
+  const int gb = KT * bits / 8, pieces = gb / 16;  // bytes and 16-byte pieces of a group in a row
+  uint8_t* dst = out + ((int64_t)tile * groups + g) * (kDgRows * gb + kScaleBytes);
+  for (int i = threadIdx.x; i < kDgRows * pieces; i += blockDim.x) {
+    const int r = i / pieces, kc = i % pieces, n = tile * kDgRows + r;
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (n < N) v = *reinterpret_cast<const uint4*>(codes + (int64_t)n * rowbytes + g * gb + kc * 16);
+    const int pos = bits == 8 ? (kc ^ (r & 7)) : kc;
+    *reinterpret_cast<uint4*>(dst + r * gb + pos * 16) = v;
+  }
+  float* sdst = reinterpret_cast<float*>(dst + kDgRows * gb);
+  for (int r = threadIdx.x; r < kDgRows; r += blockDim.x) {
+    const int n = tile * kDgRows + r;
+    sdst[r] = n < N ? scale_tiles[((int64_t)(n >> 2) * groups + g) * 4 + (n & 3)] : 0.f;
+  }
+}
+
 template <typename Kern, typename... Args>
 int launch_dep(Kern kern, dim3 grid, dim3 block, size_t smem, cudaStream_t s, int pdl, const char* what, Args... args) {
   cudaLaunchConfig_t cfg = {};
@@ -455,19 +569,18 @@ int choose_splits(int tiles, int groups) {
   return best;
 }
 
+int plane_block_bytes(int TP) { return 2 * TP * KT + (TP * 4 + 127) / 128 * 128; }
+
 struct Workspace {
-  int8_t* planes;
-  float* units;
+  uint8_t* planes;
   float* partial;
   int64_t bytes;
 };
 Workspace carve(void* base, int TP, int M, int N, int groups, int splits) {
   Workspace w;
   int64_t off = 0;
-  w.planes = reinterpret_cast<int8_t*>(reinterpret_cast<uint8_t*>(base) + off);
-  off += (int64_t)groups * 2 * TP * KT;
-  w.units = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(base) + off);
-  off += ((int64_t)groups * TP * 4 + 255) / 256 * 256;
+  w.planes = reinterpret_cast<uint8_t*>(base) + off;
+  off += ((int64_t)groups * plane_block_bytes(TP) + 255) / 256 * 256;
   w.partial = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(base) + off);
   off += (int64_t)splits * M * N * 4;
   w.bytes = off;
@@ -499,10 +612,10 @@ int run_decode_gemm(const lq_gemv_args& a, cudaStream_t s) {
   }
   if (const int rc = launch_dep(act_planes_kernel, dim3((unsigned)TP), dim3(kApThreads), 0, s, a.pdl, "lq_wq_gemv_fused",
                                 (const __nv_bfloat16*)a.x, a.ldx, (const __nv_bfloat16*)a.norm_weight, a.norm_eps,
-                                w.planes, w.units, a.M, TP, a.K, groups))
+                                w.planes, plane_block_bytes(TP), a.M, TP, a.K, groups))
     return rc;
   DgParams p;
-  p.codes = (const uint8_t*)a.codes; p.scale_tiles = a.scale_tiles; p.planes = w.planes; p.units = w.units;
+  p.codes = (const uint8_t*)a.codes; p.planes = w.planes;
   p.partial = w.partial; p.T = a.M; p.N = a.N; p.groups = groups; p.rowbytes = a.Kd * a.bits / 8;
   p.gper = (groups + splits - 1) / splits; p.error_word = (int*)err_ptr;
   const dim3 grid((unsigned)tiles, (unsigned)splits);
@@ -510,7 +623,7 @@ int run_decode_gemm(const lq_gemv_args& a, cudaStream_t s) {
 #define LQ_DG_CASE(B, TPV)                                                                              \
   if (a.bits == B && TP == TPV) {                                                                       \
     auto kern = decode_gemm_kernel<B, TPV>;                                                             \
-    const size_t smem = (size_t)kDgStages * (kDgRows * KT + 2 * TPV * KT) + (B == 4 ? (size_t)kDgStages * kDgRows * (KT / 2) : 0) + 1024; \
+    const size_t smem = DgPlan<B, TPV>::SMEM;                                                           \
     if (const int rs = ensure_smem_limit(reinterpret_cast<const void*>(kern), (int)smem, "lq_wq_gemv_fused")) return rs; \
     rc = launch_dep(kern, grid, dim3(kDgThreads), smem, s, a.pdl, "lq_wq_gemv_fused", p);               \
   }
@@ -550,4 +663,41 @@ extern "C" int lq_decode_gemm_device_error(void) {
   if (cudaMemcpy(&value, ptr, sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess) return -1;
   if (value != 0) cudaMemset(ptr, 0, sizeof(int));
   return value;
+}
+
+#ifdef LQ_DIAGNOSTICS
+// Diagnostic builds only: copies the per-role clock sums out (256 CTAs x 16 slots) and clears them.
+extern "C" int lq_decode_gemm_trace(long long* out_host) {
+  void* ptr = nullptr;
+  if (cudaGetSymbolAddress(&ptr, lq::g_dg_trace) != cudaSuccess) return -1;
+  if (cudaMemcpy(out_host, ptr, sizeof(long long) * 128 * 8, cudaMemcpyDeviceToHost) != cudaSuccess) return -1;
+  cudaMemset(ptr, 0, sizeof(long long) * 128 * 8);
+  return 0;
+}
+extern "C" int lq_decode_gemm_diag(unsigned long long* out_host) {
+  void* ptr = nullptr;
+  if (cudaGetSymbolAddress(&ptr, lq::g_dg_diag) != cudaSuccess) return -1;
+  if (cudaMemcpy(out_host, ptr, sizeof(unsigned long long) * 256 * 16, cudaMemcpyDeviceToHost) != cudaSuccess) return -1;
+  cudaMemset(ptr, 0, sizeof(unsigned long long) * 256 * 16);
+  return 0;
+}
+#endif
+
+extern "C" int64_t lq_tile_weight_bytes(int N, int Kd, int bits) {
+  if (N <= 0 || Kd <= 0 || Kd % 128 != 0 || (bits != 4 && bits != 8)) return 0;
+  const int64_t tiles = (N + lq::kDgRows - 1) / lq::kDgRows, groups = Kd / 128;
+  return tiles * groups * (lq::kDgRows * (lq::KT * bits / 8) + lq::kScaleBytes);
+}
+
+extern "C" int lq_tile_weight(const void* codes, const float* scale_tiles, void* out, int N, int Kd, int bits,
+                              void* stream) {
+  using namespace lq;
+  LQ_REQUIRE(codes && scale_tiles && out, LQ_ERR_ARG, "null tensor pointer");
+  LQ_REQUIRE(N > 0 && Kd > 0 && Kd % 128 == 0 && (bits == 4 || bits == 8), LQ_ERR_ARG,
+             "tile layout: N > 0, Kd a positive multiple of 128, 4 or 8 bits");
+  LQ_REQUIRE(((uintptr_t)codes % 16) == 0 && ((uintptr_t)out % 16) == 0, LQ_ERR_ARG, "codes must be 16-byte aligned");
+  const dim3 grid((unsigned)((N + kDgRows - 1) / kDgRows), (unsigned)(Kd / 128));
+  tile_weight_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>((const uint8_t*)codes, scale_tiles, (uint8_t*)out, N,
+                                                             Kd / 128, Kd * bits / 8, bits);
+  return check_launch("lq_tile_weight");
 }

@@ -68,7 +68,6 @@ struct MmaParams {
   int pdl;
   int* error_word;
   unsigned long long* debug;
-  WarmSpans warm;  // memory to pull into L2 for later kernels
 };
 
 __device__ __forceinline__ unsigned long long global_ns() {
@@ -199,9 +198,6 @@ gemv_mma_kernel(const MmaParams p) {
   if (threadIdx.x == 0) {
     for (; next_it < nit && next_it < p.stages; ++next_it, next_row += p.R) request(next_it, next_it, next_row);
   }
-  // spans for later kernels, requested by the last warp while thread 0 asks for the first stages
-  if (warp == W - 1 && W > 1) l2_warm(p.warm, (long long)blockIdx.x * 32 + lane, (long long)gridDim.x * 32);
-  else if (W == 1 && lane != 0) l2_warm(p.warm, (long long)blockIdx.x * 31 + (lane - 1), (long long)gridDim.x * 31);
 
   // ------------------------------------------------------------------ consumer warps
   const int tid = threadIdx.x;  // 0 .. consumers-1
@@ -714,7 +710,6 @@ int run_mma(const lq_gemv_args& a, int* error_word, unsigned long long* debug, c
   p.M = a.M; p.N = a.N; p.K = a.K; p.Kd = a.Kd; p.rowbytes = a.Kd * a.bits / 8; p.groups = a.Kd / 128;
   p.ldo = a.ldo > 0 ? a.ldo : (a.epilogue == 1 ? a.N / 2 : a.N);
   p.pdl = a.pdl; p.error_word = error_word; p.debug = debug;
-  if (const int rw = take_warm_spans(a.warm, LQ_MAX_WARM_SPANS, &p.warm, "lq_wq_gemv_fused")) return rw;
   Plan q;
   LQ_REQUIRE(make_plan(a.M, a.Kd, a.span, a.bits, &q), LQ_ERR_UNSUPPORTED, "shape outside the tensor-core GEMV");
   const int nb = q.nb;

@@ -291,7 +291,6 @@ extern "C" int lq_wq_gemv_fused(const lq_gemv_args* a, void* stream) {
     if (tp->wait_cycles > 0) p.tp_wait = tp->wait_cycles;
   }
   LQ_REQUIRE(p.error_word != nullptr, LQ_ERR_LAUNCH, "cannot resolve the device error word");
-  if (const int rw = take_warm_spans(a->warm, LQ_MAX_WARM_SPANS, &p.warm, "lq_wq_gemv_fused")) return rw;
   p.S = (p.rowbytes + 511) / 512;
   int spw = 1;
   while (spw <= 4 && (p.S + spw - 1) / spw > kMaxWarps) spw *= 2;

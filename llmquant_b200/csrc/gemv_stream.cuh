@@ -78,7 +78,6 @@ struct GemvParams {
   float* tp_parts;
   __nv_bfloat16* tp_residual;
   long long tp_wait;
-  WarmSpans warm;  // memory to pull into L2 for later kernels
 };
 
 // Row-parallel epilogue of a tensor-parallel linear: lane (m, u) of the warp holds output
@@ -434,9 +433,6 @@ gemv_stream_kernel(const GemvParams p) {
 
   // ------------------------------------------------------------ producer warp
   if (warp == KW) {
-    // spans for later kernels: requested by the lanes that have nothing else to do, as early
-    // as the CTA exists (lane 0's first stage requests are independent of them)
-    if (lane != 0) l2_warm(p.warm, (long long)blockIdx.x * 31 + (lane - 1), (long long)gridDim.x * 31);
     if (lane == 0) {
       int s = 0, wrap = 0;  // ring slot and how often the ring has wrapped, kept without divisions
       for (int it = 0; it < nb; ++it) {

@@ -618,8 +618,7 @@ attn_fused_kernel(const __nv_bfloat16* __restrict__ qkv, const __nv_bfloat16* __
                   const __nv_bfloat16* __restrict__ sin_t, int8_t* kc, int8_t* vc, float* ks, float* vs,
                   __nv_bfloat16* __restrict__ out, float* part_o, float* part_ml, int* tickets,
                   int Hq, int Hkv, int Tmax, int table_len, const int64_t* pos_dev, int64_t pos_host,
-                  float scaling, float qmin, float qmax, int* error_word, unsigned long long* debug,
-                  const WarmSpans warm) {
+                  float scaling, float qmin, float qmax, int* error_word, unsigned long long* debug) {
 #ifdef LQ_DIAGNOSTICS
 #define ATT_STAMP(slot) do { if (debug != nullptr && threadIdx.x == 0) { unsigned long long t_; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_)); debug[((size_t)(blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x) * 8 + (slot)] = t_; } } while (0)
 #else
@@ -669,11 +668,6 @@ attn_fused_kernel(const __nv_bfloat16* __restrict__ qkv, const __nv_bfloat16* __
     mbar_init(bar_a, 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     if (t_lo < t_hi) issue(t_lo);
-  }
-  // weights the kernels after this one will stream: this kernel leaves HBM almost idle
-  if (warp == NT / 32 - 1) {
-    const long long cta = ((long long)blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x;
-    l2_warm(warm, cta * 32 + lane, (long long)gridDim.x * gridDim.y * gridDim.z * 32);
   }
 
   asm volatile("griddepcontrol.wait;" ::: "memory");
@@ -1048,8 +1042,7 @@ attn_mma_kernel(const __nv_bfloat16* __restrict__ qkv, const __nv_bfloat16* __re
                 const __nv_bfloat16* __restrict__ sin_t, int8_t* kc, int8_t* vc, float* ks, float* vs,
                 __nv_bfloat16* __restrict__ out, float* part_o, float* part_ml, int* tickets,
                 int Hq, int Hkv, int Tmax, int table_len, const int64_t* pos_dev, int64_t pos_host,
-                float scaling, float qmin, float qmax, int* error_word, unsigned long long* debug,
-                const WarmSpans warm) {
+                float scaling, float qmin, float qmax, int* error_word, unsigned long long* debug) {
 #ifdef LQ_DIAGNOSTICS
 #define ATT_STAMP(slot) do { if (debug != nullptr && threadIdx.x == 0) { unsigned long long t_; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_)); debug[((size_t)(blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x) * 8 + (slot)] = t_; } } while (0)
 #else
@@ -1059,8 +1052,8 @@ attn_mma_kernel(const __nv_bfloat16* __restrict__ qkv, const __nv_bfloat16* __re
   constexpr int HALF = D / 2, CAP = CL ? kClusterCap : kMmaCap, PK = D;  // unpadded rows: one bulk copy per chunk
   constexpr int KS = D / 32;   // k-steps of the score MMA
   constexpr int DT = D / 8;    // n-tiles of the value MMA
-  extern __shared__ __align__(128) uint8_t stage[];  // K rows [CAP][PK], then V rows [CAP][PK]
-  __shared__ __align__(8) uint64_t bar;
+  extern __shared__ __align__(128) uint8_t stage[];  // per staging area: K rows [CAP][PK], then V rows [CAP][PK]
+  __shared__ __align__(8) uint64_t bar[2];
   __shared__ float sk_s[CAP], sv_s[CAP];
   __shared__ float q_s[G][D];                       // rotated query heads (bf16 values)
   __shared__ __align__(16) int8_t qhi_s[G][D], qlo_s[G][D];
@@ -1089,32 +1082,32 @@ attn_mma_kernel(const __nv_bfloat16* __restrict__ qkv, const __nv_bfloat16* __re
   const int t_lo = split * per;
   const int t_hi = (int)min((int64_t)(t_lo + per), len);
   const int64_t head_row = ((int64_t)b * Hkv + kvh) * Tmax;
-  const uint32_t bar_a = smem_u32(&bar);
-  uint8_t* k_st = stage;
-  uint8_t* v_st = stage + (size_t)CAP * PK;
+  // Two staging areas (one in the cluster variant, whose chunks are larger): the copies of the
+  // next chunk travel while this one is multiplied, which is what a CTA that walks several
+  // chunks -- a batch of sequences, a long context -- spends most of its time on otherwise.
+  constexpr int NST = CL ? 1 : 2;
+  constexpr size_t STAGE_BYTES = 2 * (size_t)CAP * PK;
+  const uint32_t bar_a = smem_u32(&bar[0]);
 
-  auto issue = [&](int c_lo) {  // warp 0: the chunk's K rows and V rows, one bulk copy each
+  auto issue = [&](int c_lo, int st) {  // warp 0: the chunk's K rows and V rows, one bulk copy each
     const int n = min(CAP, t_hi - c_lo);
     if (lane == 0) {
       const uint32_t bytes = (uint32_t)n * D;
-      mbar_expect_tx(bar_a, 2u * bytes);
-      bulk_g2s(smem_u32(k_st), kc + (head_row + c_lo) * D, bytes, bar_a);
-      bulk_g2s(smem_u32(v_st), vc + (head_row + c_lo) * D, bytes, bar_a);
+      const uint32_t dst = smem_u32(stage + st * STAGE_BYTES);
+      mbar_expect_tx(bar_a + 8 * st, 2u * bytes);
+      bulk_g2s(dst, kc + (head_row + c_lo) * D, bytes, bar_a + 8 * st);
+      bulk_g2s(dst + CAP * PK, vc + (head_row + c_lo) * D, bytes, bar_a + 8 * st);
     }
     __syncwarp();
   };
   if (threadIdx.x == 0) {
     mbar_init(bar_a, 1);
+    mbar_init(bar_a + 8, 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   __syncthreads();
   // cached rows and the cursor are older than the kernel ahead of this one: prefetch first
-  if (warp == 0 && t_lo < t_hi) issue(t_lo);
-  // weights the kernels after this one will stream: this kernel leaves HBM almost idle
-  if (warp == NW - 1) {
-    const long long cta = ((long long)blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x;
-    l2_warm(warm, cta * 32 + lane, (long long)gridDim.x * gridDim.y * gridDim.z * 32);
-  }
+  if (warp == 0 && t_lo < t_hi) issue(t_lo, 0);
   // so are the rotary tables and the cached rows' scales: the pieces this thread needs first
   // are requested before the wait for the producer of q|k|v, off the dependent chain
   const int64_t tpos = pos < table_len ? pos : table_len - 1;
@@ -1234,17 +1227,25 @@ attn_mma_kernel(const __nv_bfloat16* __restrict__ qkv, const __nv_bfloat16* __re
   for (int dt = 0; dt < DT; ++dt) { o[dt][0] = o[dt][1] = o[dt][2] = o[dt][3] = 0.f; }
 
   bool dead = false;
-  int phase = 0;
+  int st = 0, phases = 0;  // staging area of the chunk at hand; one phase bit per area
   for (int c_lo = t_lo; c_lo < t_hi; c_lo += CAP) {
     const int n = min(CAP, t_hi - c_lo);
+    // the other area was released by the barrier that ended the round before: refill it now
+    if (NST == 2 && warp == 0 && c_lo + CAP < t_hi) issue(c_lo + CAP, st ^ 1);
     for (int i = threadIdx.x; i < n; i += NT) {
-      const bool pre = c_lo == t_lo && i == (int)threadIdx.x;  // the first NT scales of the first chunk are prefetched
+      const bool pre = i == (int)threadIdx.x;  // each thread's first scale of a chunk was requested a round ahead
       sk_s[i] = pre ? pre_sk : ks[head_row + c_lo + i];
       sv_s[i] = pre ? pre_sv : vs[head_row + c_lo + i];
     }
+    if (c_lo + CAP + (int)threadIdx.x < t_hi) {  // next chunk's: in flight during this chunk's products
+      pre_sk = ks[head_row + c_lo + CAP + threadIdx.x];
+      pre_sv = vs[head_row + c_lo + CAP + threadIdx.x];
+    }
     __syncthreads();
-    if (!mbar_wait(bar_a, phase)) { dead = true; break; }
-    phase ^= 1;
+    if (!mbar_wait(bar_a + 8 * st, (phases >> st) & 1)) { dead = true; break; }
+    phases ^= 1 << st;
+    const uint8_t* k_st = stage + st * STAGE_BYTES;
+    const uint8_t* v_st = k_st + (size_t)CAP * PK;
     if (c_lo == t_lo) ATT_STAMP(3);
     const int blocks = (n + 15) / 16;
     for (int blk = warp; blk < blocks; blk += NW) {
@@ -1295,8 +1296,9 @@ attn_mma_kernel(const __nv_bfloat16* __restrict__ qkv, const __nv_bfloat16* __re
         mma_bf16(o[dt], a0, a2, b0, b1);
       }
     }
-    __syncthreads();  // everyone is done with the stage before it is refilled
-    if (warp == 0 && c_lo + CAP < t_hi) issue(c_lo + CAP);
+    __syncthreads();  // everyone is done with the area before it is refilled
+    if (NST == 1 && warp == 0 && c_lo + CAP < t_hi) issue(c_lo + CAP, 0);
+    if (NST == 2) st ^= 1;
   }
   if (dead) {
     if (threadIdx.x == 0) atomicExch(error_word, 4);
@@ -1522,11 +1524,8 @@ extern "C" int lq_attn_decode_fused(const void* qkv, const void* cos_table, cons
                                     int8_t* k_codes, int8_t* v_codes, float* k_scales, float* v_scales,
                                     void* out, void* scratch, int B, int Hq, int Hkv, int D, int Tmax,
                                     int table_len, const int64_t* pos_dev, int64_t pos, int num_bits,
-                                    float scaling, int splits, int impl, const lq_span* warm, int n_warm,
-                                    int pdl, void* stream) {
+                                    float scaling, int splits, int impl, int pdl, void* stream) {
   using namespace lq;
-  WarmSpans ws;
-  if (const int rw = take_warm_spans(warm, n_warm, &ws, "lq_attn_decode_fused")) return rw;
   LQ_REQUIRE(num_bits >= 2 && num_bits <= 8, LQ_ERR_ARG, "num_bits must be in [2, 8], got %d", num_bits);
   LQ_REQUIRE(impl >= 0 && impl <= 3, LQ_ERR_ARG, "unknown attention implementation %d", impl);
   LQ_REQUIRE(B > 0 && Hq > 0 && Hkv > 0 && Hq % Hkv == 0 && Tmax > 0 && table_len > 0, LQ_ERR_ARG, "bad shape");
@@ -1565,7 +1564,7 @@ extern "C" int lq_attn_decode_fused(const void* qkv, const void* cos_table, cons
                     "lq_attn_decode_fused", (const __nv_bfloat16*)qkv, (const __nv_bfloat16*)cos_table, \
                     (const __nv_bfloat16*)sin_table, k_codes, v_codes, k_scales, v_scales,         \
                     (__nv_bfloat16*)out, part_o, part_ml, tickets, Hq, Hkv, Tmax, table_len, pos_dev, \
-                    pos, scaling, -qmax - 1.f, qmax, (int*)err_ptr, g_attn_timeline, ws);              \
+                    pos, scaling, -qmax - 1.f, qmax, (int*)err_ptr, g_attn_timeline);              \
     }                                                                                              \
   }
     LQ_CL_CASE(64, 1) LQ_CL_CASE(64, 2) LQ_CL_CASE(64, 4) LQ_CL_CASE(64, 8)
@@ -1577,7 +1576,8 @@ extern "C" int lq_attn_decode_fused(const void* qkv, const void* cos_table, cons
     return fail(LQ_ERR_UNSUPPORTED, "clusters of %d CTAs are not available for this shape on this device (head_dim %d, %d "
                 "query heads per KV head; the slice count must be 2, 4, 8 or 16)", splits, D, G);
   if (impl != LQ_ATTN_SIMT) {
-    const size_t msmem = 2 * (size_t)kMmaCap * D;
+    // K and V rows of a chunk; a second staging area only if a slice can span several chunks
+    const size_t msmem = ((Tmax + splits - 1) / splits > kMmaCap ? 2 : 1) * 2 * (size_t)kMmaCap * D;
     LQ_REQUIRE((size_t)splits * G * 4 + (size_t)(kMmaThreads / 32 + 1) * G * D * 4 + 64 <= msmem, LQ_ERR_ARG,
                "too many slices (%d) for the merge area of the attention kernel", splits);
 #define LQ_MMA_CASE(DD, GG)                                                                        \
@@ -1587,7 +1587,7 @@ extern "C" int lq_attn_decode_fused(const void* qkv, const void* cos_table, cons
                     "lq_attn_decode_fused", (const __nv_bfloat16*)qkv, (const __nv_bfloat16*)cos_table, \
                     (const __nv_bfloat16*)sin_table, k_codes, v_codes, k_scales, v_scales,         \
                     (__nv_bfloat16*)out, part_o, part_ml, tickets, Hq, Hkv, Tmax, table_len, pos_dev, \
-                    pos, scaling, -qmax - 1.f, qmax, (int*)err_ptr, g_attn_timeline, ws);              \
+                    pos, scaling, -qmax - 1.f, qmax, (int*)err_ptr, g_attn_timeline);              \
   }
     LQ_MMA_CASE(64, 1) LQ_MMA_CASE(64, 2) LQ_MMA_CASE(64, 4) LQ_MMA_CASE(64, 8)
     LQ_MMA_CASE(128, 1) LQ_MMA_CASE(128, 2) LQ_MMA_CASE(128, 4) LQ_MMA_CASE(128, 8)
@@ -1602,7 +1602,7 @@ extern "C" int lq_attn_decode_fused(const void* qkv, const void* cos_table, cons
                     "lq_attn_decode_fused", (const __nv_bfloat16*)qkv, (const __nv_bfloat16*)cos_table, \
                     (const __nv_bfloat16*)sin_table, k_codes, v_codes, k_scales, v_scales,         \
                     (__nv_bfloat16*)out, part_o, part_ml, tickets, Hq, Hkv, Tmax, table_len, pos_dev, \
-                    pos, scaling, -qmax - 1.f, qmax, (int*)err_ptr, g_attn_timeline, ws);                               \
+                    pos, scaling, -qmax - 1.f, qmax, (int*)err_ptr, g_attn_timeline);                               \
   }
   LQ_FUSED_CASE(64, 1) LQ_FUSED_CASE(64, 2) LQ_FUSED_CASE(64, 4) LQ_FUSED_CASE(64, 8)
   LQ_FUSED_CASE(128, 1) LQ_FUSED_CASE(128, 2) LQ_FUSED_CASE(128, 4) LQ_FUSED_CASE(128, 8)

@@ -26,14 +26,6 @@ DTYPE_ID = {torch.float32: LQ_F32, torch.float16: LQ_F16, torch.bfloat16: LQ_BF1
 _P, _I, _L = ctypes.c_void_p, ctypes.c_int, ctypes.c_int64
 _IP = ctypes.POINTER(ctypes.c_int)
 
-MAX_WARM_SPANS = 2
-
-
-class Span(ctypes.Structure):
-    """Mirror of `lq_span`: constant device memory a kernel pulls into L2 for later kernels."""
-
-    _fields_ = [("ptr", _P), ("bytes", _L)]
-
 # name -> argtypes; every function returns int status unless listed in _RESTYPE
 _SIGNATURES = {
     "lq_version": [],
@@ -76,25 +68,14 @@ _SIGNATURES.update({
     "lq_attn_fused_scratch_bytes": [_I, _I, _I, _I, _I],
     "lq_attn_device_error": [],
     "lq_attn_decode_fused": [_P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P, _L, _I,
-                             ctypes.c_float, _I, _I, ctypes.POINTER(Span), _I, _I, _P],
+                             ctypes.c_float, _I, _I, _I, _P],
     "lq_attn_decode_kv_i8_static": [_P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P, _L, _I,
                                     ctypes.c_float, _I, _I, _P],
 })
 _RESTYPE = {"lq_last_error": ctypes.c_char_p, "lq_attn_decode_scratch_bytes": ctypes.c_int64,
             "lq_attn_decode_static_scratch_bytes": ctypes.c_int64,
             "lq_attn_fused_scratch_bytes": ctypes.c_int64,
-            "lq_decode_gemm_workspace_bytes": ctypes.c_int64}
-
-
-def spans(tensors):
-    """(array of Span, count) for up to MAX_WARM_SPANS tensors (None / empty = no spans)."""
-    tensors = [t for t in (tensors or ()) if t is not None]
-    if len(tensors) > MAX_WARM_SPANS:
-        raise ValueError(f"at most {MAX_WARM_SPANS} spans per launch, got {len(tensors)}")
-    arr = (Span * MAX_WARM_SPANS)()
-    for i, t in enumerate(tensors):
-        arr[i].ptr, arr[i].bytes = t.data_ptr(), t.numel() * t.element_size()
-    return arr, len(tensors)
+            "lq_decode_gemm_workspace_bytes": ctypes.c_int64, "lq_tile_weight_bytes": ctypes.c_int64}
 
 
 class GemvArgs(ctypes.Structure):
@@ -105,7 +86,7 @@ class GemvArgs(ctypes.Structure):
         ("codes", _P), ("scale_tiles", _P), ("bias", _P), ("residual", _P), ("out", _P),
         ("out_dtype", _I), ("M", _I), ("N", _I), ("K", _I), ("Kd", _I), ("span", _I),
         ("bits", _I), ("epilogue", _I), ("variant", _I), ("pdl", _I), ("tp", _P), ("ldo", _I),
-        ("warm", Span * MAX_WARM_SPANS), ("workspace", _P), ("workspace_bytes", _L),
+        ("workspace", _P), ("workspace_bytes", _L),
     ]
 
 
@@ -124,6 +105,8 @@ _SIGNATURES["lq_wq_gemv_fused"] = [ctypes.POINTER(GemvArgs), _P]
 _SIGNATURES["lq_glue_device_error"] = []
 _SIGNATURES["lq_decode_gemm_device_error"] = []
 _SIGNATURES["lq_decode_gemm_workspace_bytes"] = [_I, _I, _I]
+_SIGNATURES["lq_tile_weight_bytes"] = [_I, _I, _I]
+_SIGNATURES["lq_tile_weight"] = [_P, _P, _P, _I, _I, _I, _P]
 _SIGNATURES["lq_next_token_tp"] = [_P, _L, _I, _I, _P, _L, _I, _P, _P, _P, _L, _P, _P, _I, _L, _I, _P]
 
 

@@ -33,9 +33,10 @@ GEMV_VARIANT = 0  # 0 = library default; see lq_wq_gemv_stream
 # materialising them; above that, and for narrow outputs (too few 128 x 128 tiles to fill the
 # GPU), dequantize + library GEMM is still the faster of the two (measured crossover: between
 # 512 and 768 rows at the Llama-3-8B shapes; 1024 output features lose at every row count).
-# output-row slice of a weight that the launches of one row-block sweep share through L2
-L2_SLICE_BYTES = 0  # 0 = whole passes (see _gemv_row_blocks)
 DECODE_GEMM_MAX_ROWS = 64
+# from this many rows the decode GEMM is the default (measured on B200 at the Llama-3-8B shapes,
+# 8 rows: q|k|v 11 vs 25 us, o 9 vs 13, gate|up 32 vs 44, down 17 vs 45 for the GEMV variants)
+DECODE_GEMM_MIN_ROWS = 5
 PREFILL_EXACT_MAX_ROWS = 16
 PREFILL_TENSOR_CORE_MAX_ROWS = 512
 PREFILL_TENSOR_CORE_MIN_FEATURES = 2048
@@ -140,6 +141,7 @@ class KernelQuantLinear(nn.Module):
             self.register_buffer("_qweight", qweight, persistent=False)
             self.register_buffer("_wscale", wscale, persistent=False)
         self._bias_bf16 = None
+        self._tiled = None  # the weight in the decode GEMM's tile-major layout, built on first use
 
     # ---- construction -----------------------------------------------------------------
     @classmethod
@@ -245,7 +247,7 @@ class KernelQuantLinear(nn.Module):
         return bool(self._stream and native.library().lq_gemv_tensor_core_ok(m, self._kd, self._span, self.num_bits))
 
     def gemv(self, flat, out_dtype=None, residual=None, variant=None, norm_weight=None,
-             norm_eps=1e-5, epilogue=0, pdl=False, out=None, tp=None, warm=None, workspace=None):
+             norm_eps=1e-5, epilogue=0, pdl=False, out=None, tp=None, workspace=None):
         """Streaming GEMV on `[M, K]` bf16 rows -> `[M, N]` (bf16 or fp32), 8 rows per launch.
 
         Optional fusions (see `lq_wq_gemv_fused`): RMSNorm of the input rows by `norm_weight`,
@@ -254,8 +256,6 @@ class KernelQuantLinear(nn.Module):
         `tp` (a `native.GemvTp`) couples the launch to the other ranks of a tensor-parallel
         group: as a pushing row-parallel linear (no `out`: the partial rows go to the ranks'
         exchange buffers) or as the consumer that first builds `flat` from the ranks' partials.
-        `warm`: up to two tensors of constant device memory (weights of the kernels that follow)
-        which this launch pulls into L2 while it runs.
         More than 8 rows (or `variant=5`) go through the tensor-core decode GEMM, which streams
         the weight once for up to 64 rows; `workspace` is its scratch (a uint8 tensor of
         `decode_workspace_bytes(rows)`; allocated per call when absent)."""
@@ -267,9 +267,13 @@ class KernelQuantLinear(nn.Module):
             out = torch.empty(m, n_out, dtype=out_dtype, device=flat.device)
         if m == 0:
             return out
-        if m > DECODE_MAX_ROWS or variant == 5:
+        gemm_rows = m > DECODE_MAX_ROWS or (m >= DECODE_GEMM_MIN_ROWS and variant in (None, 0) and tp is None
+                                            and self._span == 128)
+        if gemm_rows or variant == 5:
             if tp is not None:
                 raise RuntimeError(f"the tensor-parallel coupling takes the rows of one pass ({m} given)")
+            if variant == 5 and self._span != 128:
+                raise RuntimeError(f"the decode GEMM needs scale groups of 128 stored codes (this weight: {self._span})")
             if self._span == 128 and variant in (None, 0, 5):
                 return self._decode_gemm(flat, out, out_dtype, residual, norm_weight, norm_eps, epilogue, pdl,
                                          workspace)
@@ -290,8 +294,6 @@ class KernelQuantLinear(nn.Module):
             Kd=self._kd, span=self._span, bits=self.num_bits, epilogue=epilogue,
             variant=GEMV_VARIANT if variant is None else variant, pdl=1 if pdl else 0,
             tp=ctypes.addressof(tp) if tp is not None else None)
-        if warm:
-            args.warm = native.spans(warm)[0]
         with torch.cuda.device(flat.device):
             native.call("lq_wq_gemv_fused", ctypes.byref(args), native.stream_ptr(flat.device))
         return out
@@ -301,10 +303,24 @@ class KernelQuantLinear(nn.Module):
         rows = min(max(rows, 1), DECODE_GEMM_MAX_ROWS)
         return int(native.library().lq_decode_gemm_workspace_bytes(rows, self.out_features, self._kd))
 
+    def tiled_weight(self):
+        """The weight in the tile-major layout the decode GEMM streams (`lq_tile_weight`): a
+        second copy of the codes (with their scales), built on first use and kept with the module."""
+        if self._tiled is None or self._tiled.device != self.codes.device:
+            dev = self.codes.device
+            nbytes = native.library().lq_tile_weight_bytes(self.out_features, self._kd, self.num_bits)
+            tiled = torch.empty(nbytes, dtype=torch.uint8, device=dev)
+            with torch.cuda.device(dev):
+                native.call("lq_tile_weight", self.codes.data_ptr(), self.scale_tiles.data_ptr(), tiled.data_ptr(),
+                            self.out_features, self._kd, self.num_bits, native.stream_ptr(dev))
+            self._tiled = tiled
+        return self._tiled
+
     def _decode_gemm(self, flat, out, out_dtype, residual, norm_weight, norm_eps, epilogue, pdl, workspace):
         """Rows through the tensor-core decode GEMM (variant 5 of `lq_wq_gemv_fused`), 64 per
         call: activation planes, one pass over the weight, finish -- three launches."""
         m = flat.shape[0]
+        tiled = self.tiled_weight()
         bias = None
         if self.bias is not None:
             if self._bias_bf16 is None or self._bias_bf16.device != flat.device:
@@ -325,8 +341,8 @@ class KernelQuantLinear(nn.Module):
                 off = m0 * n_out * es
                 args = native.GemvArgs(
                     x=flat.data_ptr() + m0 * flat.stride(0) * 2, ldx=flat.stride(0),
-                    norm_weight=native.ptr(norm_weight), norm_eps=norm_eps, codes=self.codes.data_ptr(),
-                    scale_tiles=self.scale_tiles.data_ptr(), bias=native.ptr(bias),
+                    norm_weight=native.ptr(norm_weight), norm_eps=norm_eps, codes=tiled.data_ptr(),
+                    scale_tiles=tiled.data_ptr(), bias=native.ptr(bias),
                     residual=(residual.data_ptr() + off) if residual is not None else None,
                     out=out.data_ptr() + off, out_dtype=native.DTYPE_ID[out_dtype], M=rows, N=self.out_features,
                     K=self.in_features, Kd=self._kd, span=self._span, bits=self.num_bits, epilogue=epilogue,
@@ -337,44 +353,12 @@ class KernelQuantLinear(nn.Module):
 
     def _gemv_row_blocks(self, flat, out, out_dtype, residual, variant, norm_weight, norm_eps, epilogue, pdl):
         """More activation rows than one GEMV launch takes (8) on a weight the decode GEMM does
-        not serve (scale groups other than 128 codes): 8 rows per launch. The weight can be
-        walked in slices of L2_SLICE_BYTES of its output rows, every slice meeting all the row
-        blocks before the next slice is touched (a launch covers a block of output columns
-        through the output row stride `ldo`); by default it is not (measured on B200: the
-        per-launch set-up costs more than the second to fourth passes save)."""
-        m = flat.shape[0]
-        n, rowbytes = self.out_features, self.codes.shape[1]
-        groups = self._kd // self._span
-        bias = None
-        if self.bias is not None:
-            if self._bias_bf16 is None or self._bias_bf16.device != flat.device:
-                self._bias_bf16 = self.bias.detach().to(device=flat.device, dtype=torch.bfloat16).contiguous()
-            bias = self._bias_bf16
-        if flat.stride(-1) != 1:
-            flat = flat.contiguous()
-        es = out.element_size()
-        n_out = out.shape[1]
-        slice_rows = max(16, L2_SLICE_BYTES // max(rowbytes, 1) // 16 * 16) if L2_SLICE_BYTES else max(n, 16)
-        stream = native.stream_ptr(flat.device)
-        with torch.cuda.device(flat.device):
-            for n0 in range(0, n, slice_rows):
-                rows_n = min(slice_rows, n - n0)
-                col0 = n0 // 2 if epilogue == 1 else n0
-                for m0 in range(0, m, DECODE_MAX_ROWS):
-                    rows_m = min(DECODE_MAX_ROWS, m - m0)
-                    off = (m0 * n_out + col0) * es
-                    args = native.GemvArgs(
-                        x=flat.data_ptr() + m0 * flat.stride(0) * 2, ldx=flat.stride(0),
-                        norm_weight=native.ptr(norm_weight), norm_eps=norm_eps,
-                        codes=self.codes.data_ptr() + n0 * rowbytes,
-                        scale_tiles=self.scale_tiles.data_ptr() + (n0 // 4) * groups * 16,
-                        bias=(bias.data_ptr() + n0 * 2) if bias is not None else None,
-                        residual=(residual.data_ptr() + off) if residual is not None else None,
-                        out=out.data_ptr() + off, out_dtype=native.DTYPE_ID[out_dtype], M=rows_m, N=rows_n,
-                        K=self.in_features, Kd=self._kd, span=self._span, bits=self.num_bits,
-                        epilogue=epilogue, variant=GEMV_VARIANT if variant is None else variant,
-                        pdl=1 if pdl else 0, tp=None, ldo=n_out)
-                    native.call("lq_wq_gemv_fused", ctypes.byref(args), stream)
+        not serve (scale groups other than 128 codes): one pass over the weight per 8 rows."""
+        for m0 in range(0, flat.shape[0], DECODE_MAX_ROWS):
+            rows = slice(m0, m0 + DECODE_MAX_ROWS)
+            self.gemv(flat[rows], out_dtype=out_dtype, residual=None if residual is None else residual[rows],
+                      variant=variant, norm_weight=norm_weight, norm_eps=norm_eps, epilogue=epilogue, pdl=pdl,
+                      out=out[rows])
         return out
 
     def gemm(self, flat, a8: bool = False, fold_scales: bool = False, serial: bool = False):
@@ -423,7 +407,10 @@ class KernelQuantLinear(nn.Module):
         shape = x.shape
         flat = x.reshape(-1, shape[-1])
         m = flat.shape[0]
-        if self._stream and m <= DECODE_MAX_ROWS and flat.dtype == torch.bfloat16:
+        if self._stream and flat.dtype == torch.bfloat16 and (
+                m <= DECODE_MAX_ROWS or (m <= DECODE_GEMM_MAX_ROWS and self._span == 128)):
+            # up to 8 rows the GEMV, up to 64 the decode GEMM (one pass over the weight; faster
+            # than the prefill kernels' 128-token tiles at these row counts)
             out = self.gemv(flat)
         elif (self._stream and m <= PREFILL_TENSOR_CORE_MAX_ROWS and flat.dtype == torch.bfloat16
               and (self.out_features >= PREFILL_TENSOR_CORE_MIN_FEATURES or m <= PREFILL_EXACT_MAX_ROWS)

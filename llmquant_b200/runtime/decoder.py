@@ -29,9 +29,6 @@ from llmquant_b200.quantizers.kv_cache import KernelQuantCache
 
 
 MAX_BATCH = 64
-WARM_POLICIES = ("none", "attn", "chain", "next")
-L2_WARM = "none"                 # which launches pull later launches' weights into L2 (see _warm)
-LM_HEAD_WARM_BYTES = 48 << 20    # of lm_head, only a first part is requested ahead
 
 
 def _fuse_rows(modules, interleave=False):
@@ -101,7 +98,7 @@ class FusedLlamaDecoder:
 
     def __init__(self, model, max_batch: int, max_len: int, kv_bits: int = 8, use_graph: bool = True,
                  pdl: bool = True, tp=None, attn_splits: int = 0, gather_logits: bool = False,
-                 exchange=None, attn_impl: int = 0, l2_warm: str = L2_WARM):
+                 exchange=None, attn_impl: int = 0):
         if not supports(model):
             raise ValueError("FusedLlamaDecoder needs a Llama-layout model whose attention and MLP "
                              "linears are KernelQuantLinear (head_dim 64/128, silu MLP)")
@@ -176,15 +173,14 @@ class FusedLlamaDecoder:
         want = attn_splits if attn_splits > 0 else max(1, -(-2 * 148 // (B * self.Hkv)))
         self.splits = max(1, min(want, max_len // 64 or 1))
         self.attn_impl = attn_impl
-        if l2_warm not in WARM_POLICIES:
-            raise ValueError(f"l2_warm must be one of {WARM_POLICIES}, got {l2_warm!r}")
-        self.l2_warm = l2_warm
         nbytes = native.library().lq_attn_fused_scratch_bytes(B, self.Hq, self.Hkv, self.D, self.splits)
         self.scratch = torch.zeros(-(-nbytes // 4), dtype=torch.float32, device=dev)
         self.cache = KernelQuantCache(kv_bits, max_cache_len=max_len)
         # scratch of the tensor-core decode GEMM that batches above 8 rows go through
         self.workspace = None
-        if B > 8:
+        from llmquant_b200.quantizers.kernel import DECODE_GEMM_MIN_ROWS
+        self.decode_gemm = B >= DECODE_GEMM_MIN_ROWS and (self.tp is None or self.exchange is None)
+        if self.decode_gemm:
             linears = [spec[k] for spec in self.layers for k in ("qkv", "o", "gate_up", "down")]
             if isinstance(self.lm_head, KernelQuantLinear):
                 linears.append(self.lm_head)
@@ -192,7 +188,9 @@ class FusedLlamaDecoder:
             self.workspace = torch.empty(need, dtype=torch.uint8, device=dev)
         self.graph = None
         separate_reduce = self.tp is not None and self.exchange is None
-        self.launches_per_step = len(self.layers) * (7 if separate_reduce else 5) + 1 + (2 if self._glue else 0)
+        per_linear = 3 if self.decode_gemm else 1  # the decode GEMM is planes, product, finish
+        self.launches_per_step = (len(self.layers) * (4 * per_linear + 1 + (2 if separate_reduce else 0)) + per_linear
+                                  + (2 if self._glue else 0))
         if not self.tp:
             self.allreduce = "none"
         elif self.exchange is not None:
@@ -233,41 +231,13 @@ class FusedLlamaDecoder:
                 return
 
     # ------------------------------------------------------------------ one token
-    def _warm(self, l, launch):
-        """Weights that launch `launch` ('qkv', 'attn', 'o', 'gate_up', 'down') of layer `l` pulls
-        into L2 for the launches after it (`l2_warm`): the step is a chain of kernels that wait
-        for one another, and the attention block above all leaves HBM idle. 'attn': the
-        attention launch requests its layer's o_proj and gate|up weights. 'chain': in addition
-        o_proj requests down_proj and gate|up the next layer's q|k|v (lm_head's first part after
-        the last layer). 'next': every launch requests only the weights of the launch after it."""
-        policy = self.l2_warm
-        if policy == "none":
-            return None
-        spec = self.layers[l]
-        if l + 1 < len(self.layers):
-            after = self.layers[l + 1]["qkv"].codes
-        elif isinstance(self.lm_head, KernelQuantLinear) and self.lm_head._stream:
-            after = self.lm_head.codes.view(-1)[:LM_HEAD_WARM_BYTES]
-        else:
-            after = None
-        if policy == "attn":
-            table = {"attn": [spec["o"].codes, spec["gate_up"].codes]}
-        elif policy == "chain":
-            table = {"attn": [spec["o"].codes, spec["gate_up"].codes], "o": [spec["down"].codes],
-                     "gate_up": [after]}
-        else:  # "next"
-            table = {"attn": [spec["o"].codes], "o": [spec["gate_up"].codes],
-                     "gate_up": [spec["down"].codes], "down": [after]}
-        return table.get(launch)
-
-    def _attention(self, l, cache, pos_ptr, pdl, stream):
-        warm, n_warm = native.spans(self._warm(l, "attn"))
+    def _attention(self, cache, pos_ptr, pdl, stream):
         native.call("lq_attn_decode_fused", self.qkv.data_ptr(), self.cos.data_ptr(),
                     self.sin.data_ptr(), cache.k_codes.data_ptr(), cache.v_codes.data_ptr(),
                     cache.k_scales.data_ptr(), cache.v_scales.data_ptr(), self.attn.data_ptr(),
                     self.scratch.data_ptr(), self.B, self.Hq, self.Hkv, self.D, cache.capacity,
                     self.cos.shape[0], pos_ptr, 0, self.kv_bits, self.scaling, self.splits,
-                    self.attn_impl, warm, n_warm, pdl, stream)
+                    self.attn_impl, pdl, stream)
 
     def _folded_launches(self):
         """The step under tensor parallelism with the all-reduce folded into the GEMVs: o_proj and
@@ -289,20 +259,17 @@ class FusedLlamaDecoder:
             tp = None
             if l > 0:  # hidden = down_proj(l - 1) summed over the ranks + its residual
                 tp = ex.sum_args(1, h1)
-            spec["qkv"].gemv(h0, norm_weight=spec["ln1"], norm_eps=self.eps, pdl=self.pdl, workspace=self.workspace, out=self.qkv, tp=tp,
-                             warm=self._warm(l, "qkv"))
+            spec["qkv"].gemv(h0, norm_weight=spec["ln1"], norm_eps=self.eps, pdl=self.pdl, workspace=self.workspace, out=self.qkv, tp=tp)
             yield
-            self._attention(l, cache, pos_ptr, pdl, stream)
+            self._attention(cache, pos_ptr, pdl, stream)
             yield
-            spec["o"].gemv(self.attn, out_dtype=torch.float32, pdl=self.pdl, workspace=self.workspace, tp=ex.push_args(0),
-                           warm=self._warm(l, "o"))
+            spec["o"].gemv(self.attn, out_dtype=torch.float32, pdl=self.pdl, workspace=self.workspace, tp=ex.push_args(0))
             yield
             tp = ex.sum_args(0, h0)
             spec["gate_up"].gemv(h1, norm_weight=spec["ln2"], norm_eps=self.eps, epilogue=1,
-                                 pdl=self.pdl, workspace=self.workspace, out=self.act, tp=tp, warm=self._warm(l, "gate_up"))
+                                 pdl=self.pdl, workspace=self.workspace, out=self.act, tp=tp)
             yield
-            spec["down"].gemv(self.act, out_dtype=torch.float32, pdl=self.pdl, workspace=self.workspace, tp=ex.push_args(1),
-                              warm=self._warm(l, "down"))
+            spec["down"].gemv(self.act, out_dtype=torch.float32, pdl=self.pdl, workspace=self.workspace, tp=ex.push_args(1))
             yield
         tp = ex.sum_args(1, h1)
         self.lm_head.gemv(h0, norm_weight=self.final_norm, norm_eps=self.eps, pdl=self.pdl, workspace=self.workspace,
@@ -331,14 +298,13 @@ class FusedLlamaDecoder:
         else:
             cur.copy_(self.embed.index_select(0, self.tokens))
         pos_ptr = self.pos.data_ptr()
-        for l, (spec, cache) in enumerate(zip(self.layers, self.cache.layers)):
-            spec["qkv"].gemv(cur, norm_weight=spec["ln1"], norm_eps=self.eps, pdl=self.pdl, workspace=self.workspace, out=self.qkv,
-                             warm=self._warm(l, "qkv"))
-            self._attention(l, cache, pos_ptr, pdl, stream)
-            self._row_parallel(spec["o"], self.attn, cur, nxt, 0, warm=self._warm(l, "o"))
+        for spec, cache in zip(self.layers, self.cache.layers):
+            spec["qkv"].gemv(cur, norm_weight=spec["ln1"], norm_eps=self.eps, pdl=self.pdl, workspace=self.workspace, out=self.qkv)
+            self._attention(cache, pos_ptr, pdl, stream)
+            self._row_parallel(spec["o"], self.attn, cur, nxt, 0)
             spec["gate_up"].gemv(nxt, norm_weight=spec["ln2"], norm_eps=self.eps, epilogue=1,
-                                 pdl=self.pdl, workspace=self.workspace, out=self.act, warm=self._warm(l, "gate_up"))
-            self._row_parallel(spec["down"], self.act, nxt, cur, 1, warm=self._warm(l, "down"))
+                                 pdl=self.pdl, workspace=self.workspace, out=self.act)
+            self._row_parallel(spec["down"], self.act, nxt, cur, 1)
         if isinstance(self.lm_head, KernelQuantLinear) and self.lm_head._stream:
             head_out = self.local_logits if self.tp else self.logits
             self.lm_head.gemv(cur, norm_weight=self.final_norm, norm_eps=self.eps, pdl=self.pdl, workspace=self.workspace,
@@ -362,13 +328,12 @@ class FusedLlamaDecoder:
         buffers (no attention, no all-reduce, no token bookkeeping): what a benchmark captures
         to time the dominant kernel by itself. Leaves the hidden-state buffers overwritten."""
         cur, nxt = self.h
-        for l, spec in enumerate(self.layers):
-            spec["qkv"].gemv(cur, norm_weight=spec["ln1"], norm_eps=self.eps, pdl=self.pdl, workspace=self.workspace, out=self.qkv,
-                             warm=self._warm(l, "qkv"))
-            spec["o"].gemv(self.attn, residual=cur, pdl=self.pdl, workspace=self.workspace, out=nxt, warm=self._warm(l, "o"))
+        for spec in self.layers:
+            spec["qkv"].gemv(cur, norm_weight=spec["ln1"], norm_eps=self.eps, pdl=self.pdl, workspace=self.workspace, out=self.qkv)
+            spec["o"].gemv(self.attn, residual=cur, pdl=self.pdl, workspace=self.workspace, out=nxt)
             spec["gate_up"].gemv(nxt, norm_weight=spec["ln2"], norm_eps=self.eps, epilogue=1,
-                                 pdl=self.pdl, workspace=self.workspace, out=self.act, warm=self._warm(l, "gate_up"))
-            spec["down"].gemv(self.act, residual=nxt, pdl=self.pdl, workspace=self.workspace, out=cur, warm=self._warm(l, "down"))
+                                 pdl=self.pdl, workspace=self.workspace, out=self.act)
+            spec["down"].gemv(self.act, residual=nxt, pdl=self.pdl, workspace=self.workspace, out=cur)
         if isinstance(self.lm_head, KernelQuantLinear) and self.lm_head._stream:
             self.lm_head.gemv(cur, norm_weight=self.final_norm, norm_eps=self.eps, pdl=self.pdl, workspace=self.workspace,
                               out=self.local_logits if self.tp else self.logits)
@@ -380,19 +345,19 @@ class FusedLlamaDecoder:
             total += self.lm_head.weight_bytes()
         return total
 
-    def _row_parallel(self, linear, x, residual, out, slot, warm=None):
+    def _row_parallel(self, linear, x, residual, out, slot):
         """out = residual + linear(x). One GPU: fused in the GEMV epilogue. Tensor parallel:
         fp32 partial, summed over the ranks (one-shot kernel over peer memory, or NCCL),
         then the same rounding and residual add."""
         if not self.tp:
-            linear.gemv(x, residual=residual, pdl=self.pdl, workspace=self.workspace, out=out, warm=warm)
+            linear.gemv(x, residual=residual, pdl=self.pdl, workspace=self.workspace, out=out)
             return
         if self.peer is not None:
             linear.gemv(x, out_dtype=torch.float32, pdl=self.pdl, workspace=self.workspace,
-                        out=self.peer.slot(slot, out.shape[0], out.shape[1]), warm=warm)
+                        out=self.peer.slot(slot, out.shape[0], out.shape[1]))
             self.peer.reduce(slot, residual, out, self.pdl)
             return
-        linear.gemv(x, out_dtype=torch.float32, pdl=self.pdl, workspace=self.workspace, out=self.partial, warm=warm)
+        linear.gemv(x, out_dtype=torch.float32, pdl=self.pdl, workspace=self.workspace, out=self.partial)
         self.tp.all_reduce(self.partial)
         native.call("lq_residual_add", self.partial.data_ptr(), residual.data_ptr(), out.data_ptr(),
                     out.numel(), 1 if self.pdl else 0, native.stream_ptr(self.device))

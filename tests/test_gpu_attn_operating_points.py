@@ -74,7 +74,7 @@ def test_fused_attention_at_benchmark_contexts(hd, hq, hkv, B, T, splits, impl):
         row = rows[t].cuda()
         native.call("lq_attn_decode_fused", row.data_ptr(), cos.data_ptr(), sin.data_ptr(), kc.data_ptr(),
                     vc.data_ptr(), ks.data_ptr(), vs.data_ptr(), out.data_ptr(), scratch.data_ptr(),
-                    B, hq, hkv, hd, Tmax, Tmax, pos.data_ptr(), 0, 8, hd ** -0.5, splits, impl, None, 0, 0, stream)
+                    B, hq, hkv, hd, Tmax, Tmax, pos.data_ptr(), 0, 8, hd ** -0.5, splits, impl, 0, stream)
         p = T + t
         heads = rows[t].float().numpy().reshape(B, hq + 2 * hkv, hd)
         q_rot = llama_ops.apply_rope(heads[:, :hq], cos_np[p], sin_np[p])

@@ -63,6 +63,20 @@ def test_matches_the_oracle(bits, n, k, M):
 
 
 @pytest.mark.parametrize("bits", [4, 8])
+@pytest.mark.parametrize("M", [3, 24, 64])
+def test_long_runs_of_groups_per_cta(bits, M):
+    """Enough row tiles to fill the GPU, so a CTA walks all 40 scale groups of its rows by itself
+    and every ring of the kernel wraps several times."""
+    n, k = 19072, 5120
+    w = seeded((n, k), 81, 0.02, torch.bfloat16)
+    x = seeded((M, k), 82).bfloat16()
+    module = _module(w, bits)
+    got = module.gemv(x.cuda(), out_dtype=torch.float32, variant=5)
+    _no_device_error()
+    assert rel_l2(got.cpu().numpy(), _want(w, x, bits)) <= TOL_F32
+
+
+@pytest.mark.parametrize("bits", [4, 8])
 @pytest.mark.parametrize("M", [2, 8, 12, 16, 17, 31, 33, 50, 64, 70, 130])
 def test_every_padded_row_count(bits, M):
     """8, 16, 32 and 64 padded rows, and more rows than a call takes (64 per call)."""

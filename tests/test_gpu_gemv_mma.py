@@ -159,35 +159,36 @@ def test_rejects_groups_it_is_not_built_for():
     module.gemv(x)  # the default still serves it
 
 
-@pytest.mark.parametrize("bits,k", [(4, 2048), (8, 2048), (4, 14336)])
+@pytest.mark.parametrize("bits,m", [(4, 2), (8, 4), (4, 8)])
 @pytest.mark.parametrize("epilogue", [0, 1])
-def test_row_blocks_over_weight_slices_equal_whole_passes(bits, k, epilogue, monkeypatch):
-    """More than 8 activation rows: the weight is walked in slices of its output rows and every
-    slice meets all the row blocks (launches that address a block of output columns through
-    `ldo`). The result must be, bit for bit, what one whole pass per 8-row block gives -- with
-    the tensor-core kernel (K = 2048) and with the SIMT passes (K = 14336, where the activation
-    planes of 8 rows do not fit the tensor-core kernel), bias, residual and the SiLU epilogue."""
-    from llmquant_b200.quantizers import kernel as kq
+def test_output_row_stride(bits, m, epilogue):
+    """`ldo`: a launch can write (and read its residual from) a block of columns of a wider
+    matrix. Both GEMV kernels (2 rows: SIMT; 4 and 8 rows: tensor-core), bias, residual, SiLU."""
+    import ctypes
 
-    n, m = 600, 21
-    if epilogue == 1 and k == 14336:
-        pytest.skip("the SiLU epilogue belongs to gate|up (K = hidden)")
+    from llmquant_b200 import native
+
+    n, k, wide, col0 = 256, 1024, 700, 136
     w = seeded((n, k), 71, 0.02, torch.bfloat16)
     bias = None if epilogue == 1 else seeded((n,), 72, 0.1, torch.bfloat16)
     module = _module(w, bits, bias=bias)
     x = seeded((m, k), 73).bfloat16().cuda()
     n_out = n // 2 if epilogue == 1 else n
-    residual = None if epilogue == 1 else seeded((m, n_out), 74).bfloat16().cuda()
-    gamma = (seeded((k,), 75) * 0.1 + 1).bfloat16().cuda()
-    kwargs = dict(norm_weight=gamma, norm_eps=1e-5, epilogue=epilogue)
-    whole = torch.cat([module.gemv(x[i:i + 8], residual=None if residual is None else residual[i:i + 8], **kwargs)
-                       for i in range(0, m, 8)])
-    monkeypatch.setattr(kq, "L2_SLICE_BYTES", 160 * module.codes.shape[1])  # slices of 160 rows: 4 of them
-    sliced = module.gemv(x, residual=residual, **kwargs)
-    assert sliced.shape == (m, n_out) and torch.equal(sliced, whole)
-    normed = llama_ops.rmsnorm(x.float().cpu().numpy(), gamma.float().cpu().numpy(), 1e-5)
-    want = _want(w, torch.from_numpy(normed), bits)
-    if epilogue == 0:
-        want = want + bias.float().numpy()
-        got = (module.gemv(x, out_dtype=torch.float32, **kwargs)).cpu().numpy()
-        assert rel_l2(got, want) <= 1e-3
+    residual = None if epilogue == 1 else seeded((m, wide), 74).bfloat16().cuda()
+    plain = module.gemv(x, residual=None if residual is None else residual[:, col0:col0 + n_out].contiguous(),
+                        epilogue=epilogue)
+    out = torch.full((m, wide), 7.0, dtype=torch.bfloat16, device="cuda")
+    bias16 = None if bias is None else bias.cuda()
+    args = native.GemvArgs(
+        x=x.data_ptr(), ldx=k, norm_weight=None, norm_eps=1e-5, codes=module.codes.data_ptr(),
+        scale_tiles=module.scale_tiles.data_ptr(), bias=native.ptr(bias16),
+        residual=None if residual is None else residual.data_ptr() + col0 * 2, out=out.data_ptr() + col0 * 2,
+        out_dtype=native.LQ_BF16, M=m, N=n, K=k, Kd=k, span=128, bits=bits, epilogue=epilogue, variant=0, pdl=0,
+        tp=None, ldo=wide)
+    native.call("lq_wq_gemv_fused", ctypes.byref(args), native.stream_ptr())
+    torch.cuda.synchronize()
+    assert torch.equal(out[:, col0:col0 + n_out], plain)
+    assert bool((out[:, :col0] == 7).all()) and bool((out[:, col0 + n_out:] == 7).all())
+    args.ldo = n_out - 1
+    assert native.library().lq_wq_gemv_fused(ctypes.byref(args), native.stream_ptr()) != 0
+    assert "ldo" in native.last_error()

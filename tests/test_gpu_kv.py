@@ -165,7 +165,7 @@ def test_fused_attention_block_matches_the_separate_kernels(hd, hq, hkv, splits,
         kc, vc, ks, vs = fus
         native.call("lq_attn_decode_fused", row.data_ptr(), cos.data_ptr(), sin.data_ptr(), kc.data_ptr(),
                     vc.data_ptr(), ks.data_ptr(), vs.data_ptr(), out_fus.data_ptr(), scratch_fus.data_ptr(),
-                    B, hq, hkv, hd, Tmax, Tmax, pos.data_ptr(), 0, 8, hd ** -0.5, splits, impl, None, 0, 0, stream)
+                    B, hq, hkv, hd, Tmax, Tmax, pos.data_ptr(), 0, 8, hd ** -0.5, splits, impl, 0, stream)
         pos.add_(1)
         if t in (0, 1, 17, T - 1):
             err = rel_l2(out_fus.float().cpu().numpy(), out_ref.float().cpu().numpy())

@@ -43,9 +43,7 @@ def test_exchange_layout_and_argument_blocks():
     # the C struct: three ints, padding, then pointers and 64-bit fields
     assert native.GemvTp.peers.offset == 16 and ctypes.sizeof(native.GemvTp) == 56
     assert native.GemvArgs.tp.offset == 112 and native.GemvArgs.ldo.offset == 120
-    assert native.GemvArgs.warm.offset == 128 and native.GemvArgs.workspace.offset == 160
-    assert ctypes.sizeof(native.GemvArgs) == 176
-    assert ctypes.sizeof(native.Span) == 16 and native.MAX_WARM_SPANS == 2
+    assert native.GemvArgs.workspace.offset == 128 and ctypes.sizeof(native.GemvArgs) == 144
 
 
 def test_exchange_refuses_a_missing_peer_a_small_buffer_and_ragged_rows():
