@@ -388,7 +388,7 @@ def run_attn_one(args, device):
     sin = torch.randn(tmax, D, device=device, generator=g).to(torch.bfloat16)
     out = torch.zeros(B, Hq, D, dtype=torch.bfloat16, device=device)
     pos = torch.tensor([T], dtype=torch.long, device=device)
-    splits = args.splits or max(1, -(-2 * 148 // (B * Hkv)))
+    splits = args.splits or max(1, 2 * 148 // (B * Hkv))
     nbytes = lib.lq_attn_fused_scratch_bytes(B, Hq, Hkv, D, splits)
     scratch = torch.zeros(-(-nbytes // 4), dtype=torch.float32, device=device)
 

@@ -1035,6 +1035,30 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<const uint32_t*>(&v);
 }
+__device__ __forceinline__ void mma_h16(float (&c)[4], uint32_t a0, uint32_t a2, uint32_t b0, uint32_t b1) {
+  const uint32_t zero = 0;  // rows 8..15 of A (no query head there)
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a0), "r"(zero), "r"(a2), "r"(zero), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_h16(float lo, float hi) {
+  const __half2 v = __floats2half2_rn(lo, hi);
+  return *reinterpret_cast<const uint32_t*>(&v);
+}
+// Bytes i and i + 1 of two words of (signed code + 128) -> two half2 (code_a, code_b), exact:
+// a byte u under the high byte 0x64 is the half 1024 + u, and 1024 + 128 is subtracted.
+__device__ __forceinline__ void codes_to_h2(uint32_t wa, uint32_t wb, int i, uint32_t& h_i, uint32_t& h_i1) {
+  const uint32_t sel = i == 0 ? 0x5140u : 0x7362u;  // (a_i, b_i, a_i+1, b_i+1)
+  const uint32_t t = __byte_perm(wa, wb, sel);
+  const uint32_t x0 = __byte_perm(t, 0x64646464u, 0x5140u);  // [a_i, 0x64, b_i, 0x64]
+  const uint32_t x1 = __byte_perm(t, 0x64646464u, 0x5342u);  // [a_i+1, 0x64, b_i+1, 0x64]
+  const __half2 bias = __floats2half2_rn(1152.f, 1152.f);
+  const __half2 r0 = __hsub2(*reinterpret_cast<const __half2*>(&x0), bias);
+  const __half2 r1 = __hsub2(*reinterpret_cast<const __half2*>(&x1), bias);
+  h_i = *reinterpret_cast<const uint32_t*>(&r0);
+  h_i1 = *reinterpret_cast<const uint32_t*>(&r1);
+}
 
 template <int D, int G, bool CL>
 __global__ void __launch_bounds__(kMmaThreads)
@@ -1210,12 +1234,15 @@ attn_mma_kernel(const __nv_bfloat16* __restrict__ qkv, const __nv_bfloat16* __re
   uint32_t qa[KS][4];
 #pragma unroll
   for (int ksx = 0; ksx < KS; ++ksx) {
-    const int c = ksx * 32 + q4 * 4;
+    // The MMA's k index is mapped onto the head's dims so that the 8 K bytes a thread feeds per
+    // k-step are contiguous in a cached row and its D/4 bytes for all k-steps one vector load:
+    // thread q4 owns dims [q4 * D/4, (q4 + 1) * D/4), k-step ksx the eight from ksx * 8 on.
+    const int c = q4 * (D / 4) + ksx * 8;
     const bool have = gid < G;
     qa[ksx][0] = have ? *reinterpret_cast<const uint32_t*>(&qhi_s[have ? gid : 0][c]) : 0u;
     qa[ksx][1] = have ? *reinterpret_cast<const uint32_t*>(&qlo_s[have ? gid : 0][c]) : 0u;
-    qa[ksx][2] = have ? *reinterpret_cast<const uint32_t*>(&qhi_s[have ? gid : 0][c + 16]) : 0u;
-    qa[ksx][3] = have ? *reinterpret_cast<const uint32_t*>(&qlo_s[have ? gid : 0][c + 16]) : 0u;
+    qa[ksx][2] = have ? *reinterpret_cast<const uint32_t*>(&qhi_s[have ? gid : 0][c + 4]) : 0u;
+    qa[ksx][3] = have ? *reinterpret_cast<const uint32_t*>(&qlo_s[have ? gid : 0][c + 4]) : 0u;
   }
   const float qscale = (gid < G ? qunit_s[gid < G ? gid : 0] : 0.f) * scaling;
 
@@ -1254,13 +1281,15 @@ attn_mma_kernel(const __nv_bfloat16* __restrict__ qkv, const __nv_bfloat16* __re
 #pragma unroll
       for (int j = 0; j < 2; ++j) {
         int c[4] = {0, 0, 0, 0};
-        const uint8_t* krow = k_st + (size_t)min(r0 + j * 8 + gid, CAP - 1) * PK + q4 * 4;
+        const uint8_t* krow = k_st + (size_t)min(r0 + j * 8 + gid, CAP - 1) * PK + q4 * (D / 4);
+        uint32_t kw[2 * KS];  // this thread's D/4 dims of the token: 16-byte loads
 #pragma unroll
-        for (int ksx = 0; ksx < KS; ++ksx) {
-          const uint32_t b0 = *reinterpret_cast<const uint32_t*>(krow + ksx * 32);
-          const uint32_t b1 = *reinterpret_cast<const uint32_t*>(krow + ksx * 32 + 16);
-          mma_s8(c, qa[ksx], b0, b1);
+        for (int v = 0; v < KS / 2; ++v) {
+          const uint4 t4 = *reinterpret_cast<const uint4*>(krow + v * 16);
+          kw[4 * v] = t4.x; kw[4 * v + 1] = t4.y; kw[4 * v + 2] = t4.z; kw[4 * v + 3] = t4.w;
         }
+#pragma unroll
+        for (int ksx = 0; ksx < KS; ++ksx) mma_s8(c, qa[ksx], kw[2 * ksx], kw[2 * ksx + 1]);
         const int t0 = r0 + j * 8 + q4 * 2;
         sc[j][0] = t0 < n ? (float)(c[0] * 256 + c[2]) * qscale * sk_s[t0] : -INFINITY;
         sc[j][1] = t0 + 1 < n ? (float)(c[1] * 256 + c[3]) * qscale * sk_s[min(t0 + 1, CAP - 1)] : -INFINITY;
@@ -1283,17 +1312,38 @@ attn_mma_kernel(const __nv_bfloat16* __restrict__ qkv, const __nv_bfloat16* __re
       const int ta = r0 + q4 * 2, tb = ta + 8;  // this thread's token rows in the block
       const int ra0 = min(ta, CAP - 1), ra1 = min(ta + 1, CAP - 1), rb0 = min(tb, CAP - 1), rb1 = min(tb + 1, CAP - 1);
       // (rows past the end of the chunk hold stale bytes and no scale: their weight is a plain 0)
-      const uint32_t a0 = pack_bf16(ta < n ? pr[0][0] * sv_s[ra0] : 0.f, ta + 1 < n ? pr[0][1] * sv_s[ra1] : 0.f);
-      const uint32_t a2 = pack_bf16(tb < n ? pr[1][0] * sv_s[rb0] : 0.f, tb + 1 < n ? pr[1][1] * sv_s[rb1] : 0.f);
-      const int8_t* va0 = reinterpret_cast<const int8_t*>(v_st) + (size_t)ra0 * PK + gid;
-      const int8_t* va1 = reinterpret_cast<const int8_t*>(v_st) + (size_t)ra1 * PK + gid;
-      const int8_t* vb0 = reinterpret_cast<const int8_t*>(v_st) + (size_t)rb0 * PK + gid;
-      const int8_t* vb1 = reinterpret_cast<const int8_t*>(v_st) + (size_t)rb1 * PK + gid;
+      // probabilities x value scales and the value codes as fp16 (codes exactly; the weights with
+      // 11 significant bits), fp32 accumulate
+      const uint32_t a0 = pack_h16(ta < n ? pr[0][0] * sv_s[ra0] : 0.f, ta + 1 < n ? pr[0][1] * sv_s[ra1] : 0.f);
+      const uint32_t a2 = pack_h16(tb < n ? pr[1][0] * sv_s[rb0] : 0.f, tb + 1 < n ? pr[1][1] * sv_s[rb1] : 0.f);
+      // Output tile dt, column j of the MMA is dim j * DT + dt, so the DT codes a thread feeds for
+      // one token (its column j = gid) are contiguous: one vector load per token row.
+      uint32_t vw[4][DT / 4];
+      {
+        const uint8_t* rows[4] = {v_st + (size_t)ra0 * PK, v_st + (size_t)ra1 * PK, v_st + (size_t)rb0 * PK,
+                                  v_st + (size_t)rb1 * PK};
 #pragma unroll
-      for (int dt = 0; dt < DT; ++dt) {
-        const uint32_t b0 = pack_bf16((float)va0[dt * 8], (float)va1[dt * 8]);
-        const uint32_t b1 = pack_bf16((float)vb0[dt * 8], (float)vb1[dt * 8]);
-        mma_bf16(o[dt], a0, a2, b0, b1);
+        for (int r = 0; r < 4; ++r) {
+          if (DT == 16) {
+            const uint4 t4 = *reinterpret_cast<const uint4*>(rows[r] + gid * DT);
+            vw[r][0] = t4.x ^ 0x80808080u; vw[r][1] = t4.y ^ 0x80808080u;
+            vw[r][DT / 4 - 2] = t4.z ^ 0x80808080u; vw[r][DT / 4 - 1] = t4.w ^ 0x80808080u;
+          } else {
+            const uint2 t2 = *reinterpret_cast<const uint2*>(rows[r] + gid * DT);
+            vw[r][0] = t2.x ^ 0x80808080u; vw[r][1] = t2.y ^ 0x80808080u;
+          }
+        }
+      }
+#pragma unroll
+      for (int w = 0; w < DT / 4; ++w) {
+#pragma unroll
+        for (int i = 0; i < 4; i += 2) {
+          uint32_t b0a, b0b, b1a, b1b;
+          codes_to_h2(vw[0][w], vw[1][w], i, b0a, b0b);  // tokens ta, ta + 1
+          codes_to_h2(vw[2][w], vw[3][w], i, b1a, b1b);  // tokens tb, tb + 1
+          mma_h16(o[4 * w + i], a0, a2, b0a, b1a);
+          mma_h16(o[4 * w + i + 1], a0, a2, b0b, b1b);
+        }
       }
     }
     __syncthreads();  // everyone is done with the area before it is refilled
@@ -1315,8 +1365,8 @@ attn_mma_kernel(const __nv_bfloat16* __restrict__ qkv, const __nv_bfloat16* __re
   if (gid < G) {
 #pragma unroll
     for (int dt = 0; dt < DT; ++dt) {
-      ow_s[warp][gid][dt * 8 + q4 * 2] = o[dt][0];
-      ow_s[warp][gid][dt * 8 + q4 * 2 + 1] = o[dt][1];
+      ow_s[warp][gid][(q4 * 2) * DT + dt] = o[dt][0];  // column j of tile dt is dim j * DT + dt
+      ow_s[warp][gid][(q4 * 2 + 1) * DT + dt] = o[dt][1];
     }
   }
   __syncthreads();

@@ -170,7 +170,9 @@ class FusedLlamaDecoder:
         self.history = torch.zeros(B, max_len + 1, dtype=torch.long, device=dev)
         self.ticket = torch.zeros(1, dtype=torch.int32, device=dev)
         # slices of the cached context per KV head: about two CTAs per SM in all
-        want = attn_splits if attn_splits > 0 else max(1, -(-2 * 148 // (B * self.Hkv)))
+        # (as many as fit the GPU at two CTAs per SM in one wave: a few CTAs over that run as a
+        # second wave; measured at batch 8 and 32)
+        want = attn_splits if attn_splits > 0 else max(1, 2 * 148 // (B * self.Hkv))
         self.splits = max(1, min(want, max_len // 64 or 1))
         self.attn_impl = attn_impl
         nbytes = native.library().lq_attn_fused_scratch_bytes(B, self.Hq, self.Hkv, self.D, self.splits)

@@ -175,15 +175,16 @@ def test_output_row_stride(bits, m, epilogue):
     x = seeded((m, k), 73).bfloat16().cuda()
     n_out = n // 2 if epilogue == 1 else n
     residual = None if epilogue == 1 else seeded((m, wide), 74).bfloat16().cuda()
+    variant = 4 if m > 2 else 2
     plain = module.gemv(x, residual=None if residual is None else residual[:, col0:col0 + n_out].contiguous(),
-                        epilogue=epilogue)
+                        epilogue=epilogue, variant=variant)
     out = torch.full((m, wide), 7.0, dtype=torch.bfloat16, device="cuda")
     bias16 = None if bias is None else bias.cuda()
     args = native.GemvArgs(
         x=x.data_ptr(), ldx=k, norm_weight=None, norm_eps=1e-5, codes=module.codes.data_ptr(),
         scale_tiles=module.scale_tiles.data_ptr(), bias=native.ptr(bias16),
         residual=None if residual is None else residual.data_ptr() + col0 * 2, out=out.data_ptr() + col0 * 2,
-        out_dtype=native.LQ_BF16, M=m, N=n, K=k, Kd=k, span=128, bits=bits, epilogue=epilogue, variant=0, pdl=0,
+        out_dtype=native.LQ_BF16, M=m, N=n, K=k, Kd=k, span=128, bits=bits, epilogue=epilogue, variant=variant, pdl=0,
         tp=None, ldo=wide)
     native.call("lq_wq_gemv_fused", ctypes.byref(args), native.stream_ptr())
     torch.cuda.synchronize()
