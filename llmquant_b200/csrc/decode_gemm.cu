@@ -12,22 +12,35 @@
 //   act_planes_kernel   x [T, K] bf16 (optionally through RMSNorm) -> per scale group of 128
 //                       columns a power-of-two unit and 15-bit signed mantissas split into a
 //                       signed high byte plane and a signed low byte plane (the block
-//                       floating point of gemv_mma.cu), laid out as the B operand tiles:
-//                       planes[g][2 * TP][128] int8 (rows 0..TP-1 high planes, TP..2TP-1 low
-//                       planes), units[g][TP] fp32.
-//   decode_gemm_kernel  one CTA per (128 weight rows, slice of the scale groups). Per group:
-//                       A = 128 rows x 128 codes as signed bytes (int8 codes as they are; int4
-//                       nibbles as 16 * code, the 1/16 folded into the scale), B = the group's
-//                       2 * TP plane rows, four tcgen05.mma kind::i8 (K = 32 each) into one of
-//                       two TMEM accumulators [128 lanes = weight rows][2 * TP columns]. Warp
-//                       roles as in the prefill kernel: 4 fill warps (cp.async into 128-byte
-//                       swizzled tiles, as many groups ahead as shared memory holds), one MMA-issuing thread, 8 drain
-//                       warps (tcgen05.ld; hi * 256 + lo; times weight scale x unit; fp32
-//                       registers). This is the reference's order of operations: one exact
-//                       product sum per group, scaled, accumulated in fp32 over the groups
-//                       (quantizers/real.py:93-99). The CTA's sums go to partial[split][T][N].
+//                       floating point of gemv_mma.cu), laid out as the B operand tiles the MMA
+//                       reads from shared memory: per group one block of 2 * TP plane rows
+//                       (rows 0..TP-1 high planes, TP..2TP-1 low planes, 128-byte swizzled)
+//                       followed by the TP units.
+//   decode_gemm_kernel  one CTA per (128 weight rows, slice of the scale groups). The weight
+//                       is read in a TILE-MAJOR layout (lq_tile_weight): per tile and group one
+//                       contiguous block of codes and scales, so a group arrives with one
+//                       linear bulk copy. Per group: A = 128 rows x 128 codes as signed bytes
+//                       (int8 codes as they are; int4 nibbles as 16 * code, the 1/16 folded
+//                       into the scale), B = the group's 2 * TP plane rows, four tcgen05.mma
+//                       kind::i8 (K = 32 each) into one of up to eight TMEM accumulators
+//                       [128 lanes = weight rows][2 * TP columns]. Warp roles: two threads
+//                       issue the weight copies and one the plane copies (issuing a bulk
+//                       copy occupies a thread for ~500 clocks); eight warps widen int4
+//                       nibbles from a ring of raw bytes into the A tiles, each a whole group
+//                       by itself; two threads issue the MMAs (even / odd groups); eight drain
+//                       warps read the accumulators (tcgen05.ld), form hi * 256 + lo, multiply
+//                       by weight scale x unit and add into fp32 registers. This is the
+//                       reference's order of operations: one exact product sum per group,
+//                       scaled, accumulated in fp32 over the groups (quantizers/real.py:93-99).
+//                       The CTA's sums go to partial[split][T][N].
 //   decode_finish_kernel  adds the splits in order, then bias / residual / silu(gate) * up and
 //                       the roundings of the bf16 modules, and stores the output rows.
+//
+// What sets the pace (measured with per-role clock stamps, a diagnostic build): not HBM and
+// not the tensor core, but per-group latencies -- a bulk copy's issue, a barrier operation
+// (~100 clocks each), the proxy fence after widening, the MMA -> commit -> drain -> hand-back
+// loop. Hence: few copies per group, one arrival per warp, deep rings with a barrier ring of
+// their own each, eight accumulators, eight groups being widened at once.
 //
 // Every wait is bounded (mbar_wait); on expiry the CTA records the error word, all roles leave
 // their loops, TMEM is freed.
