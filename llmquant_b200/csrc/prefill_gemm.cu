@@ -244,6 +244,8 @@ prefill_gemm_kernel(const GemmParams p) {
 // role leaves its loop, the error word is set and TMEM is freed.
 constexpr int kWsThreads = 416;  // 8 drain warps, 4 fill warps, 1 MMA warp
 constexpr int kWsStages = 5;   // shared-memory stages (operand tiles of one group each)
+constexpr int kWsAcc = 4;      // accumulators in tensor memory (128 columns each): the MMA -> drain -> hand-back
+                               // loop is several hundred clocks of latency, which two accumulators do not cover
 constexpr int kWsAhead = 3;    // groups whose copies are in flight ahead of the one being handed over; two
                                // fewer than the stages, so a refill waits for an MMA issued two groups ago
 
@@ -251,9 +253,9 @@ template <int BITS>
 __global__ void __launch_bounds__(kWsThreads)
 prefill_gemm_ws_kernel(const GemmParams p) {
   extern __shared__ __align__(128) uint8_t smem[];
-  __shared__ __align__(8) uint64_t full_bar[kWsStages], sfree_bar[kWsStages], tfull_bar[2], tfree_bar[2];
+  __shared__ __align__(8) uint64_t full_bar[kWsStages], sfree_bar[kWsStages], tfull_bar[kWsAcc], tfree_bar[kWsAcc];
   __shared__ uint32_t tmem_base_s;
-  __shared__ float ws_s[8][BN];
+  __shared__ float ws_s[16][BN];  // a slot is rewritten 16 groups later: by then its drain is done (4 accumulators, 5 stages)
   __shared__ volatile int dead_s;
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -268,17 +270,17 @@ prefill_gemm_ws_kernel(const GemmParams p) {
 
   if (warp == 0) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
-                 ::"r"(smem_u32(&tmem_base_s)), "r"(2 * kTmemCols) : "memory");
+                 ::"r"(smem_u32(&tmem_base_s)), "r"(kWsAcc * kTmemCols) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
   if (tid == 0) {
     for (int i = 0; i < kWsStages; ++i) {
-      mbar_init(smem_u32(&full_bar[i]), 128);
+      mbar_init(smem_u32(&full_bar[i]), 4);  // one arrival per fill warp (an arrival is an atomic on the barrier word)
       mbar_init(smem_u32(&sfree_bar[i]), 1);
     }
-    for (int i = 0; i < 2; ++i) {
+    for (int i = 0; i < kWsAcc; ++i) {
       mbar_init(smem_u32(&tfull_bar[i]), 1);
-      mbar_init(smem_u32(&tfree_bar[i]), 256);
+      mbar_init(smem_u32(&tfree_bar[i]), 8);  // one arrival per drain warp
     }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     dead_s = 0;
@@ -332,7 +334,7 @@ prefill_gemm_ws_kernel(const GemmParams p) {
         const float* ssrc = p.scale_tiles + ((int64_t)((n < p.N ? n : 0) >> 2) * G + g) * 4 + (n & 3);
         const int bytes = n < p.N ? 4 : 0;
         asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;"
-                     ::"r"(smem_u32(&ws_s[g & 7][r])), "l"(ssrc), "r"(bytes) : "memory");
+                     ::"r"(smem_u32(&ws_s[g & 15][r])), "l"(ssrc), "r"(bytes) : "memory");
       }
       asm volatile("cp.async.commit_group;" ::: "memory");
       return true;
@@ -371,7 +373,8 @@ prefill_gemm_ws_kernel(const GemmParams p) {
         }
       }
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic / cp.async writes -> MMA reads
-      mbar_arrive(smem_u32(&full_bar[st]));
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&full_bar[st]));
       if (g + kWsAhead < G) ok = issue(g + kWsAhead);
     }
     if (!ok) dead_s = 1;
@@ -380,10 +383,10 @@ prefill_gemm_ws_kernel(const GemmParams p) {
     // ------------------------------------------------------------------ MMA issue
     if (lane == 0) {
       for (int g = 0; g < G; ++g) {
-        const int st = g % kWsStages, tb = g & 1;
+        const int st = g % kWsStages, tb = g % kWsAcc;
         if (dead_s) break;
         if (!mbar_wait(smem_u32(&full_bar[st]), (g / kWsStages) & 1)) { dead_s = 1; break; }
-        if (g >= 2 && !mbar_wait(smem_u32(&tfree_bar[tb]), ((g >> 1) - 1) & 1)) { dead_s = 1; break; }
+        if (g >= kWsAcc && !mbar_wait(smem_u32(&tfree_bar[tb]), ((g / kWsAcc) - 1) & 1)) { dead_s = 1; break; }
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const uint32_t a_addr = smem_u32(tiles + st * 2 * TILE), b_addr = a_addr + TILE;
 #pragma unroll
@@ -407,13 +410,13 @@ prefill_gemm_ws_kernel(const GemmParams p) {
     const int my_m = m0 + quarter * 32 + lane;
     bool dead = false;
     for (int g = 0; g < G; ++g) {
-      const int st = g & 1;
+      const int st = g % kWsAcc;
       if (dead_s) { dead = true; break; }
       // 1/16 undoes the shift that turned int4 codes into signed bytes
       const float xs = my_m < p.M ? p.x_scales[(int64_t)my_m * G + g] * (BITS == 4 ? 0.0625f : 1.f) : 0.f;
-      if (!mbar_wait(smem_u32(&tfull_bar[st]), (g >> 1) & 1)) { dead_s = 1; dead = true; break; }
+      if (!mbar_wait(smem_u32(&tfull_bar[st]), (g / kWsAcc) & 1)) { dead_s = 1; dead = true; break; }
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      const float* wsg = ws_s[g & 7] + cbase;
+      const float* wsg = ws_s[g & 15] + cbase;
 #pragma unroll
       for (int c0 = 0; c0 < HALF; c0 += 32) {
         uint32_t v[32];
@@ -422,7 +425,8 @@ prefill_gemm_ws_kernel(const GemmParams p) {
         for (int j = 0; j < 32; ++j) acc[c0 + j] = fmaf((float)(int)v[j] * xs, wsg[c0 + j], acc[c0 + j]);
       }
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-      mbar_arrive(smem_u32(&tfree_bar[st]));
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&tfree_bar[st]));
     }
     if (!dead && my_m < p.M) {
       __nv_bfloat16* dst = p.out + (int64_t)my_m * p.N + n0 + cbase;
@@ -441,7 +445,7 @@ prefill_gemm_ws_kernel(const GemmParams p) {
   if (tid == 0 && dead_s) atomicExch(p.error_word, 2);
   if (warp == 0) {
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(2 * kTmemCols)
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kWsAcc * kTmemCols)
                  : "memory");
   }
 }
@@ -487,7 +491,7 @@ prefill_gemm_f16_kernel(const GemmParams p) {
   }
   if (tid == 0) {
     for (int i = 0; i < kF16Stages; ++i) {
-      mbar_init(smem_u32(&full_bar[i]), 256);
+      mbar_init(smem_u32(&full_bar[i]), 8);  // one arrival per fill warp
       mbar_init(smem_u32(&sfree_bar[i]), 1);
     }
     mbar_init(smem_u32(&done_bar), 1);
@@ -579,7 +583,8 @@ prefill_gemm_f16_kernel(const GemmParams p) {
       if ((g & 1) == 0) { widen_store(0, g); fetch_b(0, g + 2); }
       else { widen_store(1, g); fetch_b(1, g + 2); }
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-      mbar_arrive(smem_u32(&full_bar[st]));
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&full_bar[st]));
       if (g + 2 < S) ok = issue_a(g + 2);
     }
     if (!ok) dead_s = 1;
