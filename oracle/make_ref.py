@@ -1,6 +1,8 @@
 """Stage the reference itself for use as a checker and as the timed CPU baseline.
 
-    python oracle/make_ref.py [/path/to/llm-quant]      (default: /root/reference)
+    python oracle/make_ref.py [/path/to/llm-quant]
+
+(default: $LLM_QUANT_REFERENCE, else a checkout named `reference` beside this repository)
 
 The reference is pure Python, so "building" it means placing its package where the tests and
 the benchmark's reference arm can import it: `oracle/_ref/llmquant`, plus its `examples/`
@@ -14,12 +16,19 @@ import pathlib
 import shutil
 import sys
 
+import os
+
 HERE = pathlib.Path(__file__).resolve().parent
 DEST = HERE / "_ref"
 
 
-def stage(ref_root="/root/reference") -> pathlib.Path:
-    src = pathlib.Path(ref_root)
+def default_checkout() -> pathlib.Path:
+    """Where the reference is looked for when no path is given."""
+    return pathlib.Path(os.environ.get("LLM_QUANT_REFERENCE") or HERE.parent.parent / "reference")
+
+
+def stage(ref_root=None) -> pathlib.Path:
+    src = pathlib.Path(ref_root) if ref_root else default_checkout()
     if not (src / "llmquant" / "__init__.py").exists():
         raise FileNotFoundError(f"{src} does not hold an llm-quant checkout")
     DEST.mkdir(exist_ok=True)
@@ -47,4 +56,4 @@ def import_reference():
 
 
 if __name__ == "__main__":
-    print(stage(sys.argv[1] if len(sys.argv) > 1 else "/root/reference"))
+    print(stage(sys.argv[1] if len(sys.argv) > 1 else None))
