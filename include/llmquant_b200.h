@@ -382,10 +382,10 @@ int lq_wq_gemv_fused(const lq_gemv_args* args, void* stream);
  * the GEMV variants take 8 rows per pass. `codes` is the weight in the TILE-MAJOR layout of
  * lq_tile_weight (not the streaming layout of the other variants).
  * Three launches: the activation rows (through the optional RMSNorm) become 15-bit
- * block-floating-point byte planes in `workspace`; one CTA per (128 weight rows, slice of the
- * scale groups) multiplies them with kind::i8 MMAs into tensor memory and applies (weight
+ * block-floating-point byte planes in `workspace`; CTAs that share the weight's (128-row tile,
+ * scale group) steps in equal contiguous runs multiply them with kind::i8 MMAs into tensor memory and applies (weight
  * scale x activation unit) per group in fp32 -- the order of operations of
- * quantizers/real.py:93-99; a last kernel adds the slices and applies bias, residual or
+ * quantizers/real.py:93-99; a last kernel adds the parts of every row tile and applies bias, residual or
  * silu(gate) * up. Needs span == 128. Same fusions and roundings as the other variants; no
  * tensor-parallel coupling. The workspace may be shared by consecutive launches on one stream.
  * lq_decode_gemm_device_error is non-zero if a bounded wait inside the kernel ever expired

@@ -16,7 +16,8 @@
 //                       reads from shared memory: per group one block of 2 * TP plane rows
 //                       (rows 0..TP-1 high planes, TP..2TP-1 low planes, 128-byte swizzled)
 //                       followed by the TP units.
-//   decode_gemm_kernel  one CTA per (128 weight rows, slice of the scale groups). The weight
+//   decode_gemm_kernel  one CTA per SM; the weight's (128-row tile, scale group) steps are cut
+//                       into equal contiguous runs, one per CTA. The weight
 //                       is read in a TILE-MAJOR layout (lq_tile_weight): per tile and group one
 //                       contiguous block of codes and scales, so a group arrives with one
 //                       linear bulk copy. Per group: A = 128 rows x 128 codes as signed bytes
@@ -32,8 +33,8 @@
 //                       by weight scale x unit and add into fp32 registers. This is the
 //                       reference's order of operations: one exact product sum per group,
 //                       scaled, accumulated in fp32 over the groups (quantizers/real.py:93-99).
-//                       The CTA's sums go to partial[split][T][N].
-//   decode_finish_kernel  adds the splits in order, then bias / residual / silu(gate) * up and
+//                       A tile's sums go to partial[part][T][N], one part per CTA that touched it.
+//   decode_finish_kernel  adds the parts in CTA order, then bias / residual / silu(gate) * up and
 //                       the roundings of the bf16 modules, and stores the output rows.
 //
 // What sets the pace (measured with per-role clock stamps, a diagnostic build): not HBM and
@@ -111,7 +112,7 @@ __device__ unsigned long long g_dg_diag[256 * 16];
 // warps, 1 group widened, 2 planes requested, 3 MMA thread has its operands, 4 MMAs issued,
 // 5 drain sees the group multiplied, 6 drain done, 7 raw bytes requested
 __device__ long long g_dg_trace[128 * 8];
-#define DG_EV(j, e) do { if (blockIdx.x == 0 && blockIdx.y == 0 && (j) < 128) g_dg_trace[(j) * 8 + (e)] = clock64(); } while (0)
+#define DG_EV(j, e) do { if (blockIdx.x == 0 && (j) < 128) g_dg_trace[(j) * 8 + (e)] = clock64(); } while (0)
 #define DG_T0() const long long dg_t0_ = clock64()
 #define DG_ADD(slot) do { (void)dg_t0_; } while (0)  // (sums off: they cost a round trip to memory each, which distorts the trace)
 #else
@@ -124,9 +125,20 @@ struct DgParams {
   const uint8_t* codes;      // tile-major [tiles][G] blocks: codes of 128 rows, then their 128 scales
   const uint8_t* planes;     // [G] blocks: plane rows [2 * TP][128] swizzled as the MMA reads them, then TP units
   float* partial;            // [splits][T][N]
-  int T, N, groups, rowbytes, gper;
+  int T, N, groups, rowbytes;
+  int steps, ncta;           // (row tile, scale group) steps of the whole weight; CTAs that share them evenly
+  int parts;                 // > 0: every row tile is finished in exactly this many parts (runs do not cross tiles)
   int* error_word;
 };
+
+// The weight's (row tile, scale group) steps, in tile-major order -- the order of the blocks in
+// memory -- are cut into `ncta` contiguous runs of equal length (to within one): CTA c takes steps
+// [c * steps / ncta, (c + 1) * steps / ncta). A run may end inside a row tile: the tile's sums
+// are then finished by the next CTA, and the parts are added by the finish kernel.
+__host__ __device__ inline int dg_first_step(int c, int steps, int ncta) { return (int)((long long)c * steps / ncta); }
+__host__ __device__ inline int dg_cta_of(int step, int steps, int ncta) {
+  return (int)((((long long)step + 1) * ncta + steps - 1) / steps) - 1;
+}
 
 constexpr uint32_t dg_idesc(int ncol) {
   // D = s32, A = B = s8, both K-major, N = ncol, M = 128
@@ -156,9 +168,8 @@ decode_gemm_kernel(const DgParams p) {
   __shared__ volatile int dead_s;
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int n0 = blockIdx.x * kDgRows;
-  const int g_lo = blockIdx.y * p.gper;
-  const int GL = min(p.gper, p.groups - g_lo);  // groups of this CTA
+  const int s0 = dg_first_step(blockIdx.x, p.steps, p.ncta);
+  const int GL = dg_first_step(blockIdx.x + 1, p.steps, p.ncta) - s0;  // steps of this CTA
   uint8_t* const a_ring = smem + ((1024u - (smem_u32(smem) & 1023u)) & 1023u);
   uint8_t* const b_ring = a_ring + SA * A_SLOT;
   uint8_t* const raw_base = b_ring + BN * B_SLOT;
@@ -201,9 +212,9 @@ decode_gemm_kernel(const DgParams p) {
     // copy occupies a thread for about 500 clocks, more than a group's bytes take to arrive:
     // one thread takes the even groups, another the odd ones.
     if (lane == 0) {
-      const uint8_t* my_codes = p.codes + (int64_t)blockIdx.x * p.groups * Plan::W_BLOCK;
+      const uint8_t* my_codes = p.codes + (int64_t)s0 * Plan::W_BLOCK;  // the run's blocks are contiguous
       for (int j = (warp - 18) >> 1; j < GL && !dead_s; j += 2) {
-        const uint8_t* src = my_codes + (int64_t)(g_lo + j) * Plan::W_BLOCK;
+        const uint8_t* src = my_codes + (int64_t)j * Plan::W_BLOCK;
         if (BITS == 4) {
           const int slot = j % RAWN;
           if (j >= RAWN && !mbar_wait(smem_u32(&raw_free[slot]), ((j / RAWN) - 1) & 1)) { dead_s = 1; break; }
@@ -223,12 +234,14 @@ decode_gemm_kernel(const DgParams p) {
     // The activation planes and units are the output of the kernel before this one.
     if (lane == 0) {
       asm volatile("griddepcontrol.wait;" ::: "memory");
+      int g = s0 % p.groups;  // scale group of step j
       for (int j = 0; j < GL && !dead_s; ++j) {
         // the slot's units are read by the drain of the group that used it last
         if (j >= BN && !wait_drained(j - BN)) { dead_s = 1; break; }
         mbar_expect_tx(smem_u32(&b_full[j % BN]), Plan::B_BLOCK);
-        bulk_g2s(smem_u32(b_ring + (j % BN) * B_SLOT), p.planes + (int64_t)(g_lo + j) * Plan::B_BLOCK, Plan::B_BLOCK,
+        bulk_g2s(smem_u32(b_ring + (j % BN) * B_SLOT), p.planes + (int64_t)g * Plan::B_BLOCK, Plan::B_BLOCK,
                  smem_u32(&b_full[j % BN]));
+        if (++g == p.groups) g = 0;
         DG_EV(j, 2);
       }
     }
@@ -309,8 +322,9 @@ decode_gemm_kernel(const DgParams p) {
 #pragma unroll
     for (int c = 0; c < TPH; ++c) acc[c] = 0.f;
     const int quarter = warp & 3, t0 = (warp >> 2) * TPH;  // TMEM lanes and tokens of this warp
-    const int row = quarter * 32 + lane, nrow = n0 + row;
-    bool dead = false;
+    const int row = quarter * 32 + lane;
+    bool dead = false, may_store = false;
+    int g = s0 % p.groups, tile = s0 / p.groups;  // scale group and row tile of step j
     for (int j = 0; j < GL; ++j) {
       const int tb = j % NACC, ring = j & (kDgRing - 1);
       if (dead_s) { dead = true; break; }
@@ -342,16 +356,29 @@ decode_gemm_kernel(const DgParams p) {
       __syncwarp();
       if (lane == 0) mbar_arrive(smem_u32(&drained[ring]));
       if (tid == 0) { DG_ADD(9); DG_EV(j, 6); }
-    }
-    // the buffer the sums go to may still be read by a kernel before this one: nothing of this
-    // kernel is stored before its predecessors are complete
-    asm volatile("griddepcontrol.wait;" ::: "memory");
-    if (!dead && nrow < p.N) {
-      float* dst = p.partial + ((int64_t)blockIdx.y * p.T + t0) * p.N + nrow;
+      // end of a row tile, or of this CTA's run inside one: its sums go out as one part of the tile
+      if (g == p.groups - 1 || j == GL - 1) {
+        if (!may_store) {
+          // the buffer the sums go to may still be read by a kernel before this one: nothing of
+          // this kernel is stored before its predecessors are complete
+          asm volatile("griddepcontrol.wait;" ::: "memory");
+          may_store = true;
+        }
+        const int nrow = tile * kDgRows + row;
+        const int part = p.parts > 0 ? (int)blockIdx.x % p.parts
+                                     : (int)blockIdx.x - dg_cta_of(tile * p.groups, p.steps, p.ncta);
+        if (nrow < p.N) {
+          float* dst = p.partial + ((int64_t)part * p.T + t0) * p.N + nrow;
 #pragma unroll
-      for (int c = 0; c < TPH; ++c)
-        if (t0 + c < p.T) dst[(int64_t)c * p.N] = acc[c];
+          for (int c = 0; c < TPH; ++c)
+            if (t0 + c < p.T) dst[(int64_t)c * p.N] = acc[c];
+        }
+#pragma unroll
+        for (int c = 0; c < TPH; ++c) acc[c] = 0.f;
+      }
+      if (++g == p.groups) { g = 0; ++tile; }
     }
+    (void)dead;
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
@@ -473,12 +500,13 @@ act_planes_kernel(const __nv_bfloat16* __restrict__ x, int ldx, const __nv_bfloa
 }
 
 // ---------------------------------------------------------------------------------------------
-// out = epilogue(sum over the splits): EPI 0 bias / residual, EPI 1 silu(gate) * up over
+// out = epilogue(sum over the parts of the row tile, in CTA order): EPI 0 bias / residual, EPI 1 silu(gate) * up over
 // interleaved (gate, up) rows, with the roundings of gemv_stream_kernel's epilogues.
 template <int EPI>
 __global__ void __launch_bounds__(256)
-decode_finish_kernel(const float* __restrict__ partial, int splits, int T, int N, const __nv_bfloat16* __restrict__ bias,
-                     const void* __restrict__ residual, void* __restrict__ out, int out_f32, int ldo) {
+decode_finish_kernel(const float* __restrict__ partial, int groups, int steps, int ncta, int uniform_parts, int T, int N,
+                     const __nv_bfloat16* __restrict__ bias, const void* __restrict__ residual, void* __restrict__ out,
+                     int out_f32, int ldo) {
   asm volatile("griddepcontrol.wait;" ::: "memory");
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   const int NO = EPI == 1 ? N / 2 : N;
@@ -486,6 +514,10 @@ decode_finish_kernel(const float* __restrict__ partial, int splits, int T, int N
   for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
     const int t = (int)(i / NO), j = (int)(i % NO);
     const int64_t o = (int64_t)t * ldo + j;
+    // the parts of this output's row tile: one per CTA whose run of steps touches the tile
+    const int tile = (EPI == 1 ? 2 * j : j) / kDgRows;
+    const int splits = uniform_parts > 0 ? uniform_parts
+                                         : dg_cta_of(tile * groups + groups - 1, steps, ncta) - dg_cta_of(tile * groups, steps, ncta) + 1;
     if (EPI == 1) {
       float2 gu = make_float2(0.f, 0.f);
       for (int s = 0; s < splits; ++s) {
@@ -566,20 +598,37 @@ int launch_dep(Kern kern, dim3 grid, dim3 block, size_t smem, cudaStream_t s, in
 
 int tokens_padded(int M) { return M <= 8 ? 8 : (M <= 16 ? 16 : (M <= 32 ? 32 : 64)); }
 
-// Slices of the scale groups per row tile: enough CTAs to fill the GPU's SMs, in as few
-// waves as possible (a CTA occupies an SM by itself).
-int choose_splits(int tiles, int groups) {
+// How the weight's steps are shared out, and the most parts any row tile is finished in (the
+// depth of the partial buffer). Two kinds of plan, both "equal contiguous runs": tiles x k CTAs,
+// whose runs never cross a row tile (k slices of the scale groups per tile), or one CTA per SM
+// with runs that may. A run that crosses tiles costs a few steps' time (a flush in mid-stream,
+// more parts to add), more than one wave of CTAs costs the set-up again and leaves SMs idle in
+// the last wave; the estimate below, in step times, picks (measured on the Llama-3-8B shapes:
+// q|k|v 48 tiles x 3, o and down 32 x 4, gate|up and lm_head one CTA per SM).
+struct StepPlan {
+  int steps, ncta, max_parts;
+  int uniform_parts;  // tiles x k CTAs: k; one CTA per SM: 0
+};
+StepPlan plan_steps(int tiles, int groups) {
+  StepPlan q;
+  q.steps = tiles * groups;
   const int sms = sm_count();
-  int best = 1;
-  long best_cost = -1;
-  for (int ks = 1; ks <= 8 && ks <= groups; ++ks) {
-    const int gper = (groups + ks - 1) / ks;
-    if ((ks - 1) * gper >= groups) continue;  // the last slice would be empty
-    const long waves = ((long)tiles * ks + sms - 1) / sms;
-    const long cost = waves * (gper + 4);  // 4: set-up and drain of a CTA, in group times
-    if (best_cost < 0 || cost < best_cost) { best = ks; best_cost = cost; }
+  const int by_work = (q.steps + 3) / 4;  // at least ~4 steps per CTA
+  const int per_sm = by_work < 1 ? 1 : (by_work < sms ? by_work : sms);
+  long best = ((long)q.steps + per_sm - 1) / per_sm + 4 + 3;  // one CTA per SM: runs cross tiles
+  q.ncta = per_sm;
+  q.uniform_parts = 0;
+  for (int k = 1; k <= 8 && k <= groups; ++k) {
+    const long waves = ((long)tiles * k + sms - 1) / sms;
+    const long cost = waves * ((groups + k - 1) / k + 4);
+    if (cost <= best) { best = cost; q.ncta = tiles * k; q.uniform_parts = k; }
   }
-  return best;
+  q.max_parts = 1;
+  for (int t = 0; t < tiles; ++t) {
+    const int parts = dg_cta_of(t * groups + groups - 1, q.steps, q.ncta) - dg_cta_of(t * groups, q.steps, q.ncta) + 1;
+    if (parts > q.max_parts) q.max_parts = parts;
+  }
+  return q;
 }
 
 int plane_block_bytes(int TP) { return 2 * TP * KT + (TP * 4 + 127) / 128 * 128; }
@@ -614,8 +663,8 @@ int run_decode_gemm(const lq_gemv_args& a, cudaStream_t s) {
              "the decode GEMM needs a 256-byte aligned workspace");
   LQ_REQUIRE(a.epilogue == 0 || a.N % 2 == 0, LQ_ERR_ARG, "the gate|up epilogue needs an even number of rows");
   const int groups = a.Kd / 128, TP = tokens_padded(a.M), tiles = (a.N + kDgRows - 1) / kDgRows;
-  const int splits = choose_splits(tiles, groups);
-  const Workspace w = carve(a.workspace, TP, a.M, a.N, groups, splits);
+  const StepPlan sp = plan_steps(tiles, groups);
+  const Workspace w = carve(a.workspace, TP, a.M, a.N, groups, sp.max_parts);
   LQ_REQUIRE(w.bytes <= a.workspace_bytes, LQ_ERR_ARG, "the decode GEMM needs %lld bytes of workspace, got %lld",
              (long long)w.bytes, (long long)a.workspace_bytes);
   void* err_ptr = nullptr;
@@ -630,8 +679,8 @@ int run_decode_gemm(const lq_gemv_args& a, cudaStream_t s) {
   DgParams p;
   p.codes = (const uint8_t*)a.codes; p.planes = w.planes;
   p.partial = w.partial; p.T = a.M; p.N = a.N; p.groups = groups; p.rowbytes = a.Kd * a.bits / 8;
-  p.gper = (groups + splits - 1) / splits; p.error_word = (int*)err_ptr;
-  const dim3 grid((unsigned)tiles, (unsigned)splits);
+  p.steps = sp.steps; p.ncta = sp.ncta; p.parts = sp.uniform_parts; p.error_word = (int*)err_ptr;
+  const dim3 grid((unsigned)sp.ncta);
   int rc = LQ_ERR_UNSUPPORTED;
 #define LQ_DG_CASE(B, TPV)                                                                              \
   if (a.bits == B && TP == TPV) {                                                                       \
@@ -651,11 +700,11 @@ int run_decode_gemm(const lq_gemv_args& a, cudaStream_t s) {
   const unsigned blocks = (unsigned)((total + 255) / 256 < 1184 ? (total + 255) / 256 : 1184);
   if (a.epilogue == 1)
     return launch_dep(decode_finish_kernel<1>, dim3(blocks), dim3(256), 0, s, a.pdl, "lq_wq_gemv_fused",
-                      (const float*)w.partial, splits, a.M, a.N, (const __nv_bfloat16*)a.bias, a.residual, a.out,
-                      a.out_dtype == LQ_F32 ? 1 : 0, ldo);
+                      (const float*)w.partial, groups, sp.steps, sp.ncta, sp.uniform_parts, a.M, a.N, (const __nv_bfloat16*)a.bias,
+                      a.residual, a.out, a.out_dtype == LQ_F32 ? 1 : 0, ldo);
   return launch_dep(decode_finish_kernel<0>, dim3(blocks), dim3(256), 0, s, a.pdl, "lq_wq_gemv_fused",
-                    (const float*)w.partial, splits, a.M, a.N, (const __nv_bfloat16*)a.bias, a.residual, a.out,
-                    a.out_dtype == LQ_F32 ? 1 : 0, ldo);
+                    (const float*)w.partial, groups, sp.steps, sp.ncta, sp.uniform_parts, a.M, a.N, (const __nv_bfloat16*)a.bias,
+                    a.residual, a.out, a.out_dtype == LQ_F32 ? 1 : 0, ldo);
 }
 
 }  // namespace gemv
@@ -665,8 +714,8 @@ extern "C" int64_t lq_decode_gemm_workspace_bytes(int M, int N, int Kd) {
   if (M < 1 || M > 64 || N < 1 || Kd < 128) return 0;
   const int groups = Kd / 128;
   const int TP = lq::tokens_padded(M);
-  const int splits = lq::choose_splits((N + lq::kDgRows - 1) / lq::kDgRows, groups);
-  return lq::carve(nullptr, TP, M, N, groups, splits).bytes;
+  const lq::StepPlan sp = lq::plan_steps((N + lq::kDgRows - 1) / lq::kDgRows, groups);
+  return lq::carve(nullptr, TP, M, N, groups, sp.max_parts).bytes;
 }
 
 extern "C" int lq_decode_gemm_device_error(void) {
