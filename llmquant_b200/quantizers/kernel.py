@@ -37,6 +37,9 @@ DECODE_GEMM_MAX_ROWS = 64
 # from this many rows the decode GEMM is the default (measured on B200 at the Llama-3-8B shapes,
 # 8 rows: q|k|v 11 vs 25 us, o 9 vs 13, gate|up 32 vs 44, down 17 vs 45 for the GEMV variants)
 DECODE_GEMM_MIN_ROWS = 5
+# `forward` takes the decode GEMM up to this many rows, the prefill kernels above (measured at
+# 128 rows, two passes: faster on down_proj, slower on gate/up and q/o)
+FORWARD_DECODE_GEMM_MAX_ROWS = 64
 PREFILL_EXACT_MAX_ROWS = 16
 PREFILL_TENSOR_CORE_MAX_ROWS = 512
 PREFILL_TENSOR_CORE_MIN_FEATURES = 2048
@@ -408,7 +411,7 @@ class KernelQuantLinear(nn.Module):
         flat = x.reshape(-1, shape[-1])
         m = flat.shape[0]
         if self._stream and flat.dtype == torch.bfloat16 and (
-                m <= DECODE_MAX_ROWS or (m <= DECODE_GEMM_MAX_ROWS and self._span == 128)):
+                m <= DECODE_MAX_ROWS or (m <= FORWARD_DECODE_GEMM_MAX_ROWS and self._span == 128)):
             # up to 8 rows the GEMV, up to 64 the decode GEMM (one pass over the weight; faster
             # than the prefill kernels' 128-token tiles at these row counts)
             out = self.gemv(flat)

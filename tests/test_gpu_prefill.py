@@ -93,16 +93,16 @@ def test_folded_scale_gemm_is_the_reference_kernel_mode_product(bits, shape):
     assert rel_l2(got, oracle.bf16_bits_to_f32(oracle.f32_to_bf16_bits(same))) <= 4e-4
     want = oracle.real_linear(x.float().numpy(), q, scale, bits, 128)
     assert rel_l2(got, want) <= 4e-3
-    # the module's forward takes this path above DECODE_GEMM_MAX_ROWS (up to which the decode GEMM
+    # the module's forward takes this path above FORWARD_DECODE_GEMM_MAX_ROWS (up to which the decode GEMM
     # keeps the exact per-group arithmetic) and up to PREFILL_TENSOR_CORE_MAX_ROWS rows when the
     # output is wide enough to fill the GPU, and the same bf16 weights through the library GEMM
     # otherwise
     from llmquant_b200.quantizers import kernel as kq
 
     fwd = module(x.cuda())
-    if kq.DECODE_GEMM_MAX_ROWS < m <= kq.PREFILL_TENSOR_CORE_MAX_ROWS and n >= kq.PREFILL_TENSOR_CORE_MIN_FEATURES:
+    if kq.FORWARD_DECODE_GEMM_MAX_ROWS < m <= kq.PREFILL_TENSOR_CORE_MAX_ROWS and n >= kq.PREFILL_TENSOR_CORE_MIN_FEATURES:
         assert torch.equal(fwd, module.gemm(x.cuda(), fold_scales=True))
-    elif m <= kq.DECODE_GEMM_MAX_ROWS:
+    elif m <= kq.FORWARD_DECODE_GEMM_MAX_ROWS:
         assert rel_l2(fwd.float().cpu().numpy(), want) <= 2e-3  # exact integer sums, bf16 output
     else:
         assert rel_l2(fwd.float().cpu().numpy(), got) <= 3e-3
