@@ -152,7 +152,8 @@ int lq_dequant_stream(const void* codes, const float* scale_tiles, void* out, in
  * int4, 5+ rows on int8, shapes variant 4 accepts), 1 = fp32 FMA arithmetic, 2 / 3 = integer dot products on 16- / 24-bit
  * block-floating-point activations (32-column blocks), 4 = tensor-core integer products
  * (mma.sync) on 15-bit block-floating-point activations (128-column blocks; needs span == 128
- * and a shape lq_gemv_tensor_core_ok accepts, else LQ_ERR_UNSUPPORTED).
+ * and a shape lq_gemv_tensor_core_ok accepts, else LQ_ERR_UNSUPPORTED); 5 (lq_wq_gemv_fused
+ * only) = the tcgen05 decode GEMM for up to 64 rows, described with lq_gemv_args.
  * Takes the role of wq_gemv.cu:45-130 inside KernelQuantLinear.forward
  * (quantizers/kernel.py:81-95). */
 int lq_wq_gemv_stream(const void* x, int ldx, const void* codes, const float* scale_tiles,
