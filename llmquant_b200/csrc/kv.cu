@@ -1001,7 +1001,8 @@ attn_fused_kernel(const __nv_bfloat16* __restrict__ qkv, const __nv_bfloat16* __
 //               global scratch, no ticket, no second trip through L2. Every path reaches the
 //               cluster barrier (the waits before it are bounded), so it always completes.
 constexpr int kMmaThreads = 256;
-constexpr int kMmaCap = 192;      // tokens staged per chunk
+constexpr int kMmaCap = 128;      // tokens staged per chunk: one 16-token block per warp (192 left half the
+                                  // warps waiting at the chunk's barrier for the others' second block)
 constexpr int kClusterCap = 288;  // the same for the cluster variant: 16 slices of a 4.6k context in one chunk
 constexpr int kMaxCluster = 16;
 
