@@ -55,7 +55,7 @@ constexpr int kDgThreads = 672;  // 8 drain warps, 8 widening warps, 2 MMA warps
 constexpr int kDgWidenWarps = 8;  // each widens every eighth group by itself
 constexpr int kDgRows = 128;     // weight rows per CTA = TMEM lanes
 constexpr int KT = 128;          // codes per scale group = bytes per operand row
-constexpr int kDgSmem = 200 * 1024;  // dynamic shared memory the rings are sized for
+constexpr int kDgSmem = 216 * 1024;  // dynamic shared memory the rings are sized for
 constexpr int kDgRing = 16;      // slots of the small per-group rings (weight scales, units)
 
 // Shared-memory plan of an instance. A CTA streams its rows at the rate its bytes in flight allow
@@ -80,8 +80,11 @@ struct DgPlan {
   static constexpr int B_SLOT = B_TILE + 1024;
   static constexpr int RAW_SLOT = RAW + kScaleBytes;
   static constexpr int SA8_ = kDgSmem / (A_SLOT + B_SLOT) > 8 ? 8 : kDgSmem / (A_SLOT + B_SLOT);
-  static constexpr int SA = BITS == 8 ? (SA8_ & ~1) : (TP <= 8 ? 6 : 4);
-  static constexpr int BN = BITS == 8 ? SA : (TP <= 16 ? 8 : (TP == 32 ? 6 : 4));
+  // int4: a widening warp needs a free A tile, so the A ring's depth is the number of groups being
+  // widened at once (measured: 4 tiles cost a third of the speed of 6); the plane ring takes
+  // what is left beside the eight raw slots
+  static constexpr int SA = BITS == 8 ? (SA8_ & ~1) : (TP <= 8 ? 8 : (TP <= 32 ? 6 : 4));
+  static constexpr int BN = BITS == 8 ? SA : (TP <= 16 ? 6 : 4);
   static constexpr int RAWN = BITS == 8 ? 0 : kDgWidenWarps;
   static constexpr size_t SMEM = (size_t)SA * A_SLOT + (size_t)BN * B_SLOT + (size_t)RAWN * RAW_SLOT + 1024;
   // Accumulators in tensor memory: as many as its 512 columns hold, up to 8. An MMA, the
