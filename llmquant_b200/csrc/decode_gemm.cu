@@ -24,11 +24,12 @@
 //                       (int8 codes as they are; int4 nibbles as 16 * code, the 1/16 folded
 //                       into the scale), B = the group's 2 * TP plane rows, four tcgen05.mma
 //                       kind::i8 (K = 32 each) into one of up to eight TMEM accumulators
-//                       [128 lanes = weight rows][2 * TP columns]. Warp roles: two threads
-//                       issue the weight copies and one the plane copies (issuing a bulk
-//                       copy occupies a thread for ~500 clocks); eight warps widen int4
-//                       nibbles from a ring of raw bytes into the A tiles, each a whole group
-//                       by itself; two threads issue the MMAs (even / odd groups); eight drain
+//                       [128 lanes = weight rows][2 * TP columns]. Warp roles: int8 codes
+//                       arrive in the A tiles by bulk copies, issued by two threads, and one
+//                       thread issues the plane copies (issuing a bulk copy occupies a thread
+//                       for ~500 clocks); int4 nibbles are loaded from global memory and
+//                       widened into the A tiles by eight warps, each a whole group by
+//                       itself; two threads issue the MMAs (even / odd groups); eight drain
 //                       warps read the accumulators (tcgen05.ld), form hi * 256 + lo, multiply
 //                       by weight scale x unit and add into fp32 registers. This is the
 //                       reference's order of operations: one exact product sum per group,
@@ -51,7 +52,6 @@
 namespace lq {
 namespace {
 
-constexpr int kDgThreads = 672;  // 8 drain warps, 8 widening warps, 2 MMA warps, 3 copy warps
 constexpr int kDgWidenWarps = 8;  // each widens every eighth group by itself
 constexpr int kDgRows = 128;     // weight rows per CTA = TMEM lanes
 constexpr int KT = 128;          // codes per scale group = bytes per operand row
@@ -59,12 +59,14 @@ constexpr int kDgSmem = 216 * 1024;  // dynamic shared memory the rings are size
 constexpr int kDgRing = 16;      // slots of the small per-group rings (weight scales, units)
 
 // Shared-memory plan of an instance. A CTA streams its rows at the rate its bytes in flight allow
-// (HBM answers after about a microsecond), so the rings are as deep as shared memory permits:
-// int8 codes land directly in the A operand tiles; int4 nibbles land in a deep ring of raw bytes
-// and are widened into a short ring of A tiles. The activation planes (B tiles) have a ring of
-// their own. A group's weight scales ride behind its codes and its units behind its planes, so
-// a group costs two bulk copies: issuing one occupies the issuing thread for some hundred
-// clocks, which is why there are few of them and one thread per ring.
+// (HBM answers after about a microsecond). int8 codes land directly in a ring of A operand tiles
+// by bulk copies (their scales behind them). int4 nibbles are loaded from global memory into
+// registers by the widening warps -- a whole group per warp, eight groups in flight -- and
+// stored as signed bytes into the A tiles (a ring of raw bytes in shared memory in between --
+// bulk copy in, vector load out -- was no faster and cost 70 KB). The activation planes (B
+// tiles, their units behind them) have a ring of their own. Issuing a bulk copy occupies the
+// issuing thread for some hundred clocks, which is why a group costs at most two of them and
+// every ring has its own issuing threads.
 constexpr int kScaleBytes = kDgRows * 4;  // the 128 weight scales of a group
 template <int BITS, int TP>
 struct DgPlan {
@@ -73,20 +75,23 @@ struct DgPlan {
   static constexpr int B_TILE = NCOL * KT;
   static constexpr int UNIT_BYTES = (TP * 4 + 127) / 128 * 128;
   static constexpr int B_BLOCK = B_TILE + UNIT_BYTES;   // what one copy brings: planes + units
-  static constexpr int RAW = kDgRows * (KT / 2);        // int4: a group's nibble bytes as they come
+  static constexpr int RAW = kDgRows * (KT / 2);        // int4: a group's nibble bytes
   static constexpr int W_BLOCK = (BITS == 8 ? A_TILE : RAW) + kScaleBytes;  // codes + scales
   // slots keep the operand tiles on 1024-byte boundaries (the 128-byte swizzle)
   static constexpr int A_SLOT = A_TILE + (BITS == 8 ? 1024 : 0);
   static constexpr int B_SLOT = B_TILE + 1024;
-  static constexpr int RAW_SLOT = RAW + kScaleBytes;
   static constexpr int SA8_ = kDgSmem / (A_SLOT + B_SLOT) > 8 ? 8 : kDgSmem / (A_SLOT + B_SLOT);
-  // int4: a widening warp needs a free A tile, so the A ring's depth is the number of groups being
-  // widened at once (measured: 4 tiles cost a third of the speed of 6); the plane ring takes
-  // what is left beside the eight raw slots
-  static constexpr int SA = BITS == 8 ? (SA8_ & ~1) : (TP <= 8 ? 8 : (TP <= 32 ? 6 : 4));
-  static constexpr int BN = BITS == 8 ? SA : (TP <= 16 ? 6 : 4);
-  static constexpr int RAWN = BITS == 8 ? 0 : kDgWidenWarps;
-  static constexpr size_t SMEM = (size_t)SA * A_SLOT + (size_t)BN * B_SLOT + (size_t)RAWN * RAW_SLOT + 1024;
+  // int4: one A tile per widening warp (a warp always widens into the same tile)
+  static constexpr int SA = BITS == 8 ? (SA8_ & ~1) : kDgWidenWarps;
+  static constexpr int BN_ = (kDgSmem - SA * A_SLOT) / B_SLOT > 8 ? 8 : (kDgSmem - SA * A_SLOT) / B_SLOT;
+  static constexpr int BN = BITS == 8 ? SA : (BN_ & ~1);
+  static constexpr size_t SMEM = (size_t)SA * A_SLOT + (size_t)BN * B_SLOT + 1024;
+  // warps: 0-7 drain, then (int4) 8 widening warps, 2 MMA-issuing, 1 for the plane copies,
+  // (int8) 2 for the weight copies
+  static constexpr int W_MMA = BITS == 8 ? 8 : 8 + kDgWidenWarps;
+  static constexpr int W_PLANES = W_MMA + 2;
+  static constexpr int W_WEIGHTS = W_PLANES + 1;  // int8 only
+  static constexpr int THREADS = 32 * (BITS == 8 ? W_WEIGHTS + 2 : W_PLANES + 1);
   // Accumulators in tensor memory: as many as its 512 columns hold, up to 8. An MMA, the
   // commit that follows it, the drain's tensor-memory load and the hand-back are each a few
   // hundred clocks of latency: the ring has to cover that loop.
@@ -94,14 +99,12 @@ struct DgPlan {
   // Whoever tests a barrier for its n-th completion must know the (n-1)-th has happened (a
   // test that comes a whole phase early reads as "complete"). So the rings are laid out such
   // that all uses of one slot fall to one thread, which takes them in order: even depths for
-  // the rings walked by the even / odd thread pairs, a raw ring as deep as there are widening
-  // warps, and 16-deep barrier rings ("group multiplied", "group drained") behind rings of at
+  // the rings walked by the even / odd thread pairs, one A tile per widening warp, and 16-deep
+  // barrier rings ("group multiplied", "group drained") behind rings of at
   // most 8.
-  static_assert(SA % 2 == 0 && BN % 2 == 0 && NACC % 2 == 0, "ring depths must be even");
+  static_assert(SA % 2 == 0 && BN % 2 == 0 && BN >= 4 && NACC % 2 == 0, "ring depths must be even");
   static_assert(SA <= 8 && BN <= 8 && NACC <= 8 && SA + NACC <= kDgRing, "rings deeper than the barrier rings allow");
   static_assert(kDgRing % kDgWidenWarps == 0, "a widening warp must meet a barrier slot again after 16 groups");
-  static_assert(BITS == 8 || (size_t)SA * A_SLOT + (size_t)BN * B_SLOT + (size_t)RAWN * RAW_SLOT <= kDgSmem,
-                "the rings do not fit");
 };
 
 __device__ int g_decode_gemm_error = 0;
@@ -111,9 +114,9 @@ __device__ int g_decode_gemm_error = 0;
 // summed over the rounds. [cta][slot]: widen 0 wait-copies 1 widen | mma 4 wait-operands
 // 5 wait-accumulator 6 issue | drain 8 wait 9 load+scale | 12 whole kernel
 __device__ unsigned long long g_dg_diag[256 * 16];
-// and for CTA (0, 0) the SM clock of eight events per group: 0 raw bytes seen by the widen
-// warps, 1 group widened, 2 planes requested, 3 MMA thread has its operands, 4 MMAs issued,
-// 5 drain sees the group multiplied, 6 drain done, 7 raw bytes requested
+// and for CTA (0, 0) the SM clock of eight events per group: 0 nibble loads issued by the widen
+// warp, 1 group widened, 2 planes requested, 3 MMA thread has its operands, 4 MMAs issued,
+// 5 drain sees the group multiplied, 6 drain done, 7 int8 codes requested
 __device__ long long g_dg_trace[128 * 8];
 #define DG_EV(j, e) do { if (blockIdx.x == 0 && (j) < 128) g_dg_trace[(j) * 8 + (e)] = clock64(); } while (0)
 #define DG_T0() const long long dg_t0_ = clock64()
@@ -148,26 +151,25 @@ constexpr uint32_t dg_idesc(int ncol) {
   return (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(ncol >> 3) << 17) | ((uint32_t)(kDgRows >> 4) << 24);
 }
 
-// Roles (warps): 0-7 drain, 8-15 widen (int4), 16-17 MMA issue (even / odd groups), 18 weight
-// copies, 19 plane copies.
 template <int BITS, int TP>
-__global__ void __launch_bounds__(kDgThreads)
+__global__ void __launch_bounds__(DgPlan<BITS, TP>::THREADS)
 decode_gemm_kernel(const DgParams p) {
   using Plan = DgPlan<BITS, TP>;
   constexpr int NCOL = Plan::NCOL;                  // accumulator columns: high planes, low planes
   constexpr int NACC = Plan::NACC;
   constexpr int TMEM_COLS = NACC * NCOL < 32 ? 32 : NACC * NCOL;
   constexpr int A_TILE = Plan::A_TILE, B_TILE = Plan::B_TILE, RAW = Plan::RAW;
-  constexpr int A_SLOT = Plan::A_SLOT, B_SLOT = Plan::B_SLOT, RAW_SLOT = Plan::RAW_SLOT;
-  constexpr int SA = Plan::SA, BN = Plan::BN, RAWN = Plan::RAWN > 0 ? Plan::RAWN : 1;
+  constexpr int A_SLOT = Plan::A_SLOT, B_SLOT = Plan::B_SLOT;
+  constexpr int SA = Plan::SA, BN = Plan::BN;
+  constexpr int W_MMA = Plan::W_MMA, W_PLANES = Plan::W_PLANES, W_WEIGHTS = Plan::W_WEIGHTS;
   constexpr int DW = TP >= 16 ? 8 : 4;              // drain warps in use
   constexpr int TPH = TP / (DW / 4);                // tokens per drain thread
   constexpr int CH = TPH < 16 ? 8 : 16;             // tokens per tensor-memory load
   extern __shared__ __align__(128) uint8_t smem[];
-  __shared__ __align__(8) uint64_t a_full[SA], b_full[BN], raw_full[RAWN], raw_free[RAWN];
+  __shared__ __align__(8) uint64_t a_full[SA], b_full[BN];
   __shared__ __align__(8) uint64_t mma_done[kDgRing], drained[kDgRing];
   __shared__ uint32_t tmem_base_s;
-  __shared__ __align__(16) float ws_s[BITS == 4 ? kDgRing : 1][kDgRows];  // int4: scales, saved from the raw ring
+  __shared__ __align__(16) float ws_s[BITS == 4 ? kDgRing : 1][kDgRows];  // int4: scales, kept by the widening warps
   __shared__ volatile int dead_s;
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -175,7 +177,6 @@ decode_gemm_kernel(const DgParams p) {
   const int GL = dg_first_step(blockIdx.x + 1, p.steps, p.ncta) - s0;  // steps of this CTA
   uint8_t* const a_ring = smem + ((1024u - (smem_u32(smem) & 1023u)) & 1023u);
   uint8_t* const b_ring = a_ring + SA * A_SLOT;
-  uint8_t* const raw_base = b_ring + BN * B_SLOT;
   constexpr uint32_t kIdesc = dg_idesc(NCOL);
   // "group k has been multiplied" / "... drained": slot k % 16 of the ring, its (k / 16)-th completion
   auto wait_done = [&](int k) { return mbar_wait(smem_u32(&mma_done[k & (kDgRing - 1)]), (k / kDgRing) & 1); };
@@ -191,10 +192,6 @@ decode_gemm_kernel(const DgParams p) {
     // operation on the barrier word, and hundreds of them per group are what a round would cost)
     for (int i = 0; i < SA; ++i) mbar_init(smem_u32(&a_full[i]), 1);
     for (int i = 0; i < BN; ++i) mbar_init(smem_u32(&b_full[i]), 1);
-    for (int i = 0; i < RAWN; ++i) {
-      mbar_init(smem_u32(&raw_full[i]), 1);
-      mbar_init(smem_u32(&raw_free[i]), 1);
-    }
     for (int i = 0; i < kDgRing; ++i) {
       mbar_init(smem_u32(&mma_done[i]), 1);
       mbar_init(smem_u32(&drained[i]), DW);
@@ -208,31 +205,24 @@ decode_gemm_kernel(const DgParams p) {
   const uint32_t tmem_base = tmem_base_s;
   DG_T0();
 
-  if (warp == 18 || warp == 20) {
-    // ------------------------------------------------------------------ weight copies (two threads)
+  if (BITS == 8 && (warp == W_WEIGHTS || warp == W_WEIGHTS + 1)) {
+    // ------------------------------------------------------------------ weight copies (int8; two threads)
     // Weights do not depend on the kernel before this one: their copies start at once. One
-    // contiguous block per group: the codes of the 128 rows, then their scales. Issuing a bulk
-    // copy occupies a thread for about 500 clocks, more than a group's bytes take to arrive:
-    // one thread takes the even groups, another the odd ones.
+    // contiguous block per step: the codes of the 128 rows, then their scales. Issuing a bulk
+    // copy occupies a thread for about 500 clocks, more than a step's bytes take to arrive:
+    // one thread takes the even steps, another the odd ones.
     if (lane == 0) {
       const uint8_t* my_codes = p.codes + (int64_t)s0 * Plan::W_BLOCK;  // the run's blocks are contiguous
-      for (int j = (warp - 18) >> 1; j < GL && !dead_s; j += 2) {
-        const uint8_t* src = my_codes + (int64_t)j * Plan::W_BLOCK;
-        if (BITS == 4) {
-          const int slot = j % RAWN;
-          if (j >= RAWN && !mbar_wait(smem_u32(&raw_free[slot]), ((j / RAWN) - 1) & 1)) { dead_s = 1; break; }
-          mbar_expect_tx(smem_u32(&raw_full[slot]), Plan::W_BLOCK);
-          bulk_g2s(smem_u32(raw_base + slot * RAW_SLOT), src, Plan::W_BLOCK, smem_u32(&raw_full[slot]));
-        } else {
-          // the slot's scales are read by the drain of the group that used it last
-          if (j >= SA && !wait_drained(j - SA)) { dead_s = 1; break; }
-          mbar_expect_tx(smem_u32(&a_full[j % SA]), Plan::W_BLOCK);
-          bulk_g2s(smem_u32(a_ring + (j % SA) * A_SLOT), src, Plan::W_BLOCK, smem_u32(&a_full[j % SA]));
-        }
+      for (int j = warp - W_WEIGHTS; j < GL && !dead_s; j += 2) {
+        // the slot's scales are read by the drain of the step that used it last
+        if (j >= SA && !wait_drained(j - SA)) { dead_s = 1; break; }
+        mbar_expect_tx(smem_u32(&a_full[j % SA]), Plan::W_BLOCK);
+        bulk_g2s(smem_u32(a_ring + (j % SA) * A_SLOT), my_codes + (int64_t)j * Plan::W_BLOCK, Plan::W_BLOCK,
+                 smem_u32(&a_full[j % SA]));
         DG_EV(j, 7);
       }
     }
-  } else if (warp == 19) {
+  } else if (warp == W_PLANES) {
     // ------------------------------------------------------------------ plane copies (one thread)
     // The activation planes and units are the output of the kernel before this one.
     if (lane == 0) {
@@ -248,32 +238,37 @@ decode_gemm_kernel(const DgParams p) {
         DG_EV(j, 2);
       }
     }
-  } else if (warp >= 8 && warp < 16) {
-    // ------------------------------------------------------------------ widen (int4 only)
-    // A group's way through a warp here is mostly latency (barrier operations, the proxy fence),
-    // so each warp widens every eighth group by itself and eight groups are under way at once.
-    if (BITS == 4) {
-      for (int j = warp - 8; j < GL; j += kDgWidenWarps) {
-        const int st = j % SA, slot = j % RAWN;
+  } else if (BITS == 4 && warp >= 8 && warp < 8 + kDgWidenWarps) {
+    // ------------------------------------------------------------------ widen (int4)
+    // Each warp takes every eighth step by itself and always widens into the same A tile: the
+    // step's 8 KB of nibble bytes and its scales come straight from global memory (contiguous:
+    // 512 bytes per load instruction), requested before the wait for the tile, so that with
+    // eight warps eight steps' bytes are in flight.
+    {
+      const int w = warp - 8;
+      uint8_t* const a_tile = a_ring + w * A_SLOT;
+      const uint8_t* my_codes = p.codes + (int64_t)s0 * Plan::W_BLOCK;
+      for (int j = w; j < GL; j += kDgWidenWarps) {
         if (dead_s) break;
-        { DG_T0(); if (!mbar_wait(smem_u32(&raw_full[slot]), (j / RAWN) & 1)) { dead_s = 1; break; } if (lane == 0) DG_ADD(0); }
+        const uint8_t* src = my_codes + (int64_t)j * Plan::W_BLOCK;  // [128 rows][64 bytes], then 128 scales
+        uint4 raw[16];
+#pragma unroll
+        for (int it = 0; it < 16; ++it) raw[it] = __ldg(reinterpret_cast<const uint4*>(src) + it * 32 + lane);
+        const float4 sc = __ldg(reinterpret_cast<const float4*>(src + RAW) + lane);
         if (lane == 0) DG_EV(j, 0);
         if (j >= SA && !wait_done(j - SA)) { dead_s = 1; break; }
         DG_T0();
-        uint8_t* a_tile = a_ring + st * A_SLOT;
-        const uint8_t* raw = raw_base + slot * RAW_SLOT;  // [128 rows][64 bytes], then 128 scales
-        // the scales outlive the raw slot: the drain reads them after the MMAs
-        *reinterpret_cast<float4*>(&ws_s[j & (kDgRing - 1)][lane * 4]) = *reinterpret_cast<const float4*>(raw + RAW + lane * 16);
-#pragma unroll 4
+        // the scales go where the drain finds them after the MMAs
+        *reinterpret_cast<float4*>(&ws_s[j & (kDgRing - 1)][lane * 4]) = sc;
+#pragma unroll
         for (int it = 0; it < 16; ++it) {
           const int item = it * 32 + lane, row = item >> 2, q = item & 3;
-          const uint4 v = *reinterpret_cast<const uint4*>(raw + item * 16);
-          const unsigned w4[4] = {v.x, v.y, v.z, v.w};
+          const unsigned w4[4] = {raw[it].x, raw[it].y, raw[it].z, raw[it].w};
           unsigned o[8];
 #pragma unroll
           for (int i = 0; i < 4; ++i) {
             // word of 8 nibbles (code + 8): even positions and odd positions as bytes 16 * code,
-            // interleaved back into K order. A row beyond N arrives as zeros and becomes
+            // interleaved back into K order. A row beyond N is stored as zeros and becomes
             // bytes -128: its outputs are never stored.
             const unsigned ev = ((w4[i] << 4) & 0xF0F0F0F0u) ^ 0x80808080u;
             const unsigned od = (w4[i] & 0xF0F0F0F0u) ^ 0x80808080u;
@@ -286,24 +281,21 @@ decode_gemm_kernel(const DgParams p) {
         }
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic writes -> MMA reads
         __syncwarp();
-        if (lane == 0) {
-          mbar_arrive(smem_u32(&a_full[st]));
-          mbar_arrive(smem_u32(&raw_free[slot]));
-        }
+        if (lane == 0) mbar_arrive(smem_u32(&a_full[w]));
         if (lane == 0) { DG_ADD(1); DG_EV(j, 1); }
       }
     }
-  } else if (warp == 16 || warp == 17) {
+  } else if (warp == W_MMA || warp == W_MMA + 1) {
     // ------------------------------------------------------------------ MMA issue
     // Two issuing threads, one for the even groups and one for the odd ones (a group has an
     // accumulator of its own): issuing a group's four MMAs and its commit takes one thread
     // longer than the group's bytes take to arrive.
     if (lane == 0) {
-      for (int j = warp - 16; j < GL; j += 2) {
+      for (int j = warp - W_MMA; j < GL; j += 2) {
         const int tb = j % NACC;
         if (dead_s) break;
-        { DG_T0(); if (!mbar_wait(smem_u32(&a_full[j % SA]), (j / SA) & 1) || !mbar_wait(smem_u32(&b_full[j % BN]), (j / BN) & 1)) { dead_s = 1; break; } if (warp == 16) DG_ADD(4); }
-        { DG_T0(); if (j >= NACC && !wait_drained(j - NACC)) { dead_s = 1; break; } if (warp == 16) DG_ADD(5); }
+        { DG_T0(); if (!mbar_wait(smem_u32(&a_full[j % SA]), (j / SA) & 1) || !mbar_wait(smem_u32(&b_full[j % BN]), (j / BN) & 1)) { dead_s = 1; break; } if (warp == W_MMA) DG_ADD(4); }
+        { DG_T0(); if (j >= NACC && !wait_drained(j - NACC)) { dead_s = 1; break; } if (warp == W_MMA) DG_ADD(5); }
         DG_T0();
         DG_EV(j, 3);
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -316,7 +308,7 @@ decode_gemm_kernel(const DgParams p) {
         }
         mma_commit(smem_u32(&mma_done[j & (kDgRing - 1)]));
         DG_EV(j, 4);
-        if (warp == 16) DG_ADD(6);
+        if (warp == W_MMA) DG_ADD(6);
       }
     }
   } else if (warp < DW) {
@@ -356,6 +348,12 @@ decode_gemm_kernel(const DgParams p) {
         }
       }
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+      // The loads above (units, scales) must have returned before the arrival that lets a bulk
+      // copy overwrite their slot: an arrival is not held back by an earlier shared-memory load
+      // of its warp whose data is still on its way, and with the widening warps' global loads
+      // queued in the same load path that took long enough for a warp to read the units of the
+      // step eight later. The fence waits for this thread's loads.
+      __threadfence_block();
       __syncwarp();
       if (lane == 0) mbar_arrive(smem_u32(&drained[ring]));
       if (tid == 0) { DG_ADD(9); DG_EV(j, 6); }
@@ -690,7 +688,7 @@ int run_decode_gemm(const lq_gemv_args& a, cudaStream_t s) {
     auto kern = decode_gemm_kernel<B, TPV>;                                                             \
     const size_t smem = DgPlan<B, TPV>::SMEM;                                                           \
     if (const int rs = ensure_smem_limit(reinterpret_cast<const void*>(kern), (int)smem, "lq_wq_gemv_fused")) return rs; \
-    rc = launch_dep(kern, grid, dim3(kDgThreads), smem, s, a.pdl, "lq_wq_gemv_fused", p);               \
+    rc = launch_dep(kern, grid, dim3(DgPlan<B, TPV>::THREADS), smem, s, a.pdl, "lq_wq_gemv_fused", p); \
   }
   LQ_DG_CASE(4, 8) LQ_DG_CASE(4, 16) LQ_DG_CASE(4, 32) LQ_DG_CASE(4, 64)
   LQ_DG_CASE(8, 8) LQ_DG_CASE(8, 16) LQ_DG_CASE(8, 32) LQ_DG_CASE(8, 64)

@@ -77,6 +77,28 @@ def test_long_runs_of_groups_per_cta(bits, M):
 
 
 @pytest.mark.parametrize("bits", [4, 8])
+@pytest.mark.parametrize("M", [12, 24, 64])
+def test_weights_not_in_cache(bits, M):
+    """The same product with the weights evicted from L2 before every call (256 MB written in
+    between). Then the weight side sets the pace, the activation planes wait in their ring, and
+    a slot is handed back to the copy thread the moment its group has been drained: the regime
+    in which a drain warp once read the units of a later group. The tokens here have groups
+    whose unit differs from their neighbours', which is what makes a stale unit visible."""
+    n, k = 19072, 5120
+    w = seeded((n, k), 81, 0.02, torch.bfloat16)
+    x = seeded((M, k), 82).bfloat16()
+    module = _module(w, bits)
+    want = _want(w, x, bits)
+    evict = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+    xc = x.cuda()
+    for round_ in range(6):
+        evict.fill_(round_)
+        got = module.gemv(xc, out_dtype=torch.float32, variant=5)
+        _no_device_error()
+        assert rel_l2(got.cpu().numpy(), want) <= TOL_F32, round_
+
+
+@pytest.mark.parametrize("bits", [4, 8])
 @pytest.mark.parametrize("M", [2, 8, 12, 16, 17, 31, 33, 50, 64, 70, 130])
 def test_every_padded_row_count(bits, M):
     """8, 16, 32 and 64 padded rows, and more rows than a call takes (64 per call)."""
