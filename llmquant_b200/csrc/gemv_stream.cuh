@@ -724,6 +724,10 @@ gemv_stream_kernel(const GemvParams p) {
         sc[j][2] = __uint_as_float(s4.z); sc[j][3] = __uint_as_float(s4.w);
       }
     }
+    // the loads above must have returned before the arrival that lets the next bulk copy
+    // overwrite the stage: an arrival is not held back by an earlier shared-memory load of its
+    // warp whose data is still on its way (seen in decode_gemm.cu under a busy load path)
+    __threadfence_block();
     __syncwarp();
     if (lane == 0) mbar_arrive(smem_u32(&empty_bar[s]));  // the stage can be refilled
     if (++s == p.stages) { s = 0; phase ^= 1; }

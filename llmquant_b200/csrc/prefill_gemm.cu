@@ -425,6 +425,7 @@ prefill_gemm_ws_kernel(const GemmParams p) {
         for (int j = 0; j < 32; ++j) acc[c0 + j] = fmaf((float)(int)v[j] * xs, wsg[c0 + j], acc[c0 + j]);
       }
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+      __threadfence_block();  // the scale loads have returned before their ring slot is handed back
       __syncwarp();
       if (lane == 0) mbar_arrive(smem_u32(&tfree_bar[st]));
     }
