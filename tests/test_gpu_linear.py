@@ -131,6 +131,43 @@ def test_gemv_at_model_shapes_against_oracle(shape, bits, M):
     assert torch.equal(twice, once * 2)
 
 
+@pytest.mark.parametrize("bits", [4, 8])
+def test_weights_not_in_cache_give_the_same_bits(bits):
+    """Every streaming kernel with its weight evicted from L2 before the call (256 MB written in
+    between): the stage rings then run at the pace of HBM, and a stage is handed back to the
+    copy engine the moment its consumers are done -- the regime in which a hand-back that
+    overtakes the consumer's own loads would show. Same bits as the warm call, every time."""
+    from llmquant_b200 import native
+    from llmquant_b200.quantizers import KernelQuantLinear
+
+    n, k = 8192, 4096
+    w = seeded((n, k), 61, 0.02, torch.bfloat16)
+    scheme = QuantizationScheme(
+        weights=QuantizationArgs(num_bits=bits, strategy="group", group_size=128), input_activations=None)
+    linear = torch.nn.Linear(k, n, bias=False)
+    linear.weight.data = w
+    module = KernelQuantLinear.from_linear(linear.cuda(), scheme)
+    evict = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+    q, scale = oracle.quantize_weight(w.float().numpy(), bits, 128)
+    for M, variants in ((1, (1, 2, 3)), (4, (1, 2, 4) if bits == 4 else (1, 2)), (8, (2, 4, 5))):
+        x = seeded((M, k), 62 + M, 1.0, torch.bfloat16).cuda()
+        want = oracle.real_linear(x.float().cpu().numpy(), q, scale, bits, 128)
+        for variant in variants:
+            warm = module.gemv(x, out_dtype=torch.float32, variant=variant)
+            assert rel_l2(warm.cpu().numpy(), want) <= TOL_F32, (M, variant)
+            for round_ in range(4):
+                evict.fill_(round_)
+                assert torch.equal(module.gemv(x, out_dtype=torch.float32, variant=variant), warm), (M, variant, round_)
+    x = seeded((300, k), 70, 1.0, torch.bfloat16).cuda()
+    for a8 in (False, True):
+        warm = module.gemm(x, a8=a8)
+        for round_ in range(3):
+            evict.fill_(round_)
+            assert torch.equal(module.gemm(x, a8=a8), warm), (a8, round_)
+    assert native.library().lq_gemm_device_error() == 0
+    assert native.library().lq_gemv_device_error() == 0
+
+
 def test_config1_output(golden):
     """BASELINE config 1: y = x W^T in fp32, int8 group-128 weights, rel-L2 <= 2e-3."""
     from llmquant_b200.quantizers import KernelQuantLinear
