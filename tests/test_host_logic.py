@@ -55,6 +55,30 @@ def test_argument_errors_come_back_as_messages():
     assert (kd, span, npad) == (2048, 128, 12)
 
 
+def test_decode_gemm_size_arithmetic():
+    """Sizes the decode GEMM asks its caller for (host arithmetic, no GPU): the tile-major
+    weight is one block of codes + 128 fp32 scales per (128-row tile, 128-code group); the
+    workspace is the activation planes (per group 2 * rows_padded plane rows of 128 bytes and
+    the units, 128-byte padded) followed by 1..8 fp32 parts of the output."""
+    lib = native.library()
+    for n, kd in ((4096, 4096), (1000, 1152), (28672, 4096), (128256, 4096)):
+        tiles, groups = -(-n // 128), kd // 128
+        assert lib.lq_tile_weight_bytes(n, kd, 8) == tiles * groups * (128 * 128 + 512)
+        assert lib.lq_tile_weight_bytes(n, kd, 4) == tiles * groups * (128 * 64 + 512)
+        last = 0
+        for rows in (1, 8, 9, 16, 17, 32, 33, 64):
+            padded = next(p for p in (8, 16, 32, 64) if rows <= p)
+            planes = groups * (2 * padded * 128 + -(-padded * 4 // 128) * 128)
+            planes = -(-planes // 256) * 256
+            total = lib.lq_decode_gemm_workspace_bytes(rows, n, kd)
+            parts, rest = divmod(total - planes, rows * n * 4)
+            assert rest == 0 and 1 <= parts <= 8, (n, kd, rows, total)
+            assert total > last
+            last = total
+    assert lib.lq_decode_gemm_workspace_bytes(0, 4096, 4096) == 0
+    assert lib.lq_decode_gemm_workspace_bytes(65, 4096, 4096) == 0
+
+
 def test_scheme_rules():
     with pytest.raises(ValueError, match="requires a positive group_size"):
         QuantizationArgs(num_bits=4, strategy="group")
